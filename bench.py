@@ -1,0 +1,312 @@
+#!/usr/bin/env python
+"""Benchmark of the message-passing hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N = 1: the standalone SpMM workload (R-MAT scale 21, edge factor 32, symmetrised,
+gcn_norm weights, feature width swept over 32/64/128/256).  One step = one
+aggregation at every width of the sweep.  N > 1 (under torchrun): the same graph
+split into N contiguous destination-row shards, halo feature rows exchanged over
+NCCL, strong scaling.  Prints ONE JSON line (rank 0).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WIDTHS = (32, 64, 128, 256)
+SEED = 20261125 + 1
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        self.t.join(timeout=2)
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_graph(device, scale=21, edge_factor=32):
+    """CSC of the gcn-normalised symmetric R-MAT graph (setup, outside every timed region)."""
+    from jittorgeometric_b200 import synth
+    import jittorgeometric_b200 as jg
+    ei, n = synth.rmat_graph(scale, edge_factor, SEED, device=device)
+    # self-loops appended after the edge list, unit weights, symmetric normalisation
+    # (nn/conv/gcn_conv.py:18-37); destination-major with a stable sort keeps list order per column
+    loops = torch.arange(n, dtype=torch.int32, device=device)
+    src = torch.cat([ei[0], loops]); dst = torch.cat([ei[1], loops])
+    del ei
+    deg = torch.bincount(dst.long(), minlength=n).to(torch.float32)
+    dis = (1.0 / deg.double().sqrt()).float()
+    order = torch.sort(dst.long(), stable=True)[1]
+    src, dst = src[order], dst[order]
+    w = (dis[src.long()] * 1.0) * dis[dst.long()]
+    off = torch.zeros(n + 1, dtype=torch.int32, device=device)
+    off[1:] = torch.cumsum(deg.to(torch.int64), 0).to(torch.int32)
+    return jg.CSC(src.contiguous(), off, w.contiguous()), n
+
+
+def alg_bytes(nnz, n, f):
+    """No-reuse gather model: per nonzero its index, weight and one f-wide source row;
+    offsets read once; every output row written once."""
+    return nnz * (4 + 4 + 4 * f) + 4 * (n + 1) + 4 * n * f
+
+
+def cpu_reference_sample(csc, n, widths, budget_s):
+    """Times the reference's own CPU aggregation (compiled reference body when present,
+    else the C restatement) on the first rows of the same CSC: a bounded sample."""
+    import numpy as np
+    import oracle as O
+    impl = "ref" if O.have_ref() else "port"
+    off = csc.column_offset.cpu().numpy()
+    idx_all = csc.row_indices.cpu().numpy()
+    w_all = csc.edge_weight.cpu().numpy()
+    rng = np.random.default_rng(SEED)
+    per_width = budget_s / len(widths)
+    done_ef, done_t, rows_used = 0.0, 0.0, []
+    for f in widths:
+        x = rng.standard_normal((n, f), dtype=np.float32)
+        # calibrate on 20k rows, then size the sample for the per-width budget
+        r0 = min(n, 20000)
+        t0 = time.perf_counter()
+        _sample_aggregate(O, impl, x, idx_all, off, w_all, r0)
+        dt = time.perf_counter() - t0
+        rate = max(int(off[r0]), 1) / max(dt, 1e-6)
+        target = int(rate * per_width)
+        r = int(np.searchsorted(off, min(target, int(off[-1])), side="left"))
+        r = max(min(r, n), r0)
+        t0 = time.perf_counter()
+        _sample_aggregate(O, impl, x, idx_all, off, w_all, r)
+        dt = time.perf_counter() - t0
+        done_ef += float(off[r]) * f
+        done_t += dt
+        rows_used.append(r)
+    return {"value": done_ef / done_t, "unit": "edge*feat/s", "cores": 1,
+            "kind": "reference" if impl == "ref" else "port",
+            "sample": f"first {rows_used} destination rows of the same CSC at widths {list(widths)}; "
+                      f"{done_t:.1f} s of single-thread CPU work (the reference loop is single-threaded)",
+            "seconds": done_t}
+
+
+def _sample_aggregate(O, impl, x, idx, off, w, rows):
+    """Aggregates destination rows [0, rows) with the CPU checker."""
+    import ctypes
+    import numpy as np
+    sub_off = np.ascontiguousarray(off[: rows + 1])
+    out = np.zeros((rows, x.shape[1]), np.float32)
+    if impl == "ref":
+        # the reference body takes its row count from x: hand it a view with `rows` rows whose
+        # base pointer is x itself, so gathered source rows beyond `rows` are still addressable
+        L = O.ref_lib()
+        L.ref_aggregate(out.ctypes.data_as(O.oracle.c_f32p), x.ctypes.data_as(O.oracle.c_f32p),
+                        idx.ctypes.data_as(O.oracle.c_i32p), sub_off.ctypes.data_as(O.oracle.c_i32p),
+                        w.ctypes.data_as(O.oracle.c_f32p), ctypes.c_long(rows), ctypes.c_long(x.shape[1]),
+                        ctypes.c_long(int(sub_off[-1])))
+    else:
+        O.port_lib().orc_aggregate(out.ctypes.data_as(O.oracle.c_f32p), x.ctypes.data_as(O.oracle.c_f32p),
+                                   idx.ctypes.data_as(O.oracle.c_i32p), sub_off.ctypes.data_as(O.oracle.c_i32p),
+                                   w.ctypes.data_as(O.oracle.c_f32p), ctypes.c_int64(rows), ctypes.c_int64(x.shape[1]))
+    return out
+
+
+def run_reference(args):
+    """Reference arm: the reference's CPU aggregation on this box's host cores, rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    device = "cuda" if torch.cuda.is_available() else "cpu"
+    scale = args.scale if device == "cuda" else min(args.scale, 16)
+    csc, n = build_graph(device, scale, args.edge_factor)
+    nnz = csc.row_indices.numel()
+    per_step = []
+    res = None
+    for _ in range(args.warmup + args.steps):
+        res = cpu_reference_sample(csc, n, WIDTHS, budget_s=max(2.0, 60.0 / (args.warmup + args.steps)))
+        per_step.append(res)
+    timed = per_step[args.warmup:]
+    value = sum(r["value"] for r in timed) / len(timed)
+    res = dict(timed[-1]); res["value"] = value
+    line = {
+        "impl": "reference", "metric": "spmm_edge_feat_per_s", "value": value, "unit": "edge*feat/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * sum(r["seconds"] for r in timed) / len(timed),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(scale, args.edge_factor, n, nnz, args.gpus),
+        "cpu_baseline": res,
+        "e2e": {"value": value, "unit": "edge*feat/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def workload_config(scale, ef, n, nnz, gpus):
+    return {"workload": f"standalone SpMM Y=A*X: R-MAT(0.57,0.19,0.19,0.05) scale {scale}, edge factor {ef}, "
+                        "symmetrised, deduplicated, vertex ids relabelled, self-loops + gcn_norm fp32 weights, "
+                        "int32 indices; X fp32 N(0,1); one step = widths 32,64,128,256",
+            "nodes": n, "nnz": nnz, "widths": list(WIDTHS),
+            "l2": "inputs larger than L2 (indices+weights %.0f MB, X %.0f-%.0f MB)" % (
+                nnz * 8 / 1e6, n * 32 * 4 / 1e6, n * 256 * 4 / 1e6),
+            "partition": "none" if gpus == 1 else f"{gpus} contiguous destination-row shards, halo exchange over NCCL"}
+
+
+def run_single(args):
+    import jittorgeometric_b200 as jg
+    from jittorgeometric_b200 import ops
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    csc, n = build_graph(dev, args.scale, args.edge_factor)
+    nnz = csc.row_indices.numel()
+    plan = ops.SpmmPlan(csc.column_offset, nnz)
+    g = torch.Generator(device=dev); g.manual_seed(SEED)
+    xs = {f: torch.randn((n, f), generator=g, device=dev) for f in WIDTHS}
+    ys = {f: torch.empty((n, f), device=dev) for f in WIDTHS}
+
+    def step(events=None):
+        for f in WIDTHS:
+            if events is not None:
+                events[f][0].record()
+            ops.segment_aggregate(xs[f], csc.row_indices, csc.column_offset, csc.edge_weight, plan=plan, out=ys[f])
+            if events is not None:
+                events[f][1].record()
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(dev.index); sampler.start()
+    evs = [{f: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for f in WIDTHS}
+           for _ in range(args.steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    t0.record()
+    for k in range(args.steps):
+        step(evs[k])
+    t1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms_step = t0.elapsed_time(t1) / args.steps
+    per_f = {f: sum(e[f][0].elapsed_time(e[f][1]) for e in evs) / args.steps for f in WIDTHS}
+
+    peak, peak_kind = measured_peaks()
+    sweep = {}
+    for f in WIDTHS:
+        b = alg_bytes(nnz, n, f)
+        sweep[str(f)] = {"ms": per_f[f], "gflops": 2.0 * nnz * f / per_f[f] / 1e6,
+                         "alg_gbs": b / per_f[f] / 1e6, "frac_of_hbm_peak": b / per_f[f] / 1e6 / peak}
+    total_bytes = sum(alg_bytes(nnz, n, f) for f in WIDTHS)
+    kernel_ms = sum(per_f.values())
+    achieved = total_bytes / kernel_ms / 1e6
+    value = nnz * sum(WIDTHS) / (ms_step * 1e-3)
+
+    # end to end through the public API with host buffers: X from pinned host memory, Y back to pinned host memory
+    hx = {f: torch.empty((n, f), dtype=torch.float32).pin_memory() for f in WIDTHS}
+    for f in WIDTHS:
+        hx[f].copy_(xs[f])
+    hy = {f: torch.empty((n, f), dtype=torch.float32).pin_memory() for f in WIDTHS}
+    dx = {f: torch.empty((n, f), device=dev) for f in WIDTHS}
+
+    def e2e_step():
+        for f in WIDTHS:
+            dx[f].copy_(hx[f], non_blocking=True)
+            y = ops.segment_aggregate(dx[f], csc.row_indices, csc.column_offset, csc.edge_weight, plan=plan, out=ys[f])
+            hy[f].copy_(y, non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 5))
+    e2e_step(); torch.cuda.synchronize()
+    t0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    t1.record(); torch.cuda.synchronize()
+    e2e_ms = t0.elapsed_time(t1) / e2e_steps
+    io_bytes = sum(n * f * 4 for f in WIDTHS)
+
+    cpu = cpu_reference_sample(csc, n, WIDTHS, budget_s=args.cpu_budget) if args.cpu_budget > 0 else None
+    line = {
+        "metric": "spmm_edge_feat_per_s", "value": value, "unit": "edge*feat/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.scale, args.edge_factor, n, nnz, 1),
+        "gflops": 2.0 * value / 1e9,
+        "sweep": sweep,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "aggregate_kernel",
+                     "note": "algorithmic bytes = no-reuse gather model summed over the four widths / summed launch time"},
+        "cpu_baseline": cpu,
+        "e2e": {"value": nnz * sum(WIDTHS) / (e2e_ms * 1e-3), "unit": "edge*feat/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes},
+        "gpu_launches": args.steps * len(WIDTHS) * 2,
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--scale", type=int, default=21)
+    ap.add_argument("--edge-factor", type=int, default=32)
+    ap.add_argument("--cpu-budget", type=float, default=16.0, help="seconds of CPU-baseline work (0 = skip)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    if args.gpus == 1:
+        return run_single(args)
+    from jittorgeometric_b200 import dist_bench
+    return dist_bench.run(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,74 @@
+/* jgb200 - C ABI of the B200 (sm_100a) message-passing kernels.
+ *
+ * Drop-in boundary for the operator layer of JittorGeometric
+ * (jittor_geometric/ops/*.py -> jittor_geometric/ops/cpp/*_op.cc): every entry
+ * point below replaces one native operator of that layer and is what a binding
+ * (ctypes, cffi, a Jittor custom op) would call.
+ *
+ * Conventions
+ *   - all pointers are DEVICE pointers unless the name ends in _host;
+ *   - indices int32, values fp32, dense matrices row-major and contiguous;
+ *   - `off` arrays have n+1 entries, segment v = [off[v], off[v+1]);
+ *   - the caller owns every buffer, including the workspace whose size the
+ *     matching *_workspace_bytes() call reports; the library allocates nothing
+ *     and keeps no per-call state;
+ *   - every call is asynchronous on `stream` (a cudaStream_t passed as void*);
+ *   - the return value is JG_OK or a negative jg_status; jg_last_error() gives
+ *     the detail text for the calling thread.  Nothing exits or traps.
+ */
+#ifndef JGB200_H
+#define JGB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* jg_stream_t; /* cudaStream_t */
+
+enum jg_status {
+    JG_OK = 0,
+    JG_EINVAL = -1,       /* null pointer, negative size, bad flag */
+    JG_ESHAPE = -2,       /* sizes that do not fit together or exceed int32 indexing */
+    JG_EWORKSPACE = -3,   /* workspace missing or too small */
+    JG_ECUDA = -4,        /* a CUDA runtime call failed */
+    JG_ETIMEOUT = -5,     /* a bounded device-side wait ran out */
+    JG_EUNSUPPORTED = -6  /* valid request this build does not implement */
+};
+
+int jg_version(void);
+const char* jg_status_string(int status);
+const char* jg_last_error(void);
+/* Makes `device` current for the library's CUDA runtime on the calling thread. */
+int jg_set_device(int device);
+
+/* ------------------------------------------------------------------ aggregation
+ * Weighted segment aggregation  out[v,:] = sum_{j in seg(v)} w[j] * x[idx[j],:].
+ * Replaces AggregateOp (ops/cpp/aggregate_op.cc:26-105; Python wrapper
+ * ops/aggregateWithWeight.py:19-41): called with the CSC arrays it is the forward
+ * pass, with the CSR arrays the backward pass.  It is also the kernel behind the
+ * cuSPARSE-backed SpmmCsr/SpmmCoo (ops/spmmcsr.py:21-44, ops/spmmcoo.py:19-45).
+ * Terms of a segment are added in ascending j with separately rounded multiply
+ * and add, so rows of at most `chunk` entries (and f >= 128) reproduce the
+ * reference CPU loop bit for bit; longer rows are split into `chunk`-sized pieces
+ * whose partial sums are added in piece order.  No atomics touch `out`.
+ *
+ * The hub plan lists the rows longer than `chunk`; it depends only on `off` and
+ * is reusable across calls; pass the `chunk` it was built with.  plan == NULL
+ * (chunk ignored) processes every row unsplit.
+ * `out` need not be zeroed: every row is written.  x has n_in rows, out n_out. */
+size_t jg_spmm_plan_bytes(int64_t n_out, int64_t nnz, int32_t chunk);
+int jg_spmm_plan_build(const int32_t* off, int64_t n_out, int64_t nnz, int32_t chunk, void* plan,
+                       size_t plan_bytes, jg_stream_t stream);
+size_t jg_aggregate_workspace_bytes(int64_t n_out, int64_t nnz, int64_t f, int32_t chunk);
+int jg_aggregate_f32(float* out, const float* x, const int32_t* idx, const int32_t* off,
+                     const float* w, int64_t n_out, int64_t n_in, int64_t f, int64_t nnz,
+                     const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes,
+                     jg_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JGB200_H */

@@ -1,0 +1,388 @@
+// Weighted segment aggregation (CSC forward / CSR backward SpMM) for sm_100a.
+//
+//   out[v,:] = sum_{j in [off[v], off[v+1])} w[j] * x[idx[j],:]
+//
+// Replaces the reference's AggregateOp (ops/cpp/aggregate_op.cc:26-105) and the
+// cuSPARSE SpMM behind SpmmCsr/SpmmCoo (ops/spmmcsr.py:31, ops/spmmcoo.py:34).
+//
+// Work decomposition.  A "work id" is either one piece (<= chunk entries) of a
+// hub row listed in the plan, or one ordinary row.  A persistent grid of warps
+// pulls ids eight at a time from a global ticket counter (hub pieces first, so
+// the longest items start earliest).  One warp owns one id: it loads 32 indices
+// and weights with one coalesced read each, broadcasts them by shuffle, and
+// gathers feature rows with 128-bit loads, several rows in flight per lane.
+// HBM-bound: per nonzero one 4 B index, one 4 B weight and one F*4 B row.
+//
+// Determinism.  Each output row is produced by exactly one warp (or, for a hub
+// row, by a fixed-order sum of its pieces' partial rows held in scratch), so
+// results do not depend on which warp ran which id.  No atomics touch data; the
+// only atomic is the ticket counter.
+#include "common.cuh"
+
+namespace jg {
+
+struct PlanHeader {
+    int32_t n_hubs;
+    int32_t n_items;
+    int32_t chunk;
+    int32_t max_hubs;
+    int32_t max_items;
+    int32_t pad[3];
+};
+
+struct PlanView {
+    PlanHeader* hdr;
+    int32_t* hub_row;    // [max_hubs] row id of each hub
+    int32_t* hub_first;  // [max_hubs] first partial slot of each hub
+    int32_t* item_hub;   // [max_items] hub index of each piece
+    int32_t* item_k;     // [max_items] piece number within its hub
+};
+
+static inline int64_t plan_max_hubs(int64_t nnz, int32_t chunk) { return nnz / ((int64_t)chunk + 1) + 1; }
+static inline int64_t plan_max_items(int64_t nnz, int32_t chunk) {
+    return nnz / chunk + plan_max_hubs(nnz, chunk) + 1;
+}
+
+static PlanView plan_view(void* plan, int64_t nnz, int32_t chunk, size_t* bytes) {
+    Carver c(plan);
+    PlanView v;
+    v.hdr = c.take<PlanHeader>(1);
+    v.hub_row = c.take<int32_t>(plan_max_hubs(nnz, chunk));
+    v.hub_first = c.take<int32_t>(plan_max_hubs(nnz, chunk));
+    v.item_hub = c.take<int32_t>(plan_max_items(nnz, chunk));
+    v.item_k = c.take<int32_t>(plan_max_items(nnz, chunk));
+    if (bytes) *bytes = c.total();
+    return v;
+}
+
+__global__ void plan_build_kernel(const int32_t* __restrict__ off, int64_t n, PlanView p, int32_t chunk) {
+    for (int64_t v = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; v < n;
+         v += (int64_t)gridDim.x * blockDim.x) {
+        int32_t deg = off[v + 1] - off[v];
+        if (deg > chunk) {
+            int32_t pieces = (deg + chunk - 1) / chunk;
+            int32_t h = atomicAdd(&p.hdr->n_hubs, 1);
+            int32_t first = atomicAdd(&p.hdr->n_items, pieces);
+            p.hub_row[h] = (int32_t)v;
+            p.hub_first[h] = first;
+            for (int32_t k = 0; k < pieces; k++) {
+                p.item_hub[first + k] = h;
+                p.item_k[first + k] = k;
+            }
+        }
+    }
+}
+
+constexpr int kGrab = 8;      // work ids taken per ticket
+constexpr int kBlock = 256;   // threads per CTA
+
+struct AggArgs {
+    float* out;
+    const float* x;
+    const int32_t* idx;
+    const int32_t* off;
+    const float* w;
+    int64_t n_out;
+    int64_t f;
+    const PlanHeader* hdr;  // null: no plan
+    const int32_t* hub_row;
+    const int32_t* hub_first;
+    const int32_t* item_hub;
+    const int32_t* item_k;
+    float* partial;
+    unsigned long long* ticket;
+};
+
+__device__ __forceinline__ void fma2(float4& a, const float4& v, float w) {
+    // multiply and add rounded separately, as the reference CPU loop does
+    a.x = __fadd_rn(__fmul_rn(v.x, w), a.x);
+    a.y = __fadd_rn(__fmul_rn(v.y, w), a.y);
+    a.z = __fadd_rn(__fmul_rn(v.z, w), a.z);
+    a.w = __fadd_rn(__fmul_rn(v.w, w), a.w);
+}
+
+// One warp aggregates entries [s, e) into dst (F = 4*G*VPL floats).
+// G lanes cover one feature row; 32/G entries are processed side by side.
+template <int G, int VPL, int UNROLL>
+__device__ __forceinline__ void warp_segment_vec(const AggArgs& a, int32_t s, int32_t e, float* dst) {
+    constexpr int EPS = 32 / G;
+    constexpr int F = 4 * G * VPL;
+    const int lane = lane_id();
+    const int sub = lane / G;
+    const int fl = lane % G;
+    float4 acc[VPL];
+#pragma unroll
+    for (int q = 0; q < VPL; q++) acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    int my_idx = 0;
+    float my_w = 0.f;
+    if (s + lane < e) {
+        my_idx = ld_stream(a.idx + s + lane);
+        my_w = ld_stream(a.w + s + lane);
+    }
+    for (int32_t j0 = s; j0 < e; j0 += 32) {
+        const int cnt = min(32, e - j0);
+        const int cur_idx = my_idx;
+        const float cur_w = my_w;
+        if (j0 + 32 + lane < e) {  // next tile's indices in flight while this one is gathered
+            my_idx = ld_stream(a.idx + j0 + 32 + lane);
+            my_w = ld_stream(a.w + j0 + 32 + lane);
+        }
+        for (int t = 0; t < cnt; t += EPS * UNROLL) {
+            float4 v[UNROLL][VPL];
+            float wv[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; u++) {
+                const int k = t + u * EPS + sub;
+                const int src = __shfl_sync(kFull, cur_idx, k & 31);
+                wv[u] = __shfl_sync(kFull, cur_w, k & 31);
+                if (k < cnt) {
+                    const float4* p = reinterpret_cast<const float4*>(a.x + (size_t)src * F) + fl;
+#pragma unroll
+                    for (int q = 0; q < VPL; q++) v[u][q] = __ldg(p + q * G);
+                } else {
+                    wv[u] = 0.f;
+#pragma unroll
+                    for (int q = 0; q < VPL; q++) v[u][q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; u++)
+#pragma unroll
+                for (int q = 0; q < VPL; q++) fma2(acc[q], v[u][q], wv[u]);
+        }
+    }
+    if (EPS > 1) {
+#pragma unroll
+        for (int o = G; o < 32; o <<= 1)
+#pragma unroll
+            for (int q = 0; q < VPL; q++) {
+                acc[q].x += __shfl_xor_sync(kFull, acc[q].x, o);
+                acc[q].y += __shfl_xor_sync(kFull, acc[q].y, o);
+                acc[q].z += __shfl_xor_sync(kFull, acc[q].z, o);
+                acc[q].w += __shfl_xor_sync(kFull, acc[q].w, o);
+            }
+    }
+    if (sub == 0) {
+        float4* o = reinterpret_cast<float4*>(dst) + fl;
+#pragma unroll
+        for (int q = 0; q < VPL; q++) __stcs(o + q * G, acc[q]);
+    }
+}
+
+// Any feature width: lanes stride over columns with scalar loads, up to 256 columns per sweep.
+__device__ __forceinline__ void warp_segment_any(const AggArgs& a, int32_t s, int32_t e, float* dst) {
+    constexpr int Q = 8;
+    constexpr int UNROLL = 4;
+    const int lane = lane_id();
+    const int64_t F = a.f;
+    for (int64_t c0 = 0; c0 < F; c0 += 32 * Q) {
+        float acc[Q];
+#pragma unroll
+        for (int q = 0; q < Q; q++) acc[q] = 0.f;
+        for (int32_t j0 = s; j0 < e; j0 += 32) {
+            const int cnt = min(32, e - j0);
+            int cur_idx = 0;
+            float cur_w = 0.f;
+            if (j0 + lane < e) {
+                cur_idx = ld_stream(a.idx + j0 + lane);
+                cur_w = ld_stream(a.w + j0 + lane);
+            }
+            for (int t = 0; t < cnt; t += UNROLL) {
+                float v[UNROLL][Q];
+                float wv[UNROLL];
+#pragma unroll
+                for (int u = 0; u < UNROLL; u++) {
+                    const int k = t + u;
+                    const int src = __shfl_sync(kFull, cur_idx, k & 31);
+                    wv[u] = __shfl_sync(kFull, cur_w, k & 31);
+                    const float* p = a.x + (size_t)src * F + c0 + lane;
+#pragma unroll
+                    for (int q = 0; q < Q; q++)
+                        v[u][q] = (k < cnt && c0 + q * 32 + lane < F) ? __ldg(p + q * 32) : 0.f;
+                    if (k >= cnt) wv[u] = 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < UNROLL; u++)
+#pragma unroll
+                    for (int q = 0; q < Q; q++) acc[q] = __fadd_rn(__fmul_rn(v[u][q], wv[u]), acc[q]);
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < Q; q++)
+            if (c0 + q * 32 + lane < F) dst[c0 + q * 32 + lane] = acc[q];
+    }
+}
+
+template <int G, int VPL, int UNROLL>
+__global__ void __launch_bounds__(kBlock) aggregate_kernel(AggArgs a) {
+    const int lane = lane_id();
+    const int64_t n_items = a.hdr ? a.hdr->n_items : 0;
+    const int chunk = a.hdr ? a.hdr->chunk : 0x7fffffff;
+    const int64_t total = n_items + a.n_out;
+    const int64_t F = a.f;
+    for (;;) {
+        unsigned long long base = 0;
+        if (lane == 0) base = atomicAdd(a.ticket, (unsigned long long)kGrab);
+        base = __shfl_sync(kFull, base, 0);
+        if ((int64_t)base >= total) break;
+        // offsets of up to kGrab consecutive ordinary rows with one coalesced read
+        const int64_t row0 = (int64_t)base - n_items;
+        int32_t offv = 0;
+        {
+            const int64_t r = row0 + lane;
+            if (lane <= kGrab && r >= 0 && r <= a.n_out) offv = a.off[r];
+        }
+#pragma unroll 1
+        for (int i = 0; i < kGrab; i++) {
+            const int64_t id = (int64_t)base + i;
+            if (id >= total) break;
+            int32_t s, e;
+            float* dst;
+            if (id < n_items) {
+                const int h = a.item_hub[id];
+                const int k = a.item_k[id];
+                const int row = a.hub_row[h];
+                const int32_t rs = a.off[row], re = a.off[row + 1];
+                s = rs + k * chunk;
+                e = min(re, s + chunk);
+                dst = a.partial + (size_t)(a.hub_first[h] + k) * F;
+            } else {
+                // lane i of this grab holds off[row], lane i+1 holds off[row+1]
+                const int64_t row = id - n_items;
+                s = __shfl_sync(kFull, offv, i);
+                e = __shfl_sync(kFull, offv, i + 1);
+                if (e - s > chunk) continue;  // hub row: its pieces are separate work ids
+                dst = a.out + (size_t)row * F;
+            }
+            if (G > 0)
+                warp_segment_vec<(G > 0 ? G : 32), VPL, UNROLL>(a, s, e, dst);
+            else
+                warp_segment_any(a, s, e, dst);
+        }
+    }
+}
+
+// Adds the partial rows of every hub in piece order and writes the hub's output row.
+__global__ void __launch_bounds__(kBlock) hub_fixup_kernel(AggArgs a) {
+    const int lane = lane_id();
+    const int warps = (gridDim.x * blockDim.x) / 32;
+    const int wid = (blockIdx.x * blockDim.x + threadIdx.x) / 32;
+    const int n_hubs = a.hdr->n_hubs;
+    const int chunk = a.hdr->chunk;
+    const int64_t F = a.f;
+    for (int h = wid; h < n_hubs; h += warps) {
+        const int row = a.hub_row[h];
+        const int deg = a.off[row + 1] - a.off[row];
+        const int pieces = (deg + chunk - 1) / chunk;
+        const float* p = a.partial + (size_t)a.hub_first[h] * F;
+        for (int64_t c = lane; c < F; c += 32) {
+            float acc = p[c];
+            for (int k = 1; k < pieces; k++) acc = __fadd_rn(acc, p[(size_t)k * F + c]);
+            a.out[(size_t)row * F + c] = acc;
+        }
+    }
+}
+
+template <int G, int VPL, int UNROLL>
+static int launch_aggregate(const AggArgs& a, cudaStream_t st) {
+    static thread_local int blocks_per_sm = 0;
+    auto kern = aggregate_kernel<G, VPL, UNROLL>;
+    if (blocks_per_sm == 0) {
+        int b = 0;
+        JG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, kern, kBlock, 0));
+        blocks_per_sm = b > 0 ? b : 1;
+    }
+    const int grid = sm_count() * blocks_per_sm;
+    kern<<<grid, kBlock, 0, st>>>(a);
+    JG_LAUNCH_CHECK();
+    return JG_OK;
+}
+
+}  // namespace jg
+
+using namespace jg;
+
+extern "C" {
+
+size_t jg_spmm_plan_bytes(int64_t n_out, int64_t nnz, int32_t chunk) {
+    if (n_out < 0 || nnz < 0 || chunk <= 0) return 0;
+    size_t bytes = 0;
+    plan_view(nullptr, nnz, chunk, &bytes);
+    return bytes;
+}
+
+int jg_spmm_plan_build(const int32_t* off, int64_t n_out, int64_t nnz, int32_t chunk, void* plan,
+                       size_t plan_bytes, jg_stream_t stream) {
+    JG_CHECK_ARG(off && plan, JG_EINVAL, "plan_build: null pointer");
+    JG_CHECK_ARG(n_out >= 0 && nnz >= 0 && chunk > 0, JG_EINVAL, "plan_build: bad sizes");
+    JG_CHECK_ARG(n_out < INT32_MAX && nnz <= INT32_MAX, JG_ESHAPE, "plan_build: sizes beyond int32");
+    size_t need = 0;
+    PlanView v = plan_view(plan, nnz, chunk, &need);
+    JG_CHECK_ARG(plan_bytes >= need, JG_EWORKSPACE, "plan_build: plan buffer %zu < %zu", plan_bytes, need);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    PlanHeader h = {0, 0, chunk, (int32_t)plan_max_hubs(nnz, chunk), (int32_t)plan_max_items(nnz, chunk), {0, 0, 0}};
+    JG_CUDA(cudaMemcpyAsync(v.hdr, &h, sizeof(h), cudaMemcpyHostToDevice, st));
+    if (n_out > 0) {
+        int grid = (int)((n_out + 255) / 256);
+        if (grid > sm_count() * 16) grid = sm_count() * 16;
+        plan_build_kernel<<<grid, 256, 0, st>>>(off, n_out, v, chunk);
+        JG_LAUNCH_CHECK();
+    }
+    return JG_OK;
+}
+
+size_t jg_aggregate_workspace_bytes(int64_t n_out, int64_t nnz, int64_t f, int32_t chunk) {
+    (void)n_out;
+    Carver c(nullptr);
+    c.take<unsigned long long>(1);
+    if (chunk > 0 && nnz > 0 && f > 0) c.take<float>((size_t)plan_max_items(nnz, chunk) * (size_t)f);
+    return c.total();
+}
+
+int jg_aggregate_f32(float* out, const float* x, const int32_t* idx, const int32_t* off,
+                     const float* w, int64_t n_out, int64_t n_in, int64_t f, int64_t nnz,
+                     const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes,
+                     jg_stream_t stream) {
+    JG_CHECK_ARG(n_out >= 0 && n_in >= 0 && f >= 0 && nnz >= 0, JG_EINVAL, "aggregate: negative size");
+    if (n_out == 0 || f == 0) return JG_OK;
+    JG_CHECK_ARG(out && off, JG_EINVAL, "aggregate: null out/off");
+    JG_CHECK_ARG(nnz == 0 || (x && idx && w), JG_EINVAL, "aggregate: null x/idx/w with nnz > 0");
+    JG_CHECK_ARG(n_out < INT32_MAX && n_in <= INT32_MAX && nnz <= INT32_MAX, JG_ESHAPE,
+                 "aggregate: sizes beyond int32 indexing");
+    JG_CHECK_ARG(!plan || chunk > 0, JG_EINVAL, "aggregate: a plan needs the chunk it was built with");
+    JG_CHECK_ARG(workspace, JG_EWORKSPACE, "aggregate: workspace is null");
+    const size_t need = jg_aggregate_workspace_bytes(n_out, nnz, f, plan ? chunk : 0);
+    JG_CHECK_ARG(workspace_bytes >= need, JG_EWORKSPACE, "aggregate: workspace %zu < %zu", workspace_bytes, need);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    AggArgs a = {};
+    a.out = out; a.x = x; a.idx = idx; a.off = off; a.w = w; a.n_out = n_out; a.f = f;
+    Carver c(workspace);
+    a.ticket = c.take<unsigned long long>(1);
+    if (plan) {
+        PlanView v = plan_view(const_cast<void*>(plan), nnz, chunk, nullptr);
+        a.hdr = v.hdr; a.hub_row = v.hub_row; a.hub_first = v.hub_first;
+        a.item_hub = v.item_hub; a.item_k = v.item_k;
+        a.partial = c.take<float>((size_t)plan_max_items(nnz, chunk) * (size_t)f);
+    }
+    JG_CUDA(cudaMemsetAsync(a.ticket, 0, sizeof(unsigned long long), st));
+
+    const bool vec_ok = (f % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) |
+                                          reinterpret_cast<uintptr_t>(a.partial)) % 16 == 0);
+    int rc;
+    if (vec_ok && f == 32)        rc = launch_aggregate<8, 1, 8>(a, st);
+    else if (vec_ok && f == 64)   rc = launch_aggregate<16, 1, 8>(a, st);
+    else if (vec_ok && f == 128)  rc = launch_aggregate<32, 1, 8>(a, st);
+    else if (vec_ok && f == 256)  rc = launch_aggregate<32, 2, 4>(a, st);
+    else if (vec_ok && f == 512)  rc = launch_aggregate<32, 4, 2>(a, st);
+    else                          rc = launch_aggregate<0, 1, 1>(a, st);
+    if (rc != JG_OK) return rc;
+    if (plan) {
+        hub_fixup_kernel<<<sm_count() * 2, kBlock, 0, st>>>(a);
+        JG_LAUNCH_CHECK();
+    }
+    return JG_OK;
+}
+
+}  // extern "C"

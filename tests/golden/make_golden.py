@@ -1,0 +1,123 @@
+"""Generates the committed golden vectors (``tests/golden/*.npz``).
+
+Inputs are the hand-written graphs of the reference's own smoke scripts
+(jittor_geometric/tests/test_*.py, which print but never assert) plus one seeded
+citation-graph-shaped instance; outputs come from the reference's OWN CPU
+operator bodies compiled by ``oracle/Makefile`` (``impl="ref"``), so this script
+needs a reference checkout at build time.  Run from the repository root:
+
+    python tests/golden/make_golden.py
+"""
+import hashlib
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+import oracle as O  # noqa: E402
+
+OUT = os.path.dirname(os.path.abspath(__file__))
+I = "ref"
+
+
+def save(name, **arrays):
+    np.savez_compressed(os.path.join(OUT, name + ".npz"), **arrays)
+    print(name, {k: v.shape for k, v in arrays.items()})
+
+
+def main():
+    O.build()
+    assert O.have_ref(), "reference CPU library missing: golden vectors need it"
+
+    # tests/test_csr.py:16-18
+    ei = np.array([[0, 0, 1, 1, 2], [1, 2, 2, 3, 3]], np.int32)
+    w = np.array([1, 2, 3, 4, 5], np.float32)
+    ci, ro, cw = O.coo_to_csr(ei, w, 4, I)
+    ri, co, sw = O.coo_to_csc(ei, w, 4, I)
+    save("ref_test_csr", edge_index=ei, edge_weight=w, n=np.int64(4), column_indices=ci, row_offset=ro,
+         csr_weight=cw, row_indices=ri, column_offset=co, csc_weight=sw)
+
+    # tests/test_mp_spmm.py:14-27
+    x = np.array([[3, 2, 1, 0, 5, 0, 1, 0, 2, 0], [1, 0, 2, 3, 0, 4, 0, 5, 1, 0],
+                  [0, 6, 0, 0, 7, 0, 8, 0, 9, 0], [4, 0, 0, 1, 0, 5, 0, 0, 0, 6],
+                  [0, 0, 3, 0, 4, 0, 2, 1, 0, 0], [7, 0, 2, 0, 3, 0, 4, 5, 0, 6],
+                  [1, 3, 0, 2, 0, 0, 4, 5, 6, 0], [0, 8, 0, 0, 7, 1, 0, 9, 2, 0],
+                  [9, 0, 6, 0, 0, 2, 0, 0, 1, 3], [0, 1, 0, 4, 0, 0, 6, 0, 5, 7]], np.float32)
+    ei = np.array([[0, 0, 1, 1, 2, 2, 3, 4, 4, 5, 5, 7, 8], [1, 2, 2, 3, 3, 4, 5, 8, 9, 5, 8, 9, 9]], np.int32)
+    w = np.array([1, 2, 3, 4, 5, 3, 5, 1, 2, 3, 2, 3, 2], np.float32)
+    ci, ro, cw = O.coo_to_csr(ei, w, 10, I)
+    ri, co, sw = O.coo_to_csc(ei, w, 10, I)
+    y = O.aggregate(x, ri, co, sw, impl=I)         # forward (CSC) == SpmmCsr(x, csr) == SpmmCoo
+    gy = O.aggregate(x, ci, ro, cw, impl=I)        # backward kernel (CSR) on the same matrix
+    save("ref_test_mp_spmm", x=x, edge_index=ei, edge_weight=w, n=np.int64(10), column_indices=ci,
+         row_offset=ro, csr_weight=cw, row_indices=ri, column_offset=co, csc_weight=sw, out_csc=y, out_csr=gy)
+
+    # tests/test_aggregate.py:43-54 (its offsets describe 3 vertices; the first three rows of x
+    # are used, and the weight literals are the five the script spells out)
+    x = np.array([[3, 2, 1], [3, 2, 1], [3, 2, 1]], np.float32)
+    ri, co = np.array([0, 0, 1, 2], np.int32), np.array([0, 1, 3, 4], np.int32)
+    sw = np.array([1.0, 2.0, 3, 0, 4.0], np.float32)[:4]
+    ci, ro = np.array([0, 1, 1, 2], np.int32), np.array([0, 2, 3, 4], np.int32)
+    cw = np.array([3.0, 1.0, 4, 0, 2.0], np.float32)[:4]
+    save("ref_test_aggregate", x=x, row_indices=ri, column_offset=co, csc_weight=sw, column_indices=ci,
+         row_offset=ro, csr_weight=cw, out_fwd=O.aggregate(x, ri, co, sw, impl=I),
+         out_bwd=O.aggregate(x, ci, ro, cw, impl=I))
+
+    # tests/test_edgesoftmax.py:19-25, plus a gradient vector for the backward op
+    xs = np.array([1, 2, 3, 4], np.float32)
+    ys = O.edge_softmax(xs, co, I)
+    g = np.array([0.5, -1.0, 2.0, 0.25], np.float32)
+    save("ref_test_edgesoftmax", x=xs, row_indices=ri, column_offset=co, out=ys, grad=g,
+         grad_in=O.edge_softmax_backward(g, ys, co, I))
+
+    # tests/test_scatter_to_edge.py:14-20 and tests/test_edgetovertex.py:20-26
+    xv = np.array([[1, 1, 1], [2, 2, 2], [3, 3, 3]], np.float32)
+    xe = np.array([[1, 1, 1], [2, 2, 2], [3, 3, 3], [3, 2, 1]], np.float32)
+    save("ref_test_scatter", x_vertex=xv, x_edge=xe, row_indices=ri, column_offset=co,
+         to_edge_src=O.scatter_to_edge(xv, ri, co, 0, I), to_edge_dst=O.scatter_to_edge(xv, ri, co, 1, I),
+         to_vertex_dst=O.edge_to_vertex(xe, ri, co, 1, I), to_vertex_src=O.edge_to_vertex(xe, ri, co, 0, I))
+
+    # tests/test_undirected.py:12-16
+    ei = np.array([[0, 1, 1], [2, 0, 2]], np.int32)
+    ea = np.array([1, 3, 2], np.float32)
+    nei, nea = O.to_undirected(ei, ea, 3, I)
+    save("ref_test_undirected", edge_index=ei, edge_attr=ea, new_edge_index=nei, new_edge_attr=nea)
+
+    # tests/test_spmmcsr.py:13-17 (int64 indices there) and tests/test_spmmcoo.py:15-17.  Both go
+    # through cuSPARSE in the reference with trans_A=True, i.e. out[dst] += w * x[src]; the CPU
+    # aggregate over the transposed structure is the stated equivalent (tests/test_mp_spmm.py:28-36).
+    x3 = np.array([[3, 2, 1], [3, 2, 1], [3, 2, 1]], np.float32)
+    ci, ro = np.array([0, 1, 1, 2], np.int64), np.array([0, 2, 3, 4], np.int64)
+    cw = np.array([3, 1, 4, 2], np.float32)
+    src = np.repeat(np.arange(3), np.diff(ro)).astype(np.int32)
+    tri, tco, tw = O.coo_to_csc(np.stack([src, ci.astype(np.int32)]), cw, 3, I)
+    x4 = np.array([[3, 2, 1], [4, 2, 2], [1, 2, 3]], np.float32)
+    ei = np.array([[0, 0, 1, 2], [1, 2, 2, 1]], np.int32)
+    ew = np.ones(4, np.float32)
+    cri, cco, cw2 = O.coo_to_csc(ei, ew, 3, I)
+    save("ref_test_spmm", csr_x=x3, column_indices=ci, row_offset=ro, csr_weight=cw,
+         csr_out=O.aggregate(x3, tri, tco, tw, impl=I), coo_x=x4, edge_index=ei, edge_weight=ew,
+         coo_out=O.aggregate(x4, cri, cco, cw2, impl=I))
+
+    # Seeded citation-graph-shaped instance: 2708 nodes, 5278 undirected edges, gcn_norm weights.
+    import torch  # noqa: F401  (generator lives in the package)
+    from jittorgeometric_b200 import synth
+    ei = synth.preferential_attachment(2708, 5278, seed=20261125).numpy()
+    nei, nw = O.gcn_norm(ei, None, 2708)
+    ci, ro, cw = O.coo_to_csr(nei, nw, 2708, I)
+    ri, co, sw = O.coo_to_csc(nei, nw, 2708, I)
+    rng = np.random.default_rng(20261125)
+    x7 = rng.standard_normal((2708, 7)).astype(np.float32)
+    x256 = rng.standard_normal((2708, 256)).astype(np.float32)
+    y7 = O.aggregate(x7, ri, co, sw, impl=I)
+    y256 = O.aggregate(x256, ri, co, sw, impl=I)
+    save("citation_2708", edge_index=ei, norm_edge_index=nei, norm_weight=nw, column_indices=ci, row_offset=ro,
+         csr_weight=cw, row_indices=ri, column_offset=co, csc_weight=sw, x7=x7, y7=y7,
+         x256_seed=np.int64(20261125), y256_rows=y256[::97].copy(),
+         y256_sha256=np.frombuffer(hashlib.sha256(y256.tobytes()).digest(), np.uint8))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,138 @@
+"""CPU-only: the plain-C restatement must reproduce the golden vectors (which were
+produced by the reference's own compiled CPU bodies) bit for bit, and must agree
+with those bodies live wherever the compiled reference library is present."""
+import os
+
+import numpy as np
+import pytest
+
+G = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def load(name):
+    return dict(np.load(os.path.join(G, name + ".npz")))
+
+
+def impls(oracle):
+    return ["port", "ref"] if oracle.have_ref() else ["port"]
+
+
+def test_conversion_goldens(oracle):
+    for impl in impls(oracle):
+        for name in ("ref_test_csr", "ref_test_mp_spmm"):
+            d = load(name)
+            n = int(d["n"])
+            ci, ro, cw = oracle.coo_to_csr(d["edge_index"], d["edge_weight"], n, impl)
+            ri, co, sw = oracle.coo_to_csc(d["edge_index"], d["edge_weight"], n, impl)
+            for got, key in ((ci, "column_indices"), (ro, "row_offset"), (cw, "csr_weight"),
+                             (ri, "row_indices"), (co, "column_offset"), (sw, "csc_weight")):
+                assert np.array_equal(got, d[key]), (impl, name, key)
+    d = load("ref_test_csr")
+    assert d["row_offset"].tolist() == [0, 2, 4, 5, 5]
+
+
+def test_aggregate_goldens(oracle):
+    for impl in impls(oracle):
+        d = load("ref_test_mp_spmm")
+        assert np.array_equal(oracle.aggregate(d["x"], d["row_indices"], d["column_offset"], d["csc_weight"], impl=impl), d["out_csc"])
+        assert np.array_equal(oracle.aggregate(d["x"], d["column_indices"], d["row_offset"], d["csr_weight"], impl=impl), d["out_csr"])
+        d = load("ref_test_aggregate")
+        assert np.array_equal(oracle.aggregate(d["x"], d["row_indices"], d["column_offset"], d["csc_weight"], impl=impl), d["out_fwd"])
+        assert np.array_equal(oracle.aggregate(d["x"], d["column_indices"], d["row_offset"], d["csr_weight"], impl=impl), d["out_bwd"])
+        d = load("citation_2708")
+        assert np.array_equal(oracle.aggregate(d["x7"], d["row_indices"], d["column_offset"], d["csc_weight"], impl=impl), d["y7"])
+
+
+def test_aggregate_matches_float64_truth(oracle):
+    d = load("citation_2708")
+    y = oracle.aggregate(d["x7"], d["row_indices"], d["column_offset"], d["csc_weight"])
+    truth, scale = oracle.aggregate_f64(d["x7"], d["row_indices"], d["column_offset"], d["csc_weight"])
+    assert (np.abs(y - truth) / (scale + 1e-30)).max() <= 1e-5
+
+
+def test_edge_ops_goldens(oracle):
+    for impl in impls(oracle):
+        d = load("ref_test_edgesoftmax")
+        y = oracle.edge_softmax(d["x"], d["column_offset"], impl)
+        assert np.array_equal(y, d["out"])
+        assert np.array_equal(oracle.edge_softmax_backward(d["grad"], y, d["column_offset"], impl), d["grad_in"])
+        d = load("ref_test_scatter")
+        assert np.array_equal(oracle.scatter_to_edge(d["x_vertex"], d["row_indices"], d["column_offset"], 0, impl), d["to_edge_src"])
+        assert np.array_equal(oracle.scatter_to_edge(d["x_vertex"], d["row_indices"], d["column_offset"], 1, impl), d["to_edge_dst"])
+        assert np.array_equal(oracle.edge_to_vertex(d["x_edge"], d["row_indices"], d["column_offset"], 1, impl), d["to_vertex_dst"])
+        assert np.array_equal(oracle.edge_to_vertex(d["x_edge"], d["row_indices"], d["column_offset"], 0, impl), d["to_vertex_src"])
+        d = load("ref_test_undirected")
+        nei, _ = oracle.to_undirected(d["edge_index"], d["edge_attr"], 3, impl)
+        assert np.array_equal(nei, d["new_edge_index"])
+    d = load("ref_test_edgesoftmax")
+    assert abs(float(d["out"][1] + d["out"][2]) - 1.0) < 1e-6
+
+
+def test_multihead_softmax_is_per_column(oracle):
+    rng = np.random.default_rng(3)
+    off = np.array([0, 3, 3, 10, 11], np.int32)
+    x = rng.standard_normal((11, 4)).astype(np.float32)
+    y = oracle.edge_softmax(x, off)
+    for h in range(4):
+        assert np.array_equal(y[:, h], oracle.edge_softmax(x[:, h].copy(), off))
+
+
+def test_gcn_norm_golden_and_numpy(oracle):
+    d = load("citation_2708")
+    ei, w = oracle.gcn_norm(d["edge_index"], None, 2708)
+    assert np.array_equal(ei, d["norm_edge_index"]) and np.array_equal(w, d["norm_weight"])
+    assert ei.shape[1] == 10556 + 2708
+    assert np.array_equal(ei[:, -2708:], np.stack([np.arange(2708)] * 2))  # loops appended last, in node order
+    ei2, w2 = oracle.gcn_norm_numpy(d["edge_index"], None, 2708)
+    assert np.array_equal(ei, ei2)
+    ulp = np.abs(w.view(np.int32).astype(np.int64) - w2.view(np.int32).astype(np.int64)).max()
+    assert ulp <= 8  # numpy's float32 power and libm's powf differ in the last bits
+
+
+def test_gcn_norm_existing_loops_keep_their_weight(oracle):
+    ei = np.array([[0, 1, 1, 2], [1, 1, 2, 0]], np.int32)
+    w = np.array([1.0, 5.0, 2.0, 3.0], np.float32)
+    nei, nw = oracle.gcn_norm(ei, w, 3)
+    assert nei.tolist() == [[0, 1, 2, 0, 1, 2], [1, 2, 0, 0, 1, 2]]
+    nei2, nw2 = oracle.gcn_norm_numpy(ei, w, 3)
+    assert np.array_equal(nei, nei2) and np.allclose(nw, nw2, rtol=1e-6)
+    # degree of node 1 = w(0->1) + loop weight 5
+    assert np.isclose(nw[4], 5.0 / 6.0, rtol=1e-6)
+
+
+@pytest.mark.parametrize("n,E,f", [(1, 0, 3), (7, 0, 4), (50, 400, 5), (300, 9000, 33)])
+def test_port_equals_compiled_reference_on_random_graphs(oracle, n, E, f):
+    if not oracle.have_ref():
+        pytest.skip("compiled reference bodies not present")
+    rng = np.random.default_rng(n * 1000 + E)
+    ei = rng.integers(0, n, size=(2, E)).astype(np.int32)
+    w = rng.standard_normal(E).astype(np.float32)
+    for fn in (oracle.coo_to_csr, oracle.coo_to_csc):
+        for a, b in zip(fn(ei, w, n, "port"), fn(ei, w, n, "ref")):
+            assert np.array_equal(a, b)
+    idx, off, cw = oracle.coo_to_csc(ei, w, n)
+    x = rng.standard_normal((n, f)).astype(np.float32)
+    assert np.array_equal(oracle.aggregate(x, idx, off, cw, impl="port"), oracle.aggregate(x, idx, off, cw, impl="ref"))
+    sc = (rng.standard_normal(E) * 4).astype(np.float32)
+    y = oracle.edge_softmax(sc, off, "port")
+    assert np.array_equal(y, oracle.edge_softmax(sc, off, "ref"))
+    g = rng.standard_normal(E).astype(np.float32)
+    assert np.array_equal(oracle.edge_softmax_backward(g, y, off, "port"), oracle.edge_softmax_backward(g, y, off, "ref"))
+    m = rng.standard_normal((E, f)).astype(np.float32)
+    for flag in (0, 1):
+        assert np.array_equal(oracle.scatter_to_edge(x, idx, off, flag, "port"), oracle.scatter_to_edge(x, idx, off, flag, "ref"))
+        assert np.array_equal(oracle.edge_to_vertex(m, idx, off, flag, "port"), oracle.edge_to_vertex(m, idx, off, flag, "ref"))
+
+
+def test_fused_gat_restatement_equals_unfused_reference_pipeline(oracle):
+    rng = np.random.default_rng(11)
+    n, E, C = 200, 3000, 8
+    ei = rng.integers(0, n, size=(2, E)).astype(np.int32)
+    nei, nw = oracle.gcn_norm(ei, None, n)
+    idx, off, _ = oracle.coo_to_csc(nei, nw, n)
+    h = np.maximum(rng.standard_normal((n, C)), 0).astype(np.float32)
+    a = (rng.standard_normal(2 * C) * 0.3).astype(np.float32)
+    impl = "ref" if oracle.have_ref() else "port"
+    unfused = oracle.gat_unfused(h, a, idx, off, impl)
+    fused = oracle.gat_aggregate(h, a[:C].reshape(1, C), a[C:].reshape(1, C), idx, off, 1, C)
+    assert np.abs(unfused - fused).max() <= 2e-6
