@@ -259,12 +259,14 @@ def run_single(args):
             hy[f].copy_(y, non_blocking=True)
 
     e2e_steps = max(1, min(args.steps, 5))
-    e2e_step(); torch.cuda.synchronize()
-    t0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    t1.record(); torch.cuda.synchronize()
-    e2e_ms = t0.elapsed_time(t1) / e2e_steps
+    e2e_ms = float("nan")
+    if not args.skip_e2e:
+        e2e_step(); torch.cuda.synchronize()
+        t0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        t1.record(); torch.cuda.synchronize()
+        e2e_ms = t0.elapsed_time(t1) / e2e_steps
     io_bytes = sum(n * f * 4 for f in WIDTHS)
 
     cpu = cpu_reference_sample(csc, n, WIDTHS, budget_s=args.cpu_budget) if args.cpu_budget > 0 else None
@@ -296,7 +298,12 @@ def main():
     ap.add_argument("--scale", type=int, default=21)
     ap.add_argument("--edge-factor", type=int, default=32)
     ap.add_argument("--cpu-budget", type=float, default=16.0, help="seconds of CPU-baseline work (0 = skip)")
+    ap.add_argument("--widths", default=None, help="comma-separated subset of the sweep (profiling runs)")
+    ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
+    global WIDTHS
+    if args.widths:
+        WIDTHS = tuple(int(v) for v in args.widths.split(","))
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         return run_reference(args)
