@@ -68,6 +68,27 @@ int jg_aggregate_f32(float* out, const float* x, const int32_t* idx, const int32
                      const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes,
                      jg_stream_t stream);
 
+/* Aggregation for callers that cannot allocate.  No counterpart in the reference: this entry
+ * point exists for hosts that must not call cudaMalloc (or any allocating routine) once they
+ * run - a serving process with a memory pool fixed at start-up, a plugin inside a process that
+ * owns the device allocator - and therefore cannot provide the workspace jg_aggregate_f32
+ * asks for.  Same result contract as jg_aggregate_f32; the scratch (ticket counter, hub plan,
+ * partial rows of split hub rows) is a fixed array of jg_aggregate_static_capacity_bytes()
+ * (32 MiB) inside the library image, resident on every GPU that loads the library until the
+ * process exits.  The caller still passes inputs and outputs; nothing is allocated or freed.
+ *   - Hub rows are cut into pieces of 1024 entries, doubled until plan and partial rows fit
+ *     the array; if they cannot fit, JG_EWORKSPACE is returned with the sizes in
+ *     jg_last_error() and nothing is launched.
+ *   - The first call on each device looks up the array's device address; make that first call
+ *     outside any stream capture, with the device current.
+ *   - Every call on a device shares the one array (it keeps the previous call's contents; the
+ *     words that must start at zero are cleared by each call).  Calls that overlap on the GPU -
+ *     different streams, or different host threads - race on it: serialise them. */
+size_t jg_aggregate_static_capacity_bytes(void);
+int jg_aggregate_f32_static(float* out, const float* x, const int32_t* idx, const int32_t* off,
+                            const float* w, int64_t n_out, int64_t n_in, int64_t f, int64_t nnz,
+                            jg_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -30,6 +30,8 @@ SIGNATURES = {
     "jg_spmm_plan_build": (ctypes.c_int, [vp, i64, i64, i32, vp, sz, vp]),
     "jg_aggregate_workspace_bytes": (sz, [i64, i64, i64, i32]),
     "jg_aggregate_f32": (ctypes.c_int, [vp, vp, vp, vp, vp, i64, i64, i64, i64, vp, i32, vp, sz, vp]),
+    "jg_aggregate_static_capacity_bytes": (sz, []),
+    "jg_aggregate_f32_static": (ctypes.c_int, [vp, vp, vp, vp, vp, i64, i64, i64, i64, vp]),
 }
 
 

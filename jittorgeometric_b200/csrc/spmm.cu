@@ -385,4 +385,109 @@ int jg_aggregate_f32(float* out, const float* x, const int32_t* idx, const int32
     return JG_OK;
 }
 
+
+// ------------------------------------------------------------------------------------------
+// Aggregation without any allocation.
+//
+// Some callers cannot hand this library a workspace: a host program that is not allowed to call
+// cudaMalloc once it is running (an inference server whose memory pool is fixed at start-up, a
+// plugin loaded into a process that owns the allocator, code running where a device allocation
+// would force a synchronisation it cannot afford).  For them the scratch of the aggregation
+// (ticket counter, hub plan, partial rows of split hub rows) lives in one fixed array that is part
+// of the library image on every GPU that loads it, kStaticScratchBytes long.
+namespace jg {
+
+constexpr size_t kStaticScratchBytes = size_t(32) << 20;  // 32 MiB per GPU, held until exit
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch per device.  In host code the array's name is only a
+// stand-in for the symbol, so the address a kernel may use has to be asked for, once per device,
+// with that device current.
+static unsigned char* g_static_ptr[64] = {nullptr};
+
+static int static_scratch(unsigned char** out) {
+    int dev = 0;
+    JG_CUDA(cudaGetDevice(&dev));
+    JG_CHECK_ARG(dev >= 0 && dev < 64, JG_EUNSUPPORTED, "device index %d beyond 63", dev);
+    if (!g_static_ptr[dev]) {
+        void* p = nullptr;
+        JG_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        g_static_ptr[dev] = static_cast<unsigned char*>(p);
+    }
+    *out = g_static_ptr[dev];
+    return JG_OK;
+}
+
+// Bytes of scratch one call needs when hub rows are cut into `chunk`-entry pieces.
+static size_t static_need(int64_t nnz, int64_t f, int32_t chunk) {
+    size_t plan_bytes = 0;
+    plan_view(nullptr, nnz, chunk, &plan_bytes);
+    Carver c(nullptr);
+    c.take<unsigned long long>(1);
+    c.take<unsigned char>(plan_bytes);
+    c.take<float>((size_t)plan_max_items(nnz, chunk) * (size_t)f);
+    return c.total();
+}
+
+}  // namespace jg
+
+size_t jg_aggregate_static_capacity_bytes(void) { return jg::kStaticScratchBytes; }
+
+int jg_aggregate_f32_static(float* out, const float* x, const int32_t* idx, const int32_t* off,
+                            const float* w, int64_t n_out, int64_t n_in, int64_t f, int64_t nnz,
+                            jg_stream_t stream) {
+    JG_CHECK_ARG(n_out >= 0 && n_in >= 0 && f >= 0 && nnz >= 0, JG_EINVAL, "aggregate_static: negative size");
+    if (n_out == 0 || f == 0) return JG_OK;
+    JG_CHECK_ARG(out && off, JG_EINVAL, "aggregate_static: null out/off");
+    JG_CHECK_ARG(nnz == 0 || (x && idx && w), JG_EINVAL, "aggregate_static: null x/idx/w with nnz > 0");
+    JG_CHECK_ARG(n_out < INT32_MAX && n_in <= INT32_MAX && nnz <= INT32_MAX, JG_ESHAPE,
+                 "aggregate_static: sizes beyond int32 indexing");
+    // Piece length: 1024 entries, doubled until plan and partial rows fit the fixed array.
+    int32_t chunk = 1024;
+    while (static_need(nnz, f, chunk) > kStaticScratchBytes && chunk < (1 << 20)) chunk *= 2;
+    const size_t need = static_need(nnz, f, chunk);
+    JG_CHECK_ARG(need <= kStaticScratchBytes, JG_EWORKSPACE,
+                 "aggregate_static: nnz=%lld at width %lld needs %zu bytes of scratch even with %d-entry pieces; "
+                 "the built-in scratch holds %zu (use jg_aggregate_f32 with a caller-owned workspace)",
+                 (long long)nnz, (long long)f, need, chunk, kStaticScratchBytes);
+    unsigned char* base = nullptr;
+    int rc = static_scratch(&base);
+    if (rc != JG_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    size_t plan_bytes = 0;
+    plan_view(nullptr, nnz, chunk, &plan_bytes);
+    Carver c(base);
+    AggArgs a = {};
+    a.out = out; a.x = x; a.idx = idx; a.off = off; a.w = w; a.n_out = n_out; a.f = f;
+    a.ticket = c.take<unsigned long long>(1);
+    PlanView v = plan_view(c.take<unsigned char>(plan_bytes), nnz, chunk, nullptr);
+    a.hdr = v.hdr; a.hub_row = v.hub_row; a.hub_first = v.hub_first; a.item_hub = v.item_hub; a.item_k = v.item_k;
+    a.partial = c.take<float>((size_t)plan_max_items(nnz, chunk) * (size_t)f);
+
+    // The array keeps whatever the previous call left: the two words that must start at zero
+    // (ticket, plan counters) are rewritten here; everything else is written before it is read.
+    JG_CUDA(cudaMemsetAsync(a.ticket, 0, sizeof(unsigned long long), st));
+    PlanHeader h = {0, 0, chunk, (int32_t)plan_max_hubs(nnz, chunk), (int32_t)plan_max_items(nnz, chunk), {0, 0, 0}};
+    JG_CUDA(cudaMemcpyAsync(v.hdr, &h, sizeof(h), cudaMemcpyHostToDevice, st));
+    {
+        int grid = (int)((n_out + 255) / 256);
+        if (grid > sm_count() * 16) grid = sm_count() * 16;
+        plan_build_kernel<<<grid, 256, 0, st>>>(off, n_out, v, chunk);
+        JG_LAUNCH_CHECK();
+    }
+    const bool vec_ok = (f % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) |
+                                          reinterpret_cast<uintptr_t>(a.partial)) % 16 == 0);
+    if (vec_ok && f == 32)        rc = launch_aggregate<8, 1, 8>(a, st);
+    else if (vec_ok && f == 64)   rc = launch_aggregate<16, 1, 8>(a, st);
+    else if (vec_ok && f == 128)  rc = launch_aggregate<32, 1, 8>(a, st);
+    else if (vec_ok && f == 256)  rc = launch_aggregate<32, 2, 4>(a, st);
+    else if (vec_ok && f == 512)  rc = launch_aggregate<32, 4, 2>(a, st);
+    else                          rc = launch_aggregate<0, 1, 1>(a, st);
+    if (rc != JG_OK) return rc;
+    hub_fixup_kernel<<<sm_count() * 2, kBlock, 0, st>>>(a);
+    JG_LAUNCH_CHECK();
+    return JG_OK;
+}
+
 }  // extern "C"
