@@ -8,16 +8,22 @@
 // Work decomposition.  A "work id" is either one piece (<= chunk entries) of a
 // hub row listed in the plan, or one ordinary row.  A persistent grid of warps
 // pulls ids eight at a time from a global ticket counter (hub pieces first, so
-// the longest items start earliest).  One warp owns one id: it loads 32 indices
-// and weights with one coalesced read each, broadcasts them by shuffle, and
-// gathers feature rows with 128-bit loads, several rows in flight per lane.
-// HBM-bound: per nonzero one 4 B index, one 4 B weight and one F*4 B row.
+// the longest items start earliest).  One warp owns one id: it reads 32 indices
+// and weights with one coalesced load each (the next tile, which may already
+// belong to the next row, is prefetched), stages them in shared memory as
+// (index, weight) pairs so that each entry costs one 64-bit broadcast load, and
+// gathers feature rows with 128-bit loads, a batch of rows in flight per lane.
+// Full batches run without predicates: the kernel is sensitive to instruction
+// issue as well as to memory latency (about 8-12 instructions per entry).
+// Memory-bound: per nonzero one 4 B index, one 4 B weight and one F*4 B row.
 //
 // Determinism.  Each output row is produced by exactly one warp (or, for a hub
 // row, by a fixed-order sum of its pieces' partial rows held in scratch), so
 // results do not depend on which warp ran which id.  No atomics touch data; the
 // only atomic is the ticket counter.
 #include "common.cuh"
+
+#include <cstdlib>
 
 namespace jg {
 
@@ -101,72 +107,163 @@ __device__ __forceinline__ void fma2(float4& a, const float4& v, float w) {
     a.w = __fadd_rn(__fmul_rn(v.w, w), a.w);
 }
 
-// One warp aggregates entries [s, e) into dst (F = 4*G*VPL floats).
-// G lanes cover one feature row; 32/G entries are processed side by side.
-template <int G, int VPL, int UNROLL>
-__device__ __forceinline__ void warp_segment_vec(const AggArgs& a, int32_t s, int32_t e, float* dst) {
+// Exact mode rounds multiply and add separately, as the reference CPU loop does; the fused
+// mode uses one FMA per term.
+template <bool EXACT>
+__device__ __forceinline__ void axpy4(float4& a, const float4& v, float w) {
+    if (EXACT) {
+        a.x = __fadd_rn(__fmul_rn(v.x, w), a.x);
+        a.y = __fadd_rn(__fmul_rn(v.y, w), a.y);
+        a.z = __fadd_rn(__fmul_rn(v.z, w), a.z);
+        a.w = __fadd_rn(__fmul_rn(v.w, w), a.w);
+    } else {
+        a.x = fmaf(v.x, w, a.x);
+        a.y = fmaf(v.y, w, a.y);
+        a.z = fmaf(v.z, w, a.z);
+        a.w = fmaf(v.w, w, a.w);
+    }
+}
+
+// Vector-width kernel (F = 4*G*VPL).  G lanes cover one feature row, 32/G entries are gathered
+// side by side, B steps per batch.
+template <int G, int VPL, int B, int MINB, bool EXACT>
+__global__ void __launch_bounds__(kBlock, MINB) aggregate_rows_kernel(AggArgs a) {
     constexpr int EPS = 32 / G;
     constexpr int F = 4 * G * VPL;
+    __shared__ int2 s_tile[kBlock / 32][32];
     const int lane = lane_id();
     const int sub = lane / G;
     const int fl = lane % G;
-    float4 acc[VPL];
-#pragma unroll
-    for (int q = 0; q < VPL; q++) acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-
-    int my_idx = 0;
-    float my_w = 0.f;
-    if (s + lane < e) {
-        my_idx = ld_stream(a.idx + s + lane);
-        my_w = ld_stream(a.w + s + lane);
-    }
-    for (int32_t j0 = s; j0 < e; j0 += 32) {
-        const int cnt = min(32, e - j0);
-        const int cur_idx = my_idx;
-        const float cur_w = my_w;
-        if (j0 + 32 + lane < e) {  // next tile's indices in flight while this one is gathered
-            my_idx = ld_stream(a.idx + j0 + 32 + lane);
-            my_w = ld_stream(a.w + j0 + 32 + lane);
+    int2* tile = s_tile[threadIdx.x / 32];
+    const char* xb = reinterpret_cast<const char*>(a.x) + fl * 16;
+    const int64_t n_items = a.hdr ? a.hdr->n_items : 0;
+    const int chunk = a.hdr ? a.hdr->chunk : 0x7fffffff;
+    const int64_t total = n_items + a.n_out;
+    for (;;) {
+        unsigned long long base = 0;
+        if (lane == 0) base = atomicAdd(a.ticket, (unsigned long long)kGrab);
+        base = __shfl_sync(kFull, base, 0);
+        if ((int64_t)base >= total) break;
+        const int64_t row0 = (int64_t)base - n_items;
+        int32_t offv = 0;
+        {
+            const int64_t r = row0 + lane;
+            if (lane <= kGrab && r >= 0 && r <= a.n_out) offv = a.off[r];
         }
-        for (int t = 0; t < cnt; t += EPS * UNROLL) {
-            float4 v[UNROLL][VPL];
-            float wv[UNROLL];
+        int32_t pf_pos = -1;  // position of the prefetched tile
+        int32_t pf_lim = -1;  // ... which holds entries below this bound only
+        int pf_idx = 0;
+        float pf_w = 0.f;
+#pragma unroll 1
+        for (int i = 0; i < kGrab; i++) {
+            const int64_t id = (int64_t)base + i;
+            if (id >= total) break;
+            int32_t s, e, lim;
+            float* dst;
+            if (id < n_items) {
+                const int h = a.item_hub[id];
+                const int k = a.item_k[id];
+                const int row = a.hub_row[h];
+                const int32_t rs = a.off[row], re = a.off[row + 1];
+                s = rs + k * chunk;
+                e = min(re, s + chunk);
+                lim = re;  // the next piece of the same hub continues where this one ends
+                dst = a.partial + (size_t)(a.hub_first[h] + k) * F;
+            } else {
+                s = __shfl_sync(kFull, offv, i);
+                e = __shfl_sync(kFull, offv, i + 1);
+                if (e - s > chunk) continue;  // hub row: its pieces are separate work ids
+                // entries of the following rows of this grab are contiguous with this row's
+                const int64_t left = a.n_out - row0;
+                const int last = left < kGrab ? (int)left : kGrab;
+                lim = __shfl_sync(kFull, offv, last);
+                dst = a.out + (size_t)(id - n_items) * F;
+            }
+            if (lim != pf_lim) pf_pos = -1;  // a tile prefetched under another bound is not reusable
+            pf_lim = lim;
+            float4 acc[VPL];
 #pragma unroll
-            for (int u = 0; u < UNROLL; u++) {
-                const int k = t + u * EPS + sub;
-                const int src = __shfl_sync(kFull, cur_idx, k & 31);
-                wv[u] = __shfl_sync(kFull, cur_w, k & 31);
-                if (k < cnt) {
-                    const float4* p = reinterpret_cast<const float4*>(a.x + (size_t)src * F) + fl;
+            for (int q = 0; q < VPL; q++) acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int32_t j0 = s; j0 < e; j0 += 32) {
+                int cur_idx = pf_idx;
+                float cur_w = pf_w;
+                if (pf_pos != j0) {
+                    cur_idx = 0;
+                    cur_w = 0.f;
+                    if (j0 + lane < lim) {
+                        cur_idx = ld_stream(a.idx + j0 + lane);
+                        cur_w = ld_stream(a.w + j0 + lane);
+                    }
+                }
+                // next tile: the rest of this row, or the start of the next row of the grab
+                pf_pos = min(j0 + 32, e);
+                pf_idx = 0;
+                pf_w = 0.f;
+                if (pf_pos + lane < lim) {
+                    pf_idx = ld_stream(a.idx + pf_pos + lane);
+                    pf_w = ld_stream(a.w + pf_pos + lane);
+                }
+                __syncwarp();
+                tile[lane] = make_int2(cur_idx, __float_as_int(cur_w));
+                __syncwarp();
+                const int cnt = min(32, e - j0);
+                int t = 0;
+                for (; t + EPS * B <= cnt; t += EPS * B) {  // full batches: no predicates
+                    float4 v[B][VPL];
+                    float wv[B];
 #pragma unroll
-                    for (int q = 0; q < VPL; q++) v[u][q] = __ldg(p + q * G);
-                } else {
-                    wv[u] = 0.f;
+                    for (int u = 0; u < B; u++) {
+                        const int2 p = tile[t + u * EPS + sub];
+                        wv[u] = __int_as_float(p.y);
+                        const float4* g = reinterpret_cast<const float4*>(xb + (size_t)(unsigned)p.x * (F * 4));
 #pragma unroll
-                    for (int q = 0; q < VPL; q++) v[u][q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        for (int q = 0; q < VPL; q++) v[u][q] = __ldg(g + q * G);
+                    }
+#pragma unroll
+                    for (int u = 0; u < B; u++)
+#pragma unroll
+                        for (int q = 0; q < VPL; q++) axpy4<EXACT>(acc[q], v[u][q], wv[u]);
+                }
+                if (t < cnt) {  // last, partial batch
+                    float4 v[B][VPL];
+                    float wv[B];
+#pragma unroll
+                    for (int u = 0; u < B; u++) {
+                        const int k = t + u * EPS + sub;
+                        wv[u] = 0.f;
+#pragma unroll
+                        for (int q = 0; q < VPL; q++) v[u][q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (k < cnt) {
+                            const int2 p = tile[k];
+                            wv[u] = __int_as_float(p.y);
+                            const float4* g = reinterpret_cast<const float4*>(xb + (size_t)(unsigned)p.x * (F * 4));
+#pragma unroll
+                            for (int q = 0; q < VPL; q++) v[u][q] = __ldg(g + q * G);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < B; u++)
+#pragma unroll
+                        for (int q = 0; q < VPL; q++) axpy4<EXACT>(acc[q], v[u][q], wv[u]);
                 }
             }
+            if (EPS > 1) {
 #pragma unroll
-            for (int u = 0; u < UNROLL; u++)
+                for (int o = G; o < 32; o <<= 1)
 #pragma unroll
-                for (int q = 0; q < VPL; q++) fma2(acc[q], v[u][q], wv[u]);
-        }
-    }
-    if (EPS > 1) {
-#pragma unroll
-        for (int o = G; o < 32; o <<= 1)
-#pragma unroll
-            for (int q = 0; q < VPL; q++) {
-                acc[q].x += __shfl_xor_sync(kFull, acc[q].x, o);
-                acc[q].y += __shfl_xor_sync(kFull, acc[q].y, o);
-                acc[q].z += __shfl_xor_sync(kFull, acc[q].z, o);
-                acc[q].w += __shfl_xor_sync(kFull, acc[q].w, o);
+                    for (int q = 0; q < VPL; q++) {
+                        acc[q].x += __shfl_xor_sync(kFull, acc[q].x, o);
+                        acc[q].y += __shfl_xor_sync(kFull, acc[q].y, o);
+                        acc[q].z += __shfl_xor_sync(kFull, acc[q].z, o);
+                        acc[q].w += __shfl_xor_sync(kFull, acc[q].w, o);
+                    }
             }
-    }
-    if (sub == 0) {
-        float4* o = reinterpret_cast<float4*>(dst) + fl;
+            if (sub == 0) {
+                float4* o = reinterpret_cast<float4*>(dst) + fl;
 #pragma unroll
-        for (int q = 0; q < VPL; q++) __stcs(o + q * G, acc[q]);
+                for (int q = 0; q < VPL; q++) __stcs(o + q * G, acc[q]);
+            }
+        }
     }
 }
 
@@ -214,8 +311,8 @@ __device__ __forceinline__ void warp_segment_any(const AggArgs& a, int32_t s, in
     }
 }
 
-template <int G, int VPL, int UNROLL>
-__global__ void __launch_bounds__(kBlock) aggregate_kernel(AggArgs a) {
+// Any feature width: one warp per work id, column-strided scalar loads.
+__global__ void __launch_bounds__(kBlock) aggregate_any_kernel(AggArgs a) {
     const int lane = lane_id();
     const int64_t n_items = a.hdr ? a.hdr->n_items : 0;
     const int chunk = a.hdr ? a.hdr->chunk : 0x7fffffff;
@@ -255,10 +352,7 @@ __global__ void __launch_bounds__(kBlock) aggregate_kernel(AggArgs a) {
                 if (e - s > chunk) continue;  // hub row: its pieces are separate work ids
                 dst = a.out + (size_t)row * F;
             }
-            if (G > 0)
-                warp_segment_vec<(G > 0 ? G : 32), VPL, UNROLL>(a, s, e, dst);
-            else
-                warp_segment_any(a, s, e, dst);
+            warp_segment_any(a, s, e, dst);
         }
     }
 }
@@ -284,19 +378,59 @@ __global__ void __launch_bounds__(kBlock) hub_fixup_kernel(AggArgs a) {
     }
 }
 
-template <int G, int VPL, int UNROLL>
-static int launch_aggregate(const AggArgs& a, cudaStream_t st) {
-    static thread_local int blocks_per_sm = 0;
-    auto kern = aggregate_kernel<G, VPL, UNROLL>;
-    if (blocks_per_sm == 0) {
+template <class K>
+static int launch_persistent(K kern, int* blocks_per_sm, const AggArgs& a, cudaStream_t st) {
+    if (*blocks_per_sm == 0) {
         int b = 0;
         JG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, kern, kBlock, 0));
-        blocks_per_sm = b > 0 ? b : 1;
+        *blocks_per_sm = b > 0 ? b : 1;
     }
-    const int grid = sm_count() * blocks_per_sm;
-    kern<<<grid, kBlock, 0, st>>>(a);
+    kern<<<sm_count() * *blocks_per_sm, kBlock, 0, st>>>(a);
     JG_LAUNCH_CHECK();
     return JG_OK;
+}
+
+template <int G, int VPL, int B, int MINB, bool EXACT>
+static int launch_rows(const AggArgs& a, cudaStream_t st) {
+    static int blocks_per_sm = 0;
+    return launch_persistent(aggregate_rows_kernel<G, VPL, B, MINB, EXACT>, &blocks_per_sm, a, st);
+}
+
+// Picks the kernel for a feature width: the vector kernel for the 128-bit-aligned widths it is
+// specialised for, the column-strided kernel for everything else.
+static int dispatch_aggregate(const AggArgs& a, cudaStream_t st) {
+    const int64_t f = a.f;
+    const bool vec_ok = (f % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.out) |
+                                          reinterpret_cast<uintptr_t>(a.partial)) % 16 == 0);
+    static const int variant = [] { const char* v = getenv("JG_SPMM_VARIANT"); return v ? atoi(v) : 0; }();
+    if (vec_ok && variant == 1) {  // tuning: fused multiply-add
+        if (f == 32) return launch_rows<8, 1, 8, 4, false>(a, st);
+        if (f == 64) return launch_rows<16, 1, 8, 4, false>(a, st);
+        if (f == 128) return launch_rows<32, 1, 8, 4, false>(a, st);
+        if (f == 256) return launch_rows<32, 2, 4, 4, false>(a, st);
+    } else if (vec_ok && variant == 2) {  // tuning: smaller batch, more resident warps
+        if (f == 32) return launch_rows<8, 1, 4, 6, true>(a, st);
+        if (f == 64) return launch_rows<16, 1, 4, 6, true>(a, st);
+        if (f == 128) return launch_rows<32, 1, 4, 6, true>(a, st);
+        if (f == 256) return launch_rows<32, 2, 2, 6, true>(a, st);
+    } else if (vec_ok && variant == 3) {  // tuning: both
+        if (f == 32) return launch_rows<8, 1, 4, 6, false>(a, st);
+        if (f == 64) return launch_rows<16, 1, 4, 6, false>(a, st);
+        if (f == 128) return launch_rows<32, 1, 4, 6, false>(a, st);
+        if (f == 256) return launch_rows<32, 2, 2, 6, false>(a, st);
+    } else if (vec_ok && variant == 4) {  // tuning: larger batch
+        if (f == 32) return launch_rows<8, 1, 8, 3, true>(a, st);
+        if (f == 64) return launch_rows<16, 1, 16, 3, true>(a, st);
+        if (f == 128) return launch_rows<32, 1, 16, 3, true>(a, st);
+        if (f == 256) return launch_rows<32, 2, 8, 3, true>(a, st);
+    }
+    if (vec_ok && f == 32) return launch_rows<8, 1, 8, 4, true>(a, st);
+    if (vec_ok && f == 64) return launch_rows<16, 1, 8, 4, true>(a, st);
+    if (vec_ok && f == 128) return launch_rows<32, 1, 8, 4, true>(a, st);
+    if (vec_ok && f == 256) return launch_rows<32, 2, 4, 4, true>(a, st);
+    if (vec_ok && f == 512) return launch_rows<32, 4, 2, 3, true>(a, st);
+    static int any_blocks = 0;
+    return launch_persistent(aggregate_any_kernel, &any_blocks, a, st);
 }
 
 }  // namespace jg
@@ -368,15 +502,7 @@ int jg_aggregate_f32(float* out, const float* x, const int32_t* idx, const int32
     }
     JG_CUDA(cudaMemsetAsync(a.ticket, 0, sizeof(unsigned long long), st));
 
-    const bool vec_ok = (f % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) |
-                                          reinterpret_cast<uintptr_t>(a.partial)) % 16 == 0);
-    int rc;
-    if (vec_ok && f == 32)        rc = launch_aggregate<8, 1, 8>(a, st);
-    else if (vec_ok && f == 64)   rc = launch_aggregate<16, 1, 8>(a, st);
-    else if (vec_ok && f == 128)  rc = launch_aggregate<32, 1, 8>(a, st);
-    else if (vec_ok && f == 256)  rc = launch_aggregate<32, 2, 4>(a, st);
-    else if (vec_ok && f == 512)  rc = launch_aggregate<32, 4, 2>(a, st);
-    else                          rc = launch_aggregate<0, 1, 1>(a, st);
+    int rc = dispatch_aggregate(a, st);
     if (rc != JG_OK) return rc;
     if (plan) {
         hub_fixup_kernel<<<sm_count() * 2, kBlock, 0, st>>>(a);
@@ -476,14 +602,7 @@ int jg_aggregate_f32_static(float* out, const float* x, const int32_t* idx, cons
         plan_build_kernel<<<grid, 256, 0, st>>>(off, n_out, v, chunk);
         JG_LAUNCH_CHECK();
     }
-    const bool vec_ok = (f % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) |
-                                          reinterpret_cast<uintptr_t>(a.partial)) % 16 == 0);
-    if (vec_ok && f == 32)        rc = launch_aggregate<8, 1, 8>(a, st);
-    else if (vec_ok && f == 64)   rc = launch_aggregate<16, 1, 8>(a, st);
-    else if (vec_ok && f == 128)  rc = launch_aggregate<32, 1, 8>(a, st);
-    else if (vec_ok && f == 256)  rc = launch_aggregate<32, 2, 4>(a, st);
-    else if (vec_ok && f == 512)  rc = launch_aggregate<32, 4, 2>(a, st);
-    else                          rc = launch_aggregate<0, 1, 1>(a, st);
+    rc = dispatch_aggregate(a, st);
     if (rc != JG_OK) return rc;
     hub_fixup_kernel<<<sm_count() * 2, kBlock, 0, st>>>(a);
     JG_LAUNCH_CHECK();
