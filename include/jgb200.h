@@ -68,6 +68,31 @@ int jg_aggregate_f32(float* out, const float* x, const int32_t* idx, const int32
                      const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes,
                      jg_stream_t stream);
 
+/* ------------------------------------------------------------------ conversion
+ * COO -> CSR (by = 0, rows keyed by source) or CSC (by = 1, columns keyed by destination).
+ * Replaces CootocsrOp / CootocscOp (ops/cpp/cootocsr_op.cc:24-57, ops/cpp/cootocsc_op.cc:23-53;
+ * Python wrappers ops/cootocsr.py:28-35, ops/cootocsc.py:29-36).  edge_index is [2, n_edges]
+ * row-major (all sources, then all destinations).  Entry i lands at
+ * off[key_i] + #{j < i : key_j == key_i}: the reference's stable order, bit for bit.
+ * canonical != 0 orders the entries of one row by their index instead.  w == NULL means unit
+ * weights.  Outputs: out_idx[n_edges], out_off[n_nodes + 1], out_w[n_edges]. */
+size_t jg_convert_workspace_bytes(int64_t n_edges, int64_t n_nodes);
+int jg_coo_to_compressed(const int32_t* edge_index, const float* w, int64_t n_edges, int64_t n_nodes, int by,
+                         int canonical, int32_t* out_idx, int32_t* out_off, float* out_w, void* workspace,
+                         size_t workspace_bytes, jg_stream_t stream);
+
+/* gcn_norm fused with the conversion: replaces gcn_norm + add_remaining_self_loops
+ * (nn/conv/gcn_conv.py:18-37, utils/loop.py:120-134) followed by cootocsc / cootocsr, without
+ * materialising the normalised COO list.  (v,v) input entries are dropped, one loop per node is
+ * appended in node order (weight `fill`, or the weight of the node's last (v,v) input entry),
+ * deg = weighted in-degree, w' = (deg^-1/2[src] * w) * deg^-1/2[dst].  Output arrays need room for
+ * n_edges + n_nodes entries; the actual entry count is written to *out_count (device, int64).
+ * The CSR triple may be NULL (all three) when only the CSC is wanted. */
+int jg_gcn_norm_compressed(const int32_t* edge_index, const float* w, int64_t n_edges, int64_t n_nodes, float fill,
+                           int canonical, int32_t* csc_idx, int32_t* csc_off, float* csc_w, int32_t* csr_idx,
+                           int32_t* csr_off, float* csr_w, int64_t* out_count, void* workspace,
+                           size_t workspace_bytes, jg_stream_t stream);
+
 /* Aggregation for callers that cannot allocate.  No counterpart in the reference: this entry
  * point exists for hosts that must not call cudaMalloc (or any allocating routine) once they
  * run - a serving process with a memory pool fixed at start-up, a plugin inside a process that

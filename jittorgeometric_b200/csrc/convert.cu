@@ -1,0 +1,552 @@
+// COO -> CSR / CSC conversion with optional fused gcn_norm, for sm_100a.
+//
+// Replaces the reference's host-side, single-thread counting sorts
+// (ops/cpp/cootocsr_op.cc:24-57, ops/cpp/cootocsc_op.cc:23-53) and the tensor-level
+// gcn_norm / add_remaining_self_loops (nn/conv/gcn_conv.py:18-37, utils/loop.py:120-134).
+//
+// Layout contract (bit-exact with the reference): entry i of the COO list lands at
+// off[key_i] + #{j < i : key_j == key_i}, i.e. a STABLE sort on the row key; with gcn_norm the
+// list is the input with (v,v) entries removed followed by one loop per node in node order.
+//
+// Method: stable least-significant-digit radix sort, 8 bits per pass, ceil(bits(n)/8) passes,
+// carrying (key, other index, weight).  Each pass = per-tile digit histogram, one device-wide
+// exclusive scan of the [digit][tile] matrix, and a stable scatter: ranks inside a tile come from
+// warp match masks in element order, elements are staged in shared memory in digit order and
+// written out in coalesced runs.  The first pass reads the caller's COO directly (self-loop
+// removal and the appended loops are folded into it: removed entries are simply never counted),
+// the last pass writes the caller's output arrays.  Offsets are found from the sorted keys by
+// boundary detection; nothing uses floating-point atomics, so results are run-to-run identical.
+// HBM-bound: about 28 bytes per entry and pass (4 histogram read, 12 read, 12 write).
+#include "common.cuh"
+
+namespace jg {
+
+constexpr int kSortThreads = 256;
+constexpr int kSortItems = 16;
+constexpr int kSortTile = kSortThreads * kSortItems;  // 4096 entries per tile
+constexpr int kSortWarps = kSortThreads / 32;
+constexpr int kRadix = 256;
+
+// ------------------------------------------------------------------------------- device scan
+constexpr int kScanThreads = 512;
+constexpr int kScanItems = 8;
+constexpr int kScanTile = kScanThreads * kScanItems;
+
+__device__ __forceinline__ int block_exclusive_scan(int v, int* total, int* s_warp /*[32]*/) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int t = __shfl_up_sync(kFull, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) s_warp[wid] = inc;
+    __syncthreads();
+    if (wid == 0) {
+        const int nw = blockDim.x >> 5;
+        int w = lane < nw ? s_warp[lane] : 0;
+        int winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int t = __shfl_up_sync(kFull, winc, o);
+            if (lane >= o) winc += t;
+        }
+        s_warp[lane] = winc - w;  // exclusive prefix of warp sums
+        if (lane == 31) *total = winc;
+    }
+    __syncthreads();
+    const int r = s_warp[wid] + inc - v;
+    __syncthreads();
+    return r;
+}
+
+__global__ void __launch_bounds__(kScanThreads) scan_reduce_kernel(const int* __restrict__ in, int64_t n, int* __restrict__ sums) {
+    __shared__ int s_warp[32];
+    __shared__ int s_total;
+    const int64_t base = (int64_t)blockIdx.x * kScanTile;
+    int v = 0;
+#pragma unroll
+    for (int i = 0; i < kScanItems; i++) {
+        const int64_t p = base + (int64_t)i * kScanThreads + threadIdx.x;
+        if (p < n) v += in[p];
+    }
+    block_exclusive_scan(v, &s_total, s_warp);
+    if (threadIdx.x == 0) sums[blockIdx.x] = s_total;
+}
+
+// One block: exclusive scan of `m` block sums in place.
+__global__ void __launch_bounds__(1024) scan_sums_kernel(int* sums, int64_t m) {
+    __shared__ int s_warp[32];
+    __shared__ int s_total;
+    int carry = 0;
+    for (int64_t base = 0; base < m; base += 1024) {
+        const int64_t p = base + threadIdx.x;
+        const int v = p < m ? sums[p] : 0;
+        const int ex = block_exclusive_scan(v, &s_total, s_warp);
+        if (p < m) sums[p] = carry + ex;
+        carry += s_total;
+        __syncthreads();
+    }
+}
+
+__global__ void __launch_bounds__(kScanThreads) scan_apply_kernel(const int* __restrict__ in, int* __restrict__ out, int64_t n,
+                                                                  const int* __restrict__ sums) {
+    __shared__ int s_warp[32];
+    __shared__ int s_total;
+    const int64_t base = (int64_t)blockIdx.x * kScanTile + (int64_t)threadIdx.x * kScanItems;
+    int v[kScanItems];
+    int local = 0;
+#pragma unroll
+    for (int i = 0; i < kScanItems; i++) {
+        v[i] = (base + i < n) ? in[base + i] : 0;
+        local += v[i];
+    }
+    int ex = block_exclusive_scan(local, &s_total, s_warp) + sums[blockIdx.x];
+#pragma unroll
+    for (int i = 0; i < kScanItems; i++) {
+        if (base + i < n) out[base + i] = ex;
+        ex += v[i];
+    }
+}
+
+static size_t scan_temp_ints(int64_t n) { return (size_t)((n + kScanTile - 1) / kScanTile) + 1; }
+
+// Exclusive scan of n int32 (in place allowed).  `sums` holds scan_temp_ints(n) ints.
+static int exclusive_scan(const int* in, int* out, int64_t n, int* sums, cudaStream_t st) {
+    if (n <= 0) return JG_OK;
+    const int64_t blocks = (n + kScanTile - 1) / kScanTile;
+    scan_reduce_kernel<<<(unsigned)blocks, kScanThreads, 0, st>>>(in, n, sums);
+    JG_LAUNCH_CHECK();
+    scan_sums_kernel<<<1, 1024, 0, st>>>(sums, blocks);
+    JG_LAUNCH_CHECK();
+    scan_apply_kernel<<<(unsigned)blocks, kScanThreads, 0, st>>>(in, out, n, sums);
+    JG_LAUNCH_CHECK();
+    return JG_OK;
+}
+
+// ------------------------------------------------------------------------------- sort passes
+// Where a pass reads its elements from.
+struct SortSrc {
+    // mode 0: SoA buffers (key, idx, w) of `count` entries
+    const int32_t* key;
+    const int32_t* idx;
+    const float* w;
+    // mode 1: the caller's COO list (first pass)
+    const int32_t* coo_src;
+    const int32_t* coo_dst;
+    const float* coo_w;       // null: unit weights
+    const float* loop_w;      // weight of the appended loop of node v (null: 1)
+    int64_t e0;               // input entries
+    int64_t n_loops;          // appended loops (0 or n)
+    int by;                   // 0: key = source, 1: key = destination
+    int drop_loops;           // skip (v,v) input entries
+    int mode;
+    int64_t count;            // positions of the (virtual) list, an upper bound when dcount is set
+    const unsigned long long* dcount;  // device-resident element count (mode 0 after a dropping pass)
+};
+
+struct Elem {
+    int32_t key, idx;
+    float w;
+    bool valid;
+};
+
+__device__ __forceinline__ Elem load_elem(const SortSrc& s, int64_t p) {
+    Elem e;
+    e.valid = p < (s.dcount ? (int64_t)*s.dcount : s.count);
+    e.key = 0; e.idx = 0; e.w = 0.f;
+    if (!e.valid) return e;
+    if (s.mode == 0) {
+        e.key = s.key[p]; e.idx = s.idx[p]; e.w = s.w[p];
+    } else if (p < s.e0) {
+        const int32_t a = s.coo_src[p], b = s.coo_dst[p];
+        e.key = s.by == 0 ? a : b;
+        e.idx = s.by == 0 ? b : a;
+        e.w = s.coo_w ? s.coo_w[p] : 1.f;
+        if (s.drop_loops && a == b) e.valid = false;
+    } else {
+        const int32_t v = (int32_t)(p - s.e0);
+        e.key = v; e.idx = v;
+        e.w = s.loop_w ? s.loop_w[v] : 1.f;
+    }
+    return e;
+}
+
+// digit of an element for this pass: from the key, or (canonical order passes) from the index
+__device__ __forceinline__ int digit_of(const Elem& e, int shift, int from_idx) {
+    return ((from_idx ? e.idx : e.key) >> shift) & (kRadix - 1);
+}
+
+__global__ void __launch_bounds__(kSortThreads) sort_hist_kernel(SortSrc s, int shift, int from_idx, int* __restrict__ matrix,
+                                                                 int64_t n_tiles) {
+    __shared__ int s_hist[kRadix];
+    s_hist[threadIdx.x] = 0;
+    __syncthreads();
+    const int64_t base = (int64_t)blockIdx.x * kSortTile;
+#pragma unroll 4
+    for (int i = 0; i < kSortItems; i++) {
+        const Elem e = load_elem(s, base + (int64_t)i * kSortThreads + threadIdx.x);
+        if (e.valid) atomicAdd(&s_hist[digit_of(e, shift, from_idx)], 1);
+    }
+    __syncthreads();
+    matrix[(int64_t)threadIdx.x * n_tiles + blockIdx.x] = s_hist[threadIdx.x];
+}
+
+struct SortDst {
+    int32_t* key;   // may be null on the last pass when keys are not needed
+    int32_t* idx;
+    float* w;
+};
+
+// Stable scatter of one tile.  Element order inside the tile is (warp, round, lane), which is the
+// order of the source list because warp w reads the contiguous range [w*512, (w+1)*512).
+__global__ void __launch_bounds__(kSortThreads) sort_scatter_kernel(SortSrc s, SortDst d, int shift, int from_idx,
+                                                                    const int* __restrict__ matrix, int64_t n_tiles) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    int* s_whist = reinterpret_cast<int*>(smem);                       // [kSortWarps][kRadix]
+    int* s_dstart = s_whist + kSortWarps * kRadix;                     // [kRadix] first tile slot of a digit
+    int* s_gbase = s_dstart + kRadix;                                  // [kRadix] global offset of a digit for this tile
+    int* s_scan = s_gbase + kRadix;                                    // [32]
+    int32_t* s_key = s_scan + 32;                                      // [kSortTile]
+    int32_t* s_idx = s_key + kSortTile;
+    float* s_w = reinterpret_cast<float*>(s_idx + kSortTile);
+    unsigned short* s_dig = reinterpret_cast<unsigned short*>(s_w + kSortTile);  // [kSortTile]
+    __shared__ int s_total;
+
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < kSortWarps * kRadix; i += kSortThreads) s_whist[i] = 0;
+    __syncthreads();
+
+    const int64_t wbase = (int64_t)blockIdx.x * kSortTile + (int64_t)wid * (32 * kSortItems);
+    Elem el[kSortItems];
+    int dig[kSortItems];
+    int rank[kSortItems];
+    int* my_hist = s_whist + wid * kRadix;
+    const unsigned lt_mask = (1u << lane) - 1u;
+#pragma unroll
+    for (int r = 0; r < kSortItems; r++) {
+        el[r] = load_elem(s, wbase + r * 32 + lane);
+        dig[r] = el[r].valid ? digit_of(el[r], shift, from_idx) : kRadix;  // kRadix: not an element
+        const unsigned peers = __match_any_sync(kFull, dig[r]);
+        int before = 0;
+        if (el[r].valid) before = my_hist[dig[r]];
+        __syncwarp();
+        rank[r] = before + __popc(peers & lt_mask);
+        if (el[r].valid && (peers & lt_mask) == 0) my_hist[dig[r]] = before + __popc(peers);
+        __syncwarp();
+    }
+    __syncthreads();
+    // one thread per digit: exclusive prefix over warps, tile total
+    {
+        const int dgt = threadIdx.x;
+        int run = 0;
+#pragma unroll
+        for (int w = 0; w < kSortWarps; w++) {
+            const int c = s_whist[w * kRadix + dgt];
+            s_whist[w * kRadix + dgt] = run;
+            run += c;
+        }
+        const int start = block_exclusive_scan(run, &s_total, s_scan);
+        s_dstart[dgt] = start;
+        s_gbase[dgt] = matrix[(int64_t)dgt * n_tiles + blockIdx.x] - start;  // global position = gbase + tile slot
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < kSortItems; r++) {
+        if (el[r].valid) {
+            const int q = s_dstart[dig[r]] + my_hist[dig[r]] + rank[r];
+            s_key[q] = el[r].key;
+            s_idx[q] = el[r].idx;
+            s_w[q] = el[r].w;
+            s_dig[q] = (unsigned short)dig[r];
+        }
+    }
+    __syncthreads();
+    const int total = s_total;
+    for (int q = threadIdx.x; q < total; q += kSortThreads) {
+        const int64_t g = (int64_t)s_gbase[s_dig[q]] + q;
+        if (d.key) d.key[g] = s_key[q];
+        d.idx[g] = s_idx[q];
+        d.w[g] = s_w[q];
+    }
+}
+
+constexpr size_t kScatterSmem = sizeof(int) * (kSortWarps * kRadix + kRadix + kRadix + 32) +
+                                sizeof(int32_t) * 2 * kSortTile + sizeof(float) * kSortTile +
+                                sizeof(unsigned short) * kSortTile;
+
+// ------------------------------------------------------------------------------- small kernels
+// off[k] = first position whose key is >= k, for k in [0, n]; keys sorted, E entries.
+__global__ void offsets_from_sorted_keys(const int32_t* __restrict__ key, int64_t E_host,
+                                         const unsigned long long* __restrict__ dcount, int64_t n, int32_t* __restrict__ off) {
+    const int64_t E = dcount ? (int64_t)*dcount : E_host;
+    const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j > E) return;
+    const int64_t lo = j == 0 ? -1 : key[j - 1];
+    const int64_t hi = j == E ? n : key[j];
+    for (int64_t k = lo + 1; k <= hi; k++) off[k] = (int32_t)j;
+}
+
+// Valid-entry count of the first pass (input entries that are not (v,v), plus loops).
+__global__ void count_kept_kernel(const int32_t* __restrict__ src, const int32_t* __restrict__ dst, int64_t e0,
+                                  unsigned long long* __restrict__ kept) {
+    unsigned long long c = 0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < e0; i += (int64_t)gridDim.x * blockDim.x)
+        c += src[i] != dst[i];
+#pragma unroll
+    for (int o = 16; o; o >>= 1) c += __shfl_xor_sync(kFull, c, o);
+    if ((threadIdx.x & 31) == 0 && c) atomicAdd(kept, c);
+}
+
+// Weight of the loop appended for node v: the fill value, or the weight of the LAST (v,v) input
+// entry (an indexed assignment keeps the last write, utils/loop.py:131-133).
+__global__ void last_loop_index_kernel(const int32_t* __restrict__ src, const int32_t* __restrict__ dst, int64_t e0,
+                                       int* __restrict__ last) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < e0; i += (int64_t)gridDim.x * blockDim.x)
+        if (src[i] == dst[i]) atomicMax(&last[src[i]], (int)i);
+}
+__global__ void loop_weight_kernel(const int* __restrict__ last, const float* __restrict__ w, float fill, int64_t n,
+                                   float* __restrict__ loop_w) {
+    const int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (v < n) loop_w[v] = last[v] >= 0 ? (w ? w[last[v]] : 1.f) : fill;
+}
+
+// deg[v] = sum of the raw weights of column v in list order (sequential fp32 adds, the order a
+// host scatter-add takes); dis = deg^-1/2 correctly rounded through double.
+__global__ void degree_kernel(const int32_t* __restrict__ off, const float* __restrict__ w, int64_t n, int unit,
+                              float* __restrict__ dis) {
+    const int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= n) return;
+    const int32_t s = off[v], e = off[v + 1];
+    float deg = 0.f;
+    if (unit) {
+        deg = (float)(e - s);  // exact while the count stays below 2^24, as sequential adds of 1.0f are
+        if (e - s > (1 << 24)) {
+            deg = 0.f;
+            for (int32_t j = s; j < e; j++) deg = __fadd_rn(deg, 1.f);
+        }
+    } else {
+        for (int32_t j = s; j < e; j++) deg = __fadd_rn(deg, w[j]);
+    }
+    dis[v] = (float)(1.0 / sqrt((double)deg));
+}
+
+// w'[j] = (dis[source] * w[j]) * dis[destination]  (nn/conv/gcn_conv.py:37); key is the segment
+// owner, idx the other endpoint; key_is_dst tells which is which.
+__global__ void norm_weight_kernel(const int32_t* __restrict__ key, const int32_t* __restrict__ idx, float* __restrict__ w,
+                                   const float* __restrict__ dis, const unsigned long long* __restrict__ dcount,
+                                   int key_is_dst) {
+    const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= (int64_t)*dcount) return;
+    const int32_t k = key[j], o = idx[j];
+    const float ds = dis[key_is_dst ? o : k], dd = dis[key_is_dst ? k : o];
+    w[j] = __fmul_rn(__fmul_rn(ds, w[j]), dd);
+}
+
+__global__ void fill_int_kernel(int* p, int v, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = v;
+}
+
+// ------------------------------------------------------------------------------- host driver
+static int bits_for(int64_t n) {
+    int b = 1;
+    while (b < 31 && ((int64_t)1 << b) < n) b++;
+    return b;
+}
+
+struct ConvertWs {
+    int32_t *key[2], *idx[2];
+    float* w[2];
+    int* matrix;
+    int* scan_sums;
+    float* dis;
+    float* loop_w;
+    int* last_loop;
+    unsigned long long* kept;
+    size_t bytes;
+};
+
+static ConvertWs carve_convert(void* ws, int64_t cap, int64_t n) {
+    Carver c(ws);
+    ConvertWs v;
+    for (int b = 0; b < 2; b++) {
+        v.key[b] = c.take<int32_t>(cap);
+        v.idx[b] = c.take<int32_t>(cap);
+        v.w[b] = c.take<float>(cap);
+    }
+    const int64_t tiles = (cap + kSortTile - 1) / kSortTile + 1;
+    v.matrix = c.take<int>((size_t)tiles * kRadix);
+    v.scan_sums = c.take<int>(scan_temp_ints(tiles * kRadix));
+    v.dis = c.take<float>(n + 1);
+    v.loop_w = c.take<float>(n + 1);
+    v.last_loop = c.take<int>(n + 1);
+    v.kept = c.take<unsigned long long>(1);
+    v.bytes = c.total();
+    return v;
+}
+
+// Sorts the (virtual) list described by `first` into (keys, out_idx, out_w), stable on the key;
+// canonical additionally orders the entries of one key by their index.  `kept` (device) is the
+// element count after a first pass that drops entries, or null when first.count is exact.
+// *sorted_key receives the buffer holding the sorted keys.
+static int radix_sort(SortSrc first, int64_t n, int canonical, const unsigned long long* kept, ConvertWs& ws,
+                      int32_t* out_idx, float* out_w, int32_t** sorted_key, cudaStream_t st) {
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    JG_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        JG_CUDA(cudaFuncSetAttribute(sort_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScatterSmem));
+        attr_set[dev] = true;
+    }
+    const int bits = bits_for(n);
+    const int key_passes = (bits + 7) / 8;
+    const int total_passes = canonical ? 2 * key_passes : key_passes;
+    const int64_t tiles = (first.count + kSortTile - 1) / kSortTile;  // upper bound for every pass
+    SortSrc src = first;
+    int cur = 0;
+    *sorted_key = ws.key[0];
+    if (tiles == 0) return JG_OK;
+    for (int p = 0; p < total_passes; p++) {
+        const int from_idx = canonical && p < key_passes;
+        const int shift = 8 * (canonical && !from_idx ? p - key_passes : p);
+        sort_hist_kernel<<<(unsigned)tiles, kSortThreads, 0, st>>>(src, shift, from_idx, ws.matrix, tiles);
+        JG_LAUNCH_CHECK();
+        int rc = exclusive_scan(ws.matrix, ws.matrix, tiles * kRadix, ws.scan_sums, st);
+        if (rc != JG_OK) return rc;
+        const bool last = p == total_passes - 1;
+        SortDst dst;
+        dst.key = ws.key[cur];
+        dst.idx = last ? out_idx : ws.idx[cur];
+        dst.w = last ? out_w : ws.w[cur];
+        sort_scatter_kernel<<<(unsigned)tiles, kSortThreads, kScatterSmem, st>>>(src, dst, shift, from_idx, ws.matrix, tiles);
+        JG_LAUNCH_CHECK();
+        *sorted_key = dst.key;
+        SortSrc nxt = {};
+        nxt.mode = 0;
+        nxt.key = dst.key; nxt.idx = dst.idx; nxt.w = dst.w;
+        nxt.count = first.count;
+        nxt.dcount = kept;
+        src = nxt;
+        cur ^= 1;
+    }
+    return JG_OK;
+}
+
+static inline unsigned blocks_for(int64_t n, int threads) { return (unsigned)((n + threads - 1) / threads); }
+
+}  // namespace jg
+
+using namespace jg;
+
+extern "C" {
+
+size_t jg_convert_workspace_bytes(int64_t n_edges, int64_t n_nodes) {
+    if (n_edges < 0 || n_nodes < 0) return 0;
+    return carve_convert(nullptr, n_edges + n_nodes, n_nodes).bytes;
+}
+
+int jg_coo_to_compressed(const int32_t* edge_index, const float* w, int64_t n_edges, int64_t n_nodes, int by,
+                         int canonical, int32_t* out_idx, int32_t* out_off, float* out_w, void* workspace,
+                         size_t workspace_bytes, jg_stream_t stream) {
+    JG_CHECK_ARG(n_edges >= 0 && n_nodes >= 0, JG_EINVAL, "coo_to_compressed: negative size");
+    JG_CHECK_ARG(by == 0 || by == 1, JG_EINVAL, "coo_to_compressed: by must be 0 (source) or 1 (destination)");
+    JG_CHECK_ARG(out_off, JG_EINVAL, "coo_to_compressed: null offsets");
+    JG_CHECK_ARG(n_edges == 0 || (edge_index && out_idx && out_w), JG_EINVAL, "coo_to_compressed: null array");
+    JG_CHECK_ARG(n_edges <= INT32_MAX - 1 && n_nodes < INT32_MAX, JG_ESHAPE, "coo_to_compressed: sizes beyond int32");
+    JG_CHECK_ARG(workspace && workspace_bytes >= jg_convert_workspace_bytes(n_edges, n_nodes), JG_EWORKSPACE,
+                 "coo_to_compressed: workspace %zu < %zu", workspace_bytes, jg_convert_workspace_bytes(n_edges, n_nodes));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    ConvertWs ws = carve_convert(workspace, n_edges + n_nodes, n_nodes);
+    SortSrc first = {};
+    first.mode = 1;
+    first.coo_src = edge_index;
+    first.coo_dst = edge_index + n_edges;
+    first.coo_w = w;
+    first.e0 = n_edges;
+    first.by = by;
+    first.count = n_edges;
+    int32_t* skey = nullptr;
+    int rc = radix_sort(first, n_nodes, canonical, nullptr, ws, out_idx, out_w, &skey, st);
+    if (rc != JG_OK) return rc;
+    offsets_from_sorted_keys<<<blocks_for(n_edges + 1, 256), 256, 0, st>>>(skey, n_edges, nullptr, n_nodes, out_off);
+    JG_LAUNCH_CHECK();
+    return JG_OK;
+}
+
+int jg_gcn_norm_compressed(const int32_t* edge_index, const float* w, int64_t n_edges, int64_t n_nodes, float fill,
+                           int canonical, int32_t* csc_idx, int32_t* csc_off, float* csc_w, int32_t* csr_idx,
+                           int32_t* csr_off, float* csr_w, int64_t* out_count, void* workspace,
+                           size_t workspace_bytes, jg_stream_t stream) {
+    JG_CHECK_ARG(n_edges >= 0 && n_nodes >= 0, JG_EINVAL, "gcn_norm_compressed: negative size");
+    JG_CHECK_ARG(csc_idx && csc_off && csc_w && out_count, JG_EINVAL, "gcn_norm_compressed: CSC outputs and count are required");
+    JG_CHECK_ARG((csr_idx && csr_off && csr_w) || (!csr_idx && !csr_off && !csr_w), JG_EINVAL,
+                 "gcn_norm_compressed: CSR outputs must be all given or all null");
+    JG_CHECK_ARG(n_edges == 0 || edge_index, JG_EINVAL, "gcn_norm_compressed: null edge_index");
+    JG_CHECK_ARG(n_edges + n_nodes <= INT32_MAX - 1, JG_ESHAPE, "gcn_norm_compressed: sizes beyond int32");
+    JG_CHECK_ARG(workspace && workspace_bytes >= jg_convert_workspace_bytes(n_edges, n_nodes), JG_EWORKSPACE,
+                 "gcn_norm_compressed: workspace %zu < %zu", workspace_bytes, jg_convert_workspace_bytes(n_edges, n_nodes));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t cap = n_edges + n_nodes;
+    ConvertWs ws = carve_convert(workspace, cap, n_nodes);
+    const int32_t* src = edge_index;
+    const int32_t* dst = edge_index + n_edges;
+    const int grid = sm_count() * 8;
+
+    // entries that survive: non-loop input entries + one loop per node
+    const unsigned long long loops = (unsigned long long)n_nodes;
+    JG_CUDA(cudaMemcpyAsync(ws.kept, &loops, sizeof(loops), cudaMemcpyHostToDevice, st));
+    if (n_edges > 0) {
+        count_kept_kernel<<<grid, 256, 0, st>>>(src, dst, n_edges, ws.kept);
+        JG_LAUNCH_CHECK();
+    }
+    const bool unit = (w == nullptr) && fill == 1.0f;
+    const float* loop_w = nullptr;
+    if (!unit && n_nodes > 0) {
+        fill_int_kernel<<<blocks_for(n_nodes, 256), 256, 0, st>>>(ws.last_loop, -1, n_nodes);
+        JG_LAUNCH_CHECK();
+        if (n_edges > 0) {
+            last_loop_index_kernel<<<grid, 256, 0, st>>>(src, dst, n_edges, ws.last_loop);
+            JG_LAUNCH_CHECK();
+        }
+        loop_weight_kernel<<<blocks_for(n_nodes, 256), 256, 0, st>>>(ws.last_loop, w, fill, n_nodes, ws.loop_w);
+        JG_LAUNCH_CHECK();
+        loop_w = ws.loop_w;
+    }
+    SortSrc first = {};
+    first.mode = 1;
+    first.coo_src = src; first.coo_dst = dst; first.coo_w = w; first.loop_w = loop_w;
+    first.e0 = n_edges; first.n_loops = n_nodes; first.drop_loops = 1;
+    first.count = cap;
+
+    // destination-major (CSC), raw weights; degrees and dis from its segments
+    int32_t* skey = nullptr;
+    first.by = 1;
+    int rc = radix_sort(first, n_nodes, canonical, ws.kept, ws, csc_idx, csc_w, &skey, st);
+    if (rc != JG_OK) return rc;
+    offsets_from_sorted_keys<<<blocks_for(cap + 1, 256), 256, 0, st>>>(skey, 0, ws.kept, n_nodes, csc_off);
+    JG_LAUNCH_CHECK();
+    if (n_nodes > 0) {
+        degree_kernel<<<blocks_for(n_nodes, 256), 256, 0, st>>>(csc_off, csc_w, n_nodes, unit ? 1 : 0, ws.dis);
+        JG_LAUNCH_CHECK();
+    }
+    if (cap > 0) {
+        norm_weight_kernel<<<blocks_for(cap, 256), 256, 0, st>>>(skey, csc_idx, csc_w, ws.dis, ws.kept, 1);
+        JG_LAUNCH_CHECK();
+    }
+    if (csr_idx) {
+        first.by = 0;
+        rc = radix_sort(first, n_nodes, canonical, ws.kept, ws, csr_idx, csr_w, &skey, st);
+        if (rc != JG_OK) return rc;
+        offsets_from_sorted_keys<<<blocks_for(cap + 1, 256), 256, 0, st>>>(skey, 0, ws.kept, n_nodes, csr_off);
+        JG_LAUNCH_CHECK();
+        if (cap > 0) {
+            norm_weight_kernel<<<blocks_for(cap, 256), 256, 0, st>>>(skey, csr_idx, csr_w, ws.dis, ws.kept, 0);
+            JG_LAUNCH_CHECK();
+        }
+    }
+    JG_CUDA(cudaMemcpyAsync(out_count, ws.kept, sizeof(unsigned long long), cudaMemcpyDeviceToDevice, st));
+    return JG_OK;
+}
+
+}  // extern "C"

@@ -13,7 +13,7 @@ from . import _lib
 from ._lib import check, lib, ptr, stream_for, workspace
 from .data import CSC, CSR
 
-__all__ = ["aggregateWithWeight", "segment_aggregate", "SpmmPlan"]
+__all__ = ["aggregateWithWeight", "segment_aggregate", "SpmmPlan", "cootocsr", "cootocsc", "gcn_norm_csc_csr"]
 
 DEFAULT_CHUNK = int(os.environ.get("JG_SPMM_CHUNK", "1024"))
 
@@ -119,3 +119,65 @@ def aggregateWithWeight(x, csc, csr, weight=None):
     (ops/aggregateWithWeight.py:53-55).  ``weight`` overrides the containers'
     edge weights for both directions, as in the reference."""
     return _AggregateFunc.apply(x, csc, csr, weight)
+
+
+def _edge_index(edge_index):
+    ei = _as_i32(edge_index, "edge_index")
+    if ei.dim() != 2 or ei.shape[0] != 2:
+        raise RuntimeError("edge_index: expected shape [2, E]")
+    return ei
+
+
+def _compress(edge_index, edge_weight, v_num, by, sorted):
+    ei = _edge_index(edge_index)
+    E = ei.shape[1]
+    w = None if edge_weight is None else _as_f32(edge_weight, "edge_weight")
+    if w is not None and w.numel() != E:
+        raise RuntimeError(f"edge_weight has {w.numel()} entries, edge_index {E}")
+    v_num = int(v_num)
+    dev = ei.device
+    idx = torch.empty(E, dtype=torch.int32, device=dev)
+    off = torch.empty(v_num + 1, dtype=torch.int32, device=dev)
+    ow = torch.empty(E, dtype=torch.float32, device=dev)
+    ws = workspace(lib().jg_convert_workspace_bytes(E, v_num), dev)
+    check(lib().jg_coo_to_compressed(ptr(ei), ptr(w), E, v_num, by, 1 if sorted else 0, ptr(idx), ptr(off), ptr(ow),
+                                     ptr(ws), ws.numel(), stream_for(ei)), "jg_coo_to_compressed")
+    return idx, off, ow
+
+
+def cootocsr(edge_index, edge_weight, v_num, sorted=False):
+    """COO -> CSR (ops/cootocsr.py:28-35): rows keyed by source, entries of a row in COO
+    order (the reference's stable layout); ``sorted=True`` orders them by column instead."""
+    idx, off, w = _compress(edge_index, edge_weight, v_num, 0, sorted)
+    return CSR(idx, off, w)
+
+
+def cootocsc(edge_index, edge_weight, v_num, sorted=False):
+    """COO -> CSC (ops/cootocsc.py:29-36): columns keyed by destination."""
+    idx, off, w = _compress(edge_index, edge_weight, v_num, 1, sorted)
+    return CSC(idx, off, w)
+
+
+def gcn_norm_csc_csr(edge_index, edge_weight, num_nodes, improved=False, want_csr=True, sorted=False):
+    """``gcn_norm`` (nn/conv/gcn_conv.py:18-37) fused with ``cootocsc`` / ``cootocsr``: returns
+    ``(CSC, CSR)`` of the self-looped, symmetrically normalised graph without building the
+    normalised COO list (``CSR`` is ``None`` when ``want_csr`` is false)."""
+    ei = _edge_index(edge_index)
+    E0 = ei.shape[1]
+    n = int(num_nodes)
+    w = None if edge_weight is None else _as_f32(edge_weight, "edge_weight")
+    dev = ei.device
+    cap = E0 + n
+    mk_i = lambda m: torch.empty(m, dtype=torch.int32, device=dev)
+    mk_f = lambda m: torch.empty(m, dtype=torch.float32, device=dev)
+    csc = (mk_i(cap), mk_i(n + 1), mk_f(cap))
+    csr = (mk_i(cap), mk_i(n + 1), mk_f(cap)) if want_csr else (None, None, None)
+    count = torch.zeros(1, dtype=torch.int64, device=dev)
+    ws = workspace(lib().jg_convert_workspace_bytes(E0, n), dev)
+    check(lib().jg_gcn_norm_compressed(ptr(ei), ptr(w), E0, n, 2.0 if improved else 1.0, 1 if sorted else 0,
+                                       ptr(csc[0]), ptr(csc[1]), ptr(csc[2]), ptr(csr[0]), ptr(csr[1]), ptr(csr[2]),
+                                       ptr(count), ptr(ws), ws.numel(), stream_for(ei)), "jg_gcn_norm_compressed")
+    E = int(count.item())  # one synchronisation per graph: the entry count sizes the views
+    out_csc = CSC(csc[0][:E], csc[1], csc[2][:E])
+    out_csr = CSR(csr[0][:E], csr[1], csr[2][:E]) if want_csr else None
+    return out_csc, out_csr
