@@ -93,6 +93,54 @@ int jg_gcn_norm_compressed(const int32_t* edge_index, const float* w, int64_t n_
                            int32_t* csr_off, float* csr_w, int64_t* out_count, void* workspace,
                            size_t workspace_bytes, jg_stream_t stream);
 
+/* gcn_norm as a COO list, for callers that want the reference's intermediate
+ * (nn/conv/gcn_conv.py:18-37): out_src/out_dst/out_w (room for n_edges + n_nodes entries each)
+ * receive the kept entries in input order followed by one loop per node; *out_count (device,
+ * int64) the entry count.  Same weights as jg_gcn_norm_compressed. */
+size_t jg_gcn_norm_coo_workspace_bytes(int64_t n_edges, int64_t n_nodes);
+int jg_gcn_norm_coo(const int32_t* edge_index, const float* w, int64_t n_edges, int64_t n_nodes, float fill,
+                    int32_t* out_src, int32_t* out_dst, float* out_w, int64_t* out_count, void* workspace,
+                    size_t workspace_bytes, jg_stream_t stream);
+
+/* ------------------------------------------------------------------ per-edge operators
+ * Edges are in CSC order (segment v = in-edges of destination v, idx[e] = source of edge e).
+ *
+ * jg_scatter_to_edge_f32 replaces ScattertoedgeOp (ops/cpp/scattertoedge_op.cc:35-141; wrapper
+ * ops/scatterToEdge.py:22-51): out[e,:] = x[idx[e],:] (flag 0, "src") or x[v,:] for e in segment v
+ * (flag 1, "dst").  out is [n_edges, c]; every row is written.
+ *
+ * jg_edge_to_vertex_f32 replaces EdgetovertexOp (ops/cpp/edgetovertex_op.cc:27-95; wrapper
+ * ops/scatterToVertex.py:23-50): flag 1: out[v,:] = sum of msg rows of segment v, ascending e;
+ * flag 0: out[idx[e],:] += msg[e,:] (float atomics, as the reference's CUDA kernel).  Every out row
+ * is written (zeros where nothing lands).
+ *
+ * jg_edge_softmax_fwd_f32 / _bwd_f32 replace EdgesoftmaxOp / EdgesoftmaxbackwardOp
+ * (ops/cpp/edgesoftmax_op.cc:36-120, ops/cpp/edgesoftmaxbackward_op.cc:27-54; wrapper
+ * ops/edgesoftmax.py:62-80): x, y, grad, dx are [n_edges, h]; each column is normalised over each
+ * segment with the maximum subtracted (the reference's CPU recipe; h = 1 is the reference's own
+ * shape).  Backward: dx = y*g - y*sum_segment(y*g).  Empty segments write nothing. */
+int jg_scatter_to_edge_f32(float* out, const float* x, const int32_t* idx, const int32_t* off, int64_t n_nodes,
+                           int64_t n_edges, int64_t c, int flag, jg_stream_t stream);
+int jg_edge_to_vertex_f32(float* out, const float* msg, const int32_t* idx, const int32_t* off, int64_t n_nodes,
+                          int64_t n_edges, int64_t c, int flag, jg_stream_t stream);
+int jg_edge_softmax_fwd_f32(float* y, const float* x, const int32_t* off, int64_t n_nodes, int64_t n_edges, int64_t h,
+                            jg_stream_t stream);
+int jg_edge_softmax_bwd_f32(float* dx, const float* grad, const float* y, const int32_t* off, int64_t n_nodes,
+                            int64_t n_edges, int64_t h, jg_stream_t stream);
+
+/* Fused attention aggregation: the edge phase of GATConv.execute (nn/conv/gat_conv.py:60-83) in
+ * one pass over CSC - logits leaky_relu(a_src.h[src] + a_dst.h[dst]), per-destination softmax,
+ * weighted sum of source rows - with `heads` independent heads of width `dim` (heads = 1 is the
+ * reference layer: a_src / a_dst are the two halves of its [2C, 1] attention vector).
+ * h and out are [n_nodes, heads*dim]; a_src, a_dst are [heads, dim].  Supported shapes are
+ * reported by jg_gat_aggregate_supported (heads*dim/4 and dim/4 powers of two, heads*dim <= 128);
+ * others return JG_EUNSUPPORTED and are served by the per-edge operators above. */
+size_t jg_gat_aggregate_workspace_bytes(int64_t n_nodes, int64_t n_edges, int64_t heads, int64_t dim);
+int jg_gat_aggregate_supported(int64_t heads, int64_t dim);
+int jg_gat_aggregate_f32(float* out, const float* h, const float* a_src, const float* a_dst, const int32_t* idx,
+                         const int32_t* off, int64_t n_nodes, int64_t n_edges, int64_t heads, int64_t dim, float slope,
+                         void* workspace, size_t workspace_bytes, jg_stream_t stream);
+
 /* Aggregation for callers that cannot allocate.  No counterpart in the reference: this entry
  * point exists for hosts that must not call cudaMalloc (or any allocating routine) once they
  * run - a serving process with a memory pool fixed at start-up, a plugin inside a process that

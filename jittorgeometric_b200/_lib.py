@@ -33,6 +33,15 @@ SIGNATURES = {
     "jg_convert_workspace_bytes": (sz, [i64, i64]),
     "jg_coo_to_compressed": (ctypes.c_int, [vp, vp, i64, i64, ctypes.c_int, ctypes.c_int, vp, vp, vp, vp, sz, vp]),
     "jg_gcn_norm_compressed": (ctypes.c_int, [vp, vp, i64, i64, f32, ctypes.c_int, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
+    "jg_gcn_norm_coo_workspace_bytes": (sz, [i64, i64]),
+    "jg_gcn_norm_coo": (ctypes.c_int, [vp, vp, i64, i64, f32, vp, vp, vp, vp, vp, sz, vp]),
+    "jg_scatter_to_edge_f32": (ctypes.c_int, [vp, vp, vp, vp, i64, i64, i64, ctypes.c_int, vp]),
+    "jg_edge_to_vertex_f32": (ctypes.c_int, [vp, vp, vp, vp, i64, i64, i64, ctypes.c_int, vp]),
+    "jg_edge_softmax_fwd_f32": (ctypes.c_int, [vp, vp, vp, i64, i64, i64, vp]),
+    "jg_edge_softmax_bwd_f32": (ctypes.c_int, [vp, vp, vp, vp, i64, i64, i64, vp]),
+    "jg_gat_aggregate_workspace_bytes": (sz, [i64, i64, i64, i64]),
+    "jg_gat_aggregate_supported": (ctypes.c_int, [i64, i64]),
+    "jg_gat_aggregate_f32": (ctypes.c_int, [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, f32, vp, sz, vp]),
     "jg_aggregate_static_capacity_bytes": (sz, []),
     "jg_aggregate_f32_static": (ctypes.c_int, [vp, vp, vp, vp, vp, i64, i64, i64, i64, vp]),
 }

@@ -343,6 +343,37 @@ __global__ void norm_weight_kernel(const int32_t* __restrict__ key, const int32_
     w[j] = __fmul_rn(__fmul_rn(ds, w[j]), dd);
 }
 
+// keep[i] = 1 for input entries that are not (v,v)
+__global__ void keep_flags_kernel(const int32_t* __restrict__ src, const int32_t* __restrict__ dst, int64_t e0,
+                                  int* __restrict__ keep) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < e0) keep[i] = src[i] != dst[i];
+}
+
+// Normalised COO list in the reference's order: kept entries in input order, then one loop per node.
+__global__ void write_norm_coo_kernel(const int32_t* __restrict__ src, const int32_t* __restrict__ dst,
+                                      const float* __restrict__ w, const float* __restrict__ loop_w,
+                                      const int* __restrict__ pos, const float* __restrict__ dis, int64_t e0, int64_t n,
+                                      const unsigned long long* __restrict__ total, int32_t* __restrict__ out_src,
+                                      int32_t* __restrict__ out_dst, float* __restrict__ out_w) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t kept = (int64_t)*total - n;
+    if (i < e0) {
+        const int32_t a = src[i], b = dst[i];
+        if (a != b) {
+            const int64_t p = pos[i];
+            out_src[p] = a;
+            out_dst[p] = b;
+            out_w[p] = __fmul_rn(__fmul_rn(dis[a], w ? w[i] : 1.f), dis[b]);
+        }
+    } else if (i < e0 + n) {
+        const int32_t v = (int32_t)(i - e0);
+        out_src[kept + v] = v;
+        out_dst[kept + v] = v;
+        out_w[kept + v] = __fmul_rn(__fmul_rn(dis[v], loop_w ? loop_w[v] : 1.f), dis[v]);
+    }
+}
+
 __global__ void fill_int_kernel(int* p, int v, int64_t n) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) p[i] = v;
@@ -546,6 +577,71 @@ int jg_gcn_norm_compressed(const int32_t* edge_index, const float* w, int64_t n_
         }
     }
     JG_CUDA(cudaMemcpyAsync(out_count, ws.kept, sizeof(unsigned long long), cudaMemcpyDeviceToDevice, st));
+    return JG_OK;
+}
+
+
+struct NormCooWs {
+    void* convert;
+    size_t convert_bytes;
+    int32_t* tmp_idx;
+    int32_t* tmp_off;
+    float* tmp_w;
+    int* pos;
+    int* pos_sums;
+    int64_t* count;
+    size_t bytes;
+};
+
+static NormCooWs carve_norm_coo(void* ws, int64_t n_edges, int64_t n_nodes) {
+    Carver c(ws);
+    NormCooWs v;
+    v.convert_bytes = jg_convert_workspace_bytes(n_edges, n_nodes);
+    v.convert = c.take<unsigned char>(v.convert_bytes);
+    v.tmp_idx = c.take<int32_t>(n_edges + n_nodes);
+    v.tmp_off = c.take<int32_t>(n_nodes + 1);
+    v.tmp_w = c.take<float>(n_edges + n_nodes);
+    v.pos = c.take<int>(n_edges + 1);
+    v.pos_sums = c.take<int>(scan_temp_ints(n_edges + 1));
+    v.count = c.take<int64_t>(1);
+    v.bytes = c.total();
+    return v;
+}
+
+size_t jg_gcn_norm_coo_workspace_bytes(int64_t n_edges, int64_t n_nodes) {
+    if (n_edges < 0 || n_nodes < 0) return 0;
+    return carve_norm_coo(nullptr, n_edges, n_nodes).bytes;
+}
+
+int jg_gcn_norm_coo(const int32_t* edge_index, const float* w, int64_t n_edges, int64_t n_nodes, float fill,
+                    int32_t* out_src, int32_t* out_dst, float* out_w, int64_t* out_count, void* workspace,
+                    size_t workspace_bytes, jg_stream_t stream) {
+    JG_CHECK_ARG(n_edges >= 0 && n_nodes >= 0, JG_EINVAL, "gcn_norm_coo: negative size");
+    JG_CHECK_ARG(out_count, JG_EINVAL, "gcn_norm_coo: null count");
+    JG_CHECK_ARG(n_edges + n_nodes == 0 || (out_src && out_dst && out_w), JG_EINVAL, "gcn_norm_coo: null output");
+    JG_CHECK_ARG(n_edges == 0 || edge_index, JG_EINVAL, "gcn_norm_coo: null edge_index");
+    JG_CHECK_ARG(workspace && workspace_bytes >= jg_gcn_norm_coo_workspace_bytes(n_edges, n_nodes), JG_EWORKSPACE,
+                 "gcn_norm_coo: workspace %zu < %zu", workspace_bytes, jg_gcn_norm_coo_workspace_bytes(n_edges, n_nodes));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    NormCooWs nw = carve_norm_coo(workspace, n_edges, n_nodes);
+    // degrees come from the destination-major order (sequential sums in list order); its arrays are scratch here
+    int rc = jg_gcn_norm_compressed(edge_index, w, n_edges, n_nodes, fill, 0, nw.tmp_idx, nw.tmp_off, nw.tmp_w, nullptr,
+                                    nullptr, nullptr, out_count, nw.convert, nw.convert_bytes, stream);
+    if (rc != JG_OK) return rc;
+    ConvertWs ws = carve_convert(nw.convert, n_edges + n_nodes, n_nodes);  // dis, loop_w and kept live there
+    const bool unit = (w == nullptr) && fill == 1.0f;
+    if (n_edges > 0) {
+        keep_flags_kernel<<<blocks_for(n_edges, 256), 256, 0, st>>>(edge_index, edge_index + n_edges, n_edges, nw.pos);
+        JG_LAUNCH_CHECK();
+        rc = exclusive_scan(nw.pos, nw.pos, n_edges, nw.pos_sums, st);
+        if (rc != JG_OK) return rc;
+    }
+    if (n_edges + n_nodes > 0) {
+        write_norm_coo_kernel<<<blocks_for(n_edges + n_nodes, 256), 256, 0, st>>>(
+            edge_index, edge_index + n_edges, w, unit ? nullptr : ws.loop_w, nw.pos, ws.dis, n_edges, n_nodes, ws.kept,
+            out_src, out_dst, out_w);
+        JG_LAUNCH_CHECK();
+    }
     return JG_OK;
 }
 

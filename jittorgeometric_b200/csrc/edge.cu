@@ -1,0 +1,279 @@
+// Per-edge operators of the attention path, as individually callable ops (sm_100a):
+//   scatter_to_edge   msg[e,:] = x[src(e),:] or x[dst(e),:]      (ops/cpp/scattertoedge_op.cc:35-141)
+//   edge_to_vertex    out[v,:] = sum of msg rows per destination / source (ops/cpp/edgetovertex_op.cc:27-95)
+//   edge_softmax      per-destination softmax of per-edge scores, forward and backward
+//                     (ops/cpp/edgesoftmax_op.cc:36-120, ops/cpp/edgesoftmaxbackward_op.cc:27-54)
+// Edges are in CSC order: segment v = [off[v], off[v+1]) holds the in-edges of destination v and
+// idx[e] is the source of edge e.  All four are pure bandwidth kernels (one pass over an [E, C]
+// array); the fused attention kernel in gat.cu makes the [E, C] temporaries unnecessary, these
+// exist for API parity.
+#include "common.cuh"
+
+namespace jg {
+
+constexpr int kEdgeBlock = 256;
+
+// Row (segment owner) of edge e: the v with off[v] <= e < off[v+1], searched in [lo, hi].
+__device__ __forceinline__ int32_t owner_of(const int32_t* __restrict__ off, int32_t lo, int32_t hi, int32_t e) {
+    while (lo < hi) {  // largest v with off[v] <= e
+        const int32_t mid = lo + (hi - lo + 1) / 2;
+        if (off[mid] <= e) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+
+// One warp copies node rows onto 32 consecutive edges at a time.
+__global__ void __launch_bounds__(kEdgeBlock) scatter_to_edge_kernel(float* __restrict__ out, const float* __restrict__ x,
+                                                                     const int32_t* __restrict__ idx,
+                                                                     const int32_t* __restrict__ off, int64_t n, int64_t E,
+                                                                     int64_t C, int flag) {
+    const int lane = lane_id();
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const bool vec = (C % 4 == 0) && ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x)) % 16 == 0);
+    for (int64_t e0 = warp * 32; e0 < E; e0 += n_warps * 32) {
+        const int64_t e = e0 + lane;
+        int32_t node = 0;
+        if (flag == 0) {
+            if (e < E) node = idx[e];
+        } else {
+            // rows of the tile's first and last edge bound every lane's search
+            const int32_t last = (int32_t)((e0 + 31) < (E - 1) ? (e0 + 31) : (E - 1));
+            const int32_t r_first = owner_of(off, 0, (int32_t)n - 1, (int32_t)e0);
+            const int32_t r_last = owner_of(off, r_first, (int32_t)n - 1, last);
+            if (e < E) node = owner_of(off, r_first, r_last, (int32_t)e);
+        }
+        const int cnt = (E - e0) < 32 ? (int)(E - e0) : 32;
+        for (int k = 0; k < cnt; k++) {
+            const int32_t src = __shfl_sync(kFull, node, k);
+            const float* xr = x + (size_t)src * C;
+            float* o = out + (size_t)(e0 + k) * C;
+            if (vec) {
+                for (int64_t c = lane; c < C / 4; c += 32)
+                    __stcs(reinterpret_cast<float4*>(o) + c, __ldg(reinterpret_cast<const float4*>(xr) + c));
+            } else {
+                for (int64_t c = lane; c < C; c += 32) o[c] = __ldg(xr + c);
+            }
+        }
+    }
+}
+
+// out[v,:] = sum of msg[e,:] over the in-edges of v, ascending e (flag 1): one warp per destination.
+__global__ void __launch_bounds__(kEdgeBlock) edge_to_vertex_dst_kernel(float* __restrict__ out, const float* __restrict__ msg,
+                                                                        const int32_t* __restrict__ off, int64_t n, int64_t C) {
+    const int lane = lane_id();
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t v = warp; v < n; v += n_warps) {
+        const int32_t s = off[v], e = off[v + 1];
+        for (int64_t c = lane; c < C; c += 32) {
+            float acc = 0.f;
+            int32_t j = s;
+            for (; j + 4 <= e; j += 4) {  // four independent loads in flight, added in order
+                const float a0 = __ldcs(msg + (size_t)j * C + c), a1 = __ldcs(msg + (size_t)(j + 1) * C + c);
+                const float a2 = __ldcs(msg + (size_t)(j + 2) * C + c), a3 = __ldcs(msg + (size_t)(j + 3) * C + c);
+                acc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(acc, a0), a1), a2), a3);
+            }
+            for (; j < e; j++) acc = __fadd_rn(acc, __ldcs(msg + (size_t)j * C + c));
+            out[(size_t)v * C + c] = acc;
+        }
+    }
+}
+
+// out[idx[e],:] += msg[e,:] (flag 0): scatter by source.  Float atomics, as the reference's CUDA
+// kernel does (ops/cpp/edgetovertex_op.cc:69); out must be zeroed by the launcher.
+__global__ void __launch_bounds__(kEdgeBlock) edge_to_vertex_src_kernel(float* __restrict__ out, const float* __restrict__ msg,
+                                                                        const int32_t* __restrict__ idx, int64_t E, int64_t C) {
+    const int64_t total = E * C;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t e = i / C, c = i - e * C;
+        atomicAdd(out + (size_t)idx[e] * C + c, __ldcs(msg + i));
+    }
+}
+
+__global__ void zero_kernel(float* p, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) p[i] = 0.f;
+}
+
+// ------------------------------------------------------------------------------- edge softmax
+// x, y are [E, H] row-major; the softmax runs over each segment separately for every column.
+// HP = H when H is a power of two <= 32: a lane then always meets the same column (its flat
+// index modulo H is lane % H) and columns are reduced with xor-shuffles over offsets >= H.
+template <int HP>
+__device__ __forceinline__ float reduce_same_column_max(float v) {
+#pragma unroll
+    for (int o = 16; o >= HP; o >>= 1) v = fmaxf(v, __shfl_xor_sync(kFull, v, o));
+    return v;
+}
+template <int HP>
+__device__ __forceinline__ float reduce_same_column_sum(float v) {
+#pragma unroll
+    for (int o = 16; o >= HP; o >>= 1) v += __shfl_xor_sync(kFull, v, o);
+    return v;
+}
+
+template <int HP>
+__global__ void __launch_bounds__(kEdgeBlock) edge_softmax_fwd_kernel(float* __restrict__ y, const float* __restrict__ x,
+                                                                      const int32_t* __restrict__ off, int64_t n) {
+    const int lane = lane_id();
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t v = warp; v < n; v += n_warps) {
+        const int64_t s = (int64_t)off[v] * HP, e = (int64_t)off[v + 1] * HP;
+        if (s >= e) continue;
+        float mx = -INFINITY;
+        for (int64_t i = s + lane; i < e; i += 32) mx = fmaxf(mx, x[i]);
+        mx = reduce_same_column_max<HP>(mx);
+        float sum = 0.f;
+        for (int64_t i = s + lane; i < e; i += 32) sum += expf(x[i] - mx);
+        sum = reduce_same_column_sum<HP>(sum);
+        for (int64_t i = s + lane; i < e; i += 32) y[i] = expf(x[i] - mx) / sum;
+    }
+}
+
+// Any H: one (segment, column) pair per warp pass, strided access.
+__global__ void __launch_bounds__(kEdgeBlock) edge_softmax_fwd_any_kernel(float* __restrict__ y, const float* __restrict__ x,
+                                                                          const int32_t* __restrict__ off, int64_t n, int64_t H) {
+    const int lane = lane_id();
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t t = warp; t < n * H; t += n_warps) {
+        const int64_t v = t / H, h = t - v * H;
+        const int64_t s = off[v], e = off[v + 1];
+        if (s >= e) continue;
+        float mx = -INFINITY;
+        for (int64_t j = s + lane; j < e; j += 32) mx = fmaxf(mx, x[j * H + h]);
+        mx = reduce_same_column_max<1>(mx);
+        float sum = 0.f;
+        for (int64_t j = s + lane; j < e; j += 32) sum += expf(x[j * H + h] - mx);
+        sum = reduce_same_column_sum<1>(sum);
+        for (int64_t j = s + lane; j < e; j += 32) y[j * H + h] = expf(x[j * H + h] - mx) / sum;
+    }
+}
+
+// dx = y*g - y*dot, dot = sum over the segment of y*g.
+template <int HP>
+__global__ void __launch_bounds__(kEdgeBlock) edge_softmax_bwd_kernel(float* __restrict__ dx, const float* __restrict__ g,
+                                                                      const float* __restrict__ y,
+                                                                      const int32_t* __restrict__ off, int64_t n) {
+    const int lane = lane_id();
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t v = warp; v < n; v += n_warps) {
+        const int64_t s = (int64_t)off[v] * HP, e = (int64_t)off[v + 1] * HP;
+        float dot = 0.f;
+        for (int64_t i = s + lane; i < e; i += 32) dot += y[i] * g[i];
+        dot = reduce_same_column_sum<HP>(dot);
+        for (int64_t i = s + lane; i < e; i += 32) dx[i] = __fsub_rn(__fmul_rn(y[i], g[i]), __fmul_rn(y[i], dot));
+    }
+}
+
+__global__ void __launch_bounds__(kEdgeBlock) edge_softmax_bwd_any_kernel(float* __restrict__ dx, const float* __restrict__ g,
+                                                                          const float* __restrict__ y,
+                                                                          const int32_t* __restrict__ off, int64_t n, int64_t H) {
+    const int lane = lane_id();
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t t = warp; t < n * H; t += n_warps) {
+        const int64_t v = t / H, h = t - v * H;
+        const int64_t s = off[v], e = off[v + 1];
+        float dot = 0.f;
+        for (int64_t j = s + lane; j < e; j += 32) dot += y[j * H + h] * g[j * H + h];
+        dot = reduce_same_column_sum<1>(dot);
+        for (int64_t j = s + lane; j < e; j += 32)
+            dx[j * H + h] = __fsub_rn(__fmul_rn(y[j * H + h], g[j * H + h]), __fmul_rn(y[j * H + h], dot));
+    }
+}
+
+static int grid_for_warps(int64_t warps_wanted) {
+    const int64_t max_blocks = (int64_t)sm_count() * 8;
+    int64_t blocks = (warps_wanted * 32 + kEdgeBlock - 1) / kEdgeBlock;
+    if (blocks < 1) blocks = 1;
+    return (int)(blocks < max_blocks ? blocks : max_blocks);
+}
+
+}  // namespace jg
+
+using namespace jg;
+
+extern "C" {
+
+int jg_scatter_to_edge_f32(float* out, const float* x, const int32_t* idx, const int32_t* off, int64_t n_nodes,
+                           int64_t n_edges, int64_t c, int flag, jg_stream_t stream) {
+    JG_CHECK_ARG(n_nodes >= 0 && n_edges >= 0 && c >= 0, JG_EINVAL, "scatter_to_edge: negative size");
+    JG_CHECK_ARG(flag == 0 || flag == 1, JG_EINVAL, "scatter_to_edge: flag must be 0 (source) or 1 (destination)");
+    if (n_edges == 0 || c == 0) return JG_OK;
+    JG_CHECK_ARG(out && x && idx && off, JG_EINVAL, "scatter_to_edge: null pointer");
+    JG_CHECK_ARG(n_nodes > 0, JG_ESHAPE, "scatter_to_edge: edges without nodes");
+    JG_CHECK_ARG(n_edges <= INT32_MAX && n_nodes < INT32_MAX, JG_ESHAPE, "scatter_to_edge: sizes beyond int32");
+    scatter_to_edge_kernel<<<grid_for_warps((n_edges + 31) / 32), kEdgeBlock, 0, static_cast<cudaStream_t>(stream)>>>(
+        out, x, idx, off, n_nodes, n_edges, c, flag);
+    JG_LAUNCH_CHECK();
+    return JG_OK;
+}
+
+int jg_edge_to_vertex_f32(float* out, const float* msg, const int32_t* idx, const int32_t* off, int64_t n_nodes,
+                          int64_t n_edges, int64_t c, int flag, jg_stream_t stream) {
+    JG_CHECK_ARG(n_nodes >= 0 && n_edges >= 0 && c >= 0, JG_EINVAL, "edge_to_vertex: negative size");
+    JG_CHECK_ARG(flag == 0 || flag == 1, JG_EINVAL, "edge_to_vertex: flag must be 0 (source) or 1 (destination)");
+    if (n_nodes == 0 || c == 0) return JG_OK;
+    JG_CHECK_ARG(out && off, JG_EINVAL, "edge_to_vertex: null out/off");
+    JG_CHECK_ARG(n_edges == 0 || (msg && idx), JG_EINVAL, "edge_to_vertex: null msg/idx");
+    JG_CHECK_ARG(n_edges <= INT32_MAX && n_nodes < INT32_MAX, JG_ESHAPE, "edge_to_vertex: sizes beyond int32");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (flag == 1) {
+        edge_to_vertex_dst_kernel<<<grid_for_warps(n_nodes), kEdgeBlock, 0, st>>>(out, msg, off, n_nodes, c);
+        JG_LAUNCH_CHECK();
+    } else {
+        zero_kernel<<<grid_for_warps((n_nodes * c + 31) / 32), kEdgeBlock, 0, st>>>(out, n_nodes * c);
+        JG_LAUNCH_CHECK();
+        if (n_edges > 0) {
+            edge_to_vertex_src_kernel<<<grid_for_warps((n_edges * c + 31) / 32), kEdgeBlock, 0, st>>>(out, msg, idx, n_edges, c);
+            JG_LAUNCH_CHECK();
+        }
+    }
+    return JG_OK;
+}
+
+int jg_edge_softmax_fwd_f32(float* y, const float* x, const int32_t* off, int64_t n_nodes, int64_t n_edges, int64_t h,
+                            jg_stream_t stream) {
+    JG_CHECK_ARG(n_nodes >= 0 && n_edges >= 0 && h >= 0, JG_EINVAL, "edge_softmax: negative size");
+    if (n_edges == 0 || h == 0 || n_nodes == 0) return JG_OK;
+    JG_CHECK_ARG(y && x && off, JG_EINVAL, "edge_softmax: null pointer");
+    JG_CHECK_ARG(n_edges * h <= (int64_t)INT32_MAX * 32, JG_ESHAPE, "edge_softmax: sizes too large");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = grid_for_warps(n_nodes);
+    switch (h) {
+        case 1: edge_softmax_fwd_kernel<1><<<grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes); break;
+        case 2: edge_softmax_fwd_kernel<2><<<grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes); break;
+        case 4: edge_softmax_fwd_kernel<4><<<grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes); break;
+        case 8: edge_softmax_fwd_kernel<8><<<grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes); break;
+        case 16: edge_softmax_fwd_kernel<16><<<grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes); break;
+        case 32: edge_softmax_fwd_kernel<32><<<grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes); break;
+        default: edge_softmax_fwd_any_kernel<<<grid_for_warps(n_nodes * h), kEdgeBlock, 0, st>>>(y, x, off, n_nodes, h);
+    }
+    JG_LAUNCH_CHECK();
+    return JG_OK;
+}
+
+int jg_edge_softmax_bwd_f32(float* dx, const float* grad, const float* y, const int32_t* off, int64_t n_nodes,
+                            int64_t n_edges, int64_t h, jg_stream_t stream) {
+    JG_CHECK_ARG(n_nodes >= 0 && n_edges >= 0 && h >= 0, JG_EINVAL, "edge_softmax_bwd: negative size");
+    if (n_edges == 0 || h == 0 || n_nodes == 0) return JG_OK;
+    JG_CHECK_ARG(dx && grad && y && off, JG_EINVAL, "edge_softmax_bwd: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = grid_for_warps(n_nodes);
+    switch (h) {
+        case 1: edge_softmax_bwd_kernel<1><<<grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes); break;
+        case 2: edge_softmax_bwd_kernel<2><<<grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes); break;
+        case 4: edge_softmax_bwd_kernel<4><<<grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes); break;
+        case 8: edge_softmax_bwd_kernel<8><<<grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes); break;
+        case 16: edge_softmax_bwd_kernel<16><<<grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes); break;
+        case 32: edge_softmax_bwd_kernel<32><<<grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes); break;
+        default: edge_softmax_bwd_any_kernel<<<grid_for_warps(n_nodes * h), kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes, h);
+    }
+    JG_LAUNCH_CHECK();
+    return JG_OK;
+}
+
+}  // extern "C"

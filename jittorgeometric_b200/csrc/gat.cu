@@ -1,0 +1,233 @@
+// Fused attention aggregation over CSC in-edges (sm_100a): logits, per-destination softmax and
+// weighted multi-head aggregation in ONE pass, replacing the reference's six-launch pipeline with
+// three [E, C] temporaries (nn/conv/gat_conv.py:67-83: ScatterToEdge x2, concat, matmul,
+// leaky_relu, EdgeSoftmax, multiply, ScatterToVertex).
+//
+//   h      [n, H*D]  transformed node features (after the layer's ReLU)
+//   logit(e,hd) = leaky_relu( a_src[hd] . h[src(e),hd,:] + a_dst[hd] . h[dst(e),hd,:] )
+//   alpha  = softmax of the logits over the in-edges of each destination, per head
+//   out[v,hd,:] = sum_e alpha(e,hd) * h[src(e),hd,:]
+//
+// One warp per destination.  G = C/4 lanes cover one source row with a 128-bit load each, 32/G
+// edges are processed side by side.  The source score is recomputed from the gathered row (four
+// FMAs and a shuffle) instead of being fetched from a second array: that saves one 32-byte sector
+// per edge, and the row has to be read anyway.  The softmax is the running-maximum ("online")
+// form, so each source row is read exactly once; lane groups and hub pieces are merged with the
+// usual (max, sum, accumulator) rule in a fixed order, so results are run-to-run identical.
+// Bound: L2/LSU bandwidth when h fits in L2 (the 233k-node workload: h = 59.6 MB), HBM otherwise;
+// per edge one 4 B index and one C*4 B row.
+#include "common.cuh"
+
+namespace jg {
+
+constexpr int kGatBlock = 256;
+
+struct GatArgs {
+    float* out;
+    const float* h;
+    const float* a_src;
+    const float* a_dst;
+    const int32_t* idx;
+    const int32_t* off;
+    int64_t n;
+    float slope;
+    unsigned long long* ticket;
+};
+
+__device__ __forceinline__ float dot4(const float4& a, const float4& b) {
+    return fmaf(a.w, b.w, fmaf(a.z, b.z, fmaf(a.y, b.y, a.x * b.x)));
+}
+
+struct Softmax4 {
+    float m, l;
+    float4 acc;
+    __device__ __forceinline__ void init() {
+        m = -INFINITY;
+        l = 0.f;
+        acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    // one more term with logit z and value row x
+    __device__ __forceinline__ void push(float z, const float4& x) {
+        const float d = z - m;
+        const float e = __expf(-fabsf(d));
+        const bool up = d > 0.f;
+        const float sc = up ? e : 1.f;   // rescale of what is already accumulated
+        const float p = up ? 1.f : e;    // weight of the new term
+        m = up ? z : m;
+        l = fmaf(l, sc, p);
+        acc.x = fmaf(acc.x, sc, p * x.x);
+        acc.y = fmaf(acc.y, sc, p * x.y);
+        acc.z = fmaf(acc.z, sc, p * x.z);
+        acc.w = fmaf(acc.w, sc, p * x.w);
+    }
+    // merge another partial state (either may be empty: m == -inf, l == 0)
+    __device__ __forceinline__ void merge(float m2, float l2, const float4& a2) {
+        const float mn = fmaxf(m, m2);
+        const float s1 = (m == -INFINITY) ? 0.f : __expf(m - mn);
+        const float s2 = (m2 == -INFINITY) ? 0.f : __expf(m2 - mn);
+        l = l * s1 + l2 * s2;
+        acc.x = acc.x * s1 + a2.x * s2;
+        acc.y = acc.y * s1 + a2.y * s2;
+        acc.z = acc.z * s1 + a2.z * s2;
+        acc.w = acc.w * s1 + a2.w * s2;
+        m = mn;
+    }
+};
+
+// G lanes per row (C = 4*G), DL = D/4 lanes per head; both powers of two, DL <= G <= 32.
+template <int G, int DL>
+__global__ void __launch_bounds__(kGatBlock) gat_aggregate_kernel(GatArgs a) {
+    constexpr int EPS = 32 / G;
+    constexpr int C = 4 * G;
+    constexpr int B = 4;  // steps per batch
+    const int lane = lane_id();
+    const int sub = lane / G;
+    const int fl = lane % G;
+    const float4 as4 = __ldg(reinterpret_cast<const float4*>(a.a_src) + fl);
+    const float4 ad4 = __ldg(reinterpret_cast<const float4*>(a.a_dst) + fl);
+    const char* hb = reinterpret_cast<const char*>(a.h) + fl * 16;
+    for (;;) {
+        unsigned long long t = 0;
+        if (lane == 0) t = atomicAdd(a.ticket, 1ull);
+        t = __shfl_sync(kFull, t, 0);
+        if ((int64_t)t >= a.n) break;
+        const int64_t v = (int64_t)t;
+        const int32_t s = a.off[v], e = a.off[v + 1];
+        // destination score of this lane's head
+        const float4 hv = __ldg(reinterpret_cast<const float4*>(hb + (size_t)v * (C * 4)));
+        float sd = dot4(hv, ad4);
+#pragma unroll
+        for (int o = 1; o < DL; o <<= 1) sd += __shfl_xor_sync(kFull, sd, o);
+        Softmax4 st;
+        st.init();
+        for (int32_t j0 = s; j0 < e; j0 += 32) {
+            int my_idx = 0;
+            if (j0 + lane < e) my_idx = ld_stream(a.idx + j0 + lane);
+            const int cnt = min(32, e - j0);
+            for (int tt = 0; tt < cnt; tt += EPS * B) {
+                float4 x[B];
+                bool ok[B];
+#pragma unroll
+                for (int u = 0; u < B; u++) {
+                    const int k = tt + u * EPS + sub;
+                    const int src = __shfl_sync(kFull, my_idx, k & 31);
+                    ok[u] = k < cnt;
+                    x[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (ok[u]) x[u] = __ldg(reinterpret_cast<const float4*>(hb + (size_t)(unsigned)src * (C * 4)));
+                }
+#pragma unroll
+                for (int u = 0; u < B; u++) {
+                    float ss = dot4(x[u], as4);
+#pragma unroll
+                    for (int o = 1; o < DL; o <<= 1) ss += __shfl_xor_sync(kFull, ss, o);
+                    float z = ss + sd;
+                    z = z > 0.f ? z : z * a.slope;
+                    if (ok[u]) st.push(z, x[u]);
+                }
+            }
+        }
+        // merge the lane groups that took alternate edges, in a fixed order
+#pragma unroll
+        for (int o = G; o < 32; o <<= 1) {
+            const float m2 = __shfl_xor_sync(kFull, st.m, o);
+            const float l2 = __shfl_xor_sync(kFull, st.l, o);
+            float4 a2;
+            a2.x = __shfl_xor_sync(kFull, st.acc.x, o);
+            a2.y = __shfl_xor_sync(kFull, st.acc.y, o);
+            a2.z = __shfl_xor_sync(kFull, st.acc.z, o);
+            a2.w = __shfl_xor_sync(kFull, st.acc.w, o);
+            // both partners must apply the merge in the same operand order to agree bit for bit
+            if (lane & o) {
+                Softmax4 other;
+                other.m = m2; other.l = l2; other.acc = a2;
+                other.merge(st.m, st.l, st.acc);
+                st = other;
+            } else {
+                st.merge(m2, l2, a2);
+            }
+        }
+        if (sub == 0) {
+            const float inv = st.l > 0.f ? 1.f / st.l : 0.f;
+            float4 o4 = make_float4(st.acc.x * inv, st.acc.y * inv, st.acc.z * inv, st.acc.w * inv);
+            __stcs(reinterpret_cast<float4*>(a.out + (size_t)v * C) + fl, o4);
+        }
+    }
+}
+
+template <int G, int DL>
+static int launch_gat(const GatArgs& a, cudaStream_t st) {
+    static int blocks_per_sm = 0;
+    auto kern = gat_aggregate_kernel<G, DL>;
+    if (blocks_per_sm == 0) {
+        int b = 0;
+        JG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, kern, kGatBlock, 0));
+        blocks_per_sm = b > 0 ? b : 1;
+    }
+    kern<<<sm_count() * blocks_per_sm, kGatBlock, 0, st>>>(a);
+    JG_LAUNCH_CHECK();
+    return JG_OK;
+}
+
+template <int G>
+static int launch_gat_g(int dl, const GatArgs& a, cudaStream_t st) {
+    switch (dl) {
+        case 1: return launch_gat<G, 1>(a, st);
+        case 2: if constexpr (G >= 2) return launch_gat<G, 2>(a, st); break;
+        case 4: if constexpr (G >= 4) return launch_gat<G, 4>(a, st); break;
+        case 8: if constexpr (G >= 8) return launch_gat<G, 8>(a, st); break;
+        case 16: if constexpr (G >= 16) return launch_gat<G, 16>(a, st); break;
+        case 32: if constexpr (G >= 32) return launch_gat<G, 32>(a, st); break;
+    }
+    return JG_EUNSUPPORTED;
+}
+
+}  // namespace jg
+
+using namespace jg;
+
+extern "C" {
+
+size_t jg_gat_aggregate_workspace_bytes(int64_t n_nodes, int64_t n_edges, int64_t heads, int64_t dim) {
+    (void)n_nodes; (void)n_edges; (void)heads; (void)dim;
+    return 256;
+}
+
+int jg_gat_aggregate_supported(int64_t heads, int64_t dim) {
+    if (heads <= 0 || dim <= 0 || dim % 4) return 0;
+    const int64_t g = heads * dim / 4, dl = dim / 4;
+    auto pow2 = [](int64_t v) { return v > 0 && (v & (v - 1)) == 0; };
+    return pow2(g) && pow2(dl) && g <= 32;
+}
+
+int jg_gat_aggregate_f32(float* out, const float* h, const float* a_src, const float* a_dst, const int32_t* idx,
+                         const int32_t* off, int64_t n_nodes, int64_t n_edges, int64_t heads, int64_t dim, float slope,
+                         void* workspace, size_t workspace_bytes, jg_stream_t stream) {
+    JG_CHECK_ARG(n_nodes >= 0 && n_edges >= 0 && heads > 0 && dim > 0, JG_EINVAL, "gat_aggregate: bad size");
+    if (n_nodes == 0) return JG_OK;
+    JG_CHECK_ARG(out && h && a_src && a_dst && off, JG_EINVAL, "gat_aggregate: null pointer");
+    JG_CHECK_ARG(n_edges == 0 || idx, JG_EINVAL, "gat_aggregate: null idx");
+    JG_CHECK_ARG(n_edges <= INT32_MAX && n_nodes < INT32_MAX, JG_ESHAPE, "gat_aggregate: sizes beyond int32");
+    if (!jg_gat_aggregate_supported(heads, dim)) {
+        set_error("gat_aggregate: heads*dim/4 and dim/4 must be powers of two with heads*dim <= 128 (got %lld x %lld)",
+                  (long long)heads, (long long)dim);
+        return JG_EUNSUPPORTED;
+    }
+    JG_CHECK_ARG((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(a_src) |
+                  reinterpret_cast<uintptr_t>(a_dst)) % 16 == 0, JG_EINVAL, "gat_aggregate: pointers must be 16-byte aligned");
+    JG_CHECK_ARG(workspace && workspace_bytes >= 256, JG_EWORKSPACE, "gat_aggregate: workspace missing");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    GatArgs a = {out, h, a_src, a_dst, idx, off, n_nodes, slope, static_cast<unsigned long long*>(workspace)};
+    JG_CUDA(cudaMemsetAsync(a.ticket, 0, sizeof(unsigned long long), st));
+    const int g = (int)(heads * dim / 4), dl = (int)(dim / 4);
+    switch (g) {
+        case 1: return launch_gat_g<1>(dl, a, st);
+        case 2: return launch_gat_g<2>(dl, a, st);
+        case 4: return launch_gat_g<4>(dl, a, st);
+        case 8: return launch_gat_g<8>(dl, a, st);
+        case 16: return launch_gat_g<16>(dl, a, st);
+        case 32: return launch_gat_g<32>(dl, a, st);
+    }
+    return JG_EUNSUPPORTED;
+}
+
+}  // extern "C"

@@ -1,0 +1,137 @@
+"""Layer shims with the reference's constructor and call signatures, built on the operators of
+:mod:`jittorgeometric_b200.ops`: ``gcn_norm``, ``GCNConv``, ``SGConv``, ``APPNP``, ``GATConv``
+(jittor_geometric/nn/conv/{gcn_conv,sg_conv,appnp_conv,gat_conv}.py)."""
+import math
+
+import torch
+
+from . import ops
+from .data import CSC, CSR
+
+
+def glorot_(t):
+    """In-place U(-s, s), s = sqrt(6 / (fan_in + fan_out)) (nn/inits.py:19-22)."""
+    s = math.sqrt(6.0 / (t.shape[-2] + t.shape[-1]))
+    with torch.no_grad():
+        t.uniform_(-s, s)
+    return t
+
+
+def gcn_norm(edge_index, edge_weight=None, num_nodes=None, improved=False, add_self_loops=True, dtype=None):
+    """Self-loops + symmetric normalisation as a COO list (nn/conv/gcn_conv.py:18-37).  Returned
+    in the reference's order (kept entries, then one loop per node); ``ops.gcn_norm_csc_csr`` gives
+    the CSC/CSR directly without materialising this list."""
+    if not add_self_loops:
+        raise RuntimeError("gcn_norm: add_self_loops=False is not implemented")
+    if num_nodes is None:
+        num_nodes = int(edge_index.max()) + 1 if edge_index.numel() else 0
+    return ops.gcn_norm_coo(edge_index, edge_weight, num_nodes, improved=improved)
+
+
+class GCNConv(torch.nn.Module):
+    """``out = A_hat (x W) + b`` (nn/conv/gcn_conv.py:70-112).  ``spmm`` is accepted for signature
+    compatibility; there is one backend."""
+
+    def __init__(self, in_channels, out_channels, bias=True, spmm=True, **kwargs):
+        super().__init__()
+        self.in_channels, self.out_channels, self.spmm = in_channels, out_channels, spmm
+        self.weight = torch.nn.Parameter(torch.empty(in_channels, out_channels))
+        self.bias = torch.nn.Parameter(torch.zeros(out_channels)) if bias else None
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        glorot_(self.weight)
+        if self.bias is not None:
+            with torch.no_grad():
+                self.bias.zero_()
+
+    def forward(self, x, csc, csr):
+        x = x @ self.weight
+        out = ops.aggregateWithWeight(x, csc, csr)
+        if self.bias is not None:
+            out = out + self.bias
+        return out
+
+    def __repr__(self):
+        return f"{self.__class__.__name__}({self.in_channels}, {self.out_channels})"
+
+
+class SGConv(torch.nn.Module):
+    """``lin(A_hat^K x)`` (nn/conv/sg_conv.py:43-70)."""
+
+    def __init__(self, in_channels, out_channels, K=1, bias=True, spmm=True, **kwargs):
+        super().__init__()
+        self.K = K
+        self.lin = torch.nn.Linear(in_channels, out_channels, bias=bias)
+        glorot_(self.lin.weight)
+        if bias:
+            with torch.no_grad():
+                self.lin.bias.zero_()
+
+    def forward(self, x, csc, csr):
+        for _ in range(self.K):
+            x = ops.aggregateWithWeight(x, csc, csr)
+        return self.lin(x)
+
+
+class APPNP(torch.nn.Module):
+    """``x <- (1 - alpha) A_hat x + alpha h`` repeated K times (nn/conv/appnp_conv.py:27-52)."""
+
+    def __init__(self, K, alpha, spmm=True, **kwargs):
+        super().__init__()
+        self.K, self.alpha = K, alpha
+
+    def forward(self, x, csc, csr):
+        h = x
+        for _ in range(self.K):
+            x = ops.aggregateWithWeight(x, csc, csr)
+            x = x * (1 - self.alpha)
+            x = x + self.alpha * h
+        return x
+
+
+class GATConv(torch.nn.Module):
+    """Attention layer (nn/conv/gat_conv.py:30-88): ``h = relu(x W)``, edge logits
+    ``leaky_relu([h_src, h_dst] a, 0.2)``, softmax over each destination's in-edges, weighted sum.
+    ``heads`` > 1 (an extension; the reference layer is single-head) splits the channels into
+    independent heads.  The forward pass runs the fused kernel when the shape allows and no
+    gradient is needed, else the reference's op-by-op pipeline on the per-edge operators."""
+
+    def __init__(self, in_channels, out_channels, heads=1, **kwargs):
+        super().__init__()
+        assert out_channels % heads == 0
+        self.in_channels, self.out_channels, self.heads = in_channels, out_channels, heads
+        self.weight = torch.nn.Parameter(torch.empty(in_channels, out_channels))
+        self.edge_weight = torch.nn.Parameter(torch.empty(2 * out_channels, 1))
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        glorot_(self.weight)
+        glorot_(self.edge_weight)
+
+    def attention_vectors(self):
+        c = self.out_channels
+        return self.edge_weight[:c, 0].reshape(self.heads, -1), self.edge_weight[c:, 0].reshape(self.heads, -1)
+
+    def forward(self, x, csc):
+        h = torch.relu(x @ self.weight)
+        dim = self.out_channels // self.heads
+        needs_grad = torch.is_grad_enabled() and (h.requires_grad or self.edge_weight.requires_grad)
+        if not needs_grad and ops.gat_aggregate_supported(self.heads, dim):
+            a_src, a_dst = self.attention_vectors()
+            return ops.gat_aggregate(h, a_src, a_dst, csc, self.heads)
+        return self.propagate_unfused(h, csc)
+
+    def propagate_unfused(self, h, csc):
+        e_s = ops.ScatterToEdge(h, csc, "src")
+        e_d = ops.ScatterToEdge(h, csc, "dst")
+        a_src, a_dst = self.attention_vectors()
+        E, H = e_s.shape[0], self.heads
+        m = (e_s.reshape(E, H, -1) * a_src).sum(-1) + (e_d.reshape(E, H, -1) * a_dst).sum(-1)
+        m = torch.nn.functional.leaky_relu(m, 0.2)
+        alpha = ops.EdgeSoftmax(m, csc)
+        msg = (e_s.reshape(E, H, -1) * alpha.unsqueeze(-1)).reshape(E, -1)
+        return ops.ScatterToVertex(msg, csc, "src")
+
+    def __repr__(self):
+        return f"{self.__class__.__name__}({self.in_channels}, {self.out_channels})"

@@ -13,7 +13,9 @@ from . import _lib
 from ._lib import check, lib, ptr, stream_for, workspace
 from .data import CSC, CSR
 
-__all__ = ["aggregateWithWeight", "segment_aggregate", "SpmmPlan", "cootocsr", "cootocsc", "gcn_norm_csc_csr"]
+__all__ = ["aggregateWithWeight", "segment_aggregate", "SpmmPlan", "cootocsr", "cootocsc", "gcn_norm_csc_csr",
+           "SpmmCsr", "SpmmCoo", "ScatterToEdge", "ScatterToVertex", "EdgeSoftmax", "gat_aggregate",
+           "gat_aggregate_supported", "gcn_norm_coo"]
 
 DEFAULT_CHUNK = int(os.environ.get("JG_SPMM_CHUNK", "1024"))
 
@@ -181,3 +183,227 @@ def gcn_norm_csc_csr(edge_index, edge_weight, num_nodes, improved=False, want_cs
     out_csc = CSC(csc[0][:E], csc[1], csc[2][:E])
     out_csr = CSR(csr[0][:E], csr[1], csr[2][:E]) if want_csr else None
     return out_csc, out_csr
+
+
+def gcn_norm_coo(edge_index, edge_weight, num_nodes, improved=False):
+    """``gcn_norm`` (nn/conv/gcn_conv.py:18-37) as the reference returns it: the COO list with
+    (v,v) entries removed, one loop per node appended, and symmetric-normalised weights."""
+    ei = _edge_index(edge_index)
+    E0, n, dev = ei.shape[1], int(num_nodes), ei.device
+    w = None if edge_weight is None else _as_f32(edge_weight, "edge_weight")
+    cap = E0 + n
+    out = torch.empty((2, cap), dtype=torch.int32, device=dev)
+    ow = torch.empty(cap, dtype=torch.float32, device=dev)
+    count = torch.zeros(1, dtype=torch.int64, device=dev)
+    ws = workspace(lib().jg_gcn_norm_coo_workspace_bytes(E0, n), dev)
+    check(lib().jg_gcn_norm_coo(ptr(ei), ptr(w), E0, n, 2.0 if improved else 1.0, ptr(out[0]), ptr(out[1]), ptr(ow),
+                                ptr(count), ptr(ws), ws.numel(), stream_for(ei)), "jg_gcn_norm_coo")
+    E = int(count.item())
+    return out[:, :E].contiguous(), ow[:E]
+
+
+# ------------------------------------------------------------------------------ SpMM front ends
+def _csr_rows(csr):
+    """Source of every CSR entry (row ids expanded from the offsets)."""
+    n = csr.row_offset.numel() - 1
+    counts = (csr.row_offset[1:] - csr.row_offset[:-1]).long()
+    return torch.repeat_interleave(torch.arange(n, dtype=torch.int32, device=counts.device), counts)
+
+
+def _transposed_of(csr):
+    """CSC of the same matrix, built on device once and cached on the CSR object: the
+    destination-major structure an atomics-free ``A^T x`` needs."""
+    key = (csr.column_indices.data_ptr(), csr.row_offset.data_ptr(), csr.edge_weight.data_ptr())
+    cached = getattr(csr, "_jg_transposed", None)
+    if cached is None or cached[0] != key:
+        n = csr.row_offset.numel() - 1
+        ei = torch.stack([_csr_rows(csr), _as_i32(csr.column_indices, "column_indices")])
+        cached = (key, cootocsc(ei, csr.edge_weight, n))
+        csr._jg_transposed = cached
+    return cached[1]
+
+
+class _SpmmCsrFunc(torch.autograd.Function):
+    """execute/grad pairing of SpmmCsrFunc (ops/spmmcsr.py:21-39).  The reference's grad applies the
+    SAME operator (same trans_A) to grad_output, which is the true gradient only for a symmetric
+    matrix; that behaviour is kept."""
+
+    @staticmethod
+    def forward(ctx, x, csr, trans_A, trans_B):
+        if trans_B:
+            raise RuntimeError("SpmmCsr: trans_B=True is not supported (the reference never passes it)")
+        ctx.csr, ctx.trans_A = csr, trans_A
+        return _spmm_csr(x, csr, trans_A)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return _spmm_csr(grad_output.contiguous(), ctx.csr, ctx.trans_A), None, None, None
+
+
+def _spmm_csr(x, csr, trans_A):
+    if trans_A:
+        t = _transposed_of(csr)
+        return segment_aggregate(x, t.row_indices, t.column_offset, t.edge_weight,
+                                 plan=_plan_of(t, t.column_offset, t.row_indices.numel()))
+    return segment_aggregate(x, csr.column_indices, csr.row_offset, csr.edge_weight,
+                             plan=_plan_of(csr, csr.row_offset, csr.column_indices.numel()))
+
+
+def SpmmCsr(x, csr, trans_A=True, trans_B=False):
+    """``op(A) @ x`` for a CSR matrix (ops/spmmcsr.py:42-44).  With the default ``trans_A=True`` and
+    a source-keyed CSR this is out[dst] = sum w * x[src], the same result as
+    ``aggregateWithWeight`` over the CSC."""
+    return _SpmmCsrFunc.apply(x, csr, trans_A, trans_B)
+
+
+class _SpmmCooFunc(torch.autograd.Function):
+    """SpmmCooFunc (ops/spmmcoo.py:19-41); its grad calls the operator with default flags."""
+
+    @staticmethod
+    def forward(ctx, x, edge_index, edge_weight, trans_A, trans_B):
+        if trans_B:
+            raise RuntimeError("SpmmCoo: trans_B=True is not supported (the reference never passes it)")
+        n = x.shape[0]
+        fwd = cootocsc(edge_index, edge_weight, n) if trans_A else cootocsr(edge_index, edge_weight, n)
+        ctx.n, ctx.ei, ctx.w = n, edge_index, edge_weight
+        idx = fwd.row_indices if trans_A else fwd.column_indices
+        off = fwd.column_offset if trans_A else fwd.row_offset
+        return segment_aggregate(x, idx, off, fwd.edge_weight, plan=SpmmPlan(off, idx.numel()))
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        t = cootocsr(ctx.ei, ctx.w, ctx.n)
+        g = segment_aggregate(grad_output.contiguous(), t.column_indices, t.row_offset, t.edge_weight,
+                              plan=SpmmPlan(t.row_offset, t.column_indices.numel()))
+        return g, None, None, None, None
+
+
+def SpmmCoo(x, edge_index, edge_weight, trans_A=True, trans_B=False):
+    """``op(A) @ x`` for a COO matrix whose rows are ``edge_index[0]`` (ops/spmmcoo.py:43-45)."""
+    return _SpmmCooFunc.apply(x, edge_index, edge_weight, trans_A, trans_B)
+
+
+# ------------------------------------------------------------------------------ per-edge operators
+def _scatter_to_edge(x, csc, flag):
+    x = _as_f32(x, "x")
+    idx, off = _as_i32(csc.row_indices, "row_indices"), _as_i32(csc.column_offset, "column_offset")
+    E, n, c = idx.numel(), off.numel() - 1, x.shape[1]
+    out = torch.empty((E, c), dtype=torch.float32, device=x.device)
+    check(lib().jg_scatter_to_edge_f32(ptr(out), ptr(x), ptr(idx), ptr(off), n, E, c, flag, stream_for(x)),
+          "jg_scatter_to_edge_f32")
+    return out
+
+
+def _edge_to_vertex(msg, csc, flag):
+    msg = _as_f32(msg, "msg")
+    idx, off = _as_i32(csc.row_indices, "row_indices"), _as_i32(csc.column_offset, "column_offset")
+    E, n, c = idx.numel(), off.numel() - 1, msg.shape[1]
+    if msg.shape[0] != E:
+        raise RuntimeError(f"edge tensor has {msg.shape[0]} rows, the graph {E} edges")
+    out = torch.empty((n, c), dtype=torch.float32, device=msg.device)
+    check(lib().jg_edge_to_vertex_f32(ptr(out), ptr(msg), ptr(idx), ptr(off), n, E, c, flag, stream_for(msg)),
+          "jg_edge_to_vertex_f32")
+    return out
+
+
+class _ScatterToEdgeFunc(torch.autograd.Function):
+    """ScatterToEdgeFunc (ops/scatterToEdge.py:22-46): backward is edge_to_vertex with the same flag."""
+
+    @staticmethod
+    def forward(ctx, x, csc, flow):
+        ctx.csc, ctx.flag = csc, (0 if flow == "src" else 1)
+        return _scatter_to_edge(x, csc, ctx.flag)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return _edge_to_vertex(grad_output.contiguous(), ctx.csc, ctx.flag), None, None
+
+
+def ScatterToEdge(x, csc, flow):
+    """Node rows copied onto edges in CSC order: ``flow="src"`` takes each edge's source row,
+    anything else its destination row (ops/scatterToEdge.py:49-51)."""
+    return _ScatterToEdgeFunc.apply(x, csc, flow)
+
+
+class _ScatterToVertexFunc(torch.autograd.Function):
+    """ScatterToVertexFunc (ops/scatterToVertex.py:23-46): always sums per destination, whatever
+    ``flow`` says; backward copies the destination's gradient row onto its in-edges."""
+
+    @staticmethod
+    def forward(ctx, x, csc, flow):
+        ctx.csc = csc
+        return _edge_to_vertex(x, csc, 1)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return _scatter_to_edge(grad_output.contiguous(), ctx.csc, 1), None, None
+
+
+def ScatterToVertex(x, csc, flow):
+    return _ScatterToVertexFunc.apply(x, csc, flow)
+
+
+def _edge_softmax(x, off, bwd_y=None):
+    shape = x.shape
+    x2 = _as_f32(x, "x").reshape(shape[0], -1)
+    E, h = x2.shape
+    n = off.numel() - 1
+    out = torch.zeros_like(x2)     # empty segments write nothing, like the reference
+    if bwd_y is None:
+        check(lib().jg_edge_softmax_fwd_f32(ptr(out), ptr(x2), ptr(off), n, E, h, stream_for(x2)), "jg_edge_softmax_fwd_f32")
+    else:
+        y2 = bwd_y.reshape(E, h).contiguous()
+        check(lib().jg_edge_softmax_bwd_f32(ptr(out), ptr(x2), ptr(y2), ptr(off), n, E, h, stream_for(x2)),
+              "jg_edge_softmax_bwd_f32")
+    return out.reshape(shape)
+
+
+class _EdgeSoftmaxFunc(torch.autograd.Function):
+    """EdgeSoftmaxFunc (ops/edgesoftmax.py:62-74)."""
+
+    @staticmethod
+    def forward(ctx, x, csc):
+        off = _as_i32(csc.column_offset, "column_offset")
+        if x.shape[0] != csc.row_indices.numel():
+            raise RuntimeError(f"x has {x.shape[0]} rows, the graph {csc.row_indices.numel()} edges")
+        y = _edge_softmax(x, off)
+        ctx.off = off
+        ctx.save_for_backward(y)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        (y,) = ctx.saved_tensors
+        return _edge_softmax(grad_output.contiguous(), ctx.off, bwd_y=y), None
+
+
+def EdgeSoftmax(x, csc):
+    """Softmax of per-edge scores over the in-edges of every destination
+    (ops/edgesoftmax.py:78-80).  ``x`` is ``[E]`` or ``[E, 1]`` as in the reference, or ``[E, H]``
+    for H independent heads."""
+    return _EdgeSoftmaxFunc.apply(x, csc)
+
+
+def gat_aggregate_supported(heads, dim):
+    return bool(lib().jg_gat_aggregate_supported(int(heads), int(dim)))
+
+
+def gat_aggregate(h, a_src, a_dst, csc, heads, slope=0.2):
+    """Fused edge phase of the attention layer (nn/conv/gat_conv.py:60-83): logits, per-destination
+    softmax and weighted aggregation in one pass.  ``h`` is ``[N, heads*dim]``; ``a_src`` and
+    ``a_dst`` are ``[heads, dim]``.  Forward only."""
+    h = _as_f32(h, "h")
+    n, c = h.shape
+    dim = c // int(heads)
+    a_src, a_dst = _as_f32(a_src, "a_src").reshape(-1), _as_f32(a_dst, "a_dst").reshape(-1)
+    if a_src.numel() != c or a_dst.numel() != c or dim * heads != c:
+        raise RuntimeError("gat_aggregate: a_src/a_dst must hold heads*dim values")
+    idx, off = _as_i32(csc.row_indices, "row_indices"), _as_i32(csc.column_offset, "column_offset")
+    if off.numel() != n + 1:
+        raise RuntimeError("gat_aggregate: column_offset does not match h")
+    out = torch.empty_like(h)
+    ws = workspace(lib().jg_gat_aggregate_workspace_bytes(n, idx.numel(), heads, dim), h.device)
+    check(lib().jg_gat_aggregate_f32(ptr(out), ptr(h), ptr(a_src), ptr(a_dst), ptr(idx), ptr(off), n, idx.numel(),
+                                     int(heads), dim, float(slope), ptr(ws), ws.numel(), stream_for(h)),
+          "jg_gat_aggregate_f32")
+    return out
