@@ -68,6 +68,29 @@ int jg_aggregate_f32(float* out, const float* x, const int32_t* idx, const int32
                      const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes,
                      jg_stream_t stream);
 
+/* Same aggregation, added to what `out` already holds: out[v,:] = out[v,:] + sum_j w[j]*x[idx[j],:]
+ * (the sum is formed first, then added).  Used by the partitioned path, where the rows gathered
+ * from other shards are aggregated after the shard's own rows - the place where the reference
+ * adds the per-source-rank results (ops/distspmm.py:39, `result = result + output`). */
+int jg_aggregate_add_f32(float* out, const float* x, const int32_t* idx, const int32_t* off,
+                         const float* w, int64_t n_out, int64_t n_in, int64_t f, int64_t nnz,
+                         const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes,
+                         jg_stream_t stream);
+
+/* ------------------------------------------------------------------ 1-D row partition
+ * Splits the in-edge structure of one shard (destination rows [lo, hi) of the graph, `idx`
+ * holding GLOBAL source ids) into interior entries (source inside [lo, hi), ids rebased to the
+ * shard) and halo entries (source owned by another shard, ids kept global), each keeping the
+ * order of the input within a row.  Replaces the per-source-rank sub-CSR construction of the
+ * reference's offline partitioner (partition/distchunk_manager.py:100-106,
+ * examples/dist_gcn/dist_partition.py:122-158), on device.  Output arrays need room for nnz
+ * entries (offsets n_rows + 1); out_counts[0..1] (device, int64) receive the two entry counts. */
+size_t jg_partition_split_workspace_bytes(int64_t nnz);
+int jg_partition_split(const int32_t* idx, const int32_t* off, const float* w, int64_t n_rows, int64_t nnz, int32_t lo,
+                       int32_t hi, int32_t* int_idx, int32_t* int_off, float* int_w, int32_t* halo_idx,
+                       int32_t* halo_off, float* halo_w, int64_t* out_counts, void* workspace, size_t workspace_bytes,
+                       jg_stream_t stream);
+
 /* ------------------------------------------------------------------ conversion
  * COO -> CSR (by = 0, rows keyed by source) or CSC (by = 1, columns keyed by destination).
  * Replaces CootocsrOp / CootocscOp (ops/cpp/cootocsr_op.cc:24-57, ops/cpp/cootocsc_op.cc:23-53;

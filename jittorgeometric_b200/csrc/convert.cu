@@ -374,6 +374,47 @@ __global__ void write_norm_coo_kernel(const int32_t* __restrict__ src, const int
     }
 }
 
+// ---- 1-D row partition: split a shard's in-edges into interior (source owned) and halo (remote)
+__global__ void interior_flags_kernel(const int32_t* __restrict__ idx, int64_t nnz, int32_t lo, int32_t hi,
+                                      int* __restrict__ flag) {
+    const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e < nnz) flag[e] = idx[e] >= lo && idx[e] < hi;
+    if (e == nnz) flag[e] = 0;
+}
+
+// pos[e] = number of interior entries before e (exclusive scan of the flags, nnz + 1 entries).
+__global__ void split_write_kernel(const int32_t* __restrict__ idx, const float* __restrict__ w,
+                                   const int* __restrict__ pos, int64_t nnz, int32_t lo, int32_t hi,
+                                   int32_t* __restrict__ int_idx, float* __restrict__ int_w,
+                                   int32_t* __restrict__ halo_idx, float* __restrict__ halo_w) {
+    const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= nnz) return;
+    const int32_t s = idx[e];
+    const int p = pos[e];
+    if (s >= lo && s < hi) {
+        int_idx[p] = s - lo;     // interior sources are addressed inside the shard's own rows
+        int_w[p] = w[e];
+    } else {
+        halo_idx[e - p] = s;     // halo sources keep their global id
+        halo_w[e - p] = w[e];
+    }
+}
+
+__global__ void split_offsets_kernel(const int32_t* __restrict__ off, const int* __restrict__ pos, int64_t n_rows,
+                                     int32_t* __restrict__ int_off, int32_t* __restrict__ halo_off,
+                                     int64_t* __restrict__ counts) {
+    const int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (v > n_rows) return;
+    const int32_t o = off[v];
+    const int p = pos[o];
+    int_off[v] = p;
+    halo_off[v] = o - p;
+    if (v == n_rows) {
+        counts[0] = p;
+        counts[1] = o - p;
+    }
+}
+
 __global__ void fill_int_kernel(int* p, int v, int64_t n) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) p[i] = v;
@@ -642,6 +683,42 @@ int jg_gcn_norm_coo(const int32_t* edge_index, const float* w, int64_t n_edges, 
             out_src, out_dst, out_w);
         JG_LAUNCH_CHECK();
     }
+    return JG_OK;
+}
+
+
+size_t jg_partition_split_workspace_bytes(int64_t nnz) {
+    if (nnz < 0) return 0;
+    Carver c(nullptr);
+    c.take<int>(nnz + 1);
+    c.take<int>(scan_temp_ints(nnz + 1));
+    return c.total();
+}
+
+int jg_partition_split(const int32_t* idx, const int32_t* off, const float* w, int64_t n_rows, int64_t nnz, int32_t lo,
+                       int32_t hi, int32_t* int_idx, int32_t* int_off, float* int_w, int32_t* halo_idx,
+                       int32_t* halo_off, float* halo_w, int64_t* out_counts, void* workspace, size_t workspace_bytes,
+                       jg_stream_t stream) {
+    JG_CHECK_ARG(n_rows >= 0 && nnz >= 0 && lo <= hi, JG_EINVAL, "partition_split: bad sizes");
+    JG_CHECK_ARG(off && int_off && halo_off && out_counts, JG_EINVAL, "partition_split: null offsets/counts");
+    JG_CHECK_ARG(nnz == 0 || (idx && w && int_idx && int_w && halo_idx && halo_w), JG_EINVAL, "partition_split: null array");
+    JG_CHECK_ARG(nnz < INT32_MAX && n_rows < INT32_MAX, JG_ESHAPE, "partition_split: sizes beyond int32");
+    JG_CHECK_ARG(workspace && workspace_bytes >= jg_partition_split_workspace_bytes(nnz), JG_EWORKSPACE,
+                 "partition_split: workspace too small");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    Carver c(workspace);
+    int* pos = c.take<int>(nnz + 1);
+    int* sums = c.take<int>(scan_temp_ints(nnz + 1));
+    interior_flags_kernel<<<blocks_for(nnz + 1, 256), 256, 0, st>>>(idx, nnz, lo, hi, pos);
+    JG_LAUNCH_CHECK();
+    int rc = exclusive_scan(pos, pos, nnz + 1, sums, st);
+    if (rc != JG_OK) return rc;
+    if (nnz > 0) {
+        split_write_kernel<<<blocks_for(nnz, 256), 256, 0, st>>>(idx, w, pos, nnz, lo, hi, int_idx, int_w, halo_idx, halo_w);
+        JG_LAUNCH_CHECK();
+    }
+    split_offsets_kernel<<<blocks_for(n_rows + 1, 256), 256, 0, st>>>(off, pos, n_rows, int_off, halo_off, out_counts);
+    JG_LAUNCH_CHECK();
     return JG_OK;
 }
 

@@ -97,6 +97,7 @@ struct AggArgs {
     const int32_t* item_k;
     float* partial;
     unsigned long long* ticket;
+    int accumulate;  // 1: add the aggregated row to what `out` already holds (old + sum)
 };
 
 __device__ __forceinline__ void fma2(float4& a, const float4& v, float w) {
@@ -160,6 +161,7 @@ __global__ void __launch_bounds__(kBlock, MINB) aggregate_rows_kernel(AggArgs a)
             if (id >= total) break;
             int32_t s, e, lim;
             float* dst;
+            const bool add_old = a.accumulate && id >= n_items;
             if (id < n_items) {
                 const int h = a.item_hub[id];
                 const int k = a.item_k[id];
@@ -261,14 +263,23 @@ __global__ void __launch_bounds__(kBlock, MINB) aggregate_rows_kernel(AggArgs a)
             if (sub == 0) {
                 float4* o = reinterpret_cast<float4*>(dst) + fl;
 #pragma unroll
-                for (int q = 0; q < VPL; q++) __stcs(o + q * G, acc[q]);
+                for (int q = 0; q < VPL; q++) {
+                    if (add_old) {
+                        const float4 old = o[q * G];
+                        acc[q].x = __fadd_rn(old.x, acc[q].x);
+                        acc[q].y = __fadd_rn(old.y, acc[q].y);
+                        acc[q].z = __fadd_rn(old.z, acc[q].z);
+                        acc[q].w = __fadd_rn(old.w, acc[q].w);
+                    }
+                    __stcs(o + q * G, acc[q]);
+                }
             }
         }
     }
 }
 
 // Any feature width: lanes stride over columns with scalar loads, up to 256 columns per sweep.
-__device__ __forceinline__ void warp_segment_any(const AggArgs& a, int32_t s, int32_t e, float* dst) {
+__device__ __forceinline__ void warp_segment_any(const AggArgs& a, int32_t s, int32_t e, float* dst, bool add_old) {
     constexpr int Q = 8;
     constexpr int UNROLL = 4;
     const int lane = lane_id();
@@ -307,7 +318,8 @@ __device__ __forceinline__ void warp_segment_any(const AggArgs& a, int32_t s, in
         }
 #pragma unroll
         for (int q = 0; q < Q; q++)
-            if (c0 + q * 32 + lane < F) dst[c0 + q * 32 + lane] = acc[q];
+            if (c0 + q * 32 + lane < F)
+                dst[c0 + q * 32 + lane] = add_old ? __fadd_rn(dst[c0 + q * 32 + lane], acc[q]) : acc[q];
     }
 }
 
@@ -352,7 +364,7 @@ __global__ void __launch_bounds__(kBlock) aggregate_any_kernel(AggArgs a) {
                 if (e - s > chunk) continue;  // hub row: its pieces are separate work ids
                 dst = a.out + (size_t)row * F;
             }
-            warp_segment_any(a, s, e, dst);
+            warp_segment_any(a, s, e, dst, a.accumulate && id >= n_items);
         }
     }
 }
@@ -373,7 +385,7 @@ __global__ void __launch_bounds__(kBlock) hub_fixup_kernel(AggArgs a) {
         for (int64_t c = lane; c < F; c += 32) {
             float acc = p[c];
             for (int k = 1; k < pieces; k++) acc = __fadd_rn(acc, p[(size_t)k * F + c]);
-            a.out[(size_t)row * F + c] = acc;
+            a.out[(size_t)row * F + c] = a.accumulate ? __fadd_rn(a.out[(size_t)row * F + c], acc) : acc;
         }
     }
 }
@@ -474,10 +486,10 @@ size_t jg_aggregate_workspace_bytes(int64_t n_out, int64_t nnz, int64_t f, int32
     return c.total();
 }
 
-int jg_aggregate_f32(float* out, const float* x, const int32_t* idx, const int32_t* off,
-                     const float* w, int64_t n_out, int64_t n_in, int64_t f, int64_t nnz,
-                     const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes,
-                     jg_stream_t stream) {
+static int aggregate_impl(float* out, const float* x, const int32_t* idx, const int32_t* off,
+                          const float* w, int64_t n_out, int64_t n_in, int64_t f, int64_t nnz,
+                          const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes,
+                          jg_stream_t stream, int accumulate) {
     JG_CHECK_ARG(n_out >= 0 && n_in >= 0 && f >= 0 && nnz >= 0, JG_EINVAL, "aggregate: negative size");
     if (n_out == 0 || f == 0) return JG_OK;
     JG_CHECK_ARG(out && off, JG_EINVAL, "aggregate: null out/off");
@@ -492,6 +504,7 @@ int jg_aggregate_f32(float* out, const float* x, const int32_t* idx, const int32
 
     AggArgs a = {};
     a.out = out; a.x = x; a.idx = idx; a.off = off; a.w = w; a.n_out = n_out; a.f = f;
+    a.accumulate = accumulate;
     Carver c(workspace);
     a.ticket = c.take<unsigned long long>(1);
     if (plan) {
@@ -511,6 +524,20 @@ int jg_aggregate_f32(float* out, const float* x, const int32_t* idx, const int32
     return JG_OK;
 }
 
+
+int jg_aggregate_f32(float* out, const float* x, const int32_t* idx, const int32_t* off,
+                     const float* w, int64_t n_out, int64_t n_in, int64_t f, int64_t nnz,
+                     const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes,
+                     jg_stream_t stream) {
+    return aggregate_impl(out, x, idx, off, w, n_out, n_in, f, nnz, plan, chunk, workspace, workspace_bytes, stream, 0);
+}
+
+int jg_aggregate_add_f32(float* out, const float* x, const int32_t* idx, const int32_t* off,
+                         const float* w, int64_t n_out, int64_t n_in, int64_t f, int64_t nnz,
+                         const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes,
+                         jg_stream_t stream) {
+    return aggregate_impl(out, x, idx, off, w, n_out, n_in, f, nnz, plan, chunk, workspace, workspace_bytes, stream, 1);
+}
 
 // ------------------------------------------------------------------------------------------
 // Aggregation without any allocation.

@@ -66,12 +66,12 @@ def _plan_of(holder, off, nnz):
     return plan
 
 
-def segment_aggregate(x, idx, off, w, n_out=None, plan=None, out=None):
+def segment_aggregate(x, idx, off, w, n_out=None, plan=None, out=None, accumulate=False):
     """out[v,:] = sum_{j in [off[v], off[v+1])} w[j] * x[idx[j],:]  (fp32).
 
     The one kernel behind aggregateWithWeight (forward over CSC, backward over
     CSR), SpmmCsr and SpmmCoo.  ``plan`` is an :class:`SpmmPlan` of ``off`` or
-    ``None`` to process every row unsplit."""
+    ``None`` to process every row unsplit.  ``accumulate=True`` adds the result to ``out``."""
     x = _as_f32(x, "x")
     if x.dim() != 2:
         raise RuntimeError("x: expected a 2-D feature matrix")
@@ -84,10 +84,13 @@ def segment_aggregate(x, idx, off, w, n_out=None, plan=None, out=None):
         raise RuntimeError(f"edge_weight has {w.numel()} entries, indices {nnz}")
     n_in, f = x.shape
     if out is None:
+        if accumulate:
+            raise RuntimeError("accumulate=True needs the tensor to add to (out=)")
         out = torch.empty((n_out, f), dtype=torch.float32, device=x.device)
     chunk = plan.chunk if plan is not None else 0
     ws = workspace(lib().jg_aggregate_workspace_bytes(n_out, nnz, f, chunk), x.device)
-    check(lib().jg_aggregate_f32(ptr(out), ptr(x), ptr(idx), ptr(off), ptr(w), n_out, n_in, f, nnz,
+    fn = lib().jg_aggregate_add_f32 if accumulate else lib().jg_aggregate_f32
+    check(fn(ptr(out), ptr(x), ptr(idx), ptr(off), ptr(w), n_out, n_in, f, nnz,
                                  ptr(plan.buf) if plan is not None else None, chunk, ptr(ws), ws.numel(),
                                  stream_for(x)), "jg_aggregate_f32")
     return out
@@ -210,13 +213,14 @@ def _csr_rows(csr):
     return torch.repeat_interleave(torch.arange(n, dtype=torch.int32, device=counts.device), counts)
 
 
-def _transposed_of(csr):
+def _transposed_of(csr, n_cols=None):
     """CSC of the same matrix, built on device once and cached on the CSR object: the
-    destination-major structure an atomics-free ``A^T x`` needs."""
-    key = (csr.column_indices.data_ptr(), csr.row_offset.data_ptr(), csr.edge_weight.data_ptr())
+    destination-major structure an atomics-free ``A^T x`` needs.  ``n_cols`` is the column count
+    of a rectangular block (default: square)."""
+    key = (csr.column_indices.data_ptr(), csr.row_offset.data_ptr(), csr.edge_weight.data_ptr(), n_cols)
     cached = getattr(csr, "_jg_transposed", None)
     if cached is None or cached[0] != key:
-        n = csr.row_offset.numel() - 1
+        n = csr.row_offset.numel() - 1 if n_cols is None else int(n_cols)
         ei = torch.stack([_csr_rows(csr), _as_i32(csr.column_indices, "column_indices")])
         cached = (key, cootocsc(ei, csr.edge_weight, n))
         csr._jg_transposed = cached

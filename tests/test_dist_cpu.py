@@ -1,0 +1,119 @@
+"""CPU ranks over gloo (world size 2 and 3): the row partition, interior/halo split, shard
+exchange and accumulate order of the partitioned aggregation, with the CPU checker standing in
+for the kernels.  The result must equal the single-shard aggregation."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+class OracleBackend:
+    """numpy/oracle stand-in for the CUDA backend (tests only)."""
+
+    def __init__(self):
+        import oracle
+        self.O = oracle
+
+    def split(self, idx, off, w, lo, hi):
+        idx, off, w = idx.numpy(), off.numpy(), w.numpy()
+        inside = (idx >= lo) & (idx < hi)
+        seg = np.repeat(np.arange(len(off) - 1), np.diff(off))
+        def part(mask, rebase):
+            o = np.concatenate([[0], np.cumsum(np.bincount(seg[mask], minlength=len(off) - 1))]).astype(np.int32)
+            return torch.from_numpy((idx[mask] - rebase).astype(np.int32)), torch.from_numpy(o), torch.from_numpy(w[mask])
+        return part(inside, lo), part(~inside, 0)
+
+    def plan(self, off, nnz):
+        return None
+
+    def aggregate(self, x, idx, off, w, n_out, plan, out=None, accumulate=False):
+        y = torch.from_numpy(self.O.aggregate(x.numpy(), idx.numpy(), off.numpy(), w.numpy(), n_out=n_out))
+        if accumulate:
+            out += y
+            return out
+        return y
+
+
+def make_graph(seed, n, E, f):
+    rng = np.random.default_rng(seed)
+    dst = rng.integers(0, n, size=E)
+    src = rng.integers(0, n, size=E)
+    order = np.argsort(dst, kind="stable")
+    off = np.concatenate([[0], np.cumsum(np.bincount(dst, minlength=n))]).astype(np.int32)
+    w = rng.standard_normal(E).astype(np.float32)
+    x = rng.standard_normal((n, f)).astype(np.float32)
+    return src[order].astype(np.int32), off, w[order], x
+
+
+def worker(rank, world, port, n, E, f, q):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    from jittorgeometric_b200 import dist as jd
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        idx, off, w, x = make_graph(7, n, E, f)
+        part = jd.RowPartition(n, world)
+        lo, hi = part.range(rank)
+        l_idx, l_off, l_w = jd.shard_rows(torch.from_numpy(idx), torch.from_numpy(off), torch.from_numpy(w), part, rank)
+        g = jd.ShardedGraph(part, rank, l_idx, l_off, l_w, backend=OracleBackend())
+        y = g.aggregate(torch.from_numpy(x[lo:hi].copy()))
+        # interior and halo together hold every entry of the shard exactly once
+        assert g.interior[0].numel() + g.halo[0].numel() == l_idx.numel()
+        assert g.interior[0].numel() == 0 or int(g.interior[0].max()) < hi - lo
+        q.put((rank, lo, hi, y.numpy()))
+    except Exception as exc:  # surface the failure in the parent instead of a queue timeout
+        q.put((rank, -1, -1, repr(exc)))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+def free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+@pytest.mark.parametrize("world,n", [(2, 101), (3, 64)])
+@pytest.mark.timeout(120)
+def test_partitioned_aggregation_equals_single_shard(oracle, world, n):
+    E, f = 1500, 5
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=worker, args=(r, world, port, n, E, f, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=90) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=30)
+    assert all(g[1] >= 0 for g in got), [g[3] for g in got if g[1] < 0]
+    assert all(p.exitcode == 0 for p in procs)
+    idx, off, w, x = make_graph(7, n, E, f)
+    want = oracle.aggregate(x, idx, off, w)
+    _, scale = oracle.aggregate_f64(x, idx, off, w)
+    for rank, lo, hi, y in got:
+        assert y.shape == (hi - lo, f)
+        assert (np.abs(y - want[lo:hi]) / (scale[lo:hi] + 1e-30)).max() <= 1e-5
+
+
+def test_row_partition_bounds():
+    from jittorgeometric_b200.dist import RowPartition
+    p = RowPartition(10, 4)
+    assert p.pad == 3 and p.bounds == [0, 3, 6, 9, 10]
+    assert [p.n_local(r) for r in range(4)] == [3, 3, 3, 1]
+    assert p.owner(9) == 3 and p.owner(0) == 0
+    p = RowPartition(8, 8)
+    assert p.bounds == list(range(9))
+    p = RowPartition(3, 4)       # more ranks than rows: trailing ranks own nothing
+    assert [p.n_local(r) for r in range(4)] == [1, 1, 1, 0]
+    with pytest.raises(ValueError):
+        RowPartition(5, 0)

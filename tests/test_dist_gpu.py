@@ -1,0 +1,119 @@
+"""GPU side of the partitioned aggregation: the split and accumulate kernels with the ranks of a
+partition emulated one after another on one GPU (the exchange replaced by a local copy), and the
+real NCCL path as child processes when the box has at least two GPUs."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def make_graph(seed, n, E, f, hubs=3, hub_deg=3000):
+    rng = np.random.default_rng(seed)
+    dst = np.concatenate([rng.integers(0, n, size=E), np.repeat(rng.integers(0, n, size=hubs), hub_deg)])
+    src = rng.integers(0, n, size=len(dst))
+    order = np.argsort(dst, kind="stable")
+    off = np.concatenate([[0], np.cumsum(np.bincount(dst, minlength=n))]).astype(np.int32)
+    w = rng.standard_normal(len(dst)).astype(np.float32)
+    x = rng.standard_normal((n, f)).astype(np.float32)
+    return src[order].astype(np.int32), off, w[order], x
+
+
+@pytest.mark.parametrize("world,n,f", [(2, 5001, 128), (4, 4096, 32), (8, 3000, 7)])
+def test_emulated_ranks_on_one_gpu(cuda, oracle, world, n, f):
+    from jittorgeometric_b200 import dist as jd
+    idx, off, w, x = make_graph(world, n, 60000, f)
+    want = oracle.aggregate(x, idx, off, w)
+    _, scale = oracle.aggregate_f64(x, idx, off, w)
+    part = jd.RowPartition(n, world)
+    t = lambda a: torch.from_numpy(a).cuda()
+    idx_t, off_t, w_t = t(idx), t(off), t(w)
+    x_full = torch.zeros((world * part.pad, f), device="cuda")
+    x_full[:n] = t(x)
+
+    def local_copy(shard, full):
+        full.copy_(x_full)          # stands in for the all-gather
+        return None
+
+    for rank in range(world):
+        lo, hi = part.range(rank)
+        g = jd.ShardedGraph(part, rank, *jd.shard_rows(idx_t, off_t, w_t, part, rank))
+        # split: order inside a row preserved, ids rebased / kept, nothing lost
+        li, lo_off = g.interior[0].cpu().numpy(), g.interior[1].cpu().numpy()
+        hi_idx, h_off = g.halo[0].cpu().numpy(), g.halo[1].cpu().numpy()
+        s, e = off[lo], off[hi]
+        loc = idx[s:e]
+        inside = (loc >= lo) & (loc < hi)
+        assert np.array_equal(li, loc[inside] - lo) and np.array_equal(hi_idx, loc[~inside])
+        seg = np.repeat(np.arange(hi - lo), np.diff(off[lo:hi + 1]))
+        assert np.array_equal(np.diff(lo_off), np.bincount(seg[inside], minlength=hi - lo))
+        assert np.array_equal(np.diff(h_off), np.bincount(seg[~inside], minlength=hi - lo))
+        y = g.aggregate(t(x[lo:hi].copy()), gather=local_copy).cpu().numpy()
+        assert (np.abs(y - want[lo:hi]) / (scale[lo:hi] + 1e-30)).max() <= 1e-5
+        y2 = g.aggregate(t(x[lo:hi].copy()), gather=local_copy).cpu().numpy()
+        assert np.array_equal(y, y2)
+
+
+def test_accumulate_mode(cuda, oracle):
+    idx, off, w, x = make_graph(1, 2000, 30000, 64)
+    t = lambda a: torch.from_numpy(a).cuda()
+    base = np.random.default_rng(0).standard_normal((2000, 64)).astype(np.float32)
+    for chunk in (None, 256):
+        plan = cuda.ops.SpmmPlan(t(off), len(idx), chunk) if chunk else None
+        out = t(base.copy())
+        cuda.ops.segment_aggregate(t(x), t(idx), t(off), t(w), plan=plan, out=out, accumulate=True)
+        fresh = cuda.ops.segment_aggregate(t(x), t(idx), t(off), t(w), plan=plan)
+        assert np.array_equal(out.cpu().numpy(), base + fresh.cpu().numpy())     # old + sum, one rounding
+
+
+def nccl_worker(rank, world, port, n, E, f, q):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    from jittorgeometric_b200 import dist as jd
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        idx, off, w, x = make_graph(11, n, E, f)
+        part = jd.RowPartition(n, world)
+        lo, hi = part.range(rank)
+        t = lambda a: torch.from_numpy(a).cuda()
+        g = jd.ShardedGraph(part, rank, *jd.shard_rows(t(idx), t(off), t(w), part, rank))
+        y = g.aggregate(t(x[lo:hi].copy()))
+        torch.cuda.synchronize()
+        q.put((rank, lo, hi, y.cpu().numpy()))
+    except Exception as exc:
+        q.put((rank, -1, -1, repr(exc)))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_nccl_ranks(cuda, oracle):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    import torch.multiprocessing as mp
+    n, E, f = 40000, 600000, 128
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=nccl_worker, args=(r, world, port, n, E, f, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=240) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(g[1] >= 0 for g in got), [g[3] for g in got if g[1] < 0]
+    idx, off, w, x = make_graph(11, n, E, f)
+    want = oracle.aggregate(x, idx, off, w)
+    _, scale = oracle.aggregate_f64(x, idx, off, w)
+    for rank, lo, hi, y in got:
+        assert (np.abs(y - want[lo:hi]) / (scale[lo:hi] + 1e-30)).max() <= 1e-5
