@@ -9,10 +9,11 @@ source rank, and runs P rounds of host-staged pickled ``MPI.bcast`` + cuSPARSE. 
   ids carry no degree order),
 * splits its in-edges on device into interior entries (source row owned, read from the rank's own
   shard) and halo entries (source row remote),
-* exchanges feature shards with ONE NCCL all-gather over NVLink into a local buffer laid out by
-  global row id, while the interior aggregation runs, then aggregates the halo entries from that
-  buffer and adds them to the same output rows (fixed order: interior, then halo, so results are
-  run-to-run identical).  Kernels only ever gather from local memory.
+* brings the other ranks' feature shards over NVLink into a local buffer laid out by global row
+  id - copy-engine pulls from peer memory (:class:`PeerExchange`) or one NCCL all-gather - while
+  the interior aggregation runs, then aggregates the halo entries from that buffer and adds them
+  to the same output rows (fixed order: interior, then halo, so results are run-to-run
+  identical).  Kernels only ever gather from local memory.
 
 One process per GPU; ``torch.distributed`` supplies the communicator.  The compute backend is
 pluggable so the partition and exchange logic can be exercised by CPU ranks over ``gloo``.
@@ -70,15 +71,76 @@ class DeviceBackend:
         return ops.segment_aggregate(x, idx, off, w, n_out=n_out, plan=plan, out=out, accumulate=accumulate)
 
 
+class PeerExchange:
+    """Shard exchange by peer-to-peer copies over NVLink, driven by the copy engines.
+
+    An NCCL all-gather runs as a kernel, and the aggregation kernels are persistent grids that
+    fill every SM: whichever starts first keeps the other waiting, so nothing overlaps.  Here every
+    rank publishes its shard in a buffer its peers can map (``torch.distributed`` symmetric
+    memory) and pulls the P-1 remote shards into its local gather buffer with plain device-to-device
+    copies on a side stream; those are DMA transfers that need no SM, so they proceed underneath
+    the interior aggregation.  Two small barriers order the exchange: one after the shard is
+    published (before anyone pulls), one after the pulls (before the shard may be overwritten).
+    """
+
+    BARRIER_TIMEOUT_MS = 20000
+
+    def __init__(self, part, rank, group=None):
+        import torch.distributed._symmetric_memory as symm
+        self._symm = symm
+        self.part, self.rank = part, rank
+        self.group = group if group is not None else dist.group.WORLD
+        self.side = torch.cuda.Stream()
+        self._bufs = {}
+
+    def buffer(self, f, device):
+        """The rank's publishable feature shard of width ``f`` (``pad`` rows; write features here to
+        skip one copy per aggregation)."""
+        entry = self._bufs.get(f)
+        if entry is None:
+            t = self._symm.empty((self.part.pad, f), dtype=torch.float32, device=device)
+            t.zero_()
+            hdl = self._symm.rendezvous(t, self.group.group_name)
+            entry = (t, hdl)
+            self._bufs[f] = entry
+        return entry
+
+    def start(self, xp, full):
+        f = xp.shape[1]
+        buf, hdl = self.buffer(f, xp.device)
+        if xp.data_ptr() != buf.data_ptr():
+            buf.copy_(xp)
+        hdl.barrier(channel=0, timeout_ms=self.BARRIER_TIMEOUT_MS)       # every shard is published
+        cur = torch.cuda.current_stream()
+        self.side.wait_stream(cur)
+        pad, world = self.part.pad, self.part.world
+        with torch.cuda.stream(self.side):
+            for step in range(1, world):
+                q = (self.rank + step) % world                             # staggered: no two ranks pull the same peer at once
+                peer = hdl.get_buffer(q, (pad, f), torch.float32)
+                full[q * pad:(q + 1) * pad].copy_(peer)
+        return _PeerHandle(self, hdl, cur)
+
+
+class _PeerHandle:
+    def __init__(self, ex, hdl, cur):
+        self.ex, self.hdl, self.cur = ex, hdl, cur
+
+    def wait(self):
+        self.cur.wait_stream(self.ex.side)
+        self.hdl.barrier(channel=1, timeout_ms=PeerExchange.BARRIER_TIMEOUT_MS)   # every pull has finished
+
+
 class ShardedGraph:
     """One rank's share of a row-partitioned graph: the in-edges of its destination rows.
 
     ``idx`` holds GLOBAL source ids, ``off`` the offsets of the rank's own rows (CSC of the shard).
     """
 
-    def __init__(self, part, rank, idx, off, w, backend=None, group=None):
+    def __init__(self, part, rank, idx, off, w, backend=None, group=None, exchange="nccl"):
         self.part, self.rank, self.group = part, rank, group
         self.backend = backend or DeviceBackend()
+        self.exchange = PeerExchange(part, rank, group) if exchange == "peer" else None
         self.lo, self.hi = part.range(rank)
         self.n_local = self.hi - self.lo
         if off.numel() != self.n_local + 1:
@@ -110,12 +172,15 @@ class ShardedGraph:
 
         ``x`` holds the rank's rows of the feature matrix (``n_local`` rows, or ``pad`` rows with
         a zero tail).  ``gather(shard, full)`` fills ``full`` with every rank's padded shard and
-        returns a handle whose ``wait()`` orders later work after it; the default is an
-        asynchronous ``all_gather_into_tensor`` on the process group."""
+        returns a handle whose ``wait()`` orders later work after it; the default is the
+        copy-engine peer exchange (``exchange="peer"``) or an asynchronous
+        ``all_gather_into_tensor`` on the process group (``exchange="nccl"``)."""
         f = x.shape[1]
         xp = self._padded(x)
         full = self._gather_buffer(f, xp)
-        if gather is None:
+        if gather is None and self.exchange is not None:
+            handle = self.exchange.start(xp, full)
+        elif gather is None:
             handle = dist.all_gather_into_tensor(full, xp, group=self.group, async_op=True)
         else:
             handle = gather(xp, full)

@@ -1,0 +1,110 @@
+"""Multi-GPU leg of ``bench.py``: the SpMM sweep on the same graph, split into one contiguous
+destination-row shard per rank (strong scaling).  Launched by torchrun, one process per GPU."""
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from . import dist as jd
+
+
+def run(args):
+    import bench  # the repository's bench.py (graph builder, clock sampler, workload description)
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    widths = bench.WIDTHS
+    # every rank generates the same graph from the seed and keeps its own rows
+    csc, n = bench.build_graph(dev, args.scale, args.edge_factor)
+    nnz = csc.row_indices.numel()
+    part = jd.RowPartition(n, world)
+    exchange = os.environ.get("JG_EXCHANGE", "peer")
+    g = jd.ShardedGraph(part, rank, *jd.shard_rows(csc.row_indices, csc.column_offset, csc.edge_weight, part, rank),
+                        exchange=exchange)
+    local_nnz = g.interior[0].numel() + g.halo[0].numel()
+    del csc
+    torch.cuda.empty_cache()
+    gen = torch.Generator(device=dev); gen.manual_seed(bench.SEED + 17 * rank)
+    xs = {}
+    for f in widths:
+        # features live in the shard buffer the peers pull from: no staging copy per aggregation
+        x = g.exchange.buffer(f, dev)[0] if g.exchange is not None else torch.zeros((part.pad, f), device=dev)
+        x.zero_()
+        x[: g.n_local] = torch.randn((g.n_local, f), generator=gen, device=dev)
+        xs[f] = x
+
+    def step():
+        for f in widths:
+            g.aggregate(xs[f])
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize(); dist.barrier()
+    sampler = bench.ClockSampler(dev.index)
+    if rank == 0:
+        sampler.start()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+    t0.record()
+    for _ in range(args.steps):
+        step()
+    t1.record()
+    torch.cuda.synchronize(); dist.barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = torch.tensor([t0.elapsed_time(t1) / args.steps], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_step = float(ms.item())
+
+    # end to end: the rank's feature rows from pinned host memory, its output rows back to the host
+    hx = {f: torch.empty((part.pad, f)).pin_memory() for f in widths}
+    hy = {f: torch.empty((g.n_local, f)).pin_memory() for f in widths}
+    for f in widths:
+        hx[f].copy_(xs[f])
+    e2e_ms = float("nan")
+    if not args.skip_e2e:
+        def e2e_step():
+            for f in widths:
+                xs[f].copy_(hx[f], non_blocking=True)
+                hy[f].copy_(g.aggregate(xs[f]), non_blocking=True)
+        e2e_steps = max(1, min(args.steps, 5))
+        e2e_step(); torch.cuda.synchronize(); dist.barrier()
+        t0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        t1.record(); torch.cuda.synchronize(); dist.barrier()
+        e = torch.tensor([t0.elapsed_time(t1) / e2e_steps], device=dev)
+        dist.all_reduce(e, op=dist.ReduceOp.MAX)
+        e2e_ms = float(e.item())
+    imb = torch.tensor([float(local_nnz)], device=dev)
+    dist.all_reduce(imb, op=dist.ReduceOp.MAX)
+
+    if rank == 0:
+        peak, peak_kind = bench.measured_peaks()
+        total_bytes = sum(bench.alg_bytes(nnz, n, f) for f in widths)
+        achieved = total_bytes / world / ms_step / 1e6
+        io_bytes = sum(n * f * 4 for f in widths)
+        line = {
+            "metric": "spmm_edge_feat_per_s", "value": nnz * sum(widths) / (ms_step * 1e-3), "unit": "edge*feat/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": bench.workload_config(args.scale, args.edge_factor, n, nnz, world),
+            "gflops": 2.0 * nnz * sum(widths) / (ms_step * 1e-3) / 1e9,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_kind": peak_kind, "kernel": "aggregate_rows_kernel",
+                         "note": "per-GPU algorithmic bytes (no-reuse gather model / world size) over the whole step, "
+                                 "shard exchange included"},
+            "cpu_baseline": None,
+            "e2e": {"value": nnz * sum(widths) / (e2e_ms * 1e-3), "unit": "edge*feat/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes},
+            "gpu_launches": args.steps * len(widths) * 4,
+            "max_shard_nnz_over_mean": float(imb.item()) * world / nnz,
+            "exchange": ("fp32 feature shards pulled from peer memory over NVLink by the copy engines, overlapped with "
+                         "interior rows" if exchange == "peer" else
+                         "one NCCL all-gather of fp32 feature shards per aggregation"),
+            "clocks": clocks,
+        }
+        print(json.dumps(line))
+    dist.destroy_process_group()

@@ -71,7 +71,7 @@ def test_accumulate_mode(cuda, oracle):
         assert np.array_equal(out.cpu().numpy(), base + fresh.cpu().numpy())     # old + sum, one rounding
 
 
-def nccl_worker(rank, world, port, n, E, f, q):
+def nccl_worker(rank, world, port, n, E, f, q, exchange):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
     from jittorgeometric_b200 import dist as jd
@@ -84,9 +84,11 @@ def nccl_worker(rank, world, port, n, E, f, q):
         part = jd.RowPartition(n, world)
         lo, hi = part.range(rank)
         t = lambda a: torch.from_numpy(a).cuda()
-        g = jd.ShardedGraph(part, rank, *jd.shard_rows(t(idx), t(off), t(w), part, rank))
+        g = jd.ShardedGraph(part, rank, *jd.shard_rows(t(idx), t(off), t(w), part, rank), exchange=exchange)
         y = g.aggregate(t(x[lo:hi].copy()))
+        y2 = g.aggregate(t(x[lo:hi].copy()))          # second exchange reuses the shard buffers
         torch.cuda.synchronize()
+        assert torch.equal(y, y2)
         q.put((rank, lo, hi, y.cpu().numpy()))
     except Exception as exc:
         q.put((rank, -1, -1, repr(exc)))
@@ -95,8 +97,9 @@ def nccl_worker(rank, world, port, n, E, f, q):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("exchange", ["nccl", "peer"])
 @pytest.mark.timeout(300)
-def test_nccl_ranks(cuda, oracle):
+def test_nccl_ranks(cuda, oracle, exchange):
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs at least two GPUs")
@@ -105,7 +108,7 @@ def test_nccl_ranks(cuda, oracle):
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=nccl_worker, args=(r, world, port, n, E, f, q)) for r in range(world)]
+    procs = [ctx.Process(target=nccl_worker, args=(r, world, port, n, E, f, q, exchange)) for r in range(world)]
     for p in procs:
         p.start()
     got = [q.get(timeout=240) for _ in range(world)]
