@@ -164,6 +164,20 @@ int jg_gat_aggregate_f32(float* out, const float* h, const float* a_src, const f
                          const int32_t* off, int64_t n_nodes, int64_t n_edges, int64_t heads, int64_t dim, float slope,
                          void* workspace, size_t workspace_bytes, jg_stream_t stream);
 
+/* ------------------------------------------------------------------ dense feature transform
+ * out[n_rows, m] = act(x[n_rows, k] * W + bias) with TF32 products and fp32 accumulation on the
+ * tcgen05 tensor cores; replaces the `x @ self.weight` (+ bias, + ReLU) of the reference layers
+ * (nn/conv/gcn_conv.py:95,100-101, nn/conv/gat_conv.py:86-87).  `wt` is the weight TRANSPOSED,
+ * [m, k] row-major; bias may be NULL; relu != 0 clamps at zero.  Supported when k % 4 == 0 and
+ * m <= 256 (jg_gemm_tf32_supported); other shapes return JG_EUNSUPPORTED.  The workspace
+ * (jg_gemm_tf32_workspace_bytes) receives an error word: jg_gemm_tf32_status synchronises the
+ * stream and returns JG_ETIMEOUT if a bounded wait inside the kernel ran out. */
+int jg_gemm_tf32_supported(int64_t n_rows, int64_t k, int64_t m);
+size_t jg_gemm_tf32_workspace_bytes(void);
+int jg_gemm_tf32(float* out, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k, int64_t m,
+                 int relu, void* workspace, size_t workspace_bytes, jg_stream_t stream);
+int jg_gemm_tf32_status(const void* workspace, jg_stream_t stream);
+
 /* Aggregation for callers that cannot allocate.  No counterpart in the reference: this entry
  * point exists for hosts that must not call cudaMalloc (or any allocating routine) once they
  * run - a serving process with a memory pool fixed at start-up, a plugin inside a process that

@@ -1,0 +1,344 @@
+// Dense feature transform  H = act(X * W + b)  on the 5th-generation tensor cores (sm_100a).
+//
+// Replaces the `x @ self.weight` of the reference layers (nn/conv/gcn_conv.py:95,
+// nn/conv/gat_conv.py:86), which Jittor hands to cuBLAS.  It is the only tensor-core kernel of
+// the path; shapes are skinny (K, M <= a few hundred, N in the millions), so the bound is HBM
+// (read X once, write H once) and the point of tcgen05 is to keep the SMs out of the way.
+//
+//   X  [N, K]  fp32 row-major      (A operand, K-major)
+//   Wt [M, K]  fp32 row-major      (B operand, K-major: the layer weight transposed once)
+//   H  [N, M]  fp32                (TF32 products, fp32 accumulation in TMEM)
+//
+// One CTA per SM, persistent over 128-row tiles.  Warp 0 (one lane) is the TMA producer: 128x32
+// tiles of X and Mx32 tiles of Wt land in a 4-stage shared-memory ring with the 128-byte swizzle
+// (cp.async.bulk.tensor, CTA-local, no cluster multicast; out-of-range rows and the K tail are
+// zero-filled by TMA).  Warp 1 (one lane) issues tcgen05.mma.kind::tf32 (128 x M x 8 per
+// instruction) into one of two TMEM accumulators and commits ring slots / accumulators to
+// mbarriers.  Warps 2-5 are the epilogue: tcgen05.ld of the accumulator quadrant their warp id
+// gives them access to, bias and ReLU fused, 64-byte row segments stored to H, overlapping the
+// next tile's MMAs.  Every mbarrier wait is bounded; a wait that runs out sets an error word that
+// the host reads, and the CTA still frees its TMEM and exits.
+#include "common.cuh"
+
+#include <cuda.h>
+
+namespace jg {
+
+constexpr int kGemmThreads = 192;   // 6 warps: producer, MMA, 4 epilogue
+constexpr int kTileM = 128;         // rows of X per tile
+constexpr int kTileK = 32;          // tf32 elements per 128-byte swizzle row
+constexpr int kStages = 4;
+constexpr uint32_t kWaitSpins = 1u << 22;  // bounded mbarrier wait (about a second with back-off)
+
+struct GemmParams {
+    float* out;
+    const float* bias;
+    int64_t n_rows;
+    int32_t k, m;       // reduction length, output width
+    int32_t m_pad;      // TMEM columns per accumulator (power of two >= 32)
+    int32_t relu;
+    int32_t n_tiles, k_blocks;
+    int32_t* error;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait for the phase with the given parity; false when it ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t spin = 0; spin < kWaitSpins; spin++) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if (spin > 64) __nanosleep(spin > 4096 ? 256 : 32);
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows 128 B apart, 8-row groups
+// 1024 B apart (stride byte offset), descriptor version 1.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+
+struct GemmSmem {
+    uint64_t full[kStages], empty[kStages];
+    uint64_t acc_full[2], acc_empty[2];
+    uint32_t tmem_base;
+    int32_t abort;
+};
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, GemmParams p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // ring first (1024-byte aligned stages), control block after it
+    unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t a_bytes = kTileM * kTileK * 4;                    // 16 KB
+    const uint32_t b_rows = (uint32_t)((p.m + 15) / 16 * 16);   // MMA N: a multiple of 16 when M = 128
+    const uint32_t b_bytes = ((b_rows * kTileK * 4) + 1023) / 1024 * 1024;
+    const uint32_t stage_bytes = a_bytes + b_bytes;
+    GemmSmem* ctl = reinterpret_cast<GemmSmem*>(ring + kStages * stage_bytes);
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(&ctl->full[s], 1);
+            mbar_init(&ctl->empty[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&ctl->acc_full[b], 1);
+            mbar_init(&ctl->acc_empty[b], 4);   // one arrival per epilogue warp
+        }
+        ctl->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) {  // TMEM: two accumulators of m_pad columns
+        const uint32_t cols = (uint32_t)(2 * p.m_pad);
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)), "r"(cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctl->tmem_base;
+    volatile int32_t* abort_flag = &ctl->abort;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int tile = blockIdx.x; tile < p.n_tiles && !*abort_flag; tile += gridDim.x) {
+                for (int kb = 0; kb < p.k_blocks; kb++, it++) {
+                    const int s = it % kStages;
+                    const uint32_t round = it / kStages;
+                    if (round > 0 && !mbar_wait(&ctl->empty[s], (round - 1) & 1)) { *abort_flag = 1; break; }
+                    unsigned char* a_dst = ring + s * stage_bytes;
+                    mbar_expect_tx(&ctl->full[s], a_bytes + b_rows * kTileK * 4);
+                    tma_load_2d(a_dst, &map_x, kb * kTileK, tile * kTileM, &ctl->full[s]);
+                    tma_load_2d(a_dst + a_bytes, &map_w, kb * kTileK, 0, &ctl->full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            // instruction descriptor: D fp32, A/B tf32, both K-major, N = b_rows, M = 128
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((b_rows >> 3) << 17) | ((kTileM >> 4) << 24);
+            uint32_t it = 0, local_tile = 0;
+            for (int tile = blockIdx.x; tile < p.n_tiles && !*abort_flag; tile += gridDim.x, local_tile++) {
+                const int b = local_tile & 1;
+                const uint32_t use = local_tile >> 1;
+                if (use > 0 && !mbar_wait(&ctl->acc_empty[b], (use - 1) & 1)) { *abort_flag = 1; break; }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(b * p.m_pad);
+                bool ok = true;
+                for (int kb = 0; kb < p.k_blocks; kb++, it++) {
+                    const int s = it % kStages;
+                    if (!mbar_wait(&ctl->full[s], (it / kStages) & 1)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(ring + s * stage_bytes);
+                    const uint64_t da = umma_desc(a_addr), db = umma_desc(a_addr + a_bytes);
+#pragma unroll
+                    for (int k = 0; k < kTileK / 8; k++)   // 8 tf32 = 32 bytes per instruction: +2 in 16-byte units
+                        umma_tf32(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&ctl->empty[s]);            // slot free once these MMAs have read it
+                }
+                if (!ok) { *abort_flag = 1; break; }
+                umma_commit(&ctl->acc_full[b]);             // accumulator complete
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (warps 2..5)
+        const int quad = warp & 3;                          // TMEM lanes this warp may read: 32*quad ..
+        uint32_t local_tile = 0;
+        for (int tile = blockIdx.x; tile < p.n_tiles && !*abort_flag; tile += gridDim.x, local_tile++) {
+            const int b = local_tile & 1;
+            if (!mbar_wait(&ctl->acc_full[b], (local_tile >> 1) & 1)) { *abort_flag = 1; break; }
+            tc_fence_after();
+            const int64_t row = (int64_t)tile * kTileM + quad * 32 + lane;
+            const uint32_t taddr = tmem_base + (uint32_t)(b * p.m_pad) + ((uint32_t)(quad * 32) << 16);
+            for (int c0 = 0; c0 < p.m; c0 += 16) {
+                float v[16];
+                tmem_ld16(taddr + (uint32_t)c0, v);
+                if (row < p.n_rows) {
+                    float* o = p.out + row * p.m + c0;
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        if (c0 + i < p.m) {
+                            float r = v[i] + (p.bias ? __ldg(p.bias + c0 + i) : 0.f);
+                            v[i] = (p.relu && r < 0.f) ? 0.f : r;
+                        }
+                    }
+                    if (c0 + 16 <= p.m && (p.m % 4) == 0) {
+#pragma unroll
+                        for (int i = 0; i < 4; i++)
+                            __stcs(reinterpret_cast<float4*>(o) + i, make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
+                    } else {
+                        for (int i = 0; i < 16 && c0 + i < p.m; i++) o[i] = v[i];
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctl->acc_empty[b]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        const uint32_t cols = (uint32_t)(2 * p.m_pad);
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(cols) : "memory");
+    }
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(p.error, 1);
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup: no link-time
+// dependency on the driver library.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 2-D fp32 tensor [rows, cols] row-major, box [box_rows, 32 columns], 128-byte swizzle, zero fill.
+static int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t cols, int box_rows) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    JG_CHECK_ARG(enc, JG_ECUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 4};
+    cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    JG_CHECK_ARG(r == CUDA_SUCCESS, JG_ECUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return JG_OK;
+}
+
+}  // namespace jg
+
+using namespace jg;
+
+extern "C" {
+
+int jg_gemm_tf32_supported(int64_t n_rows, int64_t k, int64_t m) {
+    return n_rows > 0 && k > 0 && m > 0 && k % 4 == 0 && m <= 256 && n_rows < ((int64_t)1 << 31) * 64;
+}
+
+size_t jg_gemm_tf32_workspace_bytes(void) { return 256; }
+
+int jg_gemm_tf32(float* out, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k, int64_t m,
+                 int relu, void* workspace, size_t workspace_bytes, jg_stream_t stream) {
+    JG_CHECK_ARG(n_rows >= 0 && k > 0 && m > 0, JG_EINVAL, "gemm_tf32: bad size");
+    if (n_rows == 0) return JG_OK;
+    JG_CHECK_ARG(out && x && wt, JG_EINVAL, "gemm_tf32: null pointer");
+    if (!jg_gemm_tf32_supported(n_rows, k, m)) {
+        set_error("gemm_tf32: needs k %% 4 == 0 (16-byte row pitch for TMA) and m <= 256 (got k=%lld, m=%lld)", (long long)k, (long long)m);
+        return JG_EUNSUPPORTED;
+    }
+    JG_CHECK_ARG((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wt) | reinterpret_cast<uintptr_t>(out)) % 16 == 0,
+                 JG_EINVAL, "gemm_tf32: x, wt and out must be 16-byte aligned");
+    JG_CHECK_ARG(workspace && workspace_bytes >= 256, JG_EWORKSPACE, "gemm_tf32: workspace missing");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int b_rows = (int)((m + 15) / 16 * 16);
+    CUtensorMap map_x, map_w;
+    int rc = make_map(&map_x, x, n_rows, k, kTileM);
+    if (rc != JG_OK) return rc;
+    rc = make_map(&map_w, wt, m, k, b_rows);
+    if (rc != JG_OK) return rc;
+    GemmParams p = {};
+    p.out = out; p.bias = bias; p.n_rows = n_rows; p.k = (int32_t)k; p.m = (int32_t)m; p.relu = relu;
+    int pad = 32;
+    while (pad < b_rows) pad *= 2;
+    p.m_pad = pad;
+    p.n_tiles = (int32_t)((n_rows + kTileM - 1) / kTileM);
+    p.k_blocks = (int32_t)((k + kTileK - 1) / kTileK);
+    p.error = static_cast<int32_t*>(workspace);
+    JG_CUDA(cudaMemsetAsync(p.error, 0, sizeof(int32_t), st));
+    const size_t a_bytes = kTileM * kTileK * 4;
+    const size_t b_bytes = ((size_t)b_rows * kTileK * 4 + 1023) / 1024 * 1024;
+    const size_t smem = 1024 + kStages * (a_bytes + b_bytes) + sizeof(GemmSmem) + 64;
+    static size_t attr_done[64] = {0};
+    int dev = 0;
+    JG_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && attr_done[dev] < smem) {
+        JG_CUDA(cudaFuncSetAttribute(gemm_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024)));
+        attr_done[dev] = 227 * 1024;
+    }
+    int grid = sm_count();
+    if (grid > p.n_tiles) grid = p.n_tiles;
+    gemm_tf32_kernel<<<grid, kGemmThreads, smem, st>>>(map_x, map_w, p);
+    JG_LAUNCH_CHECK();
+    return JG_OK;
+}
+
+/* Reads the error word a finished jg_gemm_tf32 call left in its workspace (synchronises the
+ * stream): JG_OK, or JG_ETIMEOUT when a bounded wait inside the kernel ran out. */
+int jg_gemm_tf32_status(const void* workspace, jg_stream_t stream) {
+    JG_CHECK_ARG(workspace, JG_EINVAL, "gemm_tf32_status: null workspace");
+    int32_t err = 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    JG_CUDA(cudaMemcpyAsync(&err, workspace, sizeof(err), cudaMemcpyDeviceToHost, st));
+    JG_CUDA(cudaStreamSynchronize(st));
+    if (err) {
+        set_error("gemm_tf32: a bounded wait inside the kernel ran out");
+        return JG_ETIMEOUT;
+    }
+    return JG_OK;
+}
+
+}  // extern "C"

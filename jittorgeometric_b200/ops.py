@@ -15,7 +15,7 @@ from .data import CSC, CSR
 
 __all__ = ["aggregateWithWeight", "segment_aggregate", "SpmmPlan", "cootocsr", "cootocsc", "gcn_norm_csc_csr",
            "SpmmCsr", "SpmmCoo", "ScatterToEdge", "ScatterToVertex", "EdgeSoftmax", "gat_aggregate",
-           "gat_aggregate_supported", "gcn_norm_coo"]
+           "gat_aggregate_supported", "gcn_norm_coo", "linear_tf32", "linear_tf32_supported"]
 
 DEFAULT_CHUNK = int(os.environ.get("JG_SPMM_CHUNK", "1024"))
 
@@ -410,4 +410,30 @@ def gat_aggregate(h, a_src, a_dst, csc, heads, slope=0.2):
     check(lib().jg_gat_aggregate_f32(ptr(out), ptr(h), ptr(a_src), ptr(a_dst), ptr(idx), ptr(off), n, idx.numel(),
                                      int(heads), dim, float(slope), ptr(ws), ws.numel(), stream_for(h)),
           "jg_gat_aggregate_f32")
+    return out
+
+
+# ------------------------------------------------------------------------------ dense transform
+def linear_tf32_supported(n_rows, k, m):
+    return bool(lib().jg_gemm_tf32_supported(int(n_rows), int(k), int(m)))
+
+
+def linear_tf32(x, weight, bias=None, relu=False, weight_t=None, check_status=False):
+    """``act(x @ weight + bias)`` on the tcgen05 tensor cores (TF32 products, fp32 accumulation):
+    the dense feature transform of the layers (nn/conv/gcn_conv.py:95, nn/conv/gat_conv.py:86).
+    ``weight`` is ``[k, m]`` as the layers store it; ``weight_t`` may carry its cached transpose.
+    Forward only.  ``check_status=True`` synchronises and raises if a bounded wait in the kernel
+    ran out."""
+    x = _as_f32(x, "x")
+    n, k = x.shape
+    m = weight.shape[1]
+    wt = weight_t if weight_t is not None else _as_f32(weight, "weight").t().contiguous()
+    b = None if bias is None else _as_f32(bias, "bias")
+    out = torch.empty((n, m), dtype=torch.float32, device=x.device)
+    ws = workspace(lib().jg_gemm_tf32_workspace_bytes(), x.device)
+    st = stream_for(x)
+    check(lib().jg_gemm_tf32(ptr(out), ptr(x), ptr(wt), ptr(b), n, k, m, 1 if relu else 0, ptr(ws), ws.numel(), st),
+          "jg_gemm_tf32")
+    if check_status:
+        check(lib().jg_gemm_tf32_status(ptr(ws), st), "jg_gemm_tf32_status")
     return out
