@@ -77,15 +77,17 @@ class ClockSampler:
 
 
 def build_graph(device, scale=21, edge_factor=32):
-    """CSC of the gcn-normalised symmetric R-MAT graph (setup, outside every timed region)."""
+    """CSC of the gcn-normalised symmetric R-MAT graph (setup, outside every timed region).
+    On a GPU the library's own fused gcn_norm + conversion builds it; the CPU-only reference arm
+    (no CUDA device) builds the same layout with torch tensor operations."""
     from jittorgeometric_b200 import synth
     import jittorgeometric_b200 as jg
     ei, n = synth.rmat_graph(scale, edge_factor, SEED, device=device)
-    # self-loops appended after the edge list, unit weights, symmetric normalisation
-    # (nn/conv/gcn_conv.py:18-37); destination-major with a stable sort keeps list order per column
+    if torch.device(device).type == "cuda":
+        csc, _ = jg.gcn_norm_csc_csr(ei, None, n, want_csr=False)
+        return jg.CSC(csc.row_indices.clone(), csc.column_offset, csc.edge_weight.clone()), n
     loops = torch.arange(n, dtype=torch.int32, device=device)
     src = torch.cat([ei[0], loops]); dst = torch.cat([ei[1], loops])
-    del ei
     deg = torch.bincount(dst.long(), minlength=n).to(torch.float32)
     dis = (1.0 / deg.double().sqrt()).float()
     order = torch.sort(dst.long(), stable=True)[1]
@@ -298,6 +300,8 @@ def main():
     ap.add_argument("--scale", type=int, default=21)
     ap.add_argument("--edge-factor", type=int, default=32)
     ap.add_argument("--cpu-budget", type=float, default=16.0, help="seconds of CPU-baseline work (0 = skip)")
+    ap.add_argument("--workload", default="spmm", choices=["spmm", "convert", "gat", "gcn", "gemm"],
+                    help="spmm (default, the headline) or one of the other hot-path workloads (1 GPU; gcn also N > 1)")
     ap.add_argument("--widths", default=None, help="comma-separated subset of the sweep (profiling runs)")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
@@ -309,6 +313,9 @@ def main():
         return run_reference(args)
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    if args.workload != "spmm":
+        import bench_extra
+        return bench_extra.run(args)
     if args.gpus == 1:
         return run_single(args)
     from jittorgeometric_b200 import dist_bench

@@ -1,0 +1,245 @@
+"""Secondary workloads of ``bench.py`` (``--workload convert|gat|gcn|gemm``): the other
+configurations of the hot path, each printed as one JSON line in the same shape as the headline.
+They are measurement helpers for the kernels that the default SpMM sweep does not exercise."""
+import json
+import os
+import time
+
+import torch
+
+import bench
+
+
+def _events():
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def _time(fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = _events()
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / steps
+
+
+def _line(args, metric, unit, value, ms, workload, roofline, extra):
+    line = {"metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": workload},
+            "roofline": roofline}
+    line.update(extra)
+    print(json.dumps(line))
+
+
+def run_convert(args):
+    """COO -> CSC + CSR with fused gcn_norm (R-MAT scale 24, edge factor 16, shuffled, unit weights)."""
+    import jittorgeometric_b200 as jg
+    from jittorgeometric_b200 import synth
+    dev = torch.device("cuda", 0)
+    scale = args.scale if args.scale != 21 else 24
+    ei, n = synth.rmat_coo_shuffled(scale, 16, bench.SEED + 2, device=dev)
+    E0 = ei.shape[1]
+    out = {}
+
+    def step():
+        out["csc"], out["csr"] = jg.gcn_norm_csc_csr(ei, None, n)
+
+    sampler = bench.ClockSampler(0); sampler.start()
+    ms = _time(step, args.steps, args.warmup)
+    clocks = sampler.stop()
+    E = out["csc"].row_indices.numel()
+    peak, kind = bench.measured_peaks()
+    passes = (max(n - 1, 1).bit_length() + 7) // 8
+    alg = 2 * (E0 * 8 + E * 8 + n * 12)          # both formats: read COO, write index + weight, degree/offset/dis
+    cpu = None
+    if args.cpu_budget > 0:
+        import numpy as np
+        import oracle as O
+        sub = min(E0, 1 << 22)
+        sei = ei[:, :sub].cpu().numpy()
+        t0 = time.perf_counter()
+        nei, nw = O.gcn_norm(sei, None, n)
+        impl = "ref" if O.have_ref() else "port"
+        O.coo_to_csc(nei, nw, n, impl); O.coo_to_csr(nei, nw, n, impl)
+        dt = time.perf_counter() - t0
+        cpu = {"value": sub / dt, "unit": "edge/s", "cores": 1, "kind": "reference" if impl == "ref" else "port",
+               "sample": f"first {sub} input edges of the same list, gcn_norm (C restatement) + the reference's "
+                         f"cootocsc and cootocsr bodies, {dt:.1f} s, single thread"}
+    _line(args, "coo_to_csc_csr_edges_per_s", "edge/s", E0 / (ms * 1e-3), ms,
+          f"gcn_norm + COO->CSC + COO->CSR: R-MAT scale {scale}, edge factor 16, {E0} shuffled input edges, "
+          f"{n} nodes, unit weights, int32; entry order bit-exact with the reference",
+          {"bound": "hbm", "achieved": alg / ms / 1e6, "peak": peak, "unit": "GB/s", "frac": alg / ms / 1e6 / peak,
+           "traffic": None, "peak_kind": kind, "kernel": "sort_scatter_kernel",
+           "note": f"algorithmic bytes = one read of the COO and one write of index+weight per format; the radix sort "
+                   f"takes {passes} passes per format at about 28 B per entry and pass"},
+          {"cpu_baseline": cpu, "entries": E, "gpu_launches": args.steps * (2 * passes * 5 + 10), "clocks": clocks})
+
+
+def run_gat(args):
+    """One attention layer, 8 heads x 8: 232,965 nodes, ~114.6M in-edges, input width 602."""
+    import jittorgeometric_b200 as jg
+    from jittorgeometric_b200 import synth
+    dev = torch.device("cuda", 0)
+    n, E_target, H, D, fin = 232965, 114_600_000, 8, 8, 602
+    if args.scale != 21:                       # reduced instance for profiling runs
+        n, E_target = n >> (21 - args.scale), E_target >> (21 - args.scale)
+    rows, off = synth.lognormal_degree_csc(n, E_target, bench.SEED + 3, device=dev)
+    csc = jg.CSC(rows, off, None)
+    E = rows.numel()
+    x = torch.randn((n, fin), device=dev, generator=torch.Generator(device=dev).manual_seed(5))
+    W = synth.glorot((fin, H * D), 7, dev)
+    a = synth.glorot((2 * H * D, 1), 8, dev)
+    a_src, a_dst = a[: H * D, 0].reshape(H, D).contiguous(), a[H * D:, 0].reshape(H, D).contiguous()
+    h = torch.relu(x @ W)
+    out = {}
+
+    def edge_phase():
+        out["y"] = jg.gat_aggregate(h, a_src, a_dst, csc, H)
+
+    def layer():
+        hh = torch.relu(x @ W)          # 602 is not a multiple of 4: the library GEMM takes this shape
+        out["y"] = jg.gat_aggregate(hh, a_src, a_dst, csc, H)
+
+    sampler = bench.ClockSampler(0); sampler.start()
+    ms_edge = _time(edge_phase, args.steps, args.warmup)
+    ms_layer = _time(layer, args.steps, args.warmup)
+    clocks = sampler.stop()
+    peak, kind = bench.measured_peaks()
+    C = H * D
+    alg = 4 * E + 4 * (n + 1) + 4 * n * C + 4 * n * C        # indices, offsets, h once, out once (h fits in L2)
+    gather = E * (4 + 4 * C)
+    cpu = None
+    if args.cpu_budget > 0:
+        import oracle as O
+        r = min(n, 2000)
+        o_np, i_np = off[: r + 1].cpu().numpy(), rows[: int(off[r])].cpu().numpy()
+        hn = h.cpu().numpy()
+        t0 = time.perf_counter()
+        # the reference's unfused pipeline needs rows of h for every destination < r and every source: pass full h
+        import numpy as np
+        o_full = np.concatenate([o_np, np.full(n - r, o_np[-1], np.int32)])
+        O.gat_unfused(hn[:, :8].copy(), a.cpu().numpy()[:16, 0], i_np, o_full, "ref" if O.have_ref() else "port")
+        dt = time.perf_counter() - t0
+        cpu = {"value": int(off[r]) / dt, "unit": "edge/s", "cores": 1, "kind": "reference" if O.have_ref() else "port",
+               "sample": f"in-edges of the first {r} destinations ({int(off[r])} edges), ONE head of width 8 through the "
+                         f"reference's unfused op-by-op pipeline, {dt:.1f} s, single thread (x8 heads for the full layer)"}
+    _line(args, "gat_edge_phase_edges_per_s", "edge/s", E / (ms_edge * 1e-3), ms_edge,
+          f"attention layer 8 heads x 8, LeakyReLU 0.2: {n} nodes, {E} in-edges (log-normal degrees, mean "
+          f"{E / n:.0f}), input width {fin}; fused logits + softmax + aggregation over CSC",
+          {"bound": "hbm", "achieved": alg / ms_edge / 1e6, "peak": peak, "unit": "GB/s", "frac": alg / ms_edge / 1e6 / peak,
+           "traffic": None, "peak_kind": kind, "kernel": "gat_aggregate_kernel",
+           "note": "compulsory bytes only: h (%.0f MB) fits in L2, so the kernel is L2/LSU-bound, not HBM-bound; "
+                   "effective gather bandwidth is reported beside it" % (n * C * 4 / 1e6)},
+          {"gather_gbs": gather / ms_edge / 1e6, "layer_ms": ms_layer, "cpu_baseline": cpu,
+           "gpu_launches": args.steps, "clocks": clocks})
+
+
+def run_gemm(args):
+    """Dense transform of one shard of the partitioned-GCN workload: 8.4M x 128 -> 128."""
+    import jittorgeometric_b200 as jg
+    dev = torch.device("cuda", 0)
+    n = (1 << 23) if args.scale == 21 else (1 << args.scale)
+    res = {}
+    peak, kind = bench.measured_peaks()
+    for k, m in ((128, 128), (128, 64), (256, 64)):
+        x = torch.randn((n, k), device=dev)
+        w = torch.randn((k, m), device=dev) / k ** 0.5
+        wt = w.t().contiguous()
+        ms = _time(lambda: jg.linear_tf32(x, w, weight_t=wt), args.steps, args.warmup)
+        ms_lib = _time(lambda: x @ w, args.steps, args.warmup)
+        b = 4 * n * (k + m)
+        res[f"{k}x{m}"] = {"ms": ms, "gbs": b / ms / 1e6, "frac_of_hbm_peak": b / ms / 1e6 / peak,
+                           "tflops": 2.0 * n * k * m / ms / 1e9, "library_fp32_ms": ms_lib}
+        del x
+    first = res["128x128"]
+    _line(args, "dense_transform_rows_per_s", "row/s", n / (first["ms"] * 1e-3), first["ms"],
+          f"dense feature transform H = X W, {n} rows, TF32 products with fp32 accumulation on tcgen05; shapes 128->128, "
+          "128->64, 256->64",
+          {"bound": "hbm", "achieved": first["gbs"], "peak": peak, "unit": "GB/s", "frac": first["frac_of_hbm_peak"],
+           "traffic": None, "peak_kind": kind, "kernel": "gemm_tf32_kernel",
+           "note": "skinny GEMM: read X once, write H once; tensor-pipe utilisation is reported by ncu"},
+          {"shapes": res, "dtype": "tf32", "gpu_launches": args.steps * 3})
+
+
+def run_gcn(args):
+    """Two-layer GCN forward (width 128 -> 128 -> 64) on one GPU or row-partitioned over N GPUs."""
+    import torch.distributed as dist
+    import jittorgeometric_b200 as jg
+    from jittorgeometric_b200 import dist as jd, synth
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    scale = 22 if args.scale == 21 else args.scale
+    ei, n = synth.rmat_graph(scale, 8, bench.SEED + 4, device=dev)      # 8 undirected pairs per node -> factor 16 directed
+    csc, _ = jg.gcn_norm_csc_csr(ei, None, n, want_csr=False)
+    del ei
+    nnz = csc.row_indices.numel()
+    part = jd.RowPartition(n, world)
+    W1, W2 = synth.glorot((128, 128), 1, dev), synth.glorot((128, 64), 2, dev)
+    W1t, W2t = W1.t().contiguous(), W2.t().contiguous()
+    b1, b2 = torch.zeros(128, device=dev), torch.zeros(64, device=dev)
+    if world > 1:
+        g = jd.ShardedGraph(part, rank, *jd.shard_rows(csc.row_indices, csc.column_offset, csc.edge_weight, part, rank),
+                            exchange=os.environ.get("JG_EXCHANGE", "peer"))
+        del csc
+        n_local = g.n_local
+        h1buf, h2buf = g.exchange.buffer(128, dev)[0], g.exchange.buffer(64, dev)[0]
+    else:
+        plan = jg.SpmmPlan(csc.column_offset, nnz)
+        n_local = n
+    x = torch.randn((n_local, 128), device=dev, generator=torch.Generator(device=dev).manual_seed(9 + rank))
+
+    def forward():
+        if world > 1:
+            # transform straight into the shard buffer the peers pull from, then aggregate
+            h1buf[:n_local] = jg.linear_tf32(x, W1, weight_t=W1t)
+            z1 = torch.relu(g.aggregate(h1buf) + b1)
+            h2buf[:n_local] = jg.linear_tf32(z1, W2, weight_t=W2t)
+            return g.aggregate(h2buf) + b2
+        h1 = jg.linear_tf32(x, W1, weight_t=W1t)
+        z1 = torch.relu(jg.segment_aggregate(h1, csc.row_indices, csc.column_offset, csc.edge_weight, plan=plan) + b1)
+        h2 = jg.linear_tf32(z1, W2, weight_t=W2t)
+        return jg.segment_aggregate(h2, csc.row_indices, csc.column_offset, csc.edge_weight, plan=plan) + b2
+
+    for _ in range(args.warmup):
+        forward()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    a, b = _events()
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(args.steps):
+        forward()
+    b.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([a.elapsed_time(b) / args.steps], device=dev)
+    if world > 1:
+        dist.barrier()
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    if rank == 0:
+        peak, kind = bench.measured_peaks()
+        alg = sum(nnz * (8 + 4 * f) + 4 * (n + 1) + 4 * n * f for f in (128, 64)) + 4 * n * (128 + 128) + 4 * n * (128 + 64)
+        args.gpus = world
+        _line(args, "gcn_forward_edge_feat_per_s", "edge*feat/s", nnz * (128 + 64) / (ms * 1e-3), ms,
+              f"2-layer GCN forward 128->128->64 (TF32 transform, fp32 aggregation): R-MAT scale {scale}, {n} nodes, "
+              f"{nnz} directed edges incl. self-loops, gcn_norm weights; {world} destination-row shard(s)",
+              {"bound": "hbm", "achieved": alg / world / ms / 1e6, "peak": peak, "unit": "GB/s",
+               "frac": alg / world / ms / 1e6 / peak, "traffic": None, "peak_kind": kind, "kernel": "aggregate_rows_kernel",
+               "note": "per-GPU algorithmic bytes of both aggregations and both transforms over the whole forward"},
+              {"gpu_launches": args.steps * (6 if world == 1 else 10)})
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run(args):
+    return {"convert": run_convert, "gat": run_gat, "gemm": run_gemm, "gcn": run_gcn}[args.workload](args)

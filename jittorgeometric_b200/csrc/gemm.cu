@@ -14,7 +14,7 @@
 // (cp.async.bulk.tensor, CTA-local, no cluster multicast; out-of-range rows and the K tail are
 // zero-filled by TMA).  Warp 1 (one lane) issues tcgen05.mma.kind::tf32 (128 x M x 8 per
 // instruction) into one of two TMEM accumulators and commits ring slots / accumulators to
-// mbarriers.  Warps 2-5 are the epilogue: tcgen05.ld of the accumulator quadrant their warp id
+// mbarriers.  Warps 2-9 are the epilogue: tcgen05.ld of the accumulator quadrant their warp id
 // gives them access to, bias and ReLU fused, 64-byte row segments stored to H, overlapping the
 // next tile's MMAs.  Every mbarrier wait is bounded; a wait that runs out sets an error word that
 // the host reads, and the CTA still frees its TMEM and exits.
@@ -24,7 +24,8 @@
 
 namespace jg {
 
-constexpr int kGemmThreads = 192;   // 6 warps: producer, MMA, 4 epilogue
+constexpr int kGemmThreads = 320;   // 10 warps: producer, MMA, 8 epilogue
+constexpr int kEpiWarps = 8;
 constexpr int kTileM = 128;         // rows of X per tile
 constexpr int kTileK = 32;          // tf32 elements per 128-byte swizzle row
 constexpr int kStages = 4;
@@ -105,6 +106,30 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
     for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
 }
 
+// 32 accumulator columns of this lane's row: two 16-column loads in flight, one wait.  The second
+// load is skipped (zeros) when it would reach past the accumulator's columns.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32], bool second) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    if (second) {
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+            : "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+              "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr + 16));
+    } else {
+#pragma unroll
+        for (int i = 16; i < 32; i++) r[i] = 0;
+    }
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
 struct GemmSmem {
     uint64_t full[kStages], empty[kStages];
     uint64_t acc_full[2], acc_empty[2];
@@ -131,7 +156,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(&ctl->acc_full[b], 1);
-            mbar_init(&ctl->acc_empty[b], 4);   // one arrival per epilogue warp
+            mbar_init(&ctl->acc_empty[b], kEpiWarps);   // one arrival per epilogue warp
         }
         ctl->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -192,8 +217,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             }
         }
     } else {
-        // ---------------------------------------------------------------- epilogue (warps 2..5)
-        const int quad = warp & 3;                          // TMEM lanes this warp may read: 32*quad ..
+        // ---------------------------------------------------------------- epilogue (warps 2..9)
+        // A warp may read the TMEM lanes 32*(warp % 4) .. +31; two warps share a quadrant and take
+        // alternate 32-column chunks.
+        const int quad = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const bool full_chunks = (p.m % 32) == 0;
         uint32_t local_tile = 0;
         for (int tile = blockIdx.x; tile < p.n_tiles && !*abort_flag; tile += gridDim.x, local_tile++) {
             const int b = local_tile & 1;
@@ -201,24 +230,28 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             tc_fence_after();
             const int64_t row = (int64_t)tile * kTileM + quad * 32 + lane;
             const uint32_t taddr = tmem_base + (uint32_t)(b * p.m_pad) + ((uint32_t)(quad * 32) << 16);
-            for (int c0 = 0; c0 < p.m; c0 += 16) {
-                float v[16];
-                tmem_ld16(taddr + (uint32_t)c0, v);
+            for (int c0 = half * 32; c0 < p.m; c0 += 64) {
+                float v[32];
+                tmem_ld32(taddr + (uint32_t)c0, v, c0 + 16 < (int)b_rows);
                 if (row < p.n_rows) {
                     float* o = p.out + row * p.m + c0;
+                    if (p.bias) {
 #pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        if (c0 + i < p.m) {
-                            float r = v[i] + (p.bias ? __ldg(p.bias + c0 + i) : 0.f);
-                            v[i] = (p.relu && r < 0.f) ? 0.f : r;
-                        }
+                        for (int i = 0; i < 32; i++)
+                            if (full_chunks || c0 + i < p.m) v[i] += __ldg(p.bias + c0 + i);
                     }
-                    if (c0 + 16 <= p.m && (p.m % 4) == 0) {
+                    if (p.relu) {
 #pragma unroll
-                        for (int i = 0; i < 4; i++)
+                        for (int i = 0; i < 32; i++) v[i] = fmaxf(v[i], 0.f);
+                    }
+                    if (full_chunks) {
+#pragma unroll
+                        for (int i = 0; i < 8; i++)
                             __stcs(reinterpret_cast<float4*>(o) + i, make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
                     } else {
-                        for (int i = 0; i < 16 && c0 + i < p.m; i++) o[i] = v[i];
+#pragma unroll
+                        for (int i = 0; i < 32; i++)
+                            if (c0 + i < p.m) o[i] = v[i];
                     }
                 }
             }
