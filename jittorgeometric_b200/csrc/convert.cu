@@ -22,8 +22,8 @@
 namespace jg {
 
 constexpr int kSortThreads = 256;
-constexpr int kSortItems = 16;
-constexpr int kSortTile = kSortThreads * kSortItems;  // 4096 entries per tile
+constexpr int kSortItems = 8;
+constexpr int kSortTile = kSortThreads * kSortItems;  // 2048 entries per tile
 constexpr int kSortWarps = kSortThreads / 32;
 constexpr int kRadix = 256;
 
@@ -199,8 +199,8 @@ struct SortDst {
 };
 
 // Stable scatter of one tile.  Element order inside the tile is (warp, round, lane), which is the
-// order of the source list because warp w reads the contiguous range [w*512, (w+1)*512).
-__global__ void __launch_bounds__(kSortThreads) sort_scatter_kernel(SortSrc s, SortDst d, int shift, int from_idx,
+// order of the source list because warp w reads one contiguous range of 32 * kSortItems entries.
+__global__ void __launch_bounds__(kSortThreads, 4) sort_scatter_kernel(SortSrc s, SortDst d, int shift, int from_idx,
                                                                     const int* __restrict__ matrix, int64_t n_tiles) {
     extern __shared__ __align__(16) unsigned char smem[];
     int* s_whist = reinterpret_cast<int*>(smem);                       // [kSortWarps][kRadix]

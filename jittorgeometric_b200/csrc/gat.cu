@@ -46,25 +46,28 @@ struct Softmax4 {
         l = 0.f;
         acc = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    // one more term with logit z and value row x
+    // one more term with logit z (log2 units) and value row x.  The running maximum rises only a
+    // handful of times per segment, so the rescale sits behind a branch and the common path is one
+    // exp2 and four FMAs.
     __device__ __forceinline__ void push(float z, const float4& x) {
-        const float d = z - m;
-        const float e = __expf(-fabsf(d));
-        const bool up = d > 0.f;
-        const float sc = up ? e : 1.f;   // rescale of what is already accumulated
-        const float p = up ? 1.f : e;    // weight of the new term
-        m = up ? z : m;
-        l = fmaf(l, sc, p);
-        acc.x = fmaf(acc.x, sc, p * x.x);
-        acc.y = fmaf(acc.y, sc, p * x.y);
-        acc.z = fmaf(acc.z, sc, p * x.z);
-        acc.w = fmaf(acc.w, sc, p * x.w);
+        if (z > m) {
+            const float sc = exp2f(m - z);   // m = -inf at the start: everything accumulated (nothing) scales to 0
+            l *= sc;
+            acc.x *= sc; acc.y *= sc; acc.z *= sc; acc.w *= sc;
+            m = z;
+        }
+        const float p = exp2f(z - m);
+        l += p;
+        acc.x = fmaf(p, x.x, acc.x);
+        acc.y = fmaf(p, x.y, acc.y);
+        acc.z = fmaf(p, x.z, acc.z);
+        acc.w = fmaf(p, x.w, acc.w);
     }
     // merge another partial state (either may be empty: m == -inf, l == 0)
     __device__ __forceinline__ void merge(float m2, float l2, const float4& a2) {
         const float mn = fmaxf(m, m2);
-        const float s1 = (m == -INFINITY) ? 0.f : __expf(m - mn);
-        const float s2 = (m2 == -INFINITY) ? 0.f : __expf(m2 - mn);
+        const float s1 = (m == -INFINITY) ? 0.f : exp2f(m - mn);
+        const float s2 = (m2 == -INFINITY) ? 0.f : exp2f(m2 - mn);
         l = l * s1 + l2 * s2;
         acc.x = acc.x * s1 + a2.x * s2;
         acc.y = acc.y * s1 + a2.y * s2;
@@ -83,8 +86,13 @@ __global__ void __launch_bounds__(kGatBlock) gat_aggregate_kernel(GatArgs a) {
     const int lane = lane_id();
     const int sub = lane / G;
     const int fl = lane % G;
-    const float4 as4 = __ldg(reinterpret_cast<const float4*>(a.a_src) + fl);
-    const float4 ad4 = __ldg(reinterpret_cast<const float4*>(a.a_dst) + fl);
+    // attention vectors scaled by log2(e): the positive factor commutes with leaky_relu, and the
+    // softmax can then use exp2 directly
+    constexpr float kLog2e = 1.4426950408889634f;
+    float4 as4 = __ldg(reinterpret_cast<const float4*>(a.a_src) + fl);
+    float4 ad4 = __ldg(reinterpret_cast<const float4*>(a.a_dst) + fl);
+    as4.x *= kLog2e; as4.y *= kLog2e; as4.z *= kLog2e; as4.w *= kLog2e;
+    ad4.x *= kLog2e; ad4.y *= kLog2e; ad4.z *= kLog2e; ad4.w *= kLog2e;
     const char* hb = reinterpret_cast<const char*>(a.h) + fl * 16;
     for (;;) {
         unsigned long long t = 0;
@@ -121,7 +129,7 @@ __global__ void __launch_bounds__(kGatBlock) gat_aggregate_kernel(GatArgs a) {
 #pragma unroll
                     for (int o = 1; o < DL; o <<= 1) ss += __shfl_xor_sync(kFull, ss, o);
                     float z = ss + sd;
-                    z = z > 0.f ? z : z * a.slope;
+                    z = fmaxf(z, z * a.slope);   // leaky_relu for a slope in [0, 1]
                     if (ok[u]) st.push(z, x[u]);
                 }
             }
@@ -214,6 +222,7 @@ int jg_gat_aggregate_f32(float* out, const float* h, const float* a_src, const f
     }
     JG_CHECK_ARG((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(a_src) |
                   reinterpret_cast<uintptr_t>(a_dst)) % 16 == 0, JG_EINVAL, "gat_aggregate: pointers must be 16-byte aligned");
+    JG_CHECK_ARG(slope >= 0.f && slope <= 1.f, JG_EINVAL, "gat_aggregate: slope must lie in [0, 1]");
     JG_CHECK_ARG(workspace && workspace_bytes >= 256, JG_EWORKSPACE, "gat_aggregate: workspace missing");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     GatArgs a = {out, h, a_src, a_dst, idx, off, n_nodes, slope, static_cast<unsigned long long*>(workspace)};
