@@ -308,6 +308,7 @@ def main():
     global WIDTHS
     if args.widths:
         WIDTHS = tuple(int(v) for v in args.widths.split(","))
+    args.width_list = WIDTHS
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         return run_reference(args)

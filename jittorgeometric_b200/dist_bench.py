@@ -16,7 +16,8 @@ def run(args):
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", device_id=dev)
-    widths = bench.WIDTHS
+    widths = tuple(getattr(args, "width_list", bench.WIDTHS))
+    bench.WIDTHS = widths
     # every rank generates the same graph from the seed and keeps its own rows
     csc, n = bench.build_graph(dev, args.scale, args.edge_factor)
     nnz = csc.row_indices.numel()
