@@ -98,6 +98,15 @@ def build_graph(device, scale=21, edge_factor=32):
     return jg.CSC(src.contiguous(), off, w.contiguous()), n
 
 
+def measured_traffic(args, nnz):
+    """DRAM bytes (read + write) of the four aggregation launches of one default step, from the ncu
+    capture summarised in profiles/aggregate_rows_kernel_spmm_sweep_scale21.md; None for any other
+    workload size."""
+    if args.scale == 21 and args.edge_factor == 32 and tuple(WIDTHS) == (32, 64, 128, 256) and nnz == 125548660:
+        return 2757975808 + 273128704 + 6993170176 + 572856320 + 19284060160 + 1193964288 + 51131966464 + 2204640768
+    return None
+
+
 def alg_bytes(nnz, n, f):
     """No-reuse gather model: per nonzero its index, weight and one f-wide source row;
     offsets read once; every output row written once."""
@@ -280,8 +289,12 @@ def run_single(args):
         "gflops": 2.0 * value / 1e9,
         "sweep": sweep,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind, "kernel": "aggregate_kernel",
-                     "note": "algorithmic bytes = no-reuse gather model summed over the four widths / summed launch time"},
+                     "traffic": measured_traffic(args, nnz), "peak_kind": peak_kind, "kernel": "aggregate_rows_kernel",
+                     "note": "algorithmic bytes = no-reuse gather model (index + weight + one source row per nonzero, "
+                             "output written once) summed over the four widths / summed launch time; hub source rows "
+                             "hit in L2, so real DRAM traffic (`traffic`, ncu, summed over the same four launches) is "
+                             "lower and the model figure can exceed the HBM peak",
+                     "dram_gbs": (measured_traffic(args, nnz) or 0) / kernel_ms / 1e6 or None},
         "cpu_baseline": cpu,
         "e2e": {"value": nnz * sum(WIDTHS) / (e2e_ms * 1e-3), "unit": "edge*feat/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes},

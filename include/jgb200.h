@@ -157,12 +157,16 @@ int jg_edge_softmax_bwd_f32(float* dx, const float* grad, const float* y, const 
  * reference layer: a_src / a_dst are the two halves of its [2C, 1] attention vector).
  * h and out are [n_nodes, heads*dim]; a_src, a_dst are [heads, dim].  Supported shapes are
  * reported by jg_gat_aggregate_supported (heads*dim/4 and dim/4 powers of two, heads*dim <= 128);
- * others return JG_EUNSUPPORTED and are served by the per-edge operators above. */
+ * others return JG_EUNSUPPORTED and are served by the per-edge operators above.
+ * `plan` (optional, from jg_gat_plan_build; depends only on `off`) lists the destinations longest
+ * segment first, which keeps the grid from ending on one warp that walks a hub alone. */
+size_t jg_gat_plan_bytes(int64_t n_nodes);
+int jg_gat_plan_build(const int32_t* off, int64_t n_nodes, void* plan, size_t plan_bytes, jg_stream_t stream);
 size_t jg_gat_aggregate_workspace_bytes(int64_t n_nodes, int64_t n_edges, int64_t heads, int64_t dim);
 int jg_gat_aggregate_supported(int64_t heads, int64_t dim);
 int jg_gat_aggregate_f32(float* out, const float* h, const float* a_src, const float* a_dst, const int32_t* idx,
                          const int32_t* off, int64_t n_nodes, int64_t n_edges, int64_t heads, int64_t dim, float slope,
-                         void* workspace, size_t workspace_bytes, jg_stream_t stream);
+                         const void* plan, void* workspace, size_t workspace_bytes, jg_stream_t stream);
 
 /* ------------------------------------------------------------------ dense feature transform
  * out[n_rows, m] = act(x[n_rows, k] * W + bias) with TF32 products and fp32 accumulation on the

@@ -8,7 +8,8 @@
 //   alpha  = softmax of the logits over the in-edges of each destination, per head
 //   out[v,hd,:] = sum_e alpha(e,hd) * h[src(e),hd,:]
 //
-// One warp per destination.  G = C/4 lanes cover one source row with a 128-bit load each, 32/G
+// One warp per destination (a whole CTA for destinations with 4096 or more in-edges, its warps
+// taking alternate tiles and their partial states merged in warp order).  G = C/4 lanes cover one source row with a 128-bit load each, 32/G
 // edges are processed side by side.  The source score is recomputed from the gathered row (four
 // FMAs and a shuffle) instead of being fetched from a second array: that saves one 32-byte sector
 // per edge, and the row has to be read anyway.  The softmax is the running-maximum ("online")
@@ -21,6 +22,7 @@
 namespace jg {
 
 constexpr int kGatBlock = 256;
+constexpr int kHubBucket = 13;   // degree buckets 13..32: at least 2^12 = 4096 in-edges, walked by a whole CTA
 
 struct GatArgs {
     float* out;
@@ -32,7 +34,41 @@ struct GatArgs {
     int64_t n;
     float slope;
     unsigned long long* ticket;
+    const int32_t* order;      // destinations in processing order (longest segments first), or null
+    const int32_t* hub_count;  // [1] how many leading entries of `order` have >= 4096 in-edges
 };
+
+// ---- processing order: destinations bucketed by floor(log2(degree)), largest bucket first, so the
+// longest segments start earliest and the grid does not end on one warp walking a hub alone.
+struct GatPlanView {
+    int32_t* counts;   // [64] bucket sizes, then bucket cursors
+    int32_t* order;    // [n]
+};
+__device__ __forceinline__ int degree_bucket(int32_t deg) { return deg <= 0 ? 0 : 32 - __clz(deg); }  // 0..32
+
+__global__ void gat_plan_count_kernel(const int32_t* __restrict__ off, int64_t n, int32_t* counts) {
+    __shared__ int s_cnt[33];
+    if (threadIdx.x < 33) s_cnt[threadIdx.x] = 0;
+    __syncthreads();
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < n; v += (int64_t)gridDim.x * blockDim.x)
+        atomicAdd(&s_cnt[degree_bucket(off[v + 1] - off[v])], 1);
+    __syncthreads();
+    if (threadIdx.x < 33 && s_cnt[threadIdx.x]) atomicAdd(&counts[threadIdx.x], s_cnt[threadIdx.x]);
+}
+// one thread: bucket start positions, largest bucket first
+__global__ void gat_plan_starts_kernel(int32_t* counts) {
+    int run = 0;
+    for (int b = 32; b >= 0; b--) {
+        const int c = counts[b];
+        counts[b] = run;
+        run += c;
+        if (b == kHubBucket) counts[40] = run;   // destinations with at least 4096 in-edges
+    }
+}
+__global__ void gat_plan_fill_kernel(const int32_t* __restrict__ off, int64_t n, int32_t* cursors, int32_t* order) {
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < n; v += (int64_t)gridDim.x * blockDim.x)
+        order[atomicAdd(&cursors[degree_bucket(off[v + 1] - off[v])], 1)] = (int32_t)v;
+}
 
 __device__ __forceinline__ float dot4(const float4& a, const float4& b) {
     return fmaf(a.w, b.w, fmaf(a.z, b.z, fmaf(a.y, b.y, a.x * b.x)));
@@ -78,13 +114,83 @@ struct Softmax4 {
 };
 
 // G lanes per row (C = 4*G), DL = D/4 lanes per head; both powers of two, DL <= G <= 32.
+// Walks the 32-edge tiles first_tile, first_tile + tile_stride, ... of segment [s, e).
 template <int G, int DL>
-__global__ void __launch_bounds__(kGatBlock) gat_aggregate_kernel(GatArgs a) {
+__device__ __forceinline__ void gat_walk(const GatArgs& a, int32_t s, int32_t e, int first_tile, int tile_stride,
+                                         const float4& as4, float sd, const char* hb, Softmax4& st) {
     constexpr int EPS = 32 / G;
     constexpr int C = 4 * G;
     constexpr int B = 4;  // steps per batch
     const int lane = lane_id();
     const int sub = lane / G;
+    for (int64_t j0 = (int64_t)s + 32 * (int64_t)first_tile; j0 < e; j0 += 32 * (int64_t)tile_stride) {
+        int my_idx = 0;
+        if (j0 + lane < e) my_idx = ld_stream(a.idx + j0 + lane);
+        const int cnt = (int)((e - j0) < 32 ? (e - j0) : 32);
+        for (int tt = 0; tt < cnt; tt += EPS * B) {
+            float4 x[B];
+            bool ok[B];
+#pragma unroll
+            for (int u = 0; u < B; u++) {
+                const int k = tt + u * EPS + sub;
+                const int src = __shfl_sync(kFull, my_idx, k & 31);
+                ok[u] = k < cnt;
+                x[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (ok[u]) x[u] = __ldg(reinterpret_cast<const float4*>(hb + (size_t)(unsigned)src * (C * 4)));
+            }
+#pragma unroll
+            for (int u = 0; u < B; u++) {
+                float ss = dot4(x[u], as4);
+#pragma unroll
+                for (int o = 1; o < DL; o <<= 1) ss += __shfl_xor_sync(kFull, ss, o);
+                float z = ss + sd;
+                z = fmaxf(z, z * a.slope);   // leaky_relu for a slope in [0, 1]
+                if (ok[u]) st.push(z, x[u]);
+            }
+        }
+    }
+}
+
+// Merges the lane groups that took alternate edges (fixed order) and writes the output row.
+template <int G>
+__device__ __forceinline__ void gat_finish(const GatArgs& a, int64_t v, Softmax4& st) {
+    constexpr int C = 4 * G;
+    const int lane = lane_id();
+    const int sub = lane / G, fl = lane % G;
+#pragma unroll
+    for (int o = G; o < 32; o <<= 1) {
+        const float m2 = __shfl_xor_sync(kFull, st.m, o);
+        const float l2 = __shfl_xor_sync(kFull, st.l, o);
+        float4 a2;
+        a2.x = __shfl_xor_sync(kFull, st.acc.x, o);
+        a2.y = __shfl_xor_sync(kFull, st.acc.y, o);
+        a2.z = __shfl_xor_sync(kFull, st.acc.z, o);
+        a2.w = __shfl_xor_sync(kFull, st.acc.w, o);
+        // both partners apply the merge in the same operand order, so they agree bit for bit
+        if (lane & o) {
+            Softmax4 other;
+            other.m = m2; other.l = l2; other.acc = a2;
+            other.merge(st.m, st.l, st.acc);
+            st = other;
+        } else {
+            st.merge(m2, l2, a2);
+        }
+    }
+    if (sub == 0) {
+        const float inv = st.l > 0.f ? 1.f / st.l : 0.f;
+        __stcs(reinterpret_cast<float4*>(a.out + (size_t)v * C) + fl,
+               make_float4(st.acc.x * inv, st.acc.y * inv, st.acc.z * inv, st.acc.w * inv));
+    }
+}
+
+template <int G, int DL>
+__global__ void __launch_bounds__(kGatBlock) gat_aggregate_kernel(GatArgs a) {
+    constexpr int C = 4 * G;
+    constexpr int W = kGatBlock / 32;
+    __shared__ float s_state[W][32][6];
+    __shared__ unsigned long long s_ticket;
+    const int lane = lane_id();
+    const int warp = threadIdx.x / 32;
     const int fl = lane % G;
     // attention vectors scaled by log2(e): the positive factor commutes with leaky_relu, and the
     // softmax can then use exp2 directly
@@ -94,71 +200,51 @@ __global__ void __launch_bounds__(kGatBlock) gat_aggregate_kernel(GatArgs a) {
     as4.x *= kLog2e; as4.y *= kLog2e; as4.z *= kLog2e; as4.w *= kLog2e;
     ad4.x *= kLog2e; ad4.y *= kLog2e; ad4.z *= kLog2e; ad4.w *= kLog2e;
     const char* hb = reinterpret_cast<const char*>(a.h) + fl * 16;
+    const int64_t n_hub = a.order ? (int64_t)a.hub_count[0] : 0;
+
+    // ---- hubs: one CTA per destination, its warps take alternate 32-edge tiles
     for (;;) {
-        unsigned long long t = 0;
-        if (lane == 0) t = atomicAdd(a.ticket, 1ull);
-        t = __shfl_sync(kFull, t, 0);
-        if ((int64_t)t >= a.n) break;
-        const int64_t v = (int64_t)t;
+        __syncthreads();
+        if (threadIdx.x == 0) s_ticket = atomicAdd(a.ticket + 1, 1ull);
+        __syncthreads();
+        const unsigned long long t = s_ticket;
+        if ((int64_t)t >= n_hub) break;
+        const int64_t v = a.order[t];
         const int32_t s = a.off[v], e = a.off[v + 1];
-        // destination score of this lane's head
         const float4 hv = __ldg(reinterpret_cast<const float4*>(hb + (size_t)v * (C * 4)));
         float sd = dot4(hv, ad4);
 #pragma unroll
         for (int o = 1; o < DL; o <<= 1) sd += __shfl_xor_sync(kFull, sd, o);
         Softmax4 st;
         st.init();
-        for (int32_t j0 = s; j0 < e; j0 += 32) {
-            int my_idx = 0;
-            if (j0 + lane < e) my_idx = ld_stream(a.idx + j0 + lane);
-            const int cnt = min(32, e - j0);
-            for (int tt = 0; tt < cnt; tt += EPS * B) {
-                float4 x[B];
-                bool ok[B];
-#pragma unroll
-                for (int u = 0; u < B; u++) {
-                    const int k = tt + u * EPS + sub;
-                    const int src = __shfl_sync(kFull, my_idx, k & 31);
-                    ok[u] = k < cnt;
-                    x[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (ok[u]) x[u] = __ldg(reinterpret_cast<const float4*>(hb + (size_t)(unsigned)src * (C * 4)));
-                }
-#pragma unroll
-                for (int u = 0; u < B; u++) {
-                    float ss = dot4(x[u], as4);
-#pragma unroll
-                    for (int o = 1; o < DL; o <<= 1) ss += __shfl_xor_sync(kFull, ss, o);
-                    float z = ss + sd;
-                    z = fmaxf(z, z * a.slope);   // leaky_relu for a slope in [0, 1]
-                    if (ok[u]) st.push(z, x[u]);
-                }
+        gat_walk<G, DL>(a, s, e, warp, W, as4, sd, hb, st);
+        float* mine = s_state[warp][lane];
+        mine[0] = st.m; mine[1] = st.l; mine[2] = st.acc.x; mine[3] = st.acc.y; mine[4] = st.acc.z; mine[5] = st.acc.w;
+        __syncthreads();
+        if (warp == 0) {
+            for (int w = 1; w < W; w++) {   // fixed order: warp 0's state, then 1, 2, ...
+                const float* o = s_state[w][lane];
+                st.merge(o[0], o[1], make_float4(o[2], o[3], o[4], o[5]));
             }
+            gat_finish<G>(a, v, st);
         }
-        // merge the lane groups that took alternate edges, in a fixed order
+    }
+    // ---- everything else: one warp per destination
+    for (;;) {
+        unsigned long long t = 0;
+        if (lane == 0) t = atomicAdd(a.ticket, 1ull);
+        t = __shfl_sync(kFull, t, 0) + (unsigned long long)n_hub;
+        if ((int64_t)t >= a.n) break;
+        const int64_t v = a.order ? (int64_t)a.order[t] : (int64_t)t;
+        const int32_t s = a.off[v], e = a.off[v + 1];
+        const float4 hv = __ldg(reinterpret_cast<const float4*>(hb + (size_t)v * (C * 4)));
+        float sd = dot4(hv, ad4);
 #pragma unroll
-        for (int o = G; o < 32; o <<= 1) {
-            const float m2 = __shfl_xor_sync(kFull, st.m, o);
-            const float l2 = __shfl_xor_sync(kFull, st.l, o);
-            float4 a2;
-            a2.x = __shfl_xor_sync(kFull, st.acc.x, o);
-            a2.y = __shfl_xor_sync(kFull, st.acc.y, o);
-            a2.z = __shfl_xor_sync(kFull, st.acc.z, o);
-            a2.w = __shfl_xor_sync(kFull, st.acc.w, o);
-            // both partners must apply the merge in the same operand order to agree bit for bit
-            if (lane & o) {
-                Softmax4 other;
-                other.m = m2; other.l = l2; other.acc = a2;
-                other.merge(st.m, st.l, st.acc);
-                st = other;
-            } else {
-                st.merge(m2, l2, a2);
-            }
-        }
-        if (sub == 0) {
-            const float inv = st.l > 0.f ? 1.f / st.l : 0.f;
-            float4 o4 = make_float4(st.acc.x * inv, st.acc.y * inv, st.acc.z * inv, st.acc.w * inv);
-            __stcs(reinterpret_cast<float4*>(a.out + (size_t)v * C) + fl, o4);
-        }
+        for (int o = 1; o < DL; o <<= 1) sd += __shfl_xor_sync(kFull, sd, o);
+        Softmax4 st;
+        st.init();
+        gat_walk<G, DL>(a, s, e, 0, 1, as4, sd, hb, st);
+        gat_finish<G>(a, v, st);
     }
 }
 
@@ -195,6 +281,34 @@ using namespace jg;
 
 extern "C" {
 
+size_t jg_gat_plan_bytes(int64_t n_nodes) {
+    if (n_nodes < 0) return 0;
+    Carver c(nullptr);
+    c.take<int32_t>(64);
+    c.take<int32_t>(n_nodes);
+    return c.total();
+}
+
+int jg_gat_plan_build(const int32_t* off, int64_t n_nodes, void* plan, size_t plan_bytes, jg_stream_t stream) {
+    JG_CHECK_ARG(off && plan && n_nodes >= 0, JG_EINVAL, "gat_plan_build: bad argument");
+    JG_CHECK_ARG(plan_bytes >= jg_gat_plan_bytes(n_nodes), JG_EWORKSPACE, "gat_plan_build: plan buffer too small");
+    JG_CHECK_ARG(n_nodes < INT32_MAX, JG_ESHAPE, "gat_plan_build: sizes beyond int32");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    Carver c(plan);
+    int32_t* counts = c.take<int32_t>(64);
+    int32_t* order = c.take<int32_t>(n_nodes);
+    JG_CUDA(cudaMemsetAsync(counts, 0, 64 * sizeof(int32_t), st));
+    if (n_nodes == 0) return JG_OK;
+    const int grid = sm_count() * 4;
+    gat_plan_count_kernel<<<grid, 256, 0, st>>>(off, n_nodes, counts);
+    JG_LAUNCH_CHECK();
+    gat_plan_starts_kernel<<<1, 1, 0, st>>>(counts);
+    JG_LAUNCH_CHECK();
+    gat_plan_fill_kernel<<<grid, 256, 0, st>>>(off, n_nodes, counts, order);
+    JG_LAUNCH_CHECK();
+    return JG_OK;
+}
+
 size_t jg_gat_aggregate_workspace_bytes(int64_t n_nodes, int64_t n_edges, int64_t heads, int64_t dim) {
     (void)n_nodes; (void)n_edges; (void)heads; (void)dim;
     return 256;
@@ -209,7 +323,7 @@ int jg_gat_aggregate_supported(int64_t heads, int64_t dim) {
 
 int jg_gat_aggregate_f32(float* out, const float* h, const float* a_src, const float* a_dst, const int32_t* idx,
                          const int32_t* off, int64_t n_nodes, int64_t n_edges, int64_t heads, int64_t dim, float slope,
-                         void* workspace, size_t workspace_bytes, jg_stream_t stream) {
+                         const void* plan, void* workspace, size_t workspace_bytes, jg_stream_t stream) {
     JG_CHECK_ARG(n_nodes >= 0 && n_edges >= 0 && heads > 0 && dim > 0, JG_EINVAL, "gat_aggregate: bad size");
     if (n_nodes == 0) return JG_OK;
     JG_CHECK_ARG(out && h && a_src && a_dst && off, JG_EINVAL, "gat_aggregate: null pointer");
@@ -225,8 +339,13 @@ int jg_gat_aggregate_f32(float* out, const float* h, const float* a_src, const f
     JG_CHECK_ARG(slope >= 0.f && slope <= 1.f, JG_EINVAL, "gat_aggregate: slope must lie in [0, 1]");
     JG_CHECK_ARG(workspace && workspace_bytes >= 256, JG_EWORKSPACE, "gat_aggregate: workspace missing");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    GatArgs a = {out, h, a_src, a_dst, idx, off, n_nodes, slope, static_cast<unsigned long long*>(workspace)};
-    JG_CUDA(cudaMemsetAsync(a.ticket, 0, sizeof(unsigned long long), st));
+    GatArgs a = {out, h, a_src, a_dst, idx, off, n_nodes, slope, static_cast<unsigned long long*>(workspace), nullptr, nullptr};
+    if (plan) {
+        Carver c(const_cast<void*>(plan));
+        a.hub_count = c.take<int32_t>(64) + 40;
+        a.order = c.take<int32_t>(n_nodes);
+    }
+    JG_CUDA(cudaMemsetAsync(a.ticket, 0, 2 * sizeof(unsigned long long), st));
     const int g = (int)(heads * dim / 4), dl = (int)(dim / 4);
     switch (g) {
         case 1: return launch_gat_g<1>(dl, a, st);

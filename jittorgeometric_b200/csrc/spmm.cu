@@ -369,24 +369,22 @@ __global__ void __launch_bounds__(kBlock) aggregate_any_kernel(AggArgs a) {
     }
 }
 
-// Adds the partial rows of every hub in piece order and writes the hub's output row.
+// Adds the partial rows of every hub in piece order and writes the hub's output row: one thread per
+// (hub, column), consecutive threads on consecutive columns.
 __global__ void __launch_bounds__(kBlock) hub_fixup_kernel(AggArgs a) {
-    const int lane = lane_id();
-    const int warps = (gridDim.x * blockDim.x) / 32;
-    const int wid = (blockIdx.x * blockDim.x + threadIdx.x) / 32;
-    const int n_hubs = a.hdr->n_hubs;
+    const int64_t n_hubs = a.hdr->n_hubs;
     const int chunk = a.hdr->chunk;
     const int64_t F = a.f;
-    for (int h = wid; h < n_hubs; h += warps) {
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n_hubs * F; t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t h = t / F, c = t - h * F;
         const int row = a.hub_row[h];
         const int deg = a.off[row + 1] - a.off[row];
         const int pieces = (deg + chunk - 1) / chunk;
-        const float* p = a.partial + (size_t)a.hub_first[h] * F;
-        for (int64_t c = lane; c < F; c += 32) {
-            float acc = p[c];
-            for (int k = 1; k < pieces; k++) acc = __fadd_rn(acc, p[(size_t)k * F + c]);
-            a.out[(size_t)row * F + c] = a.accumulate ? __fadd_rn(a.out[(size_t)row * F + c], acc) : acc;
-        }
+        const float* p = a.partial + (size_t)a.hub_first[h] * F + c;
+        float acc = p[0];
+        for (int k = 1; k < pieces; k++) acc = __fadd_rn(acc, p[(size_t)k * F]);
+        float* o = a.out + (size_t)row * F + c;
+        *o = a.accumulate ? __fadd_rn(*o, acc) : acc;
     }
 }
 

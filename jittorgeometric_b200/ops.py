@@ -406,9 +406,15 @@ def gat_aggregate(h, a_src, a_dst, csc, heads, slope=0.2):
     if off.numel() != n + 1:
         raise RuntimeError("gat_aggregate: column_offset does not match h")
     out = torch.empty_like(h)
+    plan = getattr(csc, "_jg_gat_plan", None)
+    if plan is None or plan[0] != off.data_ptr():
+        buf = workspace(lib().jg_gat_plan_bytes(n), h.device)
+        check(lib().jg_gat_plan_build(ptr(off), n, ptr(buf), buf.numel(), stream_for(h)), "jg_gat_plan_build")
+        plan = (off.data_ptr(), buf)
+        csc._jg_gat_plan = plan
     ws = workspace(lib().jg_gat_aggregate_workspace_bytes(n, idx.numel(), heads, dim), h.device)
     check(lib().jg_gat_aggregate_f32(ptr(out), ptr(h), ptr(a_src), ptr(a_dst), ptr(idx), ptr(off), n, idx.numel(),
-                                     int(heads), dim, float(slope), ptr(ws), ws.numel(), stream_for(h)),
+                                     int(heads), dim, float(slope), ptr(plan[1]), ptr(ws), ws.numel(), stream_for(h)),
           "jg_gat_aggregate_f32")
     return out
 

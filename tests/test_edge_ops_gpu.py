@@ -133,6 +133,27 @@ def test_fused_attention(cuda, oracle, heads, dim):
     assert np.array_equal(got, again)
 
 
+def test_fused_attention_hub_destinations(cuda, oracle):
+    """Destinations with 4096 or more in-edges take the path where a whole thread block shares one
+    segment; 9000- and 20000-edge hubs, next to ordinary and empty destinations."""
+    rng = np.random.default_rng(77)
+    n, heads, dim = 3000, 8, 8
+    dst = np.concatenate([rng.integers(10, n, size=20000), np.full(9000, 3), np.full(20000, 1500), np.full(4096, 7)])
+    src = rng.integers(0, n, size=len(dst))
+    order = np.argsort(dst, kind="stable")
+    idx = src[order].astype(np.int32)
+    off = np.concatenate([[0], np.cumsum(np.bincount(dst, minlength=n))]).astype(np.int32)
+    csc = cuda.CSC(dev(idx), dev(off), None)
+    hfeat = np.maximum(rng.standard_normal((n, heads * dim)), 0).astype(np.float32)
+    a_src = (rng.standard_normal((heads, dim)) * 0.5).astype(np.float32)
+    a_dst = (rng.standard_normal((heads, dim)) * 0.5).astype(np.float32)
+    got = host(cuda.gat_aggregate(dev(hfeat), dev(a_src), dev(a_dst), csc, heads))
+    want = oracle.gat_aggregate(hfeat, a_src, a_dst, idx, off, heads, dim)
+    assert np.abs(got - want).max() / np.abs(hfeat).max() <= 1e-5
+    assert not got[0].any() and not got[9].any()          # destinations without in-edges
+    assert np.array_equal(got, host(cuda.gat_aggregate(dev(hfeat), dev(a_src), dev(a_dst), csc, heads)))
+
+
 def test_fused_attention_equals_reference_pipeline(cuda, oracle):
     """Single head: the fused kernel against the reference's own op-by-op pipeline run on the CPU."""
     rng = np.random.default_rng(5)
