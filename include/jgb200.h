@@ -172,8 +172,9 @@ int jg_gat_aggregate_f32(float* out, const float* h, const float* a_src, const f
  * out[n_rows, m] = act(x[n_rows, k] * W + bias) with TF32 products and fp32 accumulation on the
  * tcgen05 tensor cores; replaces the `x @ self.weight` (+ bias, + ReLU) of the reference layers
  * (nn/conv/gcn_conv.py:95,100-101, nn/conv/gat_conv.py:86-87).  `wt` is the weight TRANSPOSED,
- * [m, k] row-major; bias may be NULL; relu != 0 clamps at zero.  Supported when k % 4 == 0 and
- * m <= 256 (jg_gemm_tf32_supported); other shapes return JG_EUNSUPPORTED.  The workspace
+ * [m, k] row-major; bias may be NULL; relu != 0 clamps at zero.  Supported when m <= 256
+ * (jg_gemm_tf32_supported); other shapes return JG_EUNSUPPORTED.  Operands are fetched by TMA when
+ * k % 4 == 0 and x, wt are 16-byte aligned, by plain loads otherwise.  The workspace
  * (jg_gemm_tf32_workspace_bytes) receives an error word: jg_gemm_tf32_status synchronises the
  * stream and returns JG_ETIMEOUT if a bounded wait inside the kernel ran out. */
 int jg_gemm_tf32_supported(int64_t n_rows, int64_t k, int64_t m);

@@ -12,7 +12,8 @@
 // One CTA per SM, persistent over 128-row tiles.  Warp 0 (one lane) is the TMA producer: 128x32
 // tiles of X and Mx32 tiles of Wt land in a 4-stage shared-memory ring with the 128-byte swizzle
 // (cp.async.bulk.tensor, CTA-local, no cluster multicast; out-of-range rows and the K tail are
-// zero-filled by TMA).  Warp 1 (one lane) issues tcgen05.mma.kind::tf32 (128 x M x 8 per
+// zero-filled by TMA).  When K is not a multiple of 4 (row pitch not a multiple of 16 bytes, which
+// TMA cannot address) warp 0 fills the ring with plain coalesced loads in the same layout.  Warp 1 (one lane) issues tcgen05.mma.kind::tf32 (128 x M x 8 per
 // instruction) into one of two TMEM accumulators and commits ring slots / accumulators to
 // mbarriers.  Warps 2-9 are the epilogue: tcgen05.ld of the accumulator quadrant their warp id
 // gives them access to, bias and ReLU fused, 64-byte row segments stored to H, overlapping the
@@ -21,11 +22,13 @@
 #include "common.cuh"
 
 #include <cuda.h>
+#include <cstring>
 
 namespace jg {
 
-constexpr int kGemmThreads = 320;   // 10 warps: producer, MMA, 8 epilogue
+constexpr int kGemmThreads = 416;   // 13 warps: producer, MMA, 8 epilogue, 3 more plain-load producers
 constexpr int kEpiWarps = 8;
+constexpr int kPlainWarps = 4;      // warps 0, 10, 11, 12 when operands are fetched by plain loads
 constexpr int kTileM = 128;         // rows of X per tile
 constexpr int kTileK = 32;          // tf32 elements per 128-byte swizzle row
 constexpr int kStages = 4;
@@ -40,6 +43,9 @@ struct GemmParams {
     int32_t relu;
     int32_t n_tiles, k_blocks;
     int32_t* error;
+    const float* x;     // plain-load producer only (rows whose pitch TMA cannot take)
+    const float* wt;
+    int32_t plain_loads;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -67,6 +73,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         if (spin > 64) __nanosleep(spin > 4096 ? 256 : 32);
     }
     return false;
+}
+
+// 4-byte asynchronous global->shared copy; valid == false writes zeros.
+__device__ __forceinline__ void cp_async4(uint32_t smem_dst, const float* src, bool valid) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_dst), "l"(src), "r"(valid ? 4 : 0) : "memory");
 }
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -151,7 +162,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; s++) {
-            mbar_init(&ctl->full[s], 1);
+            mbar_init(&ctl->full[s], p.plain_loads ? 32 * kPlainWarps : 1);   // one arrival per producer lane, or the TMA lane's
             mbar_init(&ctl->empty[s], 1);
         }
         for (int b = 0; b < 2; b++) {
@@ -172,7 +183,48 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const uint32_t tmem_base = ctl->tmem_base;
     volatile int32_t* abort_flag = &ctl->abort;
 
-    if (warp == 0) {
+    if ((warp == 0 || warp >= 10) && p.plain_loads) {
+        const uint32_t pw = warp == 0 ? 0u : (uint32_t)(warp - 9);   // producer index 0..3: rows pw, pw + 4, ...
+        // ---------------------------------------------------------------- plain-load producer
+        // For K not a multiple of 4 the row pitch is not a multiple of 16 bytes and TMA cannot
+        // address the matrix.  Four warps then fill the ring themselves (one warp cannot keep enough
+        // requests in flight): per row and k-block one
+        // coalesced 128-byte read (cp.async, 4 bytes per lane) lands in shared memory in the same
+        // 128-byte swizzle TMA would have produced (16-byte chunk c of row r at chunk c ^ (r & 7)).
+        // Each lane's arrival on the slot's barrier fires when its copies have landed; the MMA
+        // lane orders them before the tensor core's asynchronous proxy with a proxy fence.
+        uint32_t it = 0;
+        const uint32_t chunk_off = (uint32_t)(lane >> 2), in_chunk = (uint32_t)(lane & 3) * 4;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < p.n_tiles && ok && !*abort_flag; tile += gridDim.x) {
+            for (int kb = 0; kb < p.k_blocks; kb++, it++) {
+                const int s = it % kStages;
+                const uint32_t round = it / kStages;
+                if (round > 0 && !mbar_wait(&ctl->empty[s], (round - 1) & 1)) { ok = false; break; }
+                const uint32_t a_dst = smem_u32(ring + s * stage_bytes);
+                const int kcol = kb * kTileK + lane;
+                const bool kin = kcol < p.k;
+                const int64_t row0 = (int64_t)tile * kTileM;
+                // asynchronous 4-byte copies straight into shared memory (zero-filled outside the
+                // matrix): nothing waits here, the barrier counts the copies as they land
+                const float* src = p.x + row0 * p.k + kcol;
+#pragma unroll 8
+                for (uint32_t r = pw; r < (uint32_t)kTileM; r += kPlainWarps) {
+                    const bool in = kin && row0 + r < p.n_rows;
+                    cp_async4(a_dst + r * 128 + ((chunk_off ^ (r & 7)) << 4) + in_chunk, in ? src + (int64_t)r * p.k : p.x, in);
+                }
+                const uint32_t b_dst = a_dst + a_bytes;
+                const float* wsrc = p.wt + kcol;
+#pragma unroll 8
+                for (uint32_t r = pw; r < b_rows; r += kPlainWarps) {
+                    const bool in = kin && (int)r < p.m;
+                    cp_async4(b_dst + r * 128 + ((chunk_off ^ (r & 7)) << 4) + in_chunk, in ? wsrc + (int64_t)r * p.k : p.wt, in);
+                }
+                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&ctl->full[s])) : "memory");
+            }
+        }
+        if (!ok) *abort_flag = 1;
+    } else if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
             uint32_t it = 0;
@@ -188,6 +240,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 }
             }
         }
+    } else if (warp >= 10) {
+        // spare producer warps: idle when TMA feeds the ring
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
@@ -204,6 +258,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 for (int kb = 0; kb < p.k_blocks; kb++, it++) {
                     const int s = it % kStages;
                     if (!mbar_wait(&ctl->full[s], (it / kStages) & 1)) { ok = false; break; }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // plain-load producer: generic-proxy writes
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(ring + s * stage_bytes);
                     const uint64_t da = umma_desc(a_addr), db = umma_desc(a_addr + a_bytes);
@@ -309,7 +364,7 @@ using namespace jg;
 extern "C" {
 
 int jg_gemm_tf32_supported(int64_t n_rows, int64_t k, int64_t m) {
-    return n_rows > 0 && k > 0 && m > 0 && k % 4 == 0 && m <= 256 && n_rows < ((int64_t)1 << 31) * 64;
+    return n_rows > 0 && k > 0 && m > 0 && m <= 256 && n_rows < ((int64_t)1 << 31) * 64;
 }
 
 size_t jg_gemm_tf32_workspace_bytes(void) { return 256; }
@@ -320,20 +375,26 @@ int jg_gemm_tf32(float* out, const float* x, const float* wt, const float* bias,
     if (n_rows == 0) return JG_OK;
     JG_CHECK_ARG(out && x && wt, JG_EINVAL, "gemm_tf32: null pointer");
     if (!jg_gemm_tf32_supported(n_rows, k, m)) {
-        set_error("gemm_tf32: needs k %% 4 == 0 (16-byte row pitch for TMA) and m <= 256 (got k=%lld, m=%lld)", (long long)k, (long long)m);
+        set_error("gemm_tf32: needs m <= 256 (got k=%lld, m=%lld)", (long long)k, (long long)m);
         return JG_EUNSUPPORTED;
     }
-    JG_CHECK_ARG((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wt) | reinterpret_cast<uintptr_t>(out)) % 16 == 0,
-                 JG_EINVAL, "gemm_tf32: x, wt and out must be 16-byte aligned");
+    JG_CHECK_ARG(reinterpret_cast<uintptr_t>(out) % 16 == 0, JG_EINVAL, "gemm_tf32: out must be 16-byte aligned");
+    // TMA needs 16-byte aligned bases and row pitches; anything else goes through the plain-load producer
+    const bool plain = (k % 4 != 0) || ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wt)) % 16 != 0);
     JG_CHECK_ARG(workspace && workspace_bytes >= 256, JG_EWORKSPACE, "gemm_tf32: workspace missing");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int b_rows = (int)((m + 15) / 16 * 16);
     CUtensorMap map_x, map_w;
-    int rc = make_map(&map_x, x, n_rows, k, kTileM);
-    if (rc != JG_OK) return rc;
-    rc = make_map(&map_w, wt, m, k, b_rows);
-    if (rc != JG_OK) return rc;
+    memset(&map_x, 0, sizeof(map_x));
+    memset(&map_w, 0, sizeof(map_w));
+    if (!plain) {
+        int rc = make_map(&map_x, x, n_rows, k, kTileM);
+        if (rc != JG_OK) return rc;
+        rc = make_map(&map_w, wt, m, k, b_rows);
+        if (rc != JG_OK) return rc;
+    }
     GemmParams p = {};
+    p.x = x; p.wt = wt; p.plain_loads = plain ? 1 : 0;
     p.out = out; p.bias = bias; p.n_rows = n_rows; p.k = (int32_t)k; p.m = (int32_t)m; p.relu = relu;
     int pad = 32;
     while (pad < b_rows) pad *= 2;

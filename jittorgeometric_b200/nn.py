@@ -28,13 +28,23 @@ def gcn_norm(edge_index, edge_weight=None, num_nodes=None, improved=False, add_s
     return ops.gcn_norm_coo(edge_index, edge_weight, num_nodes, improved=improved)
 
 
+def _transform(x, weight, tf32, relu=False):
+    """``x @ weight`` (optionally ReLU): the tcgen05 TF32 kernel when asked for and no gradient is
+    needed (it is forward-only, 2e-3 tolerance), else the fp32 matmul with autograd."""
+    needs_grad = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)
+    if tf32 and not needs_grad and ops.linear_tf32_supported(x.shape[0], x.shape[1], weight.shape[1]):
+        return ops.linear_tf32(x, weight, relu=relu)
+    h = x @ weight
+    return torch.relu(h) if relu else h
+
+
 class GCNConv(torch.nn.Module):
     """``out = A_hat (x W) + b`` (nn/conv/gcn_conv.py:70-112).  ``spmm`` is accepted for signature
     compatibility; there is one backend."""
 
-    def __init__(self, in_channels, out_channels, bias=True, spmm=True, **kwargs):
+    def __init__(self, in_channels, out_channels, bias=True, spmm=True, tf32=False, **kwargs):
         super().__init__()
-        self.in_channels, self.out_channels, self.spmm = in_channels, out_channels, spmm
+        self.in_channels, self.out_channels, self.spmm, self.tf32 = in_channels, out_channels, spmm, tf32
         self.weight = torch.nn.Parameter(torch.empty(in_channels, out_channels))
         self.bias = torch.nn.Parameter(torch.zeros(out_channels)) if bias else None
         self.reset_parameters()
@@ -46,7 +56,7 @@ class GCNConv(torch.nn.Module):
                 self.bias.zero_()
 
     def forward(self, x, csc, csr):
-        x = x @ self.weight
+        x = _transform(x, self.weight, self.tf32)
         out = ops.aggregateWithWeight(x, csc, csr)
         if self.bias is not None:
             out = out + self.bias
@@ -97,10 +107,10 @@ class GATConv(torch.nn.Module):
     independent heads.  The forward pass runs the fused kernel when the shape allows and no
     gradient is needed, else the reference's op-by-op pipeline on the per-edge operators."""
 
-    def __init__(self, in_channels, out_channels, heads=1, **kwargs):
+    def __init__(self, in_channels, out_channels, heads=1, tf32=False, **kwargs):
         super().__init__()
         assert out_channels % heads == 0
-        self.in_channels, self.out_channels, self.heads = in_channels, out_channels, heads
+        self.in_channels, self.out_channels, self.heads, self.tf32 = in_channels, out_channels, heads, tf32
         self.weight = torch.nn.Parameter(torch.empty(in_channels, out_channels))
         self.edge_weight = torch.nn.Parameter(torch.empty(2 * out_channels, 1))
         self.reset_parameters()
@@ -114,7 +124,7 @@ class GATConv(torch.nn.Module):
         return self.edge_weight[:c, 0].reshape(self.heads, -1), self.edge_weight[c:, 0].reshape(self.heads, -1)
 
     def forward(self, x, csc):
-        h = torch.relu(x @ self.weight)
+        h = _transform(x, self.weight, self.tf32, relu=True)
         dim = self.out_channels // self.heads
         needs_grad = torch.is_grad_enabled() and (h.requires_grad or self.edge_weight.requires_grad)
         if not needs_grad and ops.gat_aggregate_supported(self.heads, dim):

@@ -23,7 +23,8 @@ def run(cuda, n, k, m, bias, relu, seed=0):
 
 
 @pytest.mark.parametrize("n,k,m", [(128, 32, 16), (1000, 128, 128), (5000, 256, 64), (3000, 128, 7), (777, 64, 256),
-                                   (20000, 128, 64), (129, 36, 24), (40000, 604, 64)])
+                                   (20000, 128, 64), (129, 36, 24), (40000, 604, 64),
+                                   (5000, 602, 64), (2708, 1433, 256), (300, 7, 5), (1000, 33, 16)])
 def test_against_float64(cuda, n, k, m):
     assert cuda.ops.linear_tf32_supported(n, k, m)
     got, want, scale = run(cuda, n, k, m, bias=False, relu=False, seed=n + k + m)
@@ -48,7 +49,7 @@ def test_runs_are_identical_and_large(cuda):
 
 
 def test_unsupported_shapes_are_refused(cuda):
-    assert not cuda.ops.linear_tf32_supported(100, 602, 64)      # row pitch not a multiple of 16 bytes
+    assert cuda.ops.linear_tf32_supported(100, 602, 64)          # row pitch not a multiple of 16 bytes: plain-load producer
     assert not cuda.ops.linear_tf32_supported(100, 128, 257)
     with pytest.raises(RuntimeError):
-        cuda.ops.linear_tf32(torch.zeros((10, 602), device="cuda"), torch.zeros((602, 64), device="cuda"))
+        cuda.ops.linear_tf32(torch.zeros((10, 128), device="cuda"), torch.zeros((128, 300), device="cuda"))
