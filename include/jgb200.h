@@ -125,6 +125,17 @@ int jg_gcn_norm_coo(const int32_t* edge_index, const float* w, int64_t n_edges, 
                     int32_t* out_src, int32_t* out_dst, float* out_w, int64_t* out_count, void* workspace,
                     size_t workspace_bytes, jg_stream_t stream);
 
+/* Symmetrise and deduplicate a COO list: replaces ToundirectedOp (ops/cpp/toundirected_op.cc:33-63;
+ * wrapper ops/toundirected.py:16-22).  Every edge is mirrored, the 2 * n_edges entries are sorted
+ * by (row, col) and one entry per distinct pair is kept - the first in mirrored-list order (edge i
+ * as given, then reversed, for i = 0, 1, ...); the reference sorts with an unstable sort and leaves
+ * that choice unspecified.  Outputs need room for 2 * n_edges entries; *out_count (device, int64)
+ * receives the entry count. */
+size_t jg_to_undirected_workspace_bytes(int64_t n_edges, int64_t n_nodes);
+int jg_to_undirected(const int32_t* edge_index, const float* attr, int64_t n_edges, int64_t n_nodes, int32_t* out_src,
+                     int32_t* out_dst, float* out_attr, int64_t* out_count, void* workspace, size_t workspace_bytes,
+                     jg_stream_t stream);
+
 /* ------------------------------------------------------------------ per-edge operators
  * Edges are in CSC order (segment v = in-edges of destination v, idx[e] = source of edge e).
  *

@@ -158,6 +158,13 @@ __device__ __forceinline__ Elem load_elem(const SortSrc& s, int64_t p) {
     if (!e.valid) return e;
     if (s.mode == 0) {
         e.key = s.key[p]; e.idx = s.idx[p]; e.w = s.w[p];
+    } else if (s.mode == 2) {
+        // mirrored list: position 2i is edge i as given, 2i + 1 the same edge reversed
+        const int64_t i = p >> 1;
+        const int32_t a = s.coo_src[i], b = s.coo_dst[i];
+        e.key = (p & 1) ? b : a;
+        e.idx = (p & 1) ? a : b;
+        e.w = s.coo_w ? s.coo_w[i] : 1.f;
     } else if (p < s.e0) {
         const int32_t a = s.coo_src[p], b = s.coo_dst[p];
         e.key = s.by == 0 ? a : b;
@@ -372,6 +379,30 @@ __global__ void write_norm_coo_kernel(const int32_t* __restrict__ src, const int
         out_dst[kept + v] = v;
         out_w[kept + v] = __fmul_rn(__fmul_rn(dis[v], loop_w ? loop_w[v] : 1.f), dis[v]);
     }
+}
+
+// ---- symmetrise + dedupe: first entry of every run of equal (row, col) pairs survives
+__global__ void first_of_run_kernel(const int32_t* __restrict__ key, const int32_t* __restrict__ idx, int64_t m,
+                                    int* __restrict__ flag) {
+    const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < m) flag[j] = (j == 0) || key[j] != key[j - 1] || idx[j] != idx[j - 1];
+    if (j == m) flag[j] = 0;
+}
+__global__ void compact_runs_kernel(const int32_t* __restrict__ key, const int32_t* __restrict__ idx,
+                                    const float* __restrict__ w, const int* __restrict__ pos, int64_t m,
+                                    int32_t* __restrict__ out_src, int32_t* __restrict__ out_dst,
+                                    float* __restrict__ out_w, int64_t* __restrict__ out_count) {
+    const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < m) {
+        const bool first = (j == 0) || key[j] != key[j - 1] || idx[j] != idx[j - 1];
+        if (first) {
+            const int p = pos[j];
+            out_src[p] = key[j];
+            out_dst[p] = idx[j];
+            out_w[p] = w[j];
+        }
+    }
+    if (j == m) *out_count = pos[m];
 }
 
 // ---- 1-D row partition: split a shard's in-edges into interior (source owned) and halo (remote)
@@ -718,6 +749,67 @@ int jg_partition_split(const int32_t* idx, const int32_t* off, const float* w, i
         JG_LAUNCH_CHECK();
     }
     split_offsets_kernel<<<blocks_for(n_rows + 1, 256), 256, 0, st>>>(off, pos, n_rows, int_off, halo_off, out_counts);
+    JG_LAUNCH_CHECK();
+    return JG_OK;
+}
+
+
+struct UndirectedWs {
+    void* convert;
+    size_t convert_bytes;
+    int32_t* idx;
+    float* w;
+    int* pos;
+    int* pos_sums;
+    size_t bytes;
+};
+
+static UndirectedWs carve_undirected(void* ws, int64_t n_edges, int64_t n_nodes) {
+    Carver c(ws);
+    UndirectedWs v;
+    v.convert_bytes = jg_convert_workspace_bytes(2 * n_edges, n_nodes);
+    v.convert = c.take<unsigned char>(v.convert_bytes);
+    v.idx = c.take<int32_t>(2 * n_edges + 1);
+    v.w = c.take<float>(2 * n_edges + 1);
+    v.pos = c.take<int>(2 * n_edges + 1);
+    v.pos_sums = c.take<int>(scan_temp_ints(2 * n_edges + 1));
+    v.bytes = c.total();
+    return v;
+}
+
+size_t jg_to_undirected_workspace_bytes(int64_t n_edges, int64_t n_nodes) {
+    if (n_edges < 0 || n_nodes < 0) return 0;
+    return carve_undirected(nullptr, n_edges, n_nodes).bytes;
+}
+
+int jg_to_undirected(const int32_t* edge_index, const float* attr, int64_t n_edges, int64_t n_nodes, int32_t* out_src,
+                     int32_t* out_dst, float* out_attr, int64_t* out_count, void* workspace, size_t workspace_bytes,
+                     jg_stream_t stream) {
+    JG_CHECK_ARG(n_edges >= 0 && n_nodes >= 0, JG_EINVAL, "to_undirected: negative size");
+    JG_CHECK_ARG(out_count, JG_EINVAL, "to_undirected: null count");
+    JG_CHECK_ARG(n_edges == 0 || (edge_index && out_src && out_dst && out_attr), JG_EINVAL, "to_undirected: null array");
+    JG_CHECK_ARG(2 * n_edges <= INT32_MAX - 1 && n_nodes < INT32_MAX, JG_ESHAPE, "to_undirected: sizes beyond int32");
+    JG_CHECK_ARG(workspace && workspace_bytes >= jg_to_undirected_workspace_bytes(n_edges, n_nodes), JG_EWORKSPACE,
+                 "to_undirected: workspace too small");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t m = 2 * n_edges;
+    UndirectedWs uw = carve_undirected(workspace, n_edges, n_nodes);
+    ConvertWs ws = carve_convert(uw.convert, m + n_nodes, n_nodes);
+    SortSrc first = {};
+    first.mode = 2;
+    first.coo_src = edge_index;
+    first.coo_dst = edge_index + n_edges;
+    first.coo_w = attr;
+    first.count = m;
+    int32_t* skey = nullptr;
+    int rc = radix_sort(first, n_nodes, 1, nullptr, ws, uw.idx, uw.w, &skey, st);   // by (row, col), stable
+    if (rc != JG_OK) return rc;
+    first_of_run_kernel<<<blocks_for(m + 1, 256), 256, 0, st>>>(skey, uw.idx, m, uw.pos);
+    JG_LAUNCH_CHECK();
+    rc = exclusive_scan(uw.pos, uw.pos, m + 1, uw.pos_sums, st);
+    if (rc != JG_OK) return rc;
+    compact_runs_kernel<<<blocks_for(m + 1, 256), 256, 0, st>>>(skey, uw.idx, uw.w, uw.pos, m, out_src, out_dst, out_attr,
+                                                                 out_count);
     JG_LAUNCH_CHECK();
     return JG_OK;
 }

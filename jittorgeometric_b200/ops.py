@@ -15,7 +15,7 @@ from .data import CSC, CSR
 
 __all__ = ["aggregateWithWeight", "segment_aggregate", "SpmmPlan", "cootocsr", "cootocsc", "gcn_norm_csc_csr",
            "SpmmCsr", "SpmmCoo", "ScatterToEdge", "ScatterToVertex", "EdgeSoftmax", "gat_aggregate",
-           "gat_aggregate_supported", "gcn_norm_coo", "linear_tf32", "linear_tf32_supported"]
+           "gat_aggregate_supported", "gcn_norm_coo", "linear_tf32", "linear_tf32_supported", "toUndirected"]
 
 DEFAULT_CHUNK = int(os.environ.get("JG_SPMM_CHUNK", "1024"))
 
@@ -203,6 +203,25 @@ def gcn_norm_coo(edge_index, edge_weight, num_nodes, improved=False):
                                 ptr(count), ptr(ws), ws.numel(), stream_for(ei)), "jg_gcn_norm_coo")
     E = int(count.item())
     return out[:, :E].contiguous(), ow[:E]
+
+
+def toUndirected(edge_index, edge_attr, num_nodes):
+    """Mirror every edge, sort by (row, col) and drop duplicate pairs (ops/toundirected.py:16-22).
+    Returns ``(new_edge_index [2, M], new_edge_attr [M])``."""
+    ei = _edge_index(edge_index)
+    E, dev = ei.shape[1], ei.device
+    attr = _as_f32(edge_attr, "edge_attr")
+    if attr.numel() != E:
+        raise RuntimeError(f"edge_attr has {attr.numel()} entries, edge_index {E}")
+    n = int(num_nodes) if num_nodes is not None else (int(ei.max()) + 1 if E else 0)
+    out = torch.empty((2, max(2 * E, 1)), dtype=torch.int32, device=dev)
+    oa = torch.empty(max(2 * E, 1), dtype=torch.float32, device=dev)
+    count = torch.zeros(1, dtype=torch.int64, device=dev)
+    ws = workspace(lib().jg_to_undirected_workspace_bytes(E, n), dev)
+    check(lib().jg_to_undirected(ptr(ei), ptr(attr), E, n, ptr(out[0]), ptr(out[1]), ptr(oa), ptr(count), ptr(ws),
+                                 ws.numel(), stream_for(ei)), "jg_to_undirected")
+    m = int(count.item())
+    return out[:, :m].contiguous(), oa[:m]
 
 
 # ------------------------------------------------------------------------------ SpMM front ends

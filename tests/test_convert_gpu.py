@@ -125,3 +125,20 @@ def test_bad_arguments(cuda):
         cuda.cootocsr(torch.zeros((3, 4), dtype=torch.int32, device="cuda"), torch.zeros(4, device="cuda"), 5)
     with pytest.raises(RuntimeError):
         cuda.cootocsr(torch.zeros((2, 4), dtype=torch.int32, device="cuda"), torch.zeros(3, device="cuda"), 5)
+
+
+def test_to_undirected(cuda, oracle):
+    d = load("ref_test_undirected")
+    gei, ga = cuda.toUndirected(dev(d["edge_index"]), dev(d["edge_attr"]), 3)
+    assert np.array_equal(host(gei), d["new_edge_index"])
+    assert np.array_equal(host(ga), d["new_edge_attr"])
+    rng = np.random.default_rng(12)
+    for n, E in ((1, 3), (50, 0), (300, 5000), (70000, 400000)):
+        ei = np.minimum((rng.random((2, E)) ** 2 * n).astype(np.int32), max(n - 1, 0))
+        a = rng.standard_normal(E).astype(np.float32)
+        gei, ga = cuda.toUndirected(dev(ei), dev(a), n)
+        wei, wa = oracle.to_undirected(ei, a, n, "port")         # first of every duplicate run survives
+        assert np.array_equal(host(gei), wei) and np.array_equal(host(ga), wa)
+        if oracle.have_ref() and E:
+            rei, _ = oracle.to_undirected(ei, a, n, "ref")       # the reference's indices (its attribute choice is unspecified)
+            assert np.array_equal(host(gei), rei)
