@@ -23,8 +23,6 @@
 // only atomic is the ticket counter.
 #include "common.cuh"
 
-#include <cstdlib>
-
 namespace jg {
 
 struct PlanHeader {
@@ -100,13 +98,6 @@ struct AggArgs {
     int accumulate;  // 1: add the aggregated row to what `out` already holds (old + sum)
 };
 
-__device__ __forceinline__ void fma2(float4& a, const float4& v, float w) {
-    // multiply and add rounded separately, as the reference CPU loop does
-    a.x = __fadd_rn(__fmul_rn(v.x, w), a.x);
-    a.y = __fadd_rn(__fmul_rn(v.y, w), a.y);
-    a.z = __fadd_rn(__fmul_rn(v.z, w), a.z);
-    a.w = __fadd_rn(__fmul_rn(v.w, w), a.w);
-}
 
 // Exact mode rounds multiply and add separately, as the reference CPU loop does; the fused
 // mode uses one FMA per term.
@@ -412,28 +403,6 @@ static int dispatch_aggregate(const AggArgs& a, cudaStream_t st) {
     const int64_t f = a.f;
     const bool vec_ok = (f % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.out) |
                                           reinterpret_cast<uintptr_t>(a.partial)) % 16 == 0);
-    static const int variant = [] { const char* v = getenv("JG_SPMM_VARIANT"); return v ? atoi(v) : 0; }();
-    if (vec_ok && variant == 1) {  // tuning: fused multiply-add
-        if (f == 32) return launch_rows<8, 1, 8, 4, false>(a, st);
-        if (f == 64) return launch_rows<16, 1, 8, 4, false>(a, st);
-        if (f == 128) return launch_rows<32, 1, 8, 4, false>(a, st);
-        if (f == 256) return launch_rows<32, 2, 4, 4, false>(a, st);
-    } else if (vec_ok && variant == 2) {  // tuning: smaller batch, more resident warps
-        if (f == 32) return launch_rows<8, 1, 4, 6, true>(a, st);
-        if (f == 64) return launch_rows<16, 1, 4, 6, true>(a, st);
-        if (f == 128) return launch_rows<32, 1, 4, 6, true>(a, st);
-        if (f == 256) return launch_rows<32, 2, 2, 6, true>(a, st);
-    } else if (vec_ok && variant == 3) {  // tuning: both
-        if (f == 32) return launch_rows<8, 1, 4, 6, false>(a, st);
-        if (f == 64) return launch_rows<16, 1, 4, 6, false>(a, st);
-        if (f == 128) return launch_rows<32, 1, 4, 6, false>(a, st);
-        if (f == 256) return launch_rows<32, 2, 2, 6, false>(a, st);
-    } else if (vec_ok && variant == 4) {  // tuning: larger batch
-        if (f == 32) return launch_rows<8, 1, 8, 3, true>(a, st);
-        if (f == 64) return launch_rows<16, 1, 16, 3, true>(a, st);
-        if (f == 128) return launch_rows<32, 1, 16, 3, true>(a, st);
-        if (f == 256) return launch_rows<32, 2, 8, 3, true>(a, st);
-    }
     if (vec_ok && f == 32) return launch_rows<8, 1, 8, 4, true>(a, st);
     if (vec_ok && f == 64) return launch_rows<16, 1, 8, 4, true>(a, st);
     if (vec_ok && f == 128) return launch_rows<32, 1, 8, 4, true>(a, st);

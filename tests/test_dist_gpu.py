@@ -89,7 +89,21 @@ def nccl_worker(rank, world, port, n, E, f, q, exchange):
         y2 = g.aggregate(t(x[lo:hi].copy()))          # second exchange reuses the shard buffers
         torch.cuda.synchronize()
         assert torch.equal(y, y2)
-        q.put((rank, lo, hi, y.cpu().numpy()))
+        # the reference-shaped API: one sub-CSR per source rank, one broadcast round each
+        import oracle as O
+        import jittorgeometric_b200 as jg
+        seg = np.repeat(np.arange(n), np.diff(off))
+        mine = (seg >= lo) & (seg < hi)
+        csr_list = []
+        for src_rank in range(world):
+            s_lo, s_hi = part.range(src_rank)
+            sel = mine & (idx >= s_lo) & (idx < s_hi)
+            ei = np.stack([idx[sel] - s_lo, seg[sel] - lo]).astype(np.int32)      # rows: sources of that rank, columns: local destinations
+            ci, ro, cw = O.coo_to_csr(ei, w[sel], s_hi - s_lo)
+            csr_list.append(jg.CSR(t(ci), t(ro), t(cw)))
+        z = jd.DistSpmm(jd.DistributedManager(), t(x[lo:hi].copy()), csr_list, hi - lo)
+        torch.cuda.synchronize()
+        q.put((rank, lo, hi, y.cpu().numpy(), z.cpu().numpy()))
     except Exception as exc:
         q.put((rank, -1, -1, repr(exc)))
         raise
@@ -118,5 +132,6 @@ def test_nccl_ranks(cuda, oracle, exchange):
     idx, off, w, x = make_graph(11, n, E, f)
     want = oracle.aggregate(x, idx, off, w)
     _, scale = oracle.aggregate_f64(x, idx, off, w)
-    for rank, lo, hi, y in got:
+    for rank, lo, hi, y, z in got:
         assert (np.abs(y - want[lo:hi]) / (scale[lo:hi] + 1e-30)).max() <= 1e-5
+        assert (np.abs(z - want[lo:hi]) / (scale[lo:hi] + 1e-30)).max() <= 1e-5
