@@ -10,7 +10,7 @@
 //
 // Method: stable least-significant-digit radix sort, 8 bits per pass, ceil(bits(n)/8) passes,
 // carrying (key, other index, weight).  Each pass = per-tile digit histogram, one device-wide
-// exclusive scan of the [digit][tile] matrix, and a stable scatter: ranks inside a tile come from
+// exclusive scan of the [tile][digit] count matrix in digit-major order, and a stable scatter: ranks inside a tile come from
 // warp match masks in element order, elements are staged in shared memory in digit order and
 // written out in coalesced runs.  The first pass reads the caller's COO directly (self-loop
 // removal and the appended loops are folded into it: removed entries are simply never counted),
@@ -124,6 +124,48 @@ static int exclusive_scan(const int* in, int* out, int64_t n, int* sums, cudaStr
     return JG_OK;
 }
 
+// ------------------------------------------------------------------------------- digit-major scan
+// The per-tile digit counts live as matrix[tile][digit] (rows of 256 counts, written and read
+// coalesced).  The scatter needs, for every (digit, tile), the number of entries with a smaller
+// digit anywhere plus the entries with the same digit in earlier tiles: an exclusive scan in
+// digit-major order.  It is done column-wise, thread d walking column d, so every access is a
+// coalesced row: chunk sums, one block that scans chunks and digits, then a walk down each chunk.
+constexpr int kChunkTiles = 128;
+
+__global__ void __launch_bounds__(kRadix) colscan_chunk_sums(const int* __restrict__ matrix, int64_t n_tiles,
+                                                             int* __restrict__ chunk_sums) {
+    const int64_t t0 = (int64_t)blockIdx.x * kChunkTiles;
+    const int64_t t1 = t0 + kChunkTiles < n_tiles ? t0 + kChunkTiles : n_tiles;
+    int sum = 0;
+    for (int64_t t = t0; t < t1; t++) sum += matrix[t * kRadix + threadIdx.x];
+    chunk_sums[(int64_t)blockIdx.x * kRadix + threadIdx.x] = sum;
+}
+
+__global__ void __launch_bounds__(kRadix) colscan_chunks(int* __restrict__ chunk_sums, int64_t n_chunks) {
+    __shared__ int s_warp[32];
+    __shared__ int s_total;
+    int run = 0;
+    for (int64_t c = 0; c < n_chunks; c++) {          // exclusive prefix of this digit's chunk sums
+        const int v = chunk_sums[c * kRadix + threadIdx.x];
+        chunk_sums[c * kRadix + threadIdx.x] = run;
+        run += v;
+    }
+    const int base = block_exclusive_scan(run, &s_total, s_warp);   // entries with a smaller digit
+    for (int64_t c = 0; c < n_chunks; c++) chunk_sums[c * kRadix + threadIdx.x] += base;
+}
+
+__global__ void __launch_bounds__(kRadix) colscan_apply(int* __restrict__ matrix, int64_t n_tiles,
+                                                        const int* __restrict__ chunk_sums) {
+    const int64_t t0 = (int64_t)blockIdx.x * kChunkTiles;
+    const int64_t t1 = t0 + kChunkTiles < n_tiles ? t0 + kChunkTiles : n_tiles;
+    int run = chunk_sums[(int64_t)blockIdx.x * kRadix + threadIdx.x];
+    for (int64_t t = t0; t < t1; t++) {
+        const int v = matrix[t * kRadix + threadIdx.x];
+        matrix[t * kRadix + threadIdx.x] = run;
+        run += v;
+    }
+}
+
 // ------------------------------------------------------------------------------- sort passes
 // Where a pass reads its elements from.
 struct SortSrc {
@@ -196,7 +238,8 @@ __global__ void __launch_bounds__(kSortThreads) sort_hist_kernel(SortSrc s, int 
         if (e.valid) atomicAdd(&s_hist[digit_of(e, shift, from_idx)], 1);
     }
     __syncthreads();
-    matrix[(int64_t)threadIdx.x * n_tiles + blockIdx.x] = s_hist[threadIdx.x];
+    matrix[(int64_t)blockIdx.x * kRadix + threadIdx.x] = s_hist[threadIdx.x];   // [tile][digit]: one coalesced row
+    (void)n_tiles;
 }
 
 struct SortDst {
@@ -255,7 +298,8 @@ __global__ void __launch_bounds__(kSortThreads, 4) sort_scatter_kernel(SortSrc s
         }
         const int start = block_exclusive_scan(run, &s_total, s_scan);
         s_dstart[dgt] = start;
-        s_gbase[dgt] = matrix[(int64_t)dgt * n_tiles + blockIdx.x] - start;  // global position = gbase + tile slot
+        s_gbase[dgt] = matrix[(int64_t)blockIdx.x * kRadix + dgt] - start;  // global position = gbase + tile slot
+        (void)n_tiles;
     }
     __syncthreads();
 #pragma unroll
@@ -480,7 +524,7 @@ static ConvertWs carve_convert(void* ws, int64_t cap, int64_t n) {
     }
     const int64_t tiles = (cap + kSortTile - 1) / kSortTile + 1;
     v.matrix = c.take<int>((size_t)tiles * kRadix);
-    v.scan_sums = c.take<int>(scan_temp_ints(tiles * kRadix));
+    v.scan_sums = c.take<int>((size_t)((tiles + kChunkTiles - 1) / kChunkTiles + 1) * kRadix);
     v.dis = c.take<float>(n + 1);
     v.loop_w = c.take<float>(n + 1);
     v.last_loop = c.take<int>(n + 1);
@@ -515,8 +559,15 @@ static int radix_sort(SortSrc first, int64_t n, int canonical, const unsigned lo
         const int shift = 8 * (canonical && !from_idx ? p - key_passes : p);
         sort_hist_kernel<<<(unsigned)tiles, kSortThreads, 0, st>>>(src, shift, from_idx, ws.matrix, tiles);
         JG_LAUNCH_CHECK();
-        int rc = exclusive_scan(ws.matrix, ws.matrix, tiles * kRadix, ws.scan_sums, st);
-        if (rc != JG_OK) return rc;
+        {
+            const int64_t chunks = (tiles + kChunkTiles - 1) / kChunkTiles;
+            colscan_chunk_sums<<<(unsigned)chunks, kRadix, 0, st>>>(ws.matrix, tiles, ws.scan_sums);
+            JG_LAUNCH_CHECK();
+            colscan_chunks<<<1, kRadix, 0, st>>>(ws.scan_sums, chunks);
+            JG_LAUNCH_CHECK();
+            colscan_apply<<<(unsigned)chunks, kRadix, 0, st>>>(ws.matrix, tiles, ws.scan_sums);
+            JG_LAUNCH_CHECK();
+        }
         const bool last = p == total_passes - 1;
         SortDst dst;
         dst.key = ws.key[cur];
