@@ -195,7 +195,6 @@ def run_gcn(args):
                             exchange=os.environ.get("JG_EXCHANGE", "peer"))
         del csc
         n_local = g.n_local
-        h1buf, h2buf = g.exchange.buffer(128, dev)[0], g.exchange.buffer(64, dev)[0]
     else:
         plan = jg.SpmmPlan(csc.column_offset, nnz)
         n_local = n
@@ -203,11 +202,8 @@ def run_gcn(args):
 
     def forward():
         if world > 1:
-            # transform straight into the shard buffer the peers pull from, then aggregate
-            h1buf[:n_local] = jg.linear_tf32(x, W1, weight_t=W1t)
-            z1 = torch.relu(g.aggregate(h1buf) + b1)
-            h2buf[:n_local] = jg.linear_tf32(z1, W2, weight_t=W2t)
-            return g.aggregate(h2buf) + b2
+            z1 = torch.relu(g.aggregate(jg.linear_tf32(x, W1, weight_t=W1t)) + b1)
+            return g.aggregate(jg.linear_tf32(z1, W2, weight_t=W2t)) + b2
         h1 = jg.linear_tf32(x, W1, weight_t=W1t)
         z1 = torch.relu(jg.segment_aggregate(h1, csc.row_indices, csc.column_offset, csc.edge_weight, plan=plan) + b1)
         h2 = jg.linear_tf32(z1, W2, weight_t=W2t)

@@ -9,11 +9,13 @@ source rank, and runs P rounds of host-staged pickled ``MPI.bcast`` + cuSPARSE. 
   ids carry no degree order),
 * splits its in-edges on device into interior entries (source row owned, read from the rank's own
   shard) and halo entries (source row remote),
-* brings the other ranks' feature shards over NVLink into a local buffer laid out by global row
-  id - copy-engine pulls from peer memory (:class:`PeerExchange`) or one NCCL all-gather - while
-  the interior aggregation runs, then aggregates the halo entries from that buffer and adds them
-  to the same output rows (fixed order: interior, then halo, so results are run-to-run
-  identical).  Kernels only ever gather from local memory.
+* finds, once per graph, the distinct remote rows its halo entries reference (with skewed degrees
+  a minority of all remote rows) and tells their owners; per aggregation every rank packs the rows
+  its peers asked for and the packed segments travel over NVLink into a local halo buffer -
+  copy-engine pulls from peer memory (:class:`PeerTransport`) or one NCCL all-to-all
+  (:class:`CollectiveTransport`) - while the interior aggregation runs; the halo entries are then
+  aggregated from that buffer and added to the same output rows (fixed order: interior, then
+  halo, so results are run-to-run identical).  Kernels only ever gather from local memory.
 
 One process per GPU; ``torch.distributed`` supplies the communicator.  The compute backend is
 pluggable so the partition and exchange logic can be exercised by CPU ranks over ``gloo``.
@@ -50,7 +52,7 @@ class RowPartition:
 
 
 class DeviceBackend:
-    """The CUDA library: interior/halo split and aggregation kernels."""
+    """The CUDA library: interior/halo split, halo map, row packing and aggregation kernels."""
 
     def split(self, idx, off, w, lo, hi):
         nnz, n_rows, dev = idx.numel(), off.numel() - 1, idx.device
@@ -66,6 +68,26 @@ class DeviceBackend:
         ni, nh = (int(v) for v in counts.tolist())
         return (ii[:ni].clone(), io[: n_rows + 1], iw[:ni].clone()), (hi_[:nh].clone(), ho[: n_rows + 1], hw[:nh].clone())
 
+    def halo_map(self, halo_idx, n_global, bounds):
+        """Distinct remote rows a shard references: ``(needed ids ascending, halo indices re-addressed
+        into the packed buffer, rows needed from every owner)``."""
+        nnz, dev = halo_idx.numel(), halo_idx.device
+        pos = torch.empty(n_global + 1, dtype=torch.int32, device=dev)
+        needed = torch.empty(max(min(nnz, n_global), 1), dtype=torch.int32, device=dev)
+        remapped = torch.empty(max(nnz, 1), dtype=torch.int32, device=dev)
+        ws = workspace(lib().jg_halo_map_workspace_bytes(n_global), dev)
+        check(lib().jg_halo_map_build(ptr(halo_idx), nnz, n_global, ptr(pos), ptr(needed), ptr(remapped), ptr(ws),
+                                      ws.numel(), stream_for(halo_idx)), "jg_halo_map_build")
+        at = pos[torch.tensor(bounds, device=dev, dtype=torch.long)].tolist()
+        counts = [at[q + 1] - at[q] for q in range(len(bounds) - 1)]
+        return needed[: at[-1]].clone(), remapped[:nnz].clone(), counts
+
+    def gather_rows(self, x, rows, rebase, out):
+        n = rows.numel()
+        check(lib().jg_gather_rows_f32(ptr(out), ptr(x), ptr(rows), n, x.shape[1], int(rebase), stream_for(x)),
+              "jg_gather_rows_f32")
+        return out
+
     def plan(self, off, nnz):
         return ops.SpmmPlan(off, nnz)
 
@@ -73,161 +95,191 @@ class DeviceBackend:
         return ops.segment_aggregate(x, idx, off, w, n_out=n_out, plan=plan, out=out, accumulate=accumulate)
 
 
-class PeerExchange:
-    """Shard exchange by peer-to-peer copies over NVLink, driven by the copy engines.
+class _Done:
+    def wait(self):
+        pass
 
-    An NCCL all-gather runs as a kernel, and the aggregation kernels are persistent grids that
+
+class CollectiveTransport:
+    """Row exchange with ``torch.distributed`` collectives (NCCL on GPUs, gloo on CPU ranks):
+    one ``all_to_all_single`` with per-peer row counts."""
+
+    def __init__(self, group=None):
+        self.group = group
+
+    def send_buffer(self, rows, f, like):
+        return torch.empty((max(rows, 1), f), dtype=like.dtype, device=like.device)
+
+    # set-up collectives: the matrix of request counts and the requested row ids
+    def all_gather_counts(self, g, counts):
+        if g.part.world == 1:
+            return [counts.tolist()]
+        out = [torch.empty_like(counts) for _ in range(g.part.world)]
+        dist.all_gather(out, counts, group=self.group)
+        return [t.tolist() for t in out]
+
+    def all_to_all_ids(self, g, needed, recv_counts, send_counts):
+        if g.part.world == 1:
+            return needed[:0]
+        out = torch.empty(max(sum(send_counts), 1), dtype=needed.dtype, device=needed.device)
+        src = needed if needed.numel() else torch.empty(1, dtype=needed.dtype, device=needed.device)
+        dist.all_to_all_single(out[: sum(send_counts)], src[: sum(recv_counts)], output_split_sizes=list(send_counts),
+                               input_split_sizes=list(recv_counts), group=self.group)
+        return out[: sum(send_counts)]
+
+    def exchange(self, g, send, recv, f):
+        if g.part.world == 1:
+            return _Done()
+        send_split = [int(c) for c in g.send_counts]
+        recv_split = [int(c) for c in g.recv_counts]
+        return dist.all_to_all_single(recv[: sum(recv_split)], send[: sum(send_split)], output_split_sizes=recv_split,
+                                      input_split_sizes=send_split, group=self.group, async_op=True)
+
+
+class PeerTransport(CollectiveTransport):
+    """Row exchange by peer-to-peer copies over NVLink, driven by the copy engines.
+
+    An NCCL collective runs as a kernel, and the aggregation kernels are persistent grids that
     fill every SM: whichever starts first keeps the other waiting, so nothing overlaps.  Here every
-    rank publishes its shard in a buffer its peers can map (``torch.distributed`` symmetric
-    memory) and pulls the P-1 remote shards into its local gather buffer with plain device-to-device
-    copies on a side stream; those are DMA transfers that need no SM, so they proceed underneath
-    the interior aggregation, and the halo entries of each source rank are aggregated as soon as
-    that rank's shard has arrived (one event per pull).  Two small barriers order the exchange: one
-    after the shard is published (before anyone pulls), one after the pulls (before the shard may be
-    overwritten).
+    rank packs the rows its peers asked for into a buffer the peers can map (``torch.distributed``
+    symmetric memory) and each rank pulls its segments with plain device-to-device copies on a side
+    stream; those are DMA transfers that need no SM, so they proceed underneath the interior
+    aggregation.  Two small barriers order the exchange: one after the buffers are packed (before
+    anyone pulls), one after the pulls (before a buffer may be packed again).
     """
 
     BARRIER_TIMEOUT_MS = 20000
 
-    def __init__(self, part, rank, group=None):
+    def __init__(self, group=None):
         import torch.distributed._symmetric_memory as symm
         self._symm = symm
-        self.part, self.rank = part, rank
-        self.group = group if group is not None else dist.group.WORLD
-        self.sides = [torch.cuda.Stream() for _ in range(max(1, int(os.environ.get("JG_PEER_STREAMS", "1"))))]
+        self.group = group                                                # set-up collectives
+        self.symm_group = group if group is not None else dist.group.WORLD
+        self.side = torch.cuda.Stream()
         self._bufs = {}
 
-    def buffer(self, f, device):
-        """The rank's publishable feature shard of width ``f`` (``pad`` rows; write features here to
-        skip one copy per aggregation)."""
-        entry = self._bufs.get(f)
+    def send_buffer(self, rows, f, like):
+        """Symmetric buffer of ``rows`` x ``f`` (the same shape on every rank)."""
+        rows = max(rows, 1)
+        entry = self._bufs.get((rows, f))
         if entry is None:
-            t = self._symm.empty((self.part.pad, f), dtype=torch.float32, device=device)
-            t.zero_()
-            hdl = self._symm.rendezvous(t, self.group.group_name)
+            t = self._symm.empty((rows, f), dtype=torch.float32, device=like.device)
+            hdl = self._symm.rendezvous(t, self.symm_group.group_name)
             entry = (t, hdl)
-            self._bufs[f] = entry
-        return entry
+            self._bufs[(rows, f)] = entry
+        return entry[0]
 
-    def start(self, xp, full):
-        f = xp.shape[1]
-        buf, hdl = self.buffer(f, xp.device)
-        if xp.data_ptr() != buf.data_ptr():
-            buf.copy_(xp)
-        hdl.barrier(channel=0, timeout_ms=self.BARRIER_TIMEOUT_MS)       # every shard is published
+    def exchange(self, g, send, recv, f):
+        hdl = self._bufs[(send.shape[0], f)][1]
+        hdl.barrier(channel=0, timeout_ms=self.BARRIER_TIMEOUT_MS)       # every send buffer is packed
         cur = torch.cuda.current_stream()
-        pad, world = self.part.pad, self.part.world
-        events = {}
-        for k, q in enumerate(self.order()):
-            side = self.sides[k % len(self.sides)]                       # two pulls in flight
-            if k < len(self.sides):
-                side.wait_stream(cur)
-            with torch.cuda.stream(side):
-                peer = hdl.get_buffer(q, (pad, f), torch.float32)
-                full[q * pad:(q + 1) * pad].copy_(peer)
-                events[q] = side.record_event()
-        return _PeerHandle(self, hdl, cur, events)
-
-    def order(self):
-        """Peers in the order their shards are pulled: staggered so that no two ranks start on the
-        same peer."""
-        return [(self.rank + step) % self.part.world for step in range(1, self.part.world)]
+        self.side.wait_stream(cur)
+        world, rank = g.part.world, g.rank
+        with torch.cuda.stream(self.side):
+            for step in range(1, world):
+                q = (rank + step) % world                                  # staggered: no two ranks start on the same peer
+                n = int(g.recv_counts[q])
+                if n == 0:
+                    continue
+                peer = hdl.get_buffer(q, tuple(send.shape), torch.float32)
+                src0 = int(g.peer_send_offset[q])                          # where rank q packed the rows meant for this rank
+                dst0 = int(g.recv_offset[q])
+                recv[dst0:dst0 + n].copy_(peer[src0:src0 + n])
+        return _PeerHandle(self, hdl, cur)
 
 
 class _PeerHandle:
-    def __init__(self, ex, hdl, cur, events):
-        self.ex, self.hdl, self.cur, self.events = ex, hdl, cur, events
-
-    def wait_peer(self, q):
-        """Orders later work on the calling stream after the shard of rank ``q`` has arrived."""
-        self.cur.wait_event(self.events[q])
+    def __init__(self, tr, hdl, cur):
+        self.tr, self.hdl, self.cur = tr, hdl, cur
 
     def wait(self):
-        for side in self.ex.sides:
-            self.cur.wait_stream(side)
-        self.hdl.barrier(channel=1, timeout_ms=PeerExchange.BARRIER_TIMEOUT_MS)   # every pull has finished
+        self.cur.wait_stream(self.tr.side)
+        self.hdl.barrier(channel=1, timeout_ms=PeerTransport.BARRIER_TIMEOUT_MS)   # every pull has finished
 
 
 class ShardedGraph:
     """One rank's share of a row-partitioned graph: the in-edges of its destination rows.
 
     ``idx`` holds GLOBAL source ids, ``off`` the offsets of the rank's own rows (CSC of the shard).
+    Construction is collective (every rank of the group builds its graph at the same time): the
+    ranks tell each other which rows they need.
     """
 
-    def __init__(self, part, rank, idx, off, w, backend=None, group=None, exchange="nccl"):
+    def __init__(self, part, rank, idx, off, w, backend=None, group=None, exchange="nccl", transport=None,
+                 setup=True):
         self.part, self.rank, self.group = part, rank, group
         self.backend = backend or DeviceBackend()
-        self.exchange = PeerExchange(part, rank, group) if exchange == "peer" else None
         self.lo, self.hi = part.range(rank)
         self.n_local = self.hi - self.lo
         if off.numel() != self.n_local + 1:
             raise RuntimeError(f"offsets describe {off.numel() - 1} rows, the rank owns {self.n_local}")
-        self.interior, self.halo = self.backend.split(idx, off, w, self.lo, self.hi)
+        if transport is None:
+            transport = PeerTransport(group) if exchange == "peer" else CollectiveTransport(group)
+        self.transport = transport
+        self.interior, halo = self.backend.split(idx, off, w, self.lo, self.hi)
         self.interior_plan = self.backend.plan(self.interior[1], self.interior[0].numel())
+        # compact halo: distinct remote rows, ascending (= grouped by owner), and the halo entries
+        # re-addressed into the packed buffer those rows will arrive in
+        self.needed, halo_idx, self.recv_counts = self.backend.halo_map(halo[0], part.n, part.bounds)
+        self.halo = (halo_idx, halo[1], halo[2])
         self.halo_plan = self.backend.plan(self.halo[1], self.halo[0].numel())
-        # Optional (JG_HALO_PIPELINE=1): halo entries grouped by the rank that owns their source row
-        # (ids rebased to that rank's shard), in pull order, so that each group can be aggregated as
-        # soon as its shard has arrived.  Off by default: on 4 GPUs the aggregation kernels running
-        # underneath the remaining pulls slowed both down (16.7 ms against 10.4 ms per sweep).
-        self.halo_groups = []
-        if self.exchange is not None and os.environ.get("JG_HALO_PIPELINE", "0") == "1":
-            rest = self.halo
-            for q in self.exchange.order():
-                q_lo, q_hi = part.range(q)
-                mine, rest = self.backend.split(rest[0], rest[1], rest[2], q_lo, q_hi)
-                self.halo_groups.append((q, mine, self.backend.plan(mine[1], mine[0].numel())))
-        self._full = {}
+        self.recv_offset = [sum(self.recv_counts[:q]) for q in range(part.world)]
+        self.n_halo = sum(self.recv_counts)
+        self._recv = {}
+        if setup:
+            self._setup_requests()
 
-    def _gather_buffer(self, f, like):
-        key = (f, like.device, like.dtype)
-        buf = self._full.get(key)
+    # ---- set-up: who sends which rows to whom
+    def _setup_requests(self):
+        dev = self.needed.device
+        counts = torch.tensor(self.recv_counts, dtype=torch.int64, device=dev)
+        matrix = self.transport.all_gather_counts(self, counts)           # matrix[r][q] = rows rank r needs from rank q
+        send_counts = [int(matrix[r][self.rank]) for r in range(self.part.world)]
+        send_rows = self.transport.all_to_all_ids(self, self.needed, self.recv_counts, send_counts)
+        self.apply_setup(matrix, send_rows)
+
+    def apply_setup(self, matrix, send_rows):
+        """``matrix[r][q]`` = rows rank r needs from rank q; ``send_rows`` = the global ids of this
+        rank's rows its peers asked for, grouped by requesting rank in rank order."""
+        world = self.part.world
+        self.count_matrix = matrix
+        self.send_counts = [int(matrix[r][self.rank]) for r in range(world)]
+        self.send_offset = [sum(self.send_counts[:r]) for r in range(world)]
+        # in rank q's send buffer the rows for rank r start after those for ranks 0..r-1
+        self.peer_send_offset = [sum(int(matrix[r2][q]) for r2 in range(self.rank)) for q in range(world)]
+        self.n_send = sum(self.send_counts)
+        self.max_send = max(sum(int(matrix[r][q]) for r in range(world)) for q in range(world))
+        self.send_rows = send_rows
+
+    # ---- per aggregation
+    def feature_buffer(self, f, like):
+        """Where a caller may write the rank's feature rows; any tensor with ``n_local`` rows works."""
+        return torch.empty((self.n_local, f), dtype=like.dtype, device=like.device)
+
+    def _recv_buffer(self, f, like):
+        buf = self._recv.get(f)
         if buf is None:
-            buf = torch.empty((self.part.world * self.part.pad, f), dtype=like.dtype, device=like.device)
-            self._full[key] = buf
+            buf = torch.empty((max(self.n_halo, 1), f), dtype=like.dtype, device=like.device)
+            self._recv[f] = buf
         return buf
 
-    def _padded(self, x):
-        if x.shape[0] == self.part.pad:
-            return x
-        if x.shape[0] != self.n_local:
+    def aggregate(self, x):
+        """``y[v] = sum_{(u -> v)} w * x_global[u]`` for the rank's own rows ``v``; ``x`` holds the
+        rank's ``n_local`` rows of the feature matrix (extra rows are ignored)."""
+        if x.shape[0] < self.n_local:
             raise RuntimeError(f"x has {x.shape[0]} rows, the rank owns {self.n_local}")
-        xp = torch.zeros((self.part.pad, x.shape[1]), dtype=x.dtype, device=x.device)
-        xp[: self.n_local] = x
-        return xp
-
-    def aggregate(self, x, gather=None):
-        """``y[v] = sum_{(u -> v)} w * x_global[u]`` for the rank's own rows ``v``.
-
-        ``x`` holds the rank's rows of the feature matrix (``n_local`` rows, or ``pad`` rows with
-        a zero tail).  ``gather(shard, full)`` fills ``full`` with every rank's padded shard and
-        returns a handle whose ``wait()`` orders later work after it; the default is the
-        copy-engine peer exchange (``exchange="peer"``) or an asynchronous
-        ``all_gather_into_tensor`` on the process group (``exchange="nccl"``)."""
         f = x.shape[1]
-        xp = self._padded(x)
-        full = self._gather_buffer(f, xp)
-        if gather is None and self.exchange is not None:
-            handle = self.exchange.start(xp, full)
-        elif gather is None:
-            handle = dist.all_gather_into_tensor(full, xp, group=self.group, async_op=True)
-        else:
-            handle = gather(xp, full)
-        # the rank's own rows while the shards travel
-        y = self.backend.aggregate(xp, self.interior[0], self.interior[1], self.interior[2], self.n_local,
+        recv = self._recv_buffer(f, x)
+        send = self.transport.send_buffer(self.max_send, f, x)
+        if self.n_send:
+            self.backend.gather_rows(x, self.send_rows, self.lo, send)       # rows the peers asked for
+        handle = self.transport.exchange(self, send, recv, f)
+        # the rank's own rows while the halo rows travel
+        y = self.backend.aggregate(x, self.interior[0], self.interior[1], self.interior[2], self.n_local,
                                    self.interior_plan)
-        if self.halo_groups and hasattr(handle, "wait_peer"):
-            pad = self.part.pad
-            for q, grp, plan in self.halo_groups:
-                handle.wait_peer(q)
-                if grp[0].numel():
-                    self.backend.aggregate(full[q * pad:(q + 1) * pad], grp[0], grp[1], grp[2], self.n_local, plan,
-                                           out=y, accumulate=True)
-            handle.wait()
-            return y
-        if handle is not None:
-            handle.wait()
+        handle.wait()
         if self.halo[0].numel():
-            self.backend.aggregate(full, self.halo[0], self.halo[1], self.halo[2], self.n_local, self.halo_plan,
+            self.backend.aggregate(recv, self.halo[0], self.halo[1], self.halo[2], self.n_local, self.halo_plan,
                                    out=y, accumulate=True)
         return y
 

@@ -29,6 +29,17 @@ class OracleBackend:
             return torch.from_numpy((idx[mask] - rebase).astype(np.int32)), torch.from_numpy(o), torch.from_numpy(w[mask])
         return part(inside, lo), part(~inside, 0)
 
+    def halo_map(self, halo_idx, n_global, bounds):
+        idx = halo_idx.numpy()
+        needed = np.unique(idx)
+        remapped = np.searchsorted(needed, idx).astype(np.int32)
+        counts = [int(((needed >= bounds[q]) & (needed < bounds[q + 1])).sum()) for q in range(len(bounds) - 1)]
+        return torch.from_numpy(needed.astype(np.int32)), torch.from_numpy(remapped), counts
+
+    def gather_rows(self, x, rows, rebase, out):
+        out[: rows.numel()] = x[(rows.long() - rebase)]
+        return out
+
     def plan(self, off, nnz):
         return None
 
@@ -66,6 +77,12 @@ def worker(rank, world, port, n, E, f, q):
         # interior and halo together hold every entry of the shard exactly once
         assert g.interior[0].numel() + g.halo[0].numel() == l_idx.numel()
         assert g.interior[0].numel() == 0 or int(g.interior[0].max()) < hi - lo
+        # only referenced remote rows travel, each once; requests and deliveries agree
+        assert g.n_halo == g.needed.numel() <= n - (hi - lo)
+        assert g.halo[0].numel() == 0 or int(g.halo[0].max()) < g.n_halo
+        assert all(lo <= int(v) < hi for v in g.send_rows.tolist())
+        y_again = g.aggregate(torch.from_numpy(x[lo:hi].copy()))
+        assert torch.equal(y, y_again)
         q.put((rank, lo, hi, y.numpy()))
     except Exception as exc:  # surface the failure in the parent instead of a queue timeout
         q.put((rank, -1, -1, repr(exc)))

@@ -24,6 +24,42 @@ def make_graph(seed, n, E, f, hubs=3, hub_deg=3000):
     return src[order].astype(np.int32), off, w[order], x
 
 
+class Loopback:
+    """Stands in for the process group when the ranks of a partition are emulated one after another
+    on one GPU: requests and row segments are handed over by plain copies."""
+
+    def __init__(self):
+        self.graphs, self.features = [], []
+
+    def send_buffer(self, rows, f, like):
+        return torch.empty((max(rows, 1), f), dtype=like.dtype, device=like.device)
+
+    def wire(self):
+        world = len(self.graphs)
+        matrix = [list(g.recv_counts) for g in self.graphs]
+        for q, g in enumerate(self.graphs):
+            parts = []
+            for r, h in enumerate(self.graphs):
+                s0 = h.recv_offset[q]
+                parts.append(h.needed[s0:s0 + h.recv_counts[q]])
+            g.apply_setup(matrix, torch.cat(parts) if parts else g.needed[:0])
+
+    def exchange(self, g, send, recv, f):
+        for q, h in enumerate(self.graphs):
+            n = g.recv_counts[q]
+            if q == g.rank or n == 0:
+                continue
+            packed = torch.empty((max(h.n_send, 1), f), device=recv.device)
+            h.backend.gather_rows(self.features[q], h.send_rows, h.lo, packed)
+            src0 = g.peer_send_offset[q]
+            recv[g.recv_offset[q]:g.recv_offset[q] + n] = packed[src0:src0 + n]
+
+        class Done:
+            def wait(self):
+                pass
+        return Done()
+
+
 @pytest.mark.parametrize("world,n,f", [(2, 5001, 128), (4, 4096, 32), (8, 3000, 7)])
 def test_emulated_ranks_on_one_gpu(cuda, oracle, world, n, f):
     from jittorgeometric_b200 import dist as jd
@@ -33,30 +69,31 @@ def test_emulated_ranks_on_one_gpu(cuda, oracle, world, n, f):
     part = jd.RowPartition(n, world)
     t = lambda a: torch.from_numpy(a).cuda()
     idx_t, off_t, w_t = t(idx), t(off), t(w)
-    x_full = torch.zeros((world * part.pad, f), device="cuda")
-    x_full[:n] = t(x)
-
-    def local_copy(shard, full):
-        full.copy_(x_full)          # stands in for the all-gather
-        return None
-
+    loop = Loopback()
     for rank in range(world):
         lo, hi = part.range(rank)
-        g = jd.ShardedGraph(part, rank, *jd.shard_rows(idx_t, off_t, w_t, part, rank))
-        # split: order inside a row preserved, ids rebased / kept, nothing lost
-        li, lo_off = g.interior[0].cpu().numpy(), g.interior[1].cpu().numpy()
-        hi_idx, h_off = g.halo[0].cpu().numpy(), g.halo[1].cpu().numpy()
+        loop.graphs.append(jd.ShardedGraph(part, rank, *jd.shard_rows(idx_t, off_t, w_t, part, rank), transport=loop,
+                                           setup=False))
+        loop.features.append(t(x[lo:hi].copy()))
+    loop.wire()
+    for rank, g in enumerate(loop.graphs):
+        lo, hi = part.range(rank)
+        # split: order inside a row preserved, interior ids rebased, nothing lost
         s, e = off[lo], off[hi]
         loc = idx[s:e]
         inside = (loc >= lo) & (loc < hi)
-        assert np.array_equal(li, loc[inside] - lo) and np.array_equal(hi_idx, loc[~inside])
+        assert np.array_equal(g.interior[0].cpu().numpy(), loc[inside] - lo)
         seg = np.repeat(np.arange(hi - lo), np.diff(off[lo:hi + 1]))
-        assert np.array_equal(np.diff(lo_off), np.bincount(seg[inside], minlength=hi - lo))
-        assert np.array_equal(np.diff(h_off), np.bincount(seg[~inside], minlength=hi - lo))
-        y = g.aggregate(t(x[lo:hi].copy()), gather=local_copy).cpu().numpy()
+        assert np.array_equal(np.diff(g.interior[1].cpu().numpy()), np.bincount(seg[inside], minlength=hi - lo))
+        assert np.array_equal(np.diff(g.halo[1].cpu().numpy()), np.bincount(seg[~inside], minlength=hi - lo))
+        # compact halo: the distinct remote rows, ascending, and the halo entries re-addressed into them
+        needed = np.unique(loc[~inside])
+        assert np.array_equal(g.needed.cpu().numpy(), needed)
+        assert np.array_equal(needed[g.halo[0].cpu().numpy()], loc[~inside])
+        assert g.recv_counts == [int(((needed >= part.bounds[q]) & (needed < part.bounds[q + 1])).sum()) for q in range(world)]
+        y = g.aggregate(loop.features[rank]).cpu().numpy()
         assert (np.abs(y - want[lo:hi]) / (scale[lo:hi] + 1e-30)).max() <= 1e-5
-        y2 = g.aggregate(t(x[lo:hi].copy()), gather=local_copy).cpu().numpy()
-        assert np.array_equal(y, y2)
+        assert np.array_equal(y, g.aggregate(loop.features[rank]).cpu().numpy())
 
 
 def test_accumulate_mode(cuda, oracle):
