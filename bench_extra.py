@@ -192,7 +192,7 @@ def run_gcn(args):
     b1, b2 = torch.zeros(128, device=dev), torch.zeros(64, device=dev)
     if world > 1:
         g = jd.ShardedGraph(part, rank, *jd.shard_rows(csc.row_indices, csc.column_offset, csc.edge_weight, part, rank),
-                            exchange=os.environ.get("JG_EXCHANGE", "peer"))
+                            exchange=os.environ.get("JG_EXCHANGE", "peer"), mode=os.environ.get("JG_DIST_MODE", "merged"))
         del csc
         n_local = g.n_local
     else:

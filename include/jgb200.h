@@ -91,18 +91,21 @@ int jg_partition_split(const int32_t* idx, const int32_t* off, const float* w, i
                        int32_t* halo_off, float* halo_w, int64_t* out_counts, void* workspace, size_t workspace_bytes,
                        jg_stream_t stream);
 
-/* Compact halo.  jg_halo_map_build takes the halo entries of a shard (GLOBAL source ids, from
- * jg_partition_split) and produces: pos[n_global + 1], the exclusive scan of "row g is referenced"
- * (pos[g] = slot of row g in a packed halo buffer ordered by global id, pos[n_global] = number of
- * distinct rows needed); needed[pos[n_global]], those rows ascending (grouped by owner, since owners
- * hold contiguous ranges); remapped_idx[nnz] = pos[halo_idx[e]], the halo entries re-addressed into
- * the packed buffer.  jg_gather_rows_f32 packs out[i,:] = x[rows[i] - rebase,:], the kernel a rank
+/* Compact halo.  jg_halo_map_build takes entries of a shard with GLOBAL source ids (all of them, or
+ * only the halo entries from jg_partition_split) and the shard's own row range [lo, hi), and
+ * produces: pos[n_global + 1], the exclusive scan of "remote row g is referenced" (pos[g] = slot of
+ * row g in a packed halo buffer ordered by global id, pos[n_global] = number of distinct remote rows
+ * needed); needed[pos[n_global]], those rows ascending (grouped by owner, since owners hold
+ * contiguous ranges); remapped_idx[nnz]: own rows become idx - lo, remote rows base + pos[idx]
+ * (base = where the halo rows start in the buffer the aggregation will read; lo = hi = base = 0
+ * re-addresses pure halo entries into the packed buffer alone).  jg_gather_rows_f32 packs out[i,:] = x[rows[i] - rebase,:], the kernel a rank
  * uses to fill the send buffer with the rows another rank asked for.  Together they replace the
  * whole-block broadcast of the reference (ops/distspmm.py:31-39) by an exchange of referenced rows
  * only. */
 size_t jg_halo_map_workspace_bytes(int64_t n_global);
-int jg_halo_map_build(const int32_t* halo_idx, int64_t nnz, int64_t n_global, int32_t* pos, int32_t* needed,
-                      int32_t* remapped_idx, void* workspace, size_t workspace_bytes, jg_stream_t stream);
+int jg_halo_map_build(const int32_t* halo_idx, int64_t nnz, int64_t n_global, int32_t lo, int32_t hi, int32_t base,
+                      int32_t* pos, int32_t* needed, int32_t* remapped_idx, void* workspace, size_t workspace_bytes,
+                      jg_stream_t stream);
 int jg_gather_rows_f32(float* out, const float* x, const int32_t* rows, int64_t n_rows, int64_t f, int32_t rebase,
                        jg_stream_t stream);
 

@@ -34,7 +34,7 @@ SIGNATURES = {
     "jg_partition_split_workspace_bytes": (sz, [i64]),
     "jg_partition_split": (ctypes.c_int, [vp, vp, vp, i64, i64, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
     "jg_halo_map_workspace_bytes": (sz, [i64]),
-    "jg_halo_map_build": (ctypes.c_int, [vp, i64, i64, vp, vp, vp, vp, sz, vp]),
+    "jg_halo_map_build": (ctypes.c_int, [vp, i64, i64, i32, i32, i32, vp, vp, vp, vp, sz, vp]),
     "jg_gather_rows_f32": (ctypes.c_int, [vp, vp, vp, i64, i64, i32, vp]),
     "jg_convert_workspace_bytes": (sz, [i64, i64]),
     "jg_coo_to_compressed": (ctypes.c_int, [vp, vp, i64, i64, ctypes.c_int, ctypes.c_int, vp, vp, vp, vp, sz, vp]),

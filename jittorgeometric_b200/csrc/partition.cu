@@ -13,15 +13,22 @@
 
 namespace jg {
 
-__global__ void mark_rows_kernel(const int32_t* __restrict__ idx, int64_t nnz, int* __restrict__ flag) {
-    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < nnz; e += (int64_t)gridDim.x * blockDim.x)
-        flag[idx[e]] = 1;   // benign race: every writer stores the same value
+// Rows inside [lo, hi) are the shard's own and are not marked.
+__global__ void mark_rows_kernel(const int32_t* __restrict__ idx, int64_t nnz, int32_t lo, int32_t hi,
+                                 int* __restrict__ flag) {
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < nnz; e += (int64_t)gridDim.x * blockDim.x) {
+        const int32_t s = idx[e];
+        if (s < lo || s >= hi) flag[s] = 1;   // benign race: every writer stores the same value
+    }
 }
 
-__global__ void remap_kernel(const int32_t* __restrict__ idx, const int* __restrict__ pos, int64_t nnz,
-                             int32_t* __restrict__ out) {
-    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < nnz; e += (int64_t)gridDim.x * blockDim.x)
-        out[e] = pos[idx[e]];
+// own rows -> idx - lo, remote rows -> base + slot in the packed halo buffer
+__global__ void remap_kernel(const int32_t* __restrict__ idx, const int* __restrict__ pos, int64_t nnz, int32_t lo,
+                             int32_t hi, int32_t base, int32_t* __restrict__ out) {
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < nnz; e += (int64_t)gridDim.x * blockDim.x) {
+        const int32_t s = idx[e];
+        out[e] = (s >= lo && s < hi) ? s - lo : base + pos[s];
+    }
 }
 
 // needed[pos[g]] = g for every marked global id g (ascending, because pos is an exclusive scan)
@@ -75,9 +82,10 @@ size_t jg_halo_map_workspace_bytes(int64_t n_global) {
     return carve_halo_map(nullptr, n_global).bytes;
 }
 
-int jg_halo_map_build(const int32_t* halo_idx, int64_t nnz, int64_t n_global, int32_t* pos, int32_t* needed,
-                      int32_t* remapped_idx, void* workspace, size_t workspace_bytes, jg_stream_t stream) {
-    JG_CHECK_ARG(nnz >= 0 && n_global >= 0, JG_EINVAL, "halo_map_build: negative size");
+int jg_halo_map_build(const int32_t* halo_idx, int64_t nnz, int64_t n_global, int32_t lo, int32_t hi, int32_t base,
+                      int32_t* pos, int32_t* needed, int32_t* remapped_idx, void* workspace, size_t workspace_bytes,
+                      jg_stream_t stream) {
+    JG_CHECK_ARG(nnz >= 0 && n_global >= 0 && lo <= hi, JG_EINVAL, "halo_map_build: bad size or range");
     JG_CHECK_ARG(pos && (nnz == 0 || (halo_idx && needed && remapped_idx)), JG_EINVAL, "halo_map_build: null pointer");
     JG_CHECK_ARG(n_global < INT32_MAX && nnz <= INT32_MAX, JG_ESHAPE, "halo_map_build: sizes beyond int32");
     JG_CHECK_ARG(workspace && workspace_bytes >= jg_halo_map_workspace_bytes(n_global), JG_EWORKSPACE,
@@ -87,7 +95,7 @@ int jg_halo_map_build(const int32_t* halo_idx, int64_t nnz, int64_t n_global, in
     const int grid = sm_count() * 8;
     JG_CUDA(cudaMemsetAsync(ws.flag, 0, sizeof(int) * (size_t)(n_global + 1), st));
     if (nnz > 0) {
-        mark_rows_kernel<<<grid, 256, 0, st>>>(halo_idx, nnz, ws.flag);
+        mark_rows_kernel<<<grid, 256, 0, st>>>(halo_idx, nnz, lo, hi, ws.flag);
         JG_LAUNCH_CHECK();
     }
     int rc = exclusive_scan(ws.flag, reinterpret_cast<int*>(pos), n_global + 1, ws.sums, st);
@@ -95,7 +103,7 @@ int jg_halo_map_build(const int32_t* halo_idx, int64_t nnz, int64_t n_global, in
     if (nnz > 0) {
         list_marked_kernel<<<grid, 256, 0, st>>>(ws.flag, reinterpret_cast<const int*>(pos), n_global, needed);
         JG_LAUNCH_CHECK();
-        remap_kernel<<<grid, 256, 0, st>>>(halo_idx, reinterpret_cast<const int*>(pos), nnz, remapped_idx);
+        remap_kernel<<<grid, 256, 0, st>>>(halo_idx, reinterpret_cast<const int*>(pos), nnz, lo, hi, base, remapped_idx);
         JG_LAUNCH_CHECK();
     }
     return JG_OK;

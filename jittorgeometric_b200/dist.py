@@ -68,16 +68,17 @@ class DeviceBackend:
         ni, nh = (int(v) for v in counts.tolist())
         return (ii[:ni].clone(), io[: n_rows + 1], iw[:ni].clone()), (hi_[:nh].clone(), ho[: n_rows + 1], hw[:nh].clone())
 
-    def halo_map(self, halo_idx, n_global, bounds):
-        """Distinct remote rows a shard references: ``(needed ids ascending, halo indices re-addressed
-        into the packed buffer, rows needed from every owner)``."""
+    def halo_map(self, halo_idx, n_global, bounds, lo=0, hi=0, base=0):
+        """Distinct remote rows a shard references: ``(needed ids ascending, indices re-addressed -
+        own rows [lo, hi) to ``idx - lo``, remote rows to ``base`` + slot in the packed halo buffer -
+        and the rows needed from every owner)``."""
         nnz, dev = halo_idx.numel(), halo_idx.device
         pos = torch.empty(n_global + 1, dtype=torch.int32, device=dev)
         needed = torch.empty(max(min(nnz, n_global), 1), dtype=torch.int32, device=dev)
         remapped = torch.empty(max(nnz, 1), dtype=torch.int32, device=dev)
         ws = workspace(lib().jg_halo_map_workspace_bytes(n_global), dev)
-        check(lib().jg_halo_map_build(ptr(halo_idx), nnz, n_global, ptr(pos), ptr(needed), ptr(remapped), ptr(ws),
-                                      ws.numel(), stream_for(halo_idx)), "jg_halo_map_build")
+        check(lib().jg_halo_map_build(ptr(halo_idx), nnz, n_global, int(lo), int(hi), int(base), ptr(pos), ptr(needed),
+                                      ptr(remapped), ptr(ws), ws.numel(), stream_for(halo_idx)), "jg_halo_map_build")
         at = pos[torch.tensor(bounds, device=dev, dtype=torch.long)].tolist()
         counts = [at[q + 1] - at[q] for q in range(len(bounds) - 1)]
         return needed[: at[-1]].clone(), remapped[:nnz].clone(), counts
@@ -206,7 +207,7 @@ class ShardedGraph:
     """
 
     def __init__(self, part, rank, idx, off, w, backend=None, group=None, exchange="nccl", transport=None,
-                 setup=True):
+                 setup=True, mode="merged"):
         self.part, self.rank, self.group = part, rank, group
         self.backend = backend or DeviceBackend()
         self.lo, self.hi = part.range(rank)
@@ -216,13 +217,26 @@ class ShardedGraph:
         if transport is None:
             transport = PeerTransport(group) if exchange == "peer" else CollectiveTransport(group)
         self.transport = transport
-        self.interior, halo = self.backend.split(idx, off, w, self.lo, self.hi)
-        self.interior_plan = self.backend.plan(self.interior[1], self.interior[0].numel())
-        # compact halo: distinct remote rows, ascending (= grouped by owner), and the halo entries
-        # re-addressed into the packed buffer those rows will arrive in
-        self.needed, halo_idx, self.recv_counts = self.backend.halo_map(halo[0], part.n, part.bounds)
-        self.halo = (halo_idx, halo[1], halo[2])
-        self.halo_plan = self.backend.plan(self.halo[1], self.halo[0].numel())
+        if mode not in ("merged", "overlap"):
+            raise ValueError("mode must be 'merged' or 'overlap'")
+        self.mode = mode
+        if mode == "overlap":
+            # own-source entries aggregated while the halo rows travel, halo entries added afterwards
+            self.interior, halo = self.backend.split(idx, off, w, self.lo, self.hi)
+            self.interior_plan = self.backend.plan(self.interior[1], self.interior[0].numel())
+            # compact halo: distinct remote rows, ascending (= grouped by owner), and the halo entries
+            # re-addressed into the packed buffer those rows will arrive in
+            self.needed, halo_idx, self.recv_counts = self.backend.halo_map(halo[0], part.n, part.bounds)
+            self.halo = (halo_idx, halo[1], halo[2])
+            self.halo_plan = self.backend.plan(self.halo[1], self.halo[0].numel())
+        else:
+            # one aggregation over one buffer [own rows | packed halo rows]: every entry keeps its
+            # place in its row, so each row is summed in exactly the order the unpartitioned graph
+            # sums it, once, with no second pass over the output
+            self.needed, m_idx, self.recv_counts = self.backend.halo_map(idx, part.n, part.bounds, self.lo, self.hi,
+                                                                         self.n_local)
+            self.merged = (m_idx, off, w)
+            self.merged_plan = self.backend.plan(off, idx.numel())
         self.recv_offset = [sum(self.recv_counts[:q]) for q in range(part.world)]
         self.n_halo = sum(self.recv_counts)
         self._recv = {}
@@ -253,13 +267,17 @@ class ShardedGraph:
 
     # ---- per aggregation
     def feature_buffer(self, f, like):
-        """Where a caller may write the rank's feature rows; any tensor with ``n_local`` rows works."""
+        """Where a caller should write the rank's feature rows to save a copy per aggregation (the
+        head of the buffer the merged aggregation reads); any tensor with ``n_local`` rows works."""
+        if self.mode == "merged":
+            return self._recv_buffer(f, like)[: self.n_local]
         return torch.empty((self.n_local, f), dtype=like.dtype, device=like.device)
 
     def _recv_buffer(self, f, like):
         buf = self._recv.get(f)
         if buf is None:
-            buf = torch.empty((max(self.n_halo, 1), f), dtype=like.dtype, device=like.device)
+            rows = self.n_halo + (self.n_local if self.mode == "merged" else 0)
+            buf = torch.empty((max(rows, 1), f), dtype=like.dtype, device=like.device)
             self._recv[f] = buf
         return buf
 
@@ -269,10 +287,18 @@ class ShardedGraph:
         if x.shape[0] < self.n_local:
             raise RuntimeError(f"x has {x.shape[0]} rows, the rank owns {self.n_local}")
         f = x.shape[1]
-        recv = self._recv_buffer(f, x)
+        buf = self._recv_buffer(f, x)
         send = self.transport.send_buffer(self.max_send, f, x)
         if self.n_send:
             self.backend.gather_rows(x, self.send_rows, self.lo, send)       # rows the peers asked for
+        if self.mode == "merged":
+            handle = self.transport.exchange(self, send, buf[self.n_local:], f)
+            if x.data_ptr() != buf.data_ptr():
+                buf[: self.n_local].copy_(x[: self.n_local])
+            handle.wait()
+            return self.backend.aggregate(buf, self.merged[0], self.merged[1], self.merged[2], self.n_local,
+                                          self.merged_plan)
+        recv = buf
         handle = self.transport.exchange(self, send, recv, f)
         # the rank's own rows while the halo rows travel
         y = self.backend.aggregate(x, self.interior[0], self.interior[1], self.interior[2], self.n_local,

@@ -24,15 +24,15 @@ def run(args):
     part = jd.RowPartition(n, world)
     exchange = os.environ.get("JG_EXCHANGE", "peer")
     g = jd.ShardedGraph(part, rank, *jd.shard_rows(csc.row_indices, csc.column_offset, csc.edge_weight, part, rank),
-                        exchange=exchange)
-    local_nnz = g.interior[0].numel() + g.halo[0].numel()
+                        exchange=exchange, mode=os.environ.get("JG_DIST_MODE", "merged"))
+    local_nnz = int(g.merged[0].numel()) if g.mode == "merged" else g.interior[0].numel() + g.halo[0].numel()
     halo_rows, remote_rows = g.n_halo, n - g.n_local
     del csc
     torch.cuda.empty_cache()
     gen = torch.Generator(device=dev); gen.manual_seed(bench.SEED + 17 * rank)
     xs = {}
     for f in widths:
-        x = torch.zeros((max(g.n_local, 1), f), device=dev)
+        x = g.feature_buffer(f, torch.empty(0, device=dev))     # the head of the buffer the aggregation reads
         x[: g.n_local] = torch.randn((g.n_local, f), generator=gen, device=dev)
         xs[f] = x
 

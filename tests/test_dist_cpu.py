@@ -29,10 +29,11 @@ class OracleBackend:
             return torch.from_numpy((idx[mask] - rebase).astype(np.int32)), torch.from_numpy(o), torch.from_numpy(w[mask])
         return part(inside, lo), part(~inside, 0)
 
-    def halo_map(self, halo_idx, n_global, bounds):
+    def halo_map(self, halo_idx, n_global, bounds, lo=0, hi=0, base=0):
         idx = halo_idx.numpy()
-        needed = np.unique(idx)
-        remapped = np.searchsorted(needed, idx).astype(np.int32)
+        own = (idx >= lo) & (idx < hi)
+        needed = np.unique(idx[~own])
+        remapped = np.where(own, idx - lo, base + np.searchsorted(needed, idx)).astype(np.int32)
         counts = [int(((needed >= bounds[q]) & (needed < bounds[q + 1])).sum()) for q in range(len(bounds) - 1)]
         return torch.from_numpy(needed.astype(np.int32)), torch.from_numpy(remapped), counts
 
@@ -62,7 +63,7 @@ def make_graph(seed, n, E, f):
     return src[order].astype(np.int32), off, w[order], x
 
 
-def worker(rank, world, port, n, E, f, q):
+def worker(rank, world, port, n, E, f, q, mode):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
     from jittorgeometric_b200 import dist as jd
@@ -72,14 +73,18 @@ def worker(rank, world, port, n, E, f, q):
         part = jd.RowPartition(n, world)
         lo, hi = part.range(rank)
         l_idx, l_off, l_w = jd.shard_rows(torch.from_numpy(idx), torch.from_numpy(off), torch.from_numpy(w), part, rank)
-        g = jd.ShardedGraph(part, rank, l_idx, l_off, l_w, backend=OracleBackend())
+        g = jd.ShardedGraph(part, rank, l_idx, l_off, l_w, backend=OracleBackend(), mode=mode)
         y = g.aggregate(torch.from_numpy(x[lo:hi].copy()))
-        # interior and halo together hold every entry of the shard exactly once
-        assert g.interior[0].numel() + g.halo[0].numel() == l_idx.numel()
-        assert g.interior[0].numel() == 0 or int(g.interior[0].max()) < hi - lo
+        if mode == "overlap":
+            # interior and halo together hold every entry of the shard exactly once
+            assert g.interior[0].numel() + g.halo[0].numel() == l_idx.numel()
+            assert g.interior[0].numel() == 0 or int(g.interior[0].max()) < hi - lo
+            assert g.halo[0].numel() == 0 or int(g.halo[0].max()) < g.n_halo
+        else:
+            assert g.merged[0].numel() == l_idx.numel()
+            assert l_idx.numel() == 0 or int(g.merged[0].max()) < (hi - lo) + g.n_halo
         # only referenced remote rows travel, each once; requests and deliveries agree
         assert g.n_halo == g.needed.numel() <= n - (hi - lo)
-        assert g.halo[0].numel() == 0 or int(g.halo[0].max()) < g.n_halo
         assert all(lo <= int(v) < hi for v in g.send_rows.tolist())
         y_again = g.aggregate(torch.from_numpy(x[lo:hi].copy()))
         assert torch.equal(y, y_again)
@@ -99,14 +104,14 @@ def free_port():
     return p
 
 
-@pytest.mark.parametrize("world,n", [(2, 101), (3, 64)])
+@pytest.mark.parametrize("world,n,mode", [(2, 101, "merged"), (3, 64, "merged"), (3, 64, "overlap")])
 @pytest.mark.timeout(120)
-def test_partitioned_aggregation_equals_single_shard(oracle, world, n):
+def test_partitioned_aggregation_equals_single_shard(oracle, world, n, mode):
     E, f = 1500, 5
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = free_port()
-    procs = [ctx.Process(target=worker, args=(r, world, port, n, E, f, q)) for r in range(world)]
+    procs = [ctx.Process(target=worker, args=(r, world, port, n, E, f, q, mode)) for r in range(world)]
     for p in procs:
         p.start()
     got = [q.get(timeout=90) for _ in range(world)]
@@ -120,6 +125,8 @@ def test_partitioned_aggregation_equals_single_shard(oracle, world, n):
     for rank, lo, hi, y in got:
         assert y.shape == (hi - lo, f)
         assert (np.abs(y - want[lo:hi]) / (scale[lo:hi] + 1e-30)).max() <= 1e-5
+        if mode == "merged":      # every row is summed in the order the unpartitioned graph sums it
+            assert np.array_equal(y, want[lo:hi])
 
 
 def test_row_partition_bounds():

@@ -60,8 +60,9 @@ class Loopback:
         return Done()
 
 
+@pytest.mark.parametrize("mode", ["merged", "overlap"])
 @pytest.mark.parametrize("world,n,f", [(2, 5001, 128), (4, 4096, 32), (8, 3000, 7)])
-def test_emulated_ranks_on_one_gpu(cuda, oracle, world, n, f):
+def test_emulated_ranks_on_one_gpu(cuda, oracle, world, n, f, mode):
     from jittorgeometric_b200 import dist as jd
     idx, off, w, x = make_graph(world, n, 60000, f)
     want = oracle.aggregate(x, idx, off, w)
@@ -69,31 +70,40 @@ def test_emulated_ranks_on_one_gpu(cuda, oracle, world, n, f):
     part = jd.RowPartition(n, world)
     t = lambda a: torch.from_numpy(a).cuda()
     idx_t, off_t, w_t = t(idx), t(off), t(w)
+    whole = cuda.ops.segment_aggregate(t(x), idx_t, off_t, w_t, plan=cuda.ops.SpmmPlan(off_t, len(idx))).cpu().numpy()
     loop = Loopback()
     for rank in range(world):
         lo, hi = part.range(rank)
         loop.graphs.append(jd.ShardedGraph(part, rank, *jd.shard_rows(idx_t, off_t, w_t, part, rank), transport=loop,
-                                           setup=False))
+                                           setup=False, mode=mode))
         loop.features.append(t(x[lo:hi].copy()))
     loop.wire()
     for rank, g in enumerate(loop.graphs):
         lo, hi = part.range(rank)
-        # split: order inside a row preserved, interior ids rebased, nothing lost
         s, e = off[lo], off[hi]
         loc = idx[s:e]
         inside = (loc >= lo) & (loc < hi)
-        assert np.array_equal(g.interior[0].cpu().numpy(), loc[inside] - lo)
-        seg = np.repeat(np.arange(hi - lo), np.diff(off[lo:hi + 1]))
-        assert np.array_equal(np.diff(g.interior[1].cpu().numpy()), np.bincount(seg[inside], minlength=hi - lo))
-        assert np.array_equal(np.diff(g.halo[1].cpu().numpy()), np.bincount(seg[~inside], minlength=hi - lo))
-        # compact halo: the distinct remote rows, ascending, and the halo entries re-addressed into them
         needed = np.unique(loc[~inside])
+        # compact halo: the distinct remote rows, ascending, grouped by owner
         assert np.array_equal(g.needed.cpu().numpy(), needed)
-        assert np.array_equal(needed[g.halo[0].cpu().numpy()], loc[~inside])
         assert g.recv_counts == [int(((needed >= part.bounds[q]) & (needed < part.bounds[q + 1])).sum()) for q in range(world)]
+        if mode == "overlap":
+            # split: order inside a row preserved, interior ids rebased, halo entries re-addressed
+            assert np.array_equal(g.interior[0].cpu().numpy(), loc[inside] - lo)
+            seg = np.repeat(np.arange(hi - lo), np.diff(off[lo:hi + 1]))
+            assert np.array_equal(np.diff(g.interior[1].cpu().numpy()), np.bincount(seg[inside], minlength=hi - lo))
+            assert np.array_equal(np.diff(g.halo[1].cpu().numpy()), np.bincount(seg[~inside], minlength=hi - lo))
+            assert np.array_equal(needed[g.halo[0].cpu().numpy()], loc[~inside])
+        else:
+            # one structure over [own rows | packed halo rows], entries in their original places
+            m = g.merged[0].cpu().numpy()
+            assert np.array_equal(m[inside], loc[inside] - lo)
+            assert np.array_equal(needed[m[~inside] - (hi - lo)], loc[~inside])
         y = g.aggregate(loop.features[rank]).cpu().numpy()
         assert (np.abs(y - want[lo:hi]) / (scale[lo:hi] + 1e-30)).max() <= 1e-5
         assert np.array_equal(y, g.aggregate(loop.features[rank]).cpu().numpy())
+        if mode == "merged":                              # every row summed exactly as the unpartitioned kernel sums it
+            assert np.array_equal(y, whole[lo:hi])
 
 
 def test_accumulate_mode(cuda, oracle):
@@ -121,7 +131,8 @@ def nccl_worker(rank, world, port, n, E, f, q, exchange):
         part = jd.RowPartition(n, world)
         lo, hi = part.range(rank)
         t = lambda a: torch.from_numpy(a).cuda()
-        g = jd.ShardedGraph(part, rank, *jd.shard_rows(t(idx), t(off), t(w), part, rank), exchange=exchange)
+        g = jd.ShardedGraph(part, rank, *jd.shard_rows(t(idx), t(off), t(w), part, rank), exchange=exchange,
+                            mode="overlap" if exchange == "nccl" else "merged")
         y = g.aggregate(t(x[lo:hi].copy()))
         y2 = g.aggregate(t(x[lo:hi].copy()))          # second exchange reuses the shard buffers
         torch.cuda.synchronize()
