@@ -283,7 +283,15 @@ class ShardedGraph:
 
     def aggregate(self, x):
         """``y[v] = sum_{(u -> v)} w * x_global[u]`` for the rank's own rows ``v``; ``x`` holds the
-        rank's ``n_local`` rows of the feature matrix (extra rows are ignored)."""
+        rank's ``n_local`` rows of the feature matrix (extra rows are ignored).  With autograd the
+        gradient is the same aggregation applied to the incoming gradient, which is the true
+        gradient for a symmetric matrix (the normalised adjacency of an undirected graph) - the
+        rule the reference's ``DistSpmmFunc.grad`` follows (ops/distspmm.py:42-57)."""
+        if torch.is_grad_enabled() and x.requires_grad:
+            return _ShardedAggregate.apply(x, self)
+        return self._aggregate(x)
+
+    def _aggregate(self, x):
         if x.shape[0] < self.n_local:
             raise RuntimeError(f"x has {x.shape[0]} rows, the rank owns {self.n_local}")
         f = x.shape[1]
@@ -308,6 +316,17 @@ class ShardedGraph:
             self.backend.aggregate(recv, self.halo[0], self.halo[1], self.halo[2], self.n_local, self.halo_plan,
                                    out=y, accumulate=True)
         return y
+
+
+class _ShardedAggregate(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, graph):
+        ctx.graph = graph
+        return graph._aggregate(x.detach())
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return ctx.graph._aggregate(grad_output.contiguous()), None
 
 
 def shard_rows(idx, off, w, part, rank):

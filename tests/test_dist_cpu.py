@@ -96,6 +96,64 @@ def worker(rank, world, port, n, E, f, q, mode):
         dist.destroy_process_group()
 
 
+def grad_worker(rank, world, port, n, f, q):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    from jittorgeometric_b200 import dist as jd
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        idx, off, w, x, gy = make_symmetric(3, n, f)
+        part = jd.RowPartition(n, world)
+        lo, hi = part.range(rank)
+        g = jd.ShardedGraph(part, rank, *jd.shard_rows(torch.from_numpy(idx), torch.from_numpy(off), torch.from_numpy(w), part, rank),
+                            backend=OracleBackend())
+        xl = torch.from_numpy(x[lo:hi].copy()).requires_grad_(True)
+        y = g.aggregate(xl)
+        y.backward(torch.from_numpy(gy[lo:hi].copy()))
+        q.put((rank, lo, hi, xl.grad.numpy()))
+    except Exception as exc:
+        q.put((rank, -1, -1, repr(exc)))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+def make_symmetric(seed, n, f):
+    rng = np.random.default_rng(seed)
+    a = rng.integers(0, n, size=4 * n)
+    b = rng.integers(0, n, size=4 * n)
+    wv = rng.random(4 * n).astype(np.float32)
+    src = np.concatenate([a, b]); dst = np.concatenate([b, a]); w = np.concatenate([wv, wv])
+    order = np.argsort(dst, kind="stable")
+    off = np.concatenate([[0], np.cumsum(np.bincount(dst, minlength=n))]).astype(np.int32)
+    return (src[order].astype(np.int32), off, w[order], rng.standard_normal((n, f)).astype(np.float32),
+            rng.standard_normal((n, f)).astype(np.float32))
+
+
+@pytest.mark.timeout(120)
+def test_partitioned_backward_on_a_symmetric_graph(oracle):
+    """grad_x = A^T grad_y; for a symmetric A the same partitioned aggregation gives it."""
+    world, n, f = 2, 90, 4
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=grad_worker, args=(r, world, port, n, f, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=90) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=30)
+    assert all(g[1] >= 0 for g in got), [g[3] for g in got if g[1] < 0]
+    idx, off, w, x, gy = make_symmetric(3, n, f)
+    # true gradient: transpose aggregation, computed densely in float64
+    A = np.zeros((n, n))
+    seg = np.repeat(np.arange(n), np.diff(off))
+    np.add.at(A, (seg, idx), w.astype(np.float64))
+    want = A.T @ gy.astype(np.float64)
+    for rank, lo, hi, gx in got:
+        assert np.abs(gx - want[lo:hi]).max() <= 1e-4
+
+
 def free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
