@@ -16,8 +16,8 @@
 // TMA cannot address) warp 0 fills the ring with plain coalesced loads in the same layout.  Warp 1 (one lane) issues tcgen05.mma.kind::tf32 (128 x M x 8 per
 // instruction) into one of two TMEM accumulators and commits ring slots / accumulators to
 // mbarriers.  Warps 2-9 are the epilogue: tcgen05.ld of the accumulator quadrant their warp id
-// gives them access to, bias and ReLU fused, 64-byte row segments stored to H, overlapping the
-// next tile's MMAs.  Every mbarrier wait is bounded; a wait that runs out sets an error word that
+// gives them access to, bias and ReLU fused, each warp's 32x32 block staged in shared memory and
+// written to H by a bulk tensor store (TMA), overlapping the next tile's MMAs.  Every mbarrier wait is bounded; a wait that runs out sets an error word that
 // the host reads, and the CTA still frees its TMEM and exits.
 #include "common.cuh"
 
@@ -46,6 +46,7 @@ struct GemmParams {
     const float* x;     // plain-load producer only (rows whose pitch TMA cannot take)
     const float* wt;
     int32_t plain_loads;
+    int32_t tma_store;   // epilogue stages 32x32 blocks in shared memory and stores them by TMA
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -149,7 +150,8 @@ struct GemmSmem {
 };
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, GemmParams p) {
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                 const __grid_constant__ CUtensorMap map_out, GemmParams p) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // ring first (1024-byte aligned stages), control block after it
     unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -157,7 +159,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const uint32_t b_rows = (uint32_t)((p.m + 15) / 16 * 16);   // MMA N: a multiple of 16 when M = 128
     const uint32_t b_bytes = ((b_rows * kTileK * 4) + 1023) / 1024 * 1024;
     const uint32_t stage_bytes = a_bytes + b_bytes;
-    GemmSmem* ctl = reinterpret_cast<GemmSmem*>(ring + kStages * stage_bytes);
+    unsigned char* slabs = ring + kStages * stage_bytes;                 // 4 KB per epilogue warp (TMA-store epilogue)
+    GemmSmem* ctl = reinterpret_cast<GemmSmem*>(slabs + (p.tma_store ? kEpiWarps * 4096 : 0));
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
 
     if (threadIdx.x == 0) {
@@ -288,7 +291,34 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             for (int c0 = half * 32; c0 < p.m; c0 += 64) {
                 float v[32];
                 tmem_ld32(taddr + (uint32_t)c0, v, c0 + 16 < (int)b_rows);
-                if (row < p.n_rows) {
+                if (p.tma_store) {
+                    // bias / ReLU, then the warp's 32x32 block goes to its slab in the 128-byte swizzle
+                    // (16-byte chunk c of row r at chunk c ^ (r & 7)) and leaves as ONE bulk tensor store:
+                    // full 128-byte row segments instead of 32 scattered 16-byte stores per instruction.
+                    if (p.bias) {
+#pragma unroll
+                        for (int i = 0; i < 32; i++)
+                            if (c0 + i < p.m) v[i] += __ldg(p.bias + c0 + i);
+                    }
+                    if (p.relu) {
+#pragma unroll
+                        for (int i = 0; i < 32; i++) v[i] = fmaxf(v[i], 0.f);
+                    }
+                    unsigned char* slab = slabs + (warp - 2) * 4096;
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // previous store has read the slab
+                    __syncwarp();
+#pragma unroll
+                    for (int c = 0; c < 8; c++)
+                        *reinterpret_cast<float4*>(slab + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+                            make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                                     ::"l"(&map_out), "r"(c0), "r"(tile * kTileM + quad * 32), "r"(smem_u32(slab)) : "memory");
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                } else if (row < p.n_rows) {
                     float* o = p.out + row * p.m + c0;
                     if (p.bias) {
 #pragma unroll
@@ -314,6 +344,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctl->acc_empty[b]);
         }
+        if (p.tma_store && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // stores have landed
     }
     tc_fence_before();
     __syncthreads();
@@ -342,7 +373,8 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// 2-D fp32 tensor [rows, cols] row-major, box [box_rows, 32 columns], 128-byte swizzle, zero fill.
+// 2-D fp32 tensor [rows, cols] row-major, box [box_rows, 32 columns], 128-byte swizzle, zero fill
+// on loads / clipping on stores outside the tensor.
 static int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t cols, int box_rows) {
     EncodeTiledFn enc = encode_tiled_fn();
     JG_CHECK_ARG(enc, JG_ECUDA, "cuTensorMapEncodeTiled is not available from the driver");
@@ -395,6 +427,14 @@ int jg_gemm_tf32(float* out, const float* x, const float* wt, const float* bias,
     }
     GemmParams p = {};
     p.x = x; p.wt = wt; p.plain_loads = plain ? 1 : 0;
+    // TMA store needs a 16-byte row pitch for the output
+    p.tma_store = (m % 4 == 0) ? 1 : 0;
+    CUtensorMap map_out;
+    memset(&map_out, 0, sizeof(map_out));
+    if (p.tma_store) {
+        int rc2 = make_map(&map_out, out, n_rows, m, 32);
+        if (rc2 != JG_OK) return rc2;
+    }
     p.out = out; p.bias = bias; p.n_rows = n_rows; p.k = (int32_t)k; p.m = (int32_t)m; p.relu = relu;
     int pad = 32;
     while (pad < b_rows) pad *= 2;
@@ -405,7 +445,7 @@ int jg_gemm_tf32(float* out, const float* x, const float* wt, const float* bias,
     JG_CUDA(cudaMemsetAsync(p.error, 0, sizeof(int32_t), st));
     const size_t a_bytes = kTileM * kTileK * 4;
     const size_t b_bytes = ((size_t)b_rows * kTileK * 4 + 1023) / 1024 * 1024;
-    const size_t smem = 1024 + kStages * (a_bytes + b_bytes) + sizeof(GemmSmem) + 64;
+    const size_t smem = 1024 + kStages * (a_bytes + b_bytes) + (p.tma_store ? kEpiWarps * 4096 : 0) + sizeof(GemmSmem) + 64;
     static size_t attr_done[64] = {0};
     int dev = 0;
     JG_CUDA(cudaGetDevice(&dev));
@@ -415,7 +455,7 @@ int jg_gemm_tf32(float* out, const float* x, const float* wt, const float* bias,
     }
     int grid = sm_count();
     if (grid > p.n_tiles) grid = p.n_tiles;
-    gemm_tf32_kernel<<<grid, kGemmThreads, smem, st>>>(map_x, map_w, p);
+    gemm_tf32_kernel<<<grid, kGemmThreads, smem, st>>>(map_x, map_w, map_out, p);
     JG_LAUNCH_CHECK();
     return JG_OK;
 }
