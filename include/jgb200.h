@@ -68,6 +68,14 @@ int jg_aggregate_f32(float* out, const float* x, const int32_t* idx, const int32
                      const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes,
                      jg_stream_t stream);
 
+/* Structure check for the arrays the gather kernels trust: off[0] == 0, offsets non-decreasing,
+ * off[n_out] == nnz, every idx in [0, n_in).  Returns JG_EINVAL with the violation counts in
+ * jg_last_error(); synchronises the stream; workspace of 16 bytes.  The reference has no such
+ * check (a bad index there reads out of bounds, ops/cpp/aggregate_op.cc:45-58); here it is what a
+ * debug build or a cautious caller runs once per graph instead of a memory sanitizer. */
+int jg_validate_segments(const int32_t* idx, const int32_t* off, int64_t n_out, int64_t n_in, int64_t nnz,
+                         void* workspace, size_t workspace_bytes, jg_stream_t stream);
+
 /* Same aggregation, added to what `out` already holds: out[v,:] = out[v,:] + sum_j w[j]*x[idx[j],:]
  * (the sum is formed first, then added).  Used by the partitioned path, where the rows gathered
  * from other shards are aggregated after the shard's own rows - the place where the reference

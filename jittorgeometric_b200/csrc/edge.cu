@@ -185,6 +185,22 @@ __global__ void __launch_bounds__(kEdgeBlock) edge_softmax_bwd_any_kernel(float*
     }
 }
 
+// Structure check: offsets start at 0, never decrease, end at nnz; every index lies in [0, n_in).
+// Violations are counted per kind in report[0..3]; nothing is dereferenced through a bad value.
+__global__ void validate_segments_kernel(const int32_t* __restrict__ idx, const int32_t* __restrict__ off, int64_t n_out,
+                                         int64_t n_in, int64_t nnz, int32_t* __restrict__ report) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    if (t == 0) {
+        if (off[0] != 0) atomicAdd(&report[0], 1);
+        if (off[n_out] != nnz) atomicAdd(&report[1], 1);
+    }
+    for (int64_t v = t; v < n_out; v += stride)
+        if (off[v + 1] < off[v]) atomicAdd(&report[2], 1);
+    for (int64_t e = t; e < nnz; e += stride)
+        if (idx[e] < 0 || idx[e] >= n_in) atomicAdd(&report[3], 1);
+}
+
 static int grid_for_warps(int64_t warps_wanted) {
     const int64_t max_blocks = (int64_t)sm_count() * 8;
     int64_t blocks = (warps_wanted * 32 + kEdgeBlock - 1) / kEdgeBlock;
@@ -273,6 +289,30 @@ int jg_edge_softmax_bwd_f32(float* dx, const float* grad, const float* y, const 
         default: edge_softmax_bwd_any_kernel<<<grid_for_warps(n_nodes * h), kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes, h);
     }
     JG_LAUNCH_CHECK();
+    return JG_OK;
+}
+
+
+/* Checks a CSR/CSC structure before it is handed to the gather kernels (which trust it).
+ * Synchronises the stream.  workspace: 16 bytes. */
+int jg_validate_segments(const int32_t* idx, const int32_t* off, int64_t n_out, int64_t n_in, int64_t nnz,
+                         void* workspace, size_t workspace_bytes, jg_stream_t stream) {
+    JG_CHECK_ARG(n_out >= 0 && n_in >= 0 && nnz >= 0, JG_EINVAL, "validate_segments: negative size");
+    JG_CHECK_ARG(off && (nnz == 0 || idx), JG_EINVAL, "validate_segments: null pointer");
+    JG_CHECK_ARG(workspace && workspace_bytes >= 16, JG_EWORKSPACE, "validate_segments: workspace of 16 bytes needed");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int32_t* report = static_cast<int32_t*>(workspace);
+    JG_CUDA(cudaMemsetAsync(report, 0, 16, st));
+    validate_segments_kernel<<<grid_for_warps((n_out + nnz + 31) / 32 + 1), kEdgeBlock, 0, st>>>(idx, off, n_out, n_in, nnz, report);
+    JG_LAUNCH_CHECK();
+    int32_t host[4] = {0, 0, 0, 0};
+    JG_CUDA(cudaMemcpyAsync(host, report, 16, cudaMemcpyDeviceToHost, st));
+    JG_CUDA(cudaStreamSynchronize(st));
+    if (host[0] || host[1] || host[2] || host[3]) {
+        set_error("bad structure: off[0] != 0: %d, off[n] != nnz: %d, decreasing offsets: %d, indices outside [0, %lld): %d",
+                  host[0], host[1], host[2], (long long)n_in, host[3]);
+        return JG_EINVAL;
+    }
     return JG_OK;
 }
 

@@ -15,7 +15,7 @@ from .data import CSC, CSR
 
 __all__ = ["aggregateWithWeight", "segment_aggregate", "SpmmPlan", "cootocsr", "cootocsc", "gcn_norm_csc_csr",
            "SpmmCsr", "SpmmCoo", "ScatterToEdge", "ScatterToVertex", "EdgeSoftmax", "gat_aggregate",
-           "gat_aggregate_supported", "gcn_norm_coo", "linear_tf32", "linear_tf32_supported", "toUndirected"]
+           "gat_aggregate_supported", "gcn_norm_coo", "linear_tf32", "linear_tf32_supported", "toUndirected", "validate_structure"]
 
 DEFAULT_CHUNK = int(os.environ.get("JG_SPMM_CHUNK", "1024"))
 
@@ -36,6 +36,16 @@ def _as_f32(t, name):
     if t.dtype != torch.float32:
         raise RuntimeError(f"{name}: expected float32, got {t.dtype}")
     return t.contiguous()
+
+
+def validate_structure(idx, off, n_in):
+    """Raises if a CSR/CSC structure is malformed (offsets not starting at 0, decreasing, not ending
+    at the entry count, or an index outside ``[0, n_in)``).  The aggregation kernels trust their
+    inputs; with ``JG_DEBUG_CHECKS=1`` every aggregation call runs this first."""
+    idx, off = _as_i32(idx, "indices"), _as_i32(off, "offset")
+    ws = workspace(16, idx.device if idx.numel() else off.device)
+    check(lib().jg_validate_segments(ptr(idx), ptr(off), off.numel() - 1, int(n_in), idx.numel(), ptr(ws), ws.numel(),
+                                     stream_for(off)), "jg_validate_segments")
 
 
 class SpmmPlan:
@@ -83,6 +93,8 @@ def segment_aggregate(x, idx, off, w, n_out=None, plan=None, out=None, accumulat
     if w.numel() != nnz:
         raise RuntimeError(f"edge_weight has {w.numel()} entries, indices {nnz}")
     n_in, f = x.shape
+    if os.environ.get("JG_DEBUG_CHECKS") == "1":
+        validate_structure(idx, off, n_in)
     if out is None:
         if accumulate:
             raise RuntimeError("accumulate=True needs the tensor to add to (out=)")

@@ -146,3 +146,46 @@ def test_autograd_pairing(cuda, oracle):
     y.backward(g)
     want = oracle.aggregate(g.cpu().numpy(), d["column_indices"], d["row_offset"], d["csr_weight"])
     assert np.array_equal(x.grad.cpu().numpy(), want)
+
+
+def test_structure_validation(cuda):
+    t = lambda a, dt: torch.tensor(a, dtype=dt, device="cuda")
+    good_idx, good_off = t([0, 2, 1], torch.int32), t([0, 1, 1, 3], torch.int32)
+    cuda.ops.validate_structure(good_idx, good_off, 3)
+    for idx, off in (([0, 3, 1], [0, 1, 1, 3]),        # index out of range
+                     ([0, -1, 1], [0, 1, 1, 3]),       # negative index
+                     ([0, 2, 1], [0, 2, 1, 3]),        # decreasing offsets
+                     ([0, 2, 1], [1, 1, 1, 3]),        # does not start at 0
+                     ([0, 2, 1], [0, 1, 1, 2])):       # does not end at the entry count
+        with pytest.raises(RuntimeError, match="bad structure"):
+            cuda.ops.validate_structure(t(idx, torch.int32), t(off, torch.int32), 3)
+    cuda.ops.validate_structure(t([], torch.int32), t([0, 0], torch.int32), 5)   # empty graph is fine
+
+
+def test_cuda_graph_replay(cuda, oracle):
+    """The aggregation is a fixed launch sequence with caller-owned buffers: captured once in a CUDA
+    graph it can be replayed on new feature values (launch-bound small graphs)."""
+    d = load("citation_2708")
+    idx, off, w = dev(d["row_indices"]), dev(d["column_offset"]), dev(d["csc_weight"])
+    plan = cuda.ops.SpmmPlan(off, idx.numel())
+    x = torch.zeros((2708, 64), device="cuda")
+    y = torch.empty_like(x)
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        cuda.ops.segment_aggregate(x, idx, off, w, plan=plan, out=y)      # warm-up outside capture
+    torch.cuda.current_stream().wait_stream(s)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        cuda.ops.segment_aggregate(x, idx, off, w, plan=plan, out=y)
+    rng = np.random.default_rng(3)
+    for _ in range(2):
+        xv = rng.standard_normal((2708, 64)).astype(np.float32)
+        x.copy_(torch.from_numpy(xv))
+        g.replay()
+        torch.cuda.synchronize()
+        got = y.cpu().numpy()
+        eager = cuda.ops.segment_aggregate(x, idx, off, w, plan=plan).cpu().numpy()
+        assert np.array_equal(got, eager)
+        want = oracle.aggregate(xv, d["row_indices"], d["column_offset"], d["csc_weight"])
+        truth, scale = oracle.aggregate_f64(xv, d["row_indices"], d["column_offset"], d["csc_weight"])
+        assert rel_err(got, want, scale) <= 1e-5
