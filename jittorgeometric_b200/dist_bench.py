@@ -23,8 +23,21 @@ def run(args):
     nnz = csc.row_indices.numel()
     part = jd.RowPartition(n, world)
     exchange = os.environ.get("JG_EXCHANGE", "peer")
-    g = jd.ShardedGraph(part, rank, *jd.shard_rows(csc.row_indices, csc.column_offset, csc.edge_weight, part, rank),
-                        exchange=exchange, mode=os.environ.get("JG_DIST_MODE", "merged"))
+    mode = os.environ.get("JG_DIST_MODE", "merged")
+    shard = jd.shard_rows(csc.row_indices, csc.column_offset, csc.edge_weight, part, rank)
+    if exchange == "peer":
+        # symmetric memory is probed collectively, so every rank takes the same branch
+        ok = torch.ones(1, device=dev)
+        try:
+            import torch.distributed._symmetric_memory as symm
+            probe = symm.empty((16,), dtype=torch.float32, device=dev)
+            symm.rendezvous(probe, dist.group.WORLD.group_name)
+        except Exception:
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok.item()) == 0.0:
+            exchange = "nccl"
+    g = jd.ShardedGraph(part, rank, *shard, exchange=exchange, mode=mode)
     local_nnz = int(g.merged[0].numel()) if g.mode == "merged" else g.interior[0].numel() + g.halo[0].numel()
     halo_rows, remote_rows = g.n_halo, n - g.n_local
     del csc
