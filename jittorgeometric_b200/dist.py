@@ -339,14 +339,17 @@ def shard_rows(idx, off, w, part, rank):
 
 # ------------------------------------------------------------------------------ reference API mirror
 class DistributedManager:
-    """``rank`` / ``size`` / ``broadcast`` of the reference's manager
-    (utils/distributed_utils.py:8-74) on a ``torch.distributed`` group: device-to-device NCCL
-    broadcast instead of pickled host ``MPI.bcast``."""
+    """``rank`` / ``size`` / ``broadcast`` / parameter synchronisation of the reference's manager
+    (utils/distributed_utils.py:8-74) on a ``torch.distributed`` group: device-to-device
+    collectives (NCCL on GPUs) instead of pickled host ``MPI.bcast`` / ``MPI.Allreduce``."""
 
     def __init__(self, group=None):
         self.group = group
         self.rank = dist.get_rank(group)
         self.size = dist.get_world_size(group)
+
+    def _global(self, rank):
+        return dist.get_global_rank(self.group, rank) if self.group is not None else rank
 
     def broadcast(self, x, src, rows=None):
         """Every rank receives rank ``src``'s tensor; ``rows`` is the row count of that tensor when
@@ -356,27 +359,179 @@ class DistributedManager:
         else:
             n = x.shape[0] if rows is None else rows
             buf = torch.empty((n,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
-        dist.broadcast(buf, src=dist.get_global_rank(self.group, src) if self.group is not None else src, group=self.group)
+        dist.broadcast(buf, src=self._global(src), group=self.group)
         return buf
+
+    def broadcast_args(self, args):
+        """Rank 0's Python object on every rank (utils/distributed_utils.py:30-31)."""
+        box = [args]
+        dist.broadcast_object_list(box, src=self._global(0), group=self.group)
+        return box[0]
+
+    @staticmethod
+    def _tensors(model):
+        return list(model.parameters()) if hasattr(model, "parameters") else list(model)
+
+    def _bucket_all_reduce(self, tensors, async_op=False):
+        """One all-reduce over the concatenation of ``tensors`` (a launch per tensor would be
+        latency-bound for the handful of small weight matrices of a GNN)."""
+        flat = torch.cat([t.detach().reshape(-1) for t in tensors]) if tensors else None
+        work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=async_op) if tensors else None
+        return flat, work
+
+    @staticmethod
+    def _unpack(flat, tensors, scale, into):
+        at = 0
+        for t in tensors:
+            n = t.numel()
+            into(t).copy_((flat[at: at + n] * scale).view_as(t))
+            at += n
+
+    def synchronize_model_parameters(self, model):
+        """Replaces every parameter by its mean over the ranks
+        (utils/distributed_utils.py:33-37)."""
+        self.finalize_synchronization(self.synchronize_model_parameters_non_blocking(model))
+
+    def synchronize_model_parameters_non_blocking(self, model):
+        """Starts the averaging and returns a handle for :meth:`finalize_synchronization`
+        (utils/distributed_utils.py:39-57)."""
+        tensors = self._tensors(model)
+        flat, work = self._bucket_all_reduce(tensors, async_op=True)
+        return (tensors, flat, work)
+
+    def finalize_synchronization(self, requests):
+        tensors, flat, work = requests
+        if work is not None:
+            work.wait()
+        if flat is not None:
+            with torch.no_grad():
+                self._unpack(flat, tensors, 1.0 / self.size, lambda t: t.data)
+
+    def all_reduce_gradients(self, model, scale=1.0):
+        """Sums the ``.grad`` of every parameter over the ranks (times ``scale``).  With a loss that
+        is a sum over the rank's own nodes divided by a global count, this is the exact gradient of
+        the whole-graph loss, so every rank takes the same optimiser step.  The reference's example
+        never combines gradients (examples/dist_gcn/dist_gcn.py:144-170 steps on the local loss);
+        it only offers the parameter averaging above."""
+        tensors = [p for p in self._tensors(model) if p.grad is not None]
+        flat, _ = self._bucket_all_reduce([p.grad for p in tensors])
+        if flat is not None:
+            self._unpack(flat, tensors, scale, lambda t: t.grad)
+
+
+def _device_round(fb, csr, local_vnum, out=None):
+    t = ops._transposed_of(csr, n_cols=local_vnum)
+    plan = ops._plan_of(t, t.column_offset, t.row_indices.numel())
+    return ops.segment_aggregate(fb, t.row_indices, t.column_offset, t.edge_weight, n_out=local_vnum, plan=plan,
+                                 out=out, accumulate=out is not None)
+
+
+def _dist_spmm_rounds(dist_mgr, x, csr_list, local_vnum, one_round):
+    result = None
+    for src in range(dist_mgr.size):
+        v_src = csr_list[src].row_offset.numel() - 1
+        fb = dist_mgr.broadcast(x, src, rows=v_src)
+        result = one_round(fb, csr_list[src], local_vnum, result)
+    return result
+
+
+class _DistSpmmFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, dist_mgr, csr_list, local_vnum, one_round):
+        ctx.args = (dist_mgr, csr_list, local_vnum, one_round)
+        return _dist_spmm_rounds(dist_mgr, x.detach().contiguous(), csr_list, local_vnum, one_round)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        # the reference's rule (ops/distspmm.py:42-57): the same rounds on the incoming gradient,
+        # which is the true gradient when the whole matrix is symmetric
+        dist_mgr, csr_list, local_vnum, one_round = ctx.args
+        if grad_output.shape[0] != local_vnum:
+            raise RuntimeError("DistSpmm backward: gradient rows differ from local_vnum")
+        return _dist_spmm_rounds(dist_mgr, grad_output.contiguous(), csr_list, local_vnum, one_round), None, None, None, None
 
 
 def DistSpmm(dist_mgr, x, csr_list, local_vnum, trans_A=True, trans_B=False, aggregate=None):
     """``sum_src op(A_src) @ x_src`` (ops/distspmm.py:16-61): ``csr_list[src]`` holds the edges from
     the rows of rank ``src`` (its CSR rows) to this rank's ``local_vnum`` destinations (its
-    columns).  One broadcast round per source rank, as in the reference; forward only.  The
-    optimised single-exchange path is :meth:`ShardedGraph.aggregate`."""
+    columns).  One broadcast round per source rank, as in the reference, forward and backward.
+    ``aggregate(fb, csr, local_vnum, out)`` replaces the device kernel of one round (CPU ranks in
+    tests).  The optimised single-exchange path is :meth:`ShardedGraph.aggregate`."""
     if trans_B or not trans_A:
         raise RuntimeError("DistSpmm: only trans_A=True, trans_B=False (the reference's call) is supported")
-    result = None
-    for src in range(dist_mgr.size):
-        csr = csr_list[src]
-        v_src = csr.row_offset.numel() - 1
-        fb = dist_mgr.broadcast(x, src, rows=v_src)
-        t = ops._transposed_of(csr, n_cols=local_vnum)
-        plan = ops._plan_of(t, t.column_offset, t.row_indices.numel())
-        if result is None:
-            result = ops.segment_aggregate(fb, t.row_indices, t.column_offset, t.edge_weight, n_out=local_vnum, plan=plan)
-        else:
-            ops.segment_aggregate(fb, t.row_indices, t.column_offset, t.edge_weight, n_out=local_vnum, plan=plan,
-                                  out=result, accumulate=True)
-    return result
+    one_round = aggregate or _device_round
+    if torch.is_grad_enabled() and x.requires_grad:
+        return _DistSpmmFn.apply(x, dist_mgr, csr_list, local_vnum, one_round)
+    return _dist_spmm_rounds(dist_mgr, x, csr_list, local_vnum, one_round)
+
+
+class ShardedGCN(torch.nn.Module):
+    """The model of the reference's graph-parallel example (examples/dist_gcn/dist_gcn.py:46-88):
+    ``layers`` rounds of ``h <- (A_hat h) W`` with Glorot weights drawn on rank 0 and broadcast, then
+    ``log_softmax``.  ``A_hat h`` is :meth:`ShardedGraph.aggregate` (one compact halo exchange per
+    layer) instead of ``P`` broadcast rounds.  ``relu=True`` adds the activation between layers that
+    the single-GPU example has and the graph-parallel one omits."""
+
+    def __init__(self, in_channels, hidden_channels, out_channels, layers=2, manager=None, relu=False,
+                 device=None, seed=0):
+        super().__init__()
+        widths = [in_channels] + [hidden_channels] * (layers - 1) + [out_channels]
+        gen = torch.Generator().manual_seed(seed)
+        self.weights = torch.nn.ParameterList()
+        for a, b in zip(widths[:-1], widths[1:]):
+            bound = (6.0 / (a + b)) ** 0.5                      # nn/inits.py:19-22
+            w = (torch.rand((a, b), generator=gen) * 2 - 1) * bound
+            self.weights.append(torch.nn.Parameter(w.to(device) if device is not None else w))
+        self.relu = relu
+        self.manager = manager
+        self.sync_parameters()
+
+    def sync_parameters(self):
+        """Rank 0's weights on every rank (examples/dist_gcn/dist_gcn.py:63-70)."""
+        if self.manager is None or self.manager.size == 1:
+            return
+        with torch.no_grad():
+            for w in self.weights:
+                w.copy_(self.manager.broadcast(w.data, 0))
+
+    def forward(self, x, graph):
+        h = x
+        last = len(self.weights) - 1
+        for i, w in enumerate(self.weights):
+            h = graph.aggregate(h) @ w
+            if self.relu and i != last:
+                h = torch.relu(h)
+        return torch.log_softmax(h, dim=1)
+
+
+def sharded_training_step(model, graph, x, labels, mask, optimizer, manager, sync="gradients"):
+    """One optimiser step on a row-partitioned graph; returns the whole-graph training loss.
+
+    ``sync="gradients"``: the loss is the negative log-likelihood summed over the rank's masked
+    nodes and divided by the global number of masked nodes; weight gradients are summed over the
+    ranks before the step, so the result equals single-process training on the whole graph.
+    ``sync="parameters"``: every rank steps on its local mean loss and the weights are averaged
+    afterwards (the reference manager's ``synchronize_model_parameters``).  ``sync="none"``:
+    local steps only, what the reference's example does."""
+    optimizer.zero_grad(set_to_none=True)
+    pred = model(x, graph)
+    picked = pred[mask]
+    nll = -picked.gather(1, labels[mask].long().view(-1, 1)).sum()
+    count = torch.tensor([float(picked.shape[0])], device=x.device)
+    if sync == "gradients":
+        dist.all_reduce(count, group=manager.group)
+        loss = nll / count.clamp(min=1.0)
+        loss.backward()
+        manager.all_reduce_gradients(model)
+        optimizer.step()
+        total = loss.detach().clone().view(1)
+        dist.all_reduce(total, group=manager.group)
+        return float(total)
+    loss = nll / count.clamp(min=1.0)
+    loss.backward()
+    optimizer.step()
+    if sync == "parameters":
+        manager.synchronize_model_parameters(model)
+    elif sync != "none":
+        raise ValueError(f"sync must be 'gradients', 'parameters' or 'none', got {sync!r}")
+    return float(loss.detach())

@@ -187,6 +187,144 @@ def test_partitioned_aggregation_equals_single_shard(oracle, world, n, mode):
             assert np.array_equal(y, want[lo:hi])
 
 
+def train_worker(rank, world, port, n, f, hidden, classes, steps, q):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    from jittorgeometric_b200 import dist as jd
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        idx, off, w, x, _ = make_symmetric(5, n, f)
+        labels, mask = make_labels(5, n, classes)
+        part = jd.RowPartition(n, world)
+        lo, hi = part.range(rank)
+        g = jd.ShardedGraph(part, rank, *jd.shard_rows(torch.from_numpy(idx), torch.from_numpy(off), torch.from_numpy(w), part, rank),
+                            backend=OracleBackend())
+        mgr = jd.DistributedManager()
+        assert mgr.broadcast_args({"lr": 0.5} if rank == 0 else None) == {"lr": 0.5}
+        model = jd.ShardedGCN(f, hidden, classes, layers=2, manager=mgr, seed=100 + rank)   # differing draws: the broadcast must win
+        opt = torch.optim.SGD(model.parameters(), lr=0.5)
+        losses = [jd.sharded_training_step(model, g, torch.from_numpy(x[lo:hi].copy()), torch.from_numpy(labels[lo:hi].copy()),
+                                           torch.from_numpy(mask[lo:hi].copy()), opt, mgr) for _ in range(steps)]
+        # parameter averaging of the reference's manager: make the ranks differ, then average
+        with torch.no_grad():
+            model.weights[0].add_(float(rank))
+        mgr.synchronize_model_parameters(model)
+        q.put((rank, 0, 0, [p.detach().numpy().copy() for p in model.weights], losses))
+    except Exception as exc:
+        q.put((rank, -1, -1, repr(exc), None))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+def make_labels(seed, n, classes):
+    rng = np.random.default_rng(seed + 1000)
+    return rng.integers(0, classes, size=n).astype(np.int64), rng.random(n) < 0.6
+
+
+@pytest.mark.timeout(180)
+def test_partitioned_training_equals_single_process(oracle):
+    """Two ranks, gradients summed over the ranks: weights and losses after three SGD steps equal
+    dense float64 training on the whole graph."""
+    from jittorgeometric_b200 import dist as jd
+    world, n, f, hidden, classes, steps = 2, 90, 6, 5, 3, 3
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=train_worker, args=(r, world, port, n, f, hidden, classes, steps, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=150) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=30)
+    assert all(g[1] >= 0 for g in got), [g[3] for g in got if g[1] < 0]
+    idx, off, w, x, _ = make_symmetric(5, n, f)
+    labels, mask = make_labels(5, n, classes)
+    A = np.zeros((n, n))
+    np.add.at(A, (np.repeat(np.arange(n), np.diff(off)), idx), w.astype(np.float64))
+    A = torch.from_numpy(A)
+    ref = jd.ShardedGCN(f, hidden, classes, layers=2, manager=None, seed=100)      # rank 0's draw
+    W = [p.detach().double().requires_grad_(True) for p in ref.weights]
+    X, L, M = torch.from_numpy(x).double(), torch.from_numpy(labels), torch.from_numpy(mask)
+    want_losses = []
+    for _ in range(steps):
+        h = X
+        for wt in W:
+            h = (A @ h) @ wt
+        loss = torch.nn.functional.nll_loss(torch.log_softmax(h, dim=1)[M], L[M])
+        grads = torch.autograd.grad(loss, W)
+        want_losses.append(float(loss.detach()))
+        W = [(wt - 0.5 * g).detach().requires_grad_(True) for wt, g in zip(W, grads)]
+    for rank, _, _, weights, losses in got:
+        assert np.allclose(losses, want_losses, rtol=1e-4, atol=1e-5)
+        # the first matrix was shifted by the rank and averaged: mean shift (world - 1) / 2
+        assert np.abs(weights[0] - (W[0].detach().numpy() + (world - 1) / 2)).max() <= 1e-4
+        assert np.abs(weights[1] - W[1].detach().numpy()).max() <= 1e-4
+
+
+def spmm_rounds_worker(rank, world, port, n, f, q):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    import oracle as O
+    from jittorgeometric_b200 import dist as jd
+    from jittorgeometric_b200.data import CSR
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        idx, off, w, x, gy = make_symmetric(9, n, f)
+        part = jd.RowPartition(n, world)
+        lo, hi = part.range(rank)
+        seg = np.repeat(np.arange(n), np.diff(off))
+        mine = (seg >= lo) & (seg < hi)
+        csr_list = []
+        for s_rank in range(world):
+            s_lo, s_hi = part.range(s_rank)
+            sel = mine & (idx >= s_lo) & (idx < s_hi)
+            ei = np.stack([idx[sel] - s_lo, seg[sel] - lo]).astype(np.int32)
+            ci, ro, cw = O.coo_to_csr(ei, w[sel], s_hi - s_lo)
+            csr_list.append(CSR(torch.from_numpy(ci), torch.from_numpy(ro), torch.from_numpy(cw)))
+
+        def one_round(fb, csr, local_vnum, out):
+            # op(A)^T product of one source rank's block with the CPU checker: CSR rows are sources
+            ci, ro, cw = csr.column_indices.numpy(), csr.row_offset.numpy(), csr.edge_weight.numpy()
+            rows = np.repeat(np.arange(len(ro) - 1), np.diff(ro)).astype(np.int32)
+            ti, to, tw = O.coo_to_csc(np.stack([rows, ci]).astype(np.int32), cw, local_vnum)
+            y = torch.from_numpy(O.aggregate(fb.numpy(), ti, to, tw, n_out=local_vnum))
+            return y if out is None else out + y
+
+        xl = torch.from_numpy(x[lo:hi].copy()).requires_grad_(True)
+        y = jd.DistSpmm(jd.DistributedManager(), xl, csr_list, hi - lo, aggregate=one_round)
+        y.backward(torch.from_numpy(gy[lo:hi].copy()))
+        q.put((rank, lo, hi, y.detach().numpy(), xl.grad.numpy()))
+    except Exception as exc:
+        q.put((rank, -1, -1, repr(exc), None))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(120)
+def test_broadcast_rounds_forward_and_backward(oracle):
+    """The reference-shaped DistSpmm (one broadcast round per source rank) on two CPU ranks:
+    forward equals the whole-graph aggregation, backward follows the reference's rule."""
+    world, n, f = 2, 70, 3
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=spmm_rounds_worker, args=(r, world, port, n, f, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=90) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=30)
+    assert all(g[1] >= 0 for g in got), [g[3] for g in got if g[1] < 0]
+    idx, off, w, x, gy = make_symmetric(9, n, f)
+    A = np.zeros((n, n))
+    np.add.at(A, (np.repeat(np.arange(n), np.diff(off)), idx), w.astype(np.float64))
+    for rank, lo, hi, y, gx in got:
+        assert np.abs(y - (A @ x.astype(np.float64))[lo:hi]).max() <= 1e-4
+        assert np.abs(gx - (A.T @ gy.astype(np.float64))[lo:hi]).max() <= 1e-4
+
+
 def test_row_partition_bounds():
     from jittorgeometric_b200.dist import RowPartition
     p = RowPartition(10, 4)

@@ -149,9 +149,11 @@ def nccl_worker(rank, world, port, n, E, f, q, exchange):
             ei = np.stack([idx[sel] - s_lo, seg[sel] - lo]).astype(np.int32)      # rows: sources of that rank, columns: local destinations
             ci, ro, cw = O.coo_to_csr(ei, w[sel], s_hi - s_lo)
             csr_list.append(jg.CSR(t(ci), t(ro), t(cw)))
-        z = jd.DistSpmm(jd.DistributedManager(), t(x[lo:hi].copy()), csr_list, hi - lo)
+        xl = t(x[lo:hi].copy()).requires_grad_(True)
+        z = jd.DistSpmm(jd.DistributedManager(), xl, csr_list, hi - lo)
+        z.backward(t(x[lo:hi].copy()) * 0.5)          # the reference's rule: the same rounds on the gradient
         torch.cuda.synchronize()
-        q.put((rank, lo, hi, y.cpu().numpy(), z.cpu().numpy()))
+        q.put((rank, lo, hi, y.cpu().numpy(), z.detach().cpu().numpy(), xl.grad.cpu().numpy()))
     except Exception as exc:
         q.put((rank, -1, -1, repr(exc)))
         raise
@@ -180,6 +182,92 @@ def test_nccl_ranks(cuda, oracle, exchange):
     idx, off, w, x = make_graph(11, n, E, f)
     want = oracle.aggregate(x, idx, off, w)
     _, scale = oracle.aggregate_f64(x, idx, off, w)
-    for rank, lo, hi, y, z in got:
+    for rank, lo, hi, y, z, gx in got:
         assert (np.abs(y - want[lo:hi]) / (scale[lo:hi] + 1e-30)).max() <= 1e-5
         assert (np.abs(z - want[lo:hi]) / (scale[lo:hi] + 1e-30)).max() <= 1e-5
+        assert (np.abs(gx - 0.5 * want[lo:hi]) / (scale[lo:hi] + 1e-30)).max() <= 1e-5
+
+
+def make_symmetric(seed, n, f, per_node=6):
+    rng = np.random.default_rng(seed)
+    a = rng.integers(0, n, size=per_node * n)
+    b = rng.integers(0, n, size=per_node * n)
+    wv = (rng.random(per_node * n) / per_node).astype(np.float32)
+    src = np.concatenate([a, b]); dst = np.concatenate([b, a]); w = np.concatenate([wv, wv])
+    order = np.argsort(dst, kind="stable")
+    off = np.concatenate([[0], np.cumsum(np.bincount(dst, minlength=n))]).astype(np.int32)
+    return src[order].astype(np.int32), off, w[order], rng.standard_normal((n, f)).astype(np.float32)
+
+
+def train_worker(rank, world, port, n, f, hidden, classes, steps, q):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    from jittorgeometric_b200 import dist as jd
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        idx, off, w, x = make_symmetric(21, n, f)
+        rng = np.random.default_rng(22)
+        labels, mask = rng.integers(0, classes, size=n).astype(np.int64), rng.random(n) < 0.5
+        part = jd.RowPartition(n, world)
+        lo, hi = part.range(rank)
+        t = lambda a: torch.from_numpy(a).cuda()
+        g = jd.ShardedGraph(part, rank, *jd.shard_rows(t(idx), t(off), t(w), part, rank), exchange="nccl", mode="merged")
+        mgr = jd.DistributedManager()
+        model = jd.ShardedGCN(f, hidden, classes, layers=2, manager=mgr, device="cuda", seed=300 + rank)
+        opt = torch.optim.SGD(model.parameters(), lr=0.5)
+        losses = [jd.sharded_training_step(model, g, t(x[lo:hi].copy()), t(labels[lo:hi].copy()), t(mask[lo:hi].copy()), opt, mgr)
+                  for _ in range(steps)]
+        torch.cuda.synchronize()
+        q.put((rank, 0, 0, [p.detach().cpu().numpy() for p in model.weights], losses))
+    except Exception as exc:
+        q.put((rank, -1, -1, repr(exc), None))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_nccl_training_step(cuda):
+    """Graph-parallel training (halo exchange forward and backward, weight gradients summed over
+    the ranks) equals dense float64 training of the same model on the whole graph."""
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    import torch.multiprocessing as mp
+    from jittorgeometric_b200 import dist as jd
+    n, f, hidden, classes, steps = 3000, 32, 16, 5, 3
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=train_worker, args=(r, world, port, n, f, hidden, classes, steps, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=240) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(g[1] >= 0 for g in got), [g[3] for g in got if g[1] < 0]
+    idx, off, w, x = make_symmetric(21, n, f)
+    rng = np.random.default_rng(22)
+    labels, mask = rng.integers(0, classes, size=n).astype(np.int64), rng.random(n) < 0.5
+    A = np.zeros((n, n))
+    np.add.at(A, (np.repeat(np.arange(n), np.diff(off)), idx), w.astype(np.float64))
+    A = torch.from_numpy(A)
+    ref = jd.ShardedGCN(f, hidden, classes, layers=2, manager=None, seed=300)
+    W = [p.detach().double().requires_grad_(True) for p in ref.weights]
+    X, L, M = torch.from_numpy(x).double(), torch.from_numpy(labels), torch.from_numpy(mask)
+    want_losses = []
+    for _ in range(steps):
+        h = X
+        for wt in W:
+            h = (A @ h) @ wt
+        loss = torch.nn.functional.nll_loss(torch.log_softmax(h, dim=1)[M], L[M])
+        grads = torch.autograd.grad(loss, W)
+        want_losses.append(float(loss.detach()))
+        W = [(wt - 0.5 * g).detach().requires_grad_(True) for wt, g in zip(W, grads)]
+    for rank, _, _, weights, losses in got:
+        assert np.allclose(losses, want_losses, rtol=1e-4, atol=1e-5)
+        for have, want in zip(weights, W):
+            assert np.abs(have - want.detach().numpy()).max() <= 1e-4
