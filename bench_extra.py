@@ -106,8 +106,18 @@ def run_gat(args):
         hh = jg.linear_tf32(x, W, relu=True, weight_t=Wt)     # width 602: the plain-load producer of the tcgen05 kernel
         out["y"] = jg.gat_aggregate(hh, a_src, a_dst, csc, H)
 
+    # training: forward with the saved log-sum-exp, then the fused backward (by destination, by
+    # source, score-vector reduction); the source-grouped structure is built once, outside the timing
+    hg, asg, adg = h.clone().requires_grad_(True), a_src.clone().requires_grad_(True), a_dst.clone().requires_grad_(True)
+    gy = torch.randn((n, H * D), device=dev, generator=torch.Generator(device=dev).manual_seed(6))
+
+    def train_edge_phase():
+        hg.grad = asg.grad = adg.grad = None
+        jg.gat_aggregate(hg, asg, adg, csc, H).backward(gy)
+
     sampler = bench.ClockSampler(0); sampler.start()
     ms_edge = _time(edge_phase, args.steps, args.warmup)
+    ms_train = _time(train_edge_phase, args.steps, args.warmup)
     ms_layer = _time(layer, args.steps, args.warmup)
     ms_transform = _time(lambda: jg.linear_tf32(x, W, relu=True, weight_t=Wt), args.steps, args.warmup)
     ms_transform_lib = _time(lambda: torch.relu(x @ W), args.steps, args.warmup)
@@ -138,7 +148,7 @@ def run_gat(args):
            "traffic": None, "peak_kind": kind, "kernel": "gat_aggregate_kernel",
            "note": "compulsory bytes only: h (%.0f MB) fits in L2, so the kernel is L2/LSU-bound, not HBM-bound; "
                    "effective gather bandwidth is reported beside it" % (n * C * 4 / 1e6)},
-          {"gather_gbs": gather / ms_edge / 1e6, "layer_ms": ms_layer, "transform_ms": ms_transform,
+          {"gather_gbs": gather / ms_edge / 1e6, "forward_backward_ms": ms_train, "layer_ms": ms_layer, "transform_ms": ms_transform,
            "transform_library_fp32_ms": ms_transform_lib, "cpu_baseline": cpu,
            "gpu_launches": args.steps, "clocks": clocks})
 

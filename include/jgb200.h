@@ -196,14 +196,31 @@ int jg_edge_softmax_bwd_f32(float* dx, const float* grad, const float* y, const 
  * reported by jg_gat_aggregate_supported (heads*dim/4 and dim/4 powers of two, heads*dim <= 128);
  * others return JG_EUNSUPPORTED and are served by the per-edge operators above.
  * `plan` (optional, from jg_gat_plan_build; depends only on `off`) lists the destinations longest
- * segment first, which keeps the grid from ending on one warp that walks a hub alone. */
+ * segment first, which keeps the grid from ending on one warp that walks a hub alone.  `lse` may be
+ * NULL; otherwise it receives [n_nodes, heads] values for jg_gat_backward_f32. */
 size_t jg_gat_plan_bytes(int64_t n_nodes);
 int jg_gat_plan_build(const int32_t* off, int64_t n_nodes, void* plan, size_t plan_bytes, jg_stream_t stream);
 size_t jg_gat_aggregate_workspace_bytes(int64_t n_nodes, int64_t n_edges, int64_t heads, int64_t dim);
 int jg_gat_aggregate_supported(int64_t heads, int64_t dim);
-int jg_gat_aggregate_f32(float* out, const float* h, const float* a_src, const float* a_dst, const int32_t* idx,
+int jg_gat_aggregate_f32(float* out, float* lse, const float* h, const float* a_src, const float* a_dst, const int32_t* idx,
                          const int32_t* off, int64_t n_nodes, int64_t n_edges, int64_t heads, int64_t dim, float slope,
                          const void* plan, void* workspace, size_t workspace_bytes, jg_stream_t stream);
+
+/* Backward of the fused attention aggregation (the reference differentiates the six operators one
+ * by one: ops/scatterToEdge.py:42-46, ops/edgesoftmax.py:69-74, ops/scatterToVertex.py:41-45).
+ * `lse` [n_nodes, heads] is what the forward wrote when given a non-NULL `lse` (log-sum-exp of each
+ * destination's logits, base 2); `out` is the forward result, `grad_out` its gradient.  Outputs:
+ * grad_h [n_nodes, heads*dim], grad_a_src and grad_a_dst [heads, dim].  (idx, off) is the CSC the
+ * forward used; (idx_t, off_t) is the same edge set grouped by SOURCE (for every source the
+ * destinations of its out-edges), e.g. from jg_coo_to_compressed.  `plan` / `plan_t` (optional) are
+ * jg_gat_plan_build over `off` / `off_t`.  Three gather passes (by destination, by source, a column
+ * reduction), no atomics on data: results are run-to-run identical. */
+size_t jg_gat_backward_workspace_bytes(int64_t n_nodes, int64_t heads, int64_t dim);
+int jg_gat_backward_f32(float* grad_h, float* grad_a_src, float* grad_a_dst, const float* grad_out, const float* out,
+                        const float* lse, const float* h, const float* a_src, const float* a_dst, const int32_t* idx,
+                        const int32_t* off, const int32_t* idx_t, const int32_t* off_t, int64_t n_nodes, int64_t n_edges,
+                        int64_t heads, int64_t dim, float slope, const void* plan, const void* plan_t, void* workspace,
+                        size_t workspace_bytes, jg_stream_t stream);
 
 /* ------------------------------------------------------------------ dense feature transform
  * out[n_rows, m] = act(x[n_rows, k] * W + bias) with TF32 products and fp32 accumulation on the

@@ -104,13 +104,15 @@ class GATConv(torch.nn.Module):
     """Attention layer (nn/conv/gat_conv.py:30-88): ``h = relu(x W)``, edge logits
     ``leaky_relu([h_src, h_dst] a, 0.2)``, softmax over each destination's in-edges, weighted sum.
     ``heads`` > 1 (an extension; the reference layer is single-head) splits the channels into
-    independent heads.  The forward pass runs the fused kernel when the shape allows and no
-    gradient is needed, else the reference's op-by-op pipeline on the per-edge operators."""
+    independent heads.  The edge phase runs the fused kernels (forward and backward) when the shape
+    allows, else - or with ``fused=False`` - the reference's op-by-op pipeline on the per-edge
+    operators."""
 
-    def __init__(self, in_channels, out_channels, heads=1, tf32=False, **kwargs):
+    def __init__(self, in_channels, out_channels, heads=1, tf32=False, fused=True, **kwargs):
         super().__init__()
         assert out_channels % heads == 0
         self.in_channels, self.out_channels, self.heads, self.tf32 = in_channels, out_channels, heads, tf32
+        self.fused = fused
         self.weight = torch.nn.Parameter(torch.empty(in_channels, out_channels))
         self.edge_weight = torch.nn.Parameter(torch.empty(2 * out_channels, 1))
         self.reset_parameters()
@@ -126,10 +128,9 @@ class GATConv(torch.nn.Module):
     def forward(self, x, csc):
         h = _transform(x, self.weight, self.tf32, relu=True)
         dim = self.out_channels // self.heads
-        needs_grad = torch.is_grad_enabled() and (h.requires_grad or self.edge_weight.requires_grad)
-        if not needs_grad and ops.gat_aggregate_supported(self.heads, dim):
+        if self.fused and ops.gat_aggregate_supported(self.heads, dim):
             a_src, a_dst = self.attention_vectors()
-            return ops.gat_aggregate(h, a_src, a_dst, csc, self.heads)
+            return ops.gat_aggregate(h, a_src, a_dst, csc, self.heads)      # fused forward and backward
         return self.propagate_unfused(h, csc)
 
     def propagate_unfused(self, h, csc):

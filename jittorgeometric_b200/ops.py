@@ -248,7 +248,8 @@ def _transposed_of(csr, n_cols=None):
     """CSC of the same matrix, built on device once and cached on the CSR object: the
     destination-major structure an atomics-free ``A^T x`` needs.  ``n_cols`` is the column count
     of a rectangular block (default: square)."""
-    key = (csr.column_indices.data_ptr(), csr.row_offset.data_ptr(), csr.edge_weight.data_ptr(), n_cols)
+    key = (csr.column_indices.data_ptr(), csr.row_offset.data_ptr(),
+           0 if csr.edge_weight is None else csr.edge_weight.data_ptr(), n_cols)
     cached = getattr(csr, "_jg_transposed", None)
     if cached is None or cached[0] != key:
         n = csr.row_offset.numel() - 1 if n_cols is None else int(n_cols)
@@ -423,31 +424,88 @@ def gat_aggregate_supported(heads, dim):
     return bool(lib().jg_gat_aggregate_supported(int(heads), int(dim)))
 
 
-def gat_aggregate(h, a_src, a_dst, csc, heads, slope=0.2):
-    """Fused edge phase of the attention layer (nn/conv/gat_conv.py:60-83): logits, per-destination
-    softmax and weighted aggregation in one pass.  ``h`` is ``[N, heads*dim]``; ``a_src`` and
-    ``a_dst`` are ``[heads, dim]``.  Forward only."""
-    h = _as_f32(h, "h")
+def _gat_plan(holder, attr, off, n, like):
+    plan = getattr(holder, attr, None)
+    if plan is None or plan[0] != off.data_ptr():
+        buf = workspace(lib().jg_gat_plan_bytes(n), like.device)
+        check(lib().jg_gat_plan_build(ptr(off), n, ptr(buf), buf.numel(), stream_for(like)), "jg_gat_plan_build")
+        plan = (off.data_ptr(), buf)
+        setattr(holder, attr, plan)
+    return plan[1]
+
+
+def _gat_forward(h, a_src, a_dst, csc, heads, slope, want_lse):
     n, c = h.shape
-    dim = c // int(heads)
-    a_src, a_dst = _as_f32(a_src, "a_src").reshape(-1), _as_f32(a_dst, "a_dst").reshape(-1)
-    if a_src.numel() != c or a_dst.numel() != c or dim * heads != c:
-        raise RuntimeError("gat_aggregate: a_src/a_dst must hold heads*dim values")
+    dim = c // heads
     idx, off = _as_i32(csc.row_indices, "row_indices"), _as_i32(csc.column_offset, "column_offset")
     if off.numel() != n + 1:
         raise RuntimeError("gat_aggregate: column_offset does not match h")
     out = torch.empty_like(h)
-    plan = getattr(csc, "_jg_gat_plan", None)
-    if plan is None or plan[0] != off.data_ptr():
-        buf = workspace(lib().jg_gat_plan_bytes(n), h.device)
-        check(lib().jg_gat_plan_build(ptr(off), n, ptr(buf), buf.numel(), stream_for(h)), "jg_gat_plan_build")
-        plan = (off.data_ptr(), buf)
-        csc._jg_gat_plan = plan
+    lse = torch.empty((n, heads), dtype=torch.float32, device=h.device) if want_lse else None
+    plan = _gat_plan(csc, "_jg_gat_plan", off, n, h)
     ws = workspace(lib().jg_gat_aggregate_workspace_bytes(n, idx.numel(), heads, dim), h.device)
-    check(lib().jg_gat_aggregate_f32(ptr(out), ptr(h), ptr(a_src), ptr(a_dst), ptr(idx), ptr(off), n, idx.numel(),
-                                     int(heads), dim, float(slope), ptr(plan[1]), ptr(ws), ws.numel(), stream_for(h)),
+    check(lib().jg_gat_aggregate_f32(ptr(out), ptr(lse), ptr(h), ptr(a_src), ptr(a_dst), ptr(idx), ptr(off), n, idx.numel(),
+                                     heads, dim, float(slope), ptr(plan), ptr(ws), ws.numel(), stream_for(h)),
           "jg_gat_aggregate_f32")
-    return out
+    return out, lse
+
+
+def _by_source(csc):
+    """The edges of a CSC grouped by source (for every source the destinations of its out-edges),
+    built on device once and cached on the container."""
+    view = getattr(csc, "_jg_by_source_view", None)
+    if view is None or view.column_indices.data_ptr() != csc.row_indices.data_ptr():
+        view = CSR(csc.row_indices, csc.column_offset, csc.edge_weight)
+        csc._jg_by_source_view = view
+    return _transposed_of(view)
+
+
+class _GatAggregate(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, a_src, a_dst, csc, heads, slope):
+        out, lse = _gat_forward(h, a_src, a_dst, csc, heads, slope, True)
+        ctx.save_for_backward(h, a_src, a_dst, out, lse)
+        ctx.csc, ctx.heads, ctx.slope = csc, heads, slope
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        h, a_src, a_dst, out, lse = ctx.saved_tensors
+        csc, heads = ctx.csc, ctx.heads
+        n, c = h.shape
+        dim = c // heads
+        g = _as_f32(grad_out, "grad_out")
+        t = _by_source(csc)
+        idx, off = _as_i32(csc.row_indices, "row_indices"), _as_i32(csc.column_offset, "column_offset")
+        idx_t, off_t = t.row_indices, t.column_offset
+        grad_h = torch.empty_like(h)
+        grad_as, grad_ad = torch.empty_like(a_src), torch.empty_like(a_dst)
+        plan = _gat_plan(csc, "_jg_gat_plan", off, n, h)
+        plan_t = _gat_plan(t, "_jg_gat_plan", off_t, n, h)
+        ws = workspace(lib().jg_gat_backward_workspace_bytes(n, heads, dim), h.device)
+        check(lib().jg_gat_backward_f32(ptr(grad_h), ptr(grad_as), ptr(grad_ad), ptr(g), ptr(out), ptr(lse), ptr(h), ptr(a_src),
+                                        ptr(a_dst), ptr(idx), ptr(off), ptr(idx_t), ptr(off_t), n, idx.numel(), heads, dim,
+                                        float(ctx.slope), ptr(plan), ptr(plan_t), ptr(ws), ws.numel(), stream_for(h)),
+              "jg_gat_backward_f32")
+        return grad_h, grad_as, grad_ad, None, None, None
+
+
+def gat_aggregate(h, a_src, a_dst, csc, heads, slope=0.2):
+    """Fused edge phase of the attention layer (nn/conv/gat_conv.py:60-83): logits, per-destination
+    softmax and weighted aggregation in one pass.  ``h`` is ``[N, heads*dim]``; ``a_src`` and
+    ``a_dst`` are ``[heads, dim]``.  Differentiable in ``h``, ``a_src`` and ``a_dst`` (fused
+    backward: two gather passes and a column reduction, no ``[E, C]`` temporaries)."""
+    h = _as_f32(h, "h")
+    n, c = h.shape
+    heads = int(heads)
+    dim = c // heads
+    shape_s, shape_d = a_src.shape, a_dst.shape
+    a_src, a_dst = _as_f32(a_src, "a_src").reshape(-1), _as_f32(a_dst, "a_dst").reshape(-1)
+    if a_src.numel() != c or a_dst.numel() != c or dim * heads != c:
+        raise RuntimeError("gat_aggregate: a_src/a_dst must hold heads*dim values")
+    if torch.is_grad_enabled() and (h.requires_grad or a_src.requires_grad or a_dst.requires_grad):
+        return _GatAggregate.apply(h, a_src, a_dst, csc, heads, float(slope))
+    return _gat_forward(h, a_src, a_dst, csc, heads, slope, False)[0]
 
 
 # ------------------------------------------------------------------------------ dense transform

@@ -183,9 +183,67 @@ def test_gat_layer_fused_and_unfused_agree(cuda):
         fused = layer(x, csc)
         unfused = layer.propagate_unfused(torch.relu(x @ layer.weight), csc)
     assert (fused - unfused).abs().max().item() <= 1e-5 * (unfused.abs().max().item() + 1)
-    x.requires_grad_(True)
-    layer(x, csc).sum().backward()       # training path: the per-edge operators with autograd
-    assert torch.isfinite(x.grad).all() and x.grad.abs().sum() > 0
+    # training: the fused backward against autograd through the per-edge operators
+    target = torch.randn(n, 64, device="cuda")
+    grads = []
+    for fused in (True, False):
+        layer.fused = fused
+        layer.zero_grad()
+        xg = x.clone().requires_grad_(True)
+        (layer(xg, csc) * target).sum().backward()
+        grads.append((xg.grad, layer.weight.grad.clone(), layer.edge_weight.grad.clone()))
+    for a, b in zip(*grads):
+        assert (a - b).abs().max().item() <= 2e-4 * (b.abs().max().item() + 1e-30)
+
+
+def attention_truth(h, a_src, a_dst, idx, off, slope=0.2):
+    """Differentiable float64 restatement of the edge phase with plain tensor operations."""
+    n, heads, dim = h.shape[0], a_src.shape[0], a_src.shape[1]
+    seg = torch.repeat_interleave(torch.arange(n, device=h.device), (off[1:] - off[:-1]).long())
+    e_s, e_d = h[idx.long()].view(-1, heads, dim), h[seg].view(-1, heads, dim)
+    m = torch.nn.functional.leaky_relu((e_s * a_src).sum(-1) + (e_d * a_dst).sum(-1), slope)
+    top = torch.full((n, heads), -float("inf"), dtype=h.dtype, device=h.device).scatter_reduce(
+        0, seg.view(-1, 1).expand(-1, heads), m, "amax")
+    p = torch.exp(m - top[seg])
+    alpha = p / torch.zeros((n, heads), dtype=h.dtype, device=h.device).index_add(0, seg, p)[seg]
+    return torch.zeros_like(h).index_add(0, seg, (e_s * alpha.unsqueeze(-1)).reshape(-1, heads * dim))
+
+
+@pytest.mark.parametrize("heads,dim", [(8, 8), (1, 64), (1, 8), (2, 4), (4, 16), (1, 128), (1, 4)])
+def test_fused_attention_backward(cuda, heads, dim):
+    """Gradients of the fused kernel with respect to h, a_src and a_dst against float64 autograd;
+    hubs on both sides (destinations and sources with thousands of edges), empty rows, negative and
+    positive logits (both branches of the leaky slope), identical results on a second run."""
+    rng = np.random.default_rng(1000 + heads * 10 + dim)
+    n, c = 2500, heads * dim
+    dst = np.concatenate([rng.integers(10, n, size=30000), np.full(9000, 3), np.full(5000, 1500),
+                          rng.integers(10, n, size=12000)])
+    src = np.concatenate([rng.integers(0, n, size=30000 + 9000 + 5000), np.full(7000, 42), np.full(5000, 1500)])
+    order = np.argsort(dst, kind="stable")
+    idx = src[order].astype(np.int32)
+    off = np.concatenate([[0], np.cumsum(np.bincount(dst, minlength=n))]).astype(np.int32)
+    csc = cuda.CSC(dev(idx), dev(off), None)
+    h0 = rng.standard_normal((n, c)).astype(np.float32)
+    a0 = (rng.standard_normal((2, heads, dim)) * 0.5).astype(np.float32)
+    g0 = rng.standard_normal((n, c)).astype(np.float32)
+
+    def run():
+        h, a_s, a_d = dev(h0).requires_grad_(True), dev(a0[0]).requires_grad_(True), dev(a0[1]).requires_grad_(True)
+        out = cuda.gat_aggregate(h, a_s, a_d, csc, heads)
+        out.backward(dev(g0))
+        return host(out), host(h.grad), host(a_s.grad), host(a_d.grad)
+
+    got = run()
+    hd, asd, add_ = dev(h0).double().requires_grad_(True), dev(a0[0]).double().requires_grad_(True), dev(a0[1]).double().requires_grad_(True)
+    want_out = attention_truth(hd, asd, add_, dev(idx), dev(off))
+    want_out.backward(dev(g0).double())
+    want = (host(want_out), host(hd.grad), host(asd.grad), host(add_.grad))
+    for name, a, b in zip(("out", "grad_h", "grad_a_src", "grad_a_dst"), got, want):
+        assert a.shape == b.shape, name
+        assert np.abs(a - b).max() <= 2e-5 * np.abs(b).max() + 1e-30, name
+    again = run()
+    for a, b in zip(got, again):
+        assert np.array_equal(a, b)
 
 
 def test_spmm_front_ends(cuda, oracle):
