@@ -213,9 +213,10 @@ int jg_gat_aggregate_f32(float* out, float* lse, const float* h, const float* a_
  * grad_h [n_nodes, heads*dim], grad_a_src and grad_a_dst [heads, dim].  (idx, off) is the CSC the
  * forward used; (idx_t, off_t) is the same edge set grouped by SOURCE (for every source the
  * destinations of its out-edges), e.g. from jg_coo_to_compressed.  `plan` / `plan_t` (optional) are
- * jg_gat_plan_build over `off` / `off_t`.  Three gather passes (by destination, by source, a column
- * reduction), no atomics on data: results are run-to-run identical. */
-size_t jg_gat_backward_workspace_bytes(int64_t n_nodes, int64_t heads, int64_t dim);
+ * jg_gat_plan_build over `off` / `off_t`; with `plan_t` a source with millions of out-edges is cut
+ * into pieces shared by many thread blocks.  Three gather passes (by destination, by source, a
+ * column reduction), no atomics on data: results are run-to-run identical. */
+size_t jg_gat_backward_workspace_bytes(int64_t n_nodes, int64_t n_edges, int64_t heads, int64_t dim);
 int jg_gat_backward_f32(float* grad_h, float* grad_a_src, float* grad_a_dst, const float* grad_out, const float* out,
                         const float* lse, const float* h, const float* a_src, const float* a_dst, const int32_t* idx,
                         const int32_t* off, const int32_t* idx_t, const int32_t* off_t, int64_t n_nodes, int64_t n_edges,

@@ -53,7 +53,7 @@ SIGNATURES = {
     "jg_gat_plan_bytes": (sz, [i64]),
     "jg_gat_plan_build": (ctypes.c_int, [vp, i64, vp, sz, vp]),
     "jg_gat_aggregate_f32": (ctypes.c_int, [vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, f32, vp, vp, sz, vp]),
-    "jg_gat_backward_workspace_bytes": (sz, [i64, i64, i64]),
+    "jg_gat_backward_workspace_bytes": (sz, [i64, i64, i64, i64]),
     "jg_gat_backward_f32": (ctypes.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, f32, vp, vp, vp, sz, vp]),
     "jg_gemm_tf32_supported": (ctypes.c_int, [i64, i64, i64]),
     "jg_gemm_tf32_workspace_bytes": (sz, []),

@@ -71,6 +71,57 @@ __global__ void gat_plan_fill_kernel(const int32_t* __restrict__ off, int64_t n,
         order[atomicAdd(&cursors[degree_bucket(off[v + 1] - off[v])], 1)] = (int32_t)v;
 }
 
+// Segments of 4096 or more entries ("hubs", the first counts[40] entries of `order`) are cut into
+// pieces of kGatPiece entries so that a segment of millions of entries is shared by many CTAs:
+// piece_start[i] = number of pieces of the hubs before hub i, counts[41] = total.  One block.
+constexpr int kGatPiece = 8192;
+// floats per piece partial: C column sums, then H score sums padded to a multiple of four so that
+// every partial starts on a 16-byte boundary (the column sums are stored as float4)
+__host__ __device__ constexpr int piece_stride(int c, int heads) { return c + ((heads + 3) & ~3); }
+__global__ void __launch_bounds__(1024) gat_plan_pieces_kernel(const int32_t* __restrict__ off, const int32_t* __restrict__ order,
+                                                               int32_t* counts, int32_t* __restrict__ piece_start) {
+    __shared__ int s_warp[32];
+    __shared__ int s_carry;
+    const int n_hub = counts[40];
+    if (threadIdx.x == 0) s_carry = 0;
+    __syncthreads();
+    for (int base = 0; base < n_hub; base += 1024) {
+        const int i = base + threadIdx.x;
+        int mine = 0;
+        if (i < n_hub) {
+            const int32_t v = order[i];
+            mine = (off[v + 1] - off[v] + kGatPiece - 1) / kGatPiece;
+        }
+        int incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(kFull, incl, o);
+            if ((threadIdx.x & 31) >= o) incl += t;
+        }
+        if ((threadIdx.x & 31) == 31) s_warp[threadIdx.x >> 5] = incl;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            int w = s_warp[threadIdx.x];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(kFull, w, o);
+                if (threadIdx.x >= o) w += t;
+            }
+            s_warp[threadIdx.x] = w;
+        }
+        __syncthreads();
+        const int before = s_carry + ((threadIdx.x >> 5) ? s_warp[(threadIdx.x >> 5) - 1] : 0) + incl - mine;
+        if (i < n_hub) piece_start[i] = before;
+        __syncthreads();
+        if (threadIdx.x == 1023) s_carry = before + mine;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        piece_start[n_hub] = s_carry;
+        counts[41] = s_carry;
+    }
+}
+
 __device__ __forceinline__ float dot4(const float4& a, const float4& b) {
     return fmaf(a.w, b.w, fmaf(a.z, b.z, fmaf(a.y, b.y, a.x * b.x)));
 }
@@ -309,6 +360,9 @@ struct GatBwdArgs {
     float4* info;     // [n, H]: (a_dst . h[v] in log2 units, lse2[v], delta[v], 0)
     float* d_dst;     // [n, H]
     float* d_src;     // [n, H]
+    const int32_t* piece_start_t;   // pieces of the hub sources (see gat_plan_pieces_kernel)
+    const int32_t* n_pieces_t;      // [1]
+    float* piece_partial;           // [pieces, piece_stride] partial sums of multi-piece hubs
 };
 
 template <int DL>
@@ -508,7 +562,7 @@ __global__ void __launch_bounds__(kGatBlock) gat_backward_src_kernel(GatBwdArgs 
 #pragma unroll
         for (int o = 1; o < DL; o <<= 1) ss += __shfl_xor_sync(kFull, ss, o);
     };
-    auto finish = [&](int64_t u, GatSrcAcc acc) {
+    auto fold = [&](GatSrcAcc& acc) {   // lane groups took alternate edges: butterfly sums
 #pragma unroll
         for (int o = G; o < 32; o <<= 1) {
             acc.s += __shfl_xor_sync(kFull, acc.s, o);
@@ -517,6 +571,8 @@ __global__ void __launch_bounds__(kGatBlock) gat_backward_src_kernel(GatBwdArgs 
             acc.g.z += __shfl_xor_sync(kFull, acc.g.z, o);
             acc.g.w += __shfl_xor_sync(kFull, acc.g.w, o);
         }
+    };
+    auto finish = [&](int64_t u, const GatSrcAcc& acc) {
         if (lane < G) {
             const float4 ad_raw = __ldg(reinterpret_cast<const float4*>(a.a_dst) + fl);
             const float dd = a.d_dst[(size_t)u * H + fl / DL];
@@ -530,18 +586,38 @@ __global__ void __launch_bounds__(kGatBlock) gat_backward_src_kernel(GatBwdArgs 
         }
     };
 
-    for (;;) {   // hubs: one CTA per source
+    // hub sources: one CTA per piece of kGatPiece out-edges
+    const int64_t n_piece = a.order_t ? (int64_t)a.n_pieces_t[0] : 0;
+    __shared__ int s_hub;
+    for (;;) {
         __syncthreads();
-        if (threadIdx.x == 0) s_ticket = atomicAdd(a.ticket + 3, 1ull);
+        if (threadIdx.x == 0) {
+            const unsigned long long t = atomicAdd(a.ticket + 3, 1ull);
+            s_ticket = t;
+            if ((int64_t)t < n_piece) {   // the hub whose piece range holds t: last i with piece_start[i] <= t
+                int lo = 0, hi = (int)n_hub;
+                while (hi - lo > 1) {
+                    const int mid = (lo + hi) >> 1;
+                    if ((unsigned long long)a.piece_start_t[mid] <= t) lo = mid; else hi = mid;
+                }
+                s_hub = lo;
+            }
+        }
         __syncthreads();
         const unsigned long long t = s_ticket;
-        if ((int64_t)t >= n_hub) break;
-        const int64_t u = a.order_t[t];
+        if ((int64_t)t >= n_piece) break;
+        const int hub = s_hub;
+        const int first = a.piece_start_t[hub];
+        const int pieces = a.piece_start_t[hub + 1] - first;
+        const int64_t u = a.order_t[hub];
+        const int64_t s0 = (int64_t)a.off_t[u] + (int64_t)((int)t - first) * kGatPiece;
+        const int64_t e_all = a.off_t[u + 1];
+        const int64_t e0 = s0 + kGatPiece < e_all ? s0 + kGatPiece : e_all;
         float4 hu;
         float ss;
         own(u, hu, ss);
         GatSrcAcc acc = {0.f, make_float4(0.f, 0.f, 0.f, 0.f)};
-        gat_bwd_src_walk<G, DL>(a, a.off_t[u], a.off_t[u + 1], warp, W, hu, ss, gb, info, acc);
+        gat_bwd_src_walk<G, DL>(a, (int32_t)s0, (int32_t)e0, warp, W, hu, ss, gb, info, acc);
         float* mine = s_part[warp][lane];
         mine[0] = acc.s; mine[1] = acc.g.x; mine[2] = acc.g.y; mine[3] = acc.g.z; mine[4] = acc.g.w;
         __syncthreads();
@@ -550,7 +626,14 @@ __global__ void __launch_bounds__(kGatBlock) gat_backward_src_kernel(GatBwdArgs 
                 const float* o = s_part[w][lane];
                 acc.s += o[0]; acc.g.x += o[1]; acc.g.y += o[2]; acc.g.z += o[3]; acc.g.w += o[4];
             }
-            finish(u, acc);
+            fold(acc);
+            if (pieces == 1) {
+                finish(u, acc);
+            } else if (lane < G) {   // partial of this piece; gat_backward_src_fixup_kernel adds the pieces up
+                float* dst = a.piece_partial + (size_t)t * piece_stride(C, H);
+                reinterpret_cast<float4*>(dst)[fl] = acc.g;
+                if (fl % DL == 0) dst[C + fl / DL] = acc.s;
+            }
         }
     }
     for (;;) {   // one warp per source
@@ -564,7 +647,33 @@ __global__ void __launch_bounds__(kGatBlock) gat_backward_src_kernel(GatBwdArgs 
         own(u, hu, ss);
         GatSrcAcc acc = {0.f, make_float4(0.f, 0.f, 0.f, 0.f)};
         gat_bwd_src_walk<G, DL>(a, a.off_t[u], a.off_t[u + 1], 0, 1, hu, ss, gb, info, acc);
+        fold(acc);
         finish(u, acc);
+    }
+}
+
+// Sums the piece partials of every multi-piece hub source in piece order and writes its rows.
+// One block per hub (grid-stride), one thread per column.
+__global__ void __launch_bounds__(128) gat_backward_src_fixup_kernel(GatBwdArgs a, int c, int d) {
+    const int heads = c / d;
+    const int n_hub = a.hub_count_t[0];
+    const int col = threadIdx.x;
+    if (col >= c) return;
+    const int head = col / d;
+    for (int hub = blockIdx.x; hub < n_hub; hub += gridDim.x) {
+        const int first = a.piece_start_t[hub];
+        const int pieces = a.piece_start_t[hub + 1] - first;
+        if (pieces <= 1) continue;
+        const int64_t u = a.order_t[hub];
+        float g = 0.f, sc = 0.f;
+        for (int p = 0; p < pieces; p++) {
+            const float* src = a.piece_partial + (size_t)(first + p) * piece_stride(c, heads);
+            g += src[col];
+            sc += src[c + head];
+        }
+        const float dd = a.d_dst[(size_t)u * heads + head];
+        a.grad_h[(size_t)u * c + col] = g + sc * a.a_src[col] + dd * a.a_dst[col];
+        if (col % d == 0) a.d_src[(size_t)u * heads + head] = sc;
     }
 }
 
@@ -617,12 +726,18 @@ struct GatBwdWs {
     float* d_dst;
     float* d_src;
     float* partial;
+    float* piece_partial;
     int blocks;
     size_t bytes;
 };
-static GatBwdWs carve_gat_bwd(void* ws, int64_t n, int64_t heads, int64_t c, int blocks) {
+// upper bound on the pieces of all hubs: every hub has at least 4096 entries, every piece but a
+// hub's last is full
+static int64_t max_pieces(int64_t n_edges) { return n_edges / kGatPiece + n_edges / 4096 + 1; }
+
+static GatBwdWs carve_gat_bwd(void* ws, int64_t n, int64_t n_edges, int64_t heads, int64_t c, int blocks) {
     Carver cv(ws);
     GatBwdWs v;
+    v.piece_partial = cv.take<float>((size_t)max_pieces(n_edges) * (size_t)piece_stride((int)c, (int)heads));
     v.ticket = cv.take<unsigned long long>(4);
     v.info = cv.take<float4>((size_t)n * heads);
     v.d_dst = cv.take<float>((size_t)n * heads);
@@ -650,6 +765,10 @@ static int launch_gat_bwd(const GatBwdArgs& a, cudaStream_t st) {
     JG_LAUNCH_CHECK();
     k2<<<sm_count() * bps_src, kGatBlock, 0, st>>>(a);
     JG_LAUNCH_CHECK();
+    if (a.order_t) {
+        gat_backward_src_fixup_kernel<<<sm_count() * 2, 128, 0, st>>>(a, 4 * G, 4 * DL);
+        JG_LAUNCH_CHECK();
+    }
     return JG_OK;
 }
 
@@ -677,6 +796,7 @@ size_t jg_gat_plan_bytes(int64_t n_nodes) {
     Carver c(nullptr);
     c.take<int32_t>(64);
     c.take<int32_t>(n_nodes);
+    c.take<int32_t>(n_nodes + 1);
     return c.total();
 }
 
@@ -688,6 +808,7 @@ int jg_gat_plan_build(const int32_t* off, int64_t n_nodes, void* plan, size_t pl
     Carver c(plan);
     int32_t* counts = c.take<int32_t>(64);
     int32_t* order = c.take<int32_t>(n_nodes);
+    int32_t* piece_start = c.take<int32_t>(n_nodes + 1);
     JG_CUDA(cudaMemsetAsync(counts, 0, 64 * sizeof(int32_t), st));
     if (n_nodes == 0) return JG_OK;
     const int grid = sm_count() * 4;
@@ -696,6 +817,8 @@ int jg_gat_plan_build(const int32_t* off, int64_t n_nodes, void* plan, size_t pl
     gat_plan_starts_kernel<<<1, 1, 0, st>>>(counts);
     JG_LAUNCH_CHECK();
     gat_plan_fill_kernel<<<grid, 256, 0, st>>>(off, n_nodes, counts, order);
+    JG_LAUNCH_CHECK();
+    gat_plan_pieces_kernel<<<1, 1024, 0, st>>>(off, order, counts, piece_start);
     JG_LAUNCH_CHECK();
     return JG_OK;
 }
@@ -749,9 +872,9 @@ int jg_gat_aggregate_f32(float* out, float* lse, const float* h, const float* a_
     return JG_EUNSUPPORTED;
 }
 
-size_t jg_gat_backward_workspace_bytes(int64_t n_nodes, int64_t heads, int64_t dim) {
-    if (n_nodes < 0 || heads <= 0 || dim <= 0) return 0;
-    return carve_gat_bwd(nullptr, n_nodes, heads, heads * dim, kScoreGradBlocks).bytes;
+size_t jg_gat_backward_workspace_bytes(int64_t n_nodes, int64_t n_edges, int64_t heads, int64_t dim) {
+    if (n_nodes < 0 || n_edges < 0 || heads <= 0 || dim <= 0) return 0;
+    return carve_gat_bwd(nullptr, n_nodes, n_edges, heads, heads * dim, kScoreGradBlocks).bytes;
 }
 
 int jg_gat_backward_f32(float* grad_h, float* grad_a_src, float* grad_a_dst, const float* grad_out, const float* out,
@@ -781,9 +904,9 @@ int jg_gat_backward_f32(float* grad_h, float* grad_a_src, float* grad_a_dst, con
                   reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(a_src) | reinterpret_cast<uintptr_t>(a_dst)) % 16 == 0,
                  JG_EINVAL, "gat_backward: pointers must be 16-byte aligned");
     JG_CHECK_ARG(slope >= 0.f && slope <= 1.f, JG_EINVAL, "gat_backward: slope must lie in [0, 1]");
-    JG_CHECK_ARG(workspace && workspace_bytes >= jg_gat_backward_workspace_bytes(n_nodes, heads, dim), JG_EWORKSPACE,
+    JG_CHECK_ARG(workspace && workspace_bytes >= jg_gat_backward_workspace_bytes(n_nodes, n_edges, heads, dim), JG_EWORKSPACE,
                  "gat_backward: workspace too small");
-    GatBwdWs ws = carve_gat_bwd(workspace, n_nodes, heads, c, kScoreGradBlocks);
+    GatBwdWs ws = carve_gat_bwd(workspace, n_nodes, n_edges, heads, c, kScoreGradBlocks);
     GatBwdArgs a = {};
     a.grad_h = grad_h; a.grad_out = grad_out; a.out = out; a.lse = lse; a.h = h; a.a_src = a_src; a.a_dst = a_dst;
     a.idx = idx; a.off = off; a.idx_t = idx_t; a.off_t = off_t; a.n = n_nodes; a.slope = slope;
@@ -796,7 +919,10 @@ int jg_gat_backward_f32(float* grad_h, float* grad_a_src, float* grad_a_dst, con
     if (plan_t) {
         Carver cv(const_cast<void*>(plan_t));
         a.hub_count_t = cv.take<int32_t>(64) + 40;
+        a.n_pieces_t = a.hub_count_t + 1;
         a.order_t = cv.take<int32_t>(n_nodes);
+        a.piece_start_t = cv.take<int32_t>(n_nodes + 1);
+        a.piece_partial = ws.piece_partial;
     }
     JG_CUDA(cudaMemsetAsync(a.ticket, 0, 4 * sizeof(unsigned long long), st));
     const int g = (int)(c / 4), dl = (int)(dim / 4);

@@ -482,7 +482,7 @@ class _GatAggregate(torch.autograd.Function):
         grad_as, grad_ad = torch.empty_like(a_src), torch.empty_like(a_dst)
         plan = _gat_plan(csc, "_jg_gat_plan", off, n, h)
         plan_t = _gat_plan(t, "_jg_gat_plan", off_t, n, h)
-        ws = workspace(lib().jg_gat_backward_workspace_bytes(n, heads, dim), h.device)
+        ws = workspace(lib().jg_gat_backward_workspace_bytes(n, idx.numel(), heads, dim), h.device)
         check(lib().jg_gat_backward_f32(ptr(grad_h), ptr(grad_as), ptr(grad_ad), ptr(g), ptr(out), ptr(lse), ptr(h), ptr(a_src),
                                         ptr(a_dst), ptr(idx), ptr(off), ptr(idx_t), ptr(off_t), n, idx.numel(), heads, dim,
                                         float(ctx.slope), ptr(plan), ptr(plan_t), ptr(ws), ws.numel(), stream_for(h)),
