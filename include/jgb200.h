@@ -223,6 +223,51 @@ int jg_gat_backward_f32(float* grad_h, float* grad_a_src, float* grad_a_dst, con
                         int64_t heads, int64_t dim, float slope, const void* plan, const void* plan_t, void* workspace,
                         size_t workspace_bytes, jg_stream_t stream);
 
+/* ------------------------------------------------------------------ neighbour sampling
+ * Device side of the reference's layer-wise mini-batch sampler (examples/minibatch_example.py:232-362).
+ *
+ * jg_sample_counts replaces gpuinitco_op.gpuinitco(dst_size, fanout, dst, layer_off, global_off)
+ * (ops/gpuinitco.py:30-36, ops/cpp/gpuinitco_op.cc:37-52): with cumulative == 0 it writes what that
+ * kernel writes, out[0] = 0 and out[i+1] = min(in-degree of dst[i], fanout) (counts); with
+ * cumulative != 0 it writes the running sum the sampler needs (examples/minibatch_example.py:253-262),
+ * out[n_dst] = total.  fanout < 0 means "all neighbours".  The workspace is only used when cumulative.
+ *
+ * jg_sample_neighbors replaces sampleprocessing_op.sampleprocessing(fanout, dst, layer_off, layer_idx,
+ * global_off, global_idx) (ops/sampleprocessing.py:28-35, ops/cpp/sampleprocessing_op.cc:38-176): column
+ * i of the layer receives all in-edges of dst[i] in stored order when there are at most `fanout` of
+ * them, else `fanout` entries from distinct positions of its in-edge list.  The draw is a pure
+ * function of (seed, dst[i], fanout): the same call gives the same sample.  fanout <= 1024 (the
+ * reference's CUDA limit); error_flag[0] is set to 1 if layer_off does not hold the running sums of
+ * jg_sample_counts for this (dst, fanout) or exceeds layer_capacity (nothing is written there).
+ *
+ * jg_expand_columns: out[j] = values[i] (i itself when values is NULL) for every entry j of column i.
+ *
+ * jg_csc_to_csr replaces csctocsr_op.csctocsr(col_off, row_idx, row_off, col_idx, dst, src)
+ * (ops/csctocsr.py:27-34, ops/cpp/csctocsr_op.cc:26-80): row r of the result belongs to src_ids[r],
+ * column values are dst_ids[column], entries whose source id is not listed are dropped, entries of a
+ * row keep the CSC traversal order (bit-exact with the reference's CPU body).  id_range bounds every
+ * id in src_ids (ids in row_idx outside [0, id_range) count as unlisted); col_idx needs room for
+ * n_edges entries; kept[0] receives the number of entries written.
+ *
+ * jg_degree_weights replaces getweight_op.getweight(vtx_size, dst, src, col_off, row_idx, w)
+ * (ops/getweight.py:29-37, ops/cpp/getweight_op.cc:37-84): w[j] = 1 / (sqrtf(out-degree of the
+ * entry's source) * sqrtf(in-degree of dst_ids[column])), degrees counted over this structure;
+ * bit-exact with the reference's CPU body. */
+size_t jg_sample_counts_workspace_bytes(int64_t n_dst);
+int jg_sample_counts(const int32_t* dst, int64_t n_dst, const int32_t* g_off, int32_t fanout, int cumulative, int32_t* out,
+                     void* workspace, size_t workspace_bytes, jg_stream_t stream);
+int jg_sample_neighbors(const int32_t* dst, int64_t n_dst, const int32_t* layer_off, const int32_t* g_off, const int32_t* g_idx,
+                        int32_t fanout, uint64_t seed, int32_t* layer_idx, int64_t layer_capacity, int32_t* error_flag,
+                        jg_stream_t stream);
+int jg_expand_columns(const int32_t* off, int64_t n_cols, const int32_t* values, int32_t* out, jg_stream_t stream);
+size_t jg_csc_to_csr_workspace_bytes(int64_t n_src, int64_t n_edges, int64_t id_range);
+int jg_csc_to_csr(const int32_t* col_off, const int32_t* row_idx, int64_t n_dst, int64_t n_edges, const int32_t* dst_ids,
+                  const int32_t* src_ids, int64_t n_src, int64_t id_range, int32_t* row_off, int32_t* col_idx, int64_t* kept,
+                  void* workspace, size_t workspace_bytes, jg_stream_t stream);
+size_t jg_degree_weights_workspace_bytes(int64_t vtx_size);
+int jg_degree_weights(int64_t vtx_size, const int32_t* dst_ids, int64_t n_dst, const int32_t* col_off, const int32_t* row_idx,
+                      int64_t n_edges, float* out_w, void* workspace, size_t workspace_bytes, jg_stream_t stream);
+
 /* ------------------------------------------------------------------ dense feature transform
  * out[n_rows, m] = act(x[n_rows, k] * W + bias) with TF32 products and fp32 accumulation on the
  * tcgen05 tensor cores; replaces the `x @ self.weight` (+ bias, + ReLU) of the reference layers

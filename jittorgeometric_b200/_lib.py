@@ -55,6 +55,14 @@ SIGNATURES = {
     "jg_gat_aggregate_f32": (ctypes.c_int, [vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, f32, vp, vp, sz, vp]),
     "jg_gat_backward_workspace_bytes": (sz, [i64, i64, i64, i64]),
     "jg_gat_backward_f32": (ctypes.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, f32, vp, vp, vp, sz, vp]),
+    "jg_sample_counts_workspace_bytes": (sz, [i64]),
+    "jg_sample_counts": (ctypes.c_int, [vp, i64, vp, i32, ctypes.c_int, vp, vp, sz, vp]),
+    "jg_sample_neighbors": (ctypes.c_int, [vp, i64, vp, vp, vp, i32, ctypes.c_uint64, vp, i64, vp, vp]),
+    "jg_expand_columns": (ctypes.c_int, [vp, i64, vp, vp, vp]),
+    "jg_csc_to_csr_workspace_bytes": (sz, [i64, i64, i64]),
+    "jg_csc_to_csr": (ctypes.c_int, [vp, vp, i64, i64, vp, vp, i64, i64, vp, vp, vp, vp, sz, vp]),
+    "jg_degree_weights_workspace_bytes": (sz, [i64]),
+    "jg_degree_weights": (ctypes.c_int, [i64, vp, i64, vp, vp, i64, vp, vp, sz, vp]),
     "jg_gemm_tf32_supported": (ctypes.c_int, [i64, i64, i64]),
     "jg_gemm_tf32_workspace_bytes": (sz, []),
     "jg_gemm_tf32": (ctypes.c_int, [vp, vp, vp, vp, i64, i64, i64, ctypes.c_int, vp, sz, vp]),

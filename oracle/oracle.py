@@ -221,6 +221,79 @@ def to_undirected(edge_index, attr, n, impl="port"):
     return np.stack([os_[:m], od[:m]]), oa[:m].copy()
 
 
+# --------------------------------------------------------------------- neighbour sampling
+def sample_counts(dst, g_off, fanout):
+    """``gpuinitco`` (ops/gpuinitco.py:30-36): ``out[i+1] = min(deg(dst[i]), fanout)``, ``out[0] = 0``
+    (counts, not a running sum, as the reference kernel writes them)."""
+    dst, g_off = _i32(dst), _i32(g_off)
+    out = np.zeros(len(dst) + 1, np.int32)
+    port_lib().orc_sample_counts(_ip(dst), L(len(dst)), _ip(g_off), ctypes.c_int32(fanout), _ip(out))
+    return out
+
+
+def csc_to_csr(col_off, row_idx, dst_ids, src_ids, impl="port"):
+    """``csctocsr`` (ops/csctocsr.py:27-34) -> ``(row_offset, column_indices)``."""
+    col_off, row_idx, dst_ids, src_ids = _i32(col_off), _i32(row_idx), _i32(dst_ids), _i32(src_ids)
+    E = len(row_idx)
+    ro, ci = np.zeros(len(src_ids) + 1, np.int32), np.zeros(E, np.int32)
+    if impl == "ref":
+        ref_lib().ref_csctocsr(_ip(col_off), _ip(row_idx), ctypes.c_long(len(dst_ids)), ctypes.c_long(E), _ip(dst_ids),
+                               _ip(src_ids), ctypes.c_long(len(src_ids)), _ip(ro), _ip(ci))
+    else:
+        max_id = int(max(src_ids.max(initial=0), row_idx.max(initial=0)))
+        port_lib().orc_csc_to_csr.restype = ctypes.c_int64
+        port_lib().orc_csc_to_csr(_ip(col_off), _ip(row_idx), L(len(dst_ids)), _ip(dst_ids), _ip(src_ids), L(len(src_ids)),
+                                  ctypes.c_int32(max_id), _ip(ro), _ip(ci))
+    return ro, ci[: ro[-1]].copy()
+
+
+def get_weight(vtx_size, dst_ids, src_ids, col_off, row_idx, impl="port"):
+    """``getweight`` (ops/getweight.py:29-37)."""
+    dst_ids, src_ids, col_off, row_idx = _i32(dst_ids), _i32(src_ids), _i32(col_off), _i32(row_idx)
+    w = np.zeros(len(row_idx), np.float32)
+    if impl == "ref":
+        ref_lib().ref_getweight(ctypes.c_int(vtx_size), _ip(dst_ids), ctypes.c_long(len(dst_ids)), _ip(src_ids),
+                                ctypes.c_long(len(src_ids)), _ip(col_off), _ip(row_idx), ctypes.c_long(len(row_idx)), _fp(w))
+    else:
+        port_lib().orc_get_weight(ctypes.c_int32(vtx_size), _ip(dst_ids), L(len(dst_ids)), _ip(col_off), _ip(row_idx), _fp(w))
+    return w
+
+
+def sample_reference(fanout, dst, layer_off, g_off, g_idx, seed=1):
+    """The reference's own CPU sampler (ops/cpp/sampleprocessing_op.cc:38-90; draws with ``rand()``)."""
+    dst, layer_off, g_off, g_idx = _i32(dst), _i32(layer_off), _i32(g_off), _i32(g_idx)
+    out = np.zeros(int(layer_off[-1]), np.int32)
+    ref_lib().ref_sampleprocessing(ctypes.c_int(fanout), _ip(dst), ctypes.c_long(len(dst)), _ip(layer_off), _ip(out),
+                                   ctypes.c_long(len(out)), _ip(g_off), ctypes.c_long(len(g_off) - 1), _ip(g_idx),
+                                   ctypes.c_long(len(g_idx)), ctypes.c_uint(seed))
+    return out
+
+
+def check_sample(fanout, dst, layer_off, layer_idx, g_off, g_idx):
+    """What every valid sample satisfies (the draw itself is random in the reference): column i
+    holds ``min(deg, fanout)`` entries; all of the destination's in-edges in their stored order when
+    ``deg <= fanout`` (or ``fanout < 0``), else ``fanout`` entries taken from DISTINCT positions of
+    its in-edge list.  Returns an error string or ``None``."""
+    for i, v in enumerate(dst):
+        nb = g_idx[g_off[v]: g_off[v + 1]]
+        got = layer_idx[layer_off[i]: layer_off[i + 1]]
+        want_n = len(nb) if fanout < 0 else min(len(nb), fanout)
+        if len(got) != want_n:
+            return f"column {i}: {len(got)} entries, expected {want_n}"
+        if want_n == len(nb):
+            if not np.array_equal(got, nb):
+                return f"column {i}: full copy differs"
+        else:
+            pool = {}
+            for x in nb:
+                pool[int(x)] = pool.get(int(x), 0) + 1
+            for x in got:
+                if pool.get(int(x), 0) == 0:
+                    return f"column {i}: {int(x)} drawn more often than it occurs"
+                pool[int(x)] -= 1
+    return None
+
+
 # --------------------------------------------------------------------- gcn_norm
 def gcn_norm(edge_index, w, n):
     """C restatement of gcn_norm + add_remaining_self_loops

@@ -238,3 +238,59 @@ int64_t orc_to_undirected(const int32_t* src, const int32_t* dst, const float* a
     free(ed);
     return m;
 }
+
+/* ---- neighbour-sampling operators ------------------------------------------------------------
+ * layer column counts (ops/cpp/gpuinitco_op.cc:37-52, the CUDA kernel; the CPU body is empty):
+ * out[i+1] = min(in-degree of dst[i], fanout); out[0] is left as the caller set it. */
+void orc_sample_counts(const int32_t* dst, int64_t n_dst, const int32_t* g_off, int32_t fanout, int32_t* out) {
+    for (int64_t i = 0; i < n_dst; i++) {
+        const int32_t deg = g_off[dst[i] + 1] - g_off[dst[i]];
+        out[i + 1] = deg < fanout ? deg : fanout;
+    }
+}
+
+/* CSC -> CSR over explicit id lists (ops/cpp/csctocsr_op.cc:26-80): row r of the result belongs to
+ * src_ids[r]; column values are dst_ids[column]; entries whose source id is not listed are dropped;
+ * inside a row the entries keep the CSC traversal order.  row_off must be zero-filled.  Returns the
+ * number of entries written. */
+int64_t orc_csc_to_csr(const int32_t* col_off, const int32_t* row_idx, int64_t n_dst, const int32_t* dst_ids,
+                       const int32_t* src_ids, int64_t n_src, int32_t max_id, int32_t* row_off, int32_t* col_idx) {
+    int32_t* where = (int32_t*)malloc(sizeof(int32_t) * (size_t)(max_id + 1));
+    for (int32_t i = 0; i <= max_id; i++) where[i] = -1;
+    for (int64_t i = 0; i < n_src; i++) where[src_ids[i]] = (int32_t)i;
+    for (int64_t i = 0; i < n_dst; i++)
+        for (int32_t j = col_off[i]; j < col_off[i + 1]; j++) {
+            const int32_t r = row_idx[j] <= max_id ? where[row_idx[j]] : -1;
+            if (r >= 0) row_off[r + 1]++;
+        }
+    for (int64_t i = 1; i <= n_src; i++) row_off[i] += row_off[i - 1];
+    int32_t* cur = (int32_t*)malloc(sizeof(int32_t) * (size_t)(n_src > 0 ? n_src : 1));
+    for (int64_t i = 0; i < n_src; i++) cur[i] = row_off[i];
+    for (int64_t i = 0; i < n_dst; i++)
+        for (int32_t j = col_off[i]; j < col_off[i + 1]; j++) {
+            const int32_t r = row_idx[j] <= max_id ? where[row_idx[j]] : -1;
+            if (r >= 0) col_idx[cur[r]++] = dst_ids[i];
+        }
+    const int64_t kept = row_off[n_src];
+    free(cur);
+    free(where);
+    return kept;
+}
+
+/* symmetric degree weights of a sampled layer (ops/cpp/getweight_op.cc:37-84): in-degree of
+ * dst_ids[i] += length of column i, out-degree of every listed source += 1 per entry,
+ * w = 1 / (sqrtf(out[src]) * sqrtf(in[dst])). */
+void orc_get_weight(int32_t vtx_size, const int32_t* dst_ids, int64_t n_dst, const int32_t* col_off, const int32_t* row_idx,
+                    float* out_w) {
+    int32_t* ins = (int32_t*)calloc((size_t)(vtx_size > 0 ? vtx_size : 1), sizeof(int32_t));
+    int32_t* outs = (int32_t*)calloc((size_t)(vtx_size > 0 ? vtx_size : 1), sizeof(int32_t));
+    for (int64_t i = 0; i < n_dst; i++) {
+        ins[dst_ids[i]] += col_off[i + 1] - col_off[i];
+        for (int32_t j = col_off[i]; j < col_off[i + 1]; j++) outs[row_idx[j]] += 1;
+    }
+    for (int64_t i = 0; i < n_dst; i++)
+        for (int32_t j = col_off[i]; j < col_off[i + 1]; j++)
+            out_w[j] = 1 / (sqrtf((float)outs[row_idx[j]]) * sqrtf((float)ins[dst_ids[i]]));
+    free(ins);
+    free(outs);
+}

@@ -15,6 +15,9 @@
 #include "scattertoedge_op.h"
 #include "edgetovertex_op.h"
 #include "toundirected_op.h"
+#include "csctocsr_op.h"
+#include "getweight_op.h"
+#include "sampleprocessing_op.h"
 
 namespace jittor {
 
@@ -40,6 +43,14 @@ EdgetovertexOp::EdgetovertexOp(Var* o, Var* x_, Var* i, Var* off, int fl)
 ToundirectedOp::ToundirectedOp(Var* ei, Var* ea, int ne, int nn, Var* nei, Var* nea, NanoString d)
     : output(nullptr), edge_index(ei), edge_attr(ea), new_edge_index(nei), new_edge_attr(nea),
       num_edges(ne), num_nodes(nn), dtype(d) {}
+CsctocsrOp::CsctocsrOp(Var* co, Var* ri, Var* ro, Var* ci, Var* d, Var* s_)
+    : output(nullptr), column_offset(co), row_indices(ri), row_offset(ro), column_indices(ci), src(s_), dst(d) {}
+GetweightOp::GetweightOp(int n, Var* d, Var* s_, Var* co, Var* ri, Var* w)
+    : output(nullptr), vtx_size(n), csc_layer_dst(d), csc_layer_src(s_), csc_layer_column_offset(co),
+      csc_layer_row_indices(ri), csc_layer_edge_weight(w) {}
+SampleprocessingOp::SampleprocessingOp(int f, Var* d, Var* co, Var* ri, Var* gco, Var* gri)
+    : output(nullptr), fanout_i(f), csc_layer_dst(d), csc_layer_column_offset(co), csc_layer_row_indices(ri),
+      csc_global_column_offset(gco), csc_global_row_indices(gri) {}
 
 }  // namespace jittor
 
@@ -110,6 +121,33 @@ long ref_toundirected(int* edge_index, float* attr, long E, int n, int* new_edge
     jittor::ToundirectedOp op(&ei, &ea, (int)E, n, &nei, &nea, jittor::ns_float32);
     op.jit_run();
     return nei.shape[1];
+}
+
+// row_off [n_src+1] must be zero-filled (the reference wrapper allocates it with jt.zeros).  Source
+// ids must stay below 2^20: the body's id table has that many slots.
+void ref_csctocsr(int* col_off, int* row_idx, long n_dst, long E, int* dst_ids, int* src_ids, long n_src, int* row_off,
+                  int* col_idx) {
+    Var co = mk(col_off, n_dst + 1), ri = mk(row_idx, E), ro = mk(row_off, n_src + 1), ci = mk(col_idx, E);
+    Var d = mk(dst_ids, n_dst), s = mk(src_ids, n_src);
+    jittor::CsctocsrOp op(&co, &ri, &ro, &ci, &d, &s);
+    op.jit_run();
+}
+
+void ref_getweight(int vtx_size, int* dst_ids, long n_dst, int* src_ids, long n_src, int* col_off, int* row_idx, long E,
+                   float* out_w) {
+    Var d = mk(dst_ids, n_dst), s = mk(src_ids, n_src), co = mk(col_off, n_dst + 1), ri = mk(row_idx, E), w = mk(out_w, E);
+    jittor::GetweightOp op(vtx_size, &d, &s, &co, &ri, &w);
+    op.jit_run();
+}
+
+// The body draws with rand(): `seed` goes to srand() first.
+void ref_sampleprocessing(int fanout, int* dst_ids, long n_dst, int* layer_off, int* layer_idx, long E_layer, int* g_off,
+                          long n_global, int* g_idx, long E_global, unsigned seed) {
+    Var d = mk(dst_ids, n_dst), lo = mk(layer_off, n_dst + 1), li = mk(layer_idx, E_layer);
+    Var go = mk(g_off, n_global + 1), gi = mk(g_idx, E_global);
+    srand(seed);
+    jittor::SampleprocessingOp op(fanout, &d, &lo, &li, &go, &gi);
+    op.jit_run();
 }
 
 }  // extern "C"

@@ -136,3 +136,34 @@ def test_fused_gat_restatement_equals_unfused_reference_pipeline(oracle):
     unfused = oracle.gat_unfused(h, a, idx, off, impl)
     fused = oracle.gat_aggregate(h, a[:C].reshape(1, C), a[C:].reshape(1, C), idx, off, 1, C)
     assert np.abs(unfused - fused).max() <= 2e-6
+
+
+def test_sampling_checkers_on_the_reference_fixtures(oracle):
+    """gpuinitco / csctocsr / getweight inputs of the reference's own tests (tests/test_gpuinitco.py:15-22,
+    tests/test_csctocsr.py:25-35, tests/test_getweight.py:25-48) with the outputs those files state; the C
+    restatement against the compiled reference bodies on the same inputs and on a random case."""
+    ids = np.arange(4, dtype=np.int32)
+    assert oracle.sample_counts(ids, np.array([0, 1, 3, 4, 5]), 2).tolist() == [0, 1, 2, 1, 1]
+    impls = ["port", "ref"] if oracle.have_ref() else ["port"]
+    for impl in impls:
+        ro, ci = oracle.csc_to_csr(np.array([0, 0, 1, 2, 4]), np.array([0, 0, 1, 2]), ids, ids, impl)
+        assert ro.tolist() == [0, 2, 3, 4, 4] and ci.tolist() == [1, 2, 3, 3]
+        w = oracle.get_weight(4, ids, ids, np.array([0, 1, 2, 3, 4]), np.array([0, 0, 1, 2]), impl)
+        assert np.abs(w - np.array([2 ** -0.5, 2 ** -0.5, 1, 1])).max() <= 1e-7
+    rng = np.random.default_rng(0)
+    n = 300
+    dst = rng.integers(0, n, size=4000)
+    off = np.concatenate([[0], np.cumsum(np.bincount(dst, minlength=n))]).astype(np.int32)
+    idx = rng.integers(0, n, size=4000).astype(np.int32)
+    ids = np.arange(n, dtype=np.int32)
+    if oracle.have_ref():
+        a, b = oracle.csc_to_csr(off, idx, ids, ids, "port"), oracle.csc_to_csr(off, idx, ids, ids, "ref")
+        assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+        assert np.array_equal(oracle.get_weight(n, ids, ids, off, idx, "port"), oracle.get_weight(n, ids, ids, off, idx, "ref"))
+        some = rng.permutation(n)[:40].astype(np.int32)
+        l_off = oracle.sample_counts(some, off, 6).cumsum().astype(np.int32)
+        drawn = oracle.sample_reference(6, some, l_off, off, idx, seed=5)
+        assert oracle.check_sample(6, some, l_off, drawn, off, idx) is None
+    # the property checker rejects a sample that repeats a position
+    bad_off = np.array([0, 2], np.int32)
+    assert oracle.check_sample(2, np.array([0]), bad_off, np.array([7, 7]), np.array([0, 3]), np.array([7, 8, 9])) is not None
