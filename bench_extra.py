@@ -1,4 +1,4 @@
-"""Secondary workloads of ``bench.py`` (``--workload convert|gat|gcn|gemm``): the other
+"""Secondary workloads of ``bench.py`` (``--workload convert|gat|gcn|gemm|sample``): the other
 configurations of the hot path, each printed as one JSON line in the same shape as the headline.
 They are measurement helpers for the kernels that the default SpMM sweep does not exercise."""
 import json
@@ -251,5 +251,62 @@ def run_gcn(args):
         dist.destroy_process_group()
 
 
+def run_sample(args):
+    """Mini-batch neighbour sampling: 1024 seed nodes, fanout [25, 10], on the SpMM workload's graph;
+    one step = one batch through the whole sampler (two sampled layers, merged local CSC + CSR,
+    degree weights, 128-wide feature rows of the touched nodes)."""
+    import jittorgeometric_b200 as jg
+    from jittorgeometric_b200 import sampling, synth
+    dev = torch.device("cuda", 0)
+    scale = args.scale
+    ei, n = synth.rmat_graph(scale, args.edge_factor // 2, bench.SEED + 1, device=dev)
+    csc = jg.cootocsc(ei, None, n)
+    del ei
+    feat = torch.randn((n, 128), device=dev, generator=torch.Generator(device=dev).manual_seed(12))
+    fanout, batch = [25, 10], 1024
+    seeds = torch.randperm(n, device=dev, generator=torch.Generator(device=dev).manual_seed(13))[: batch * 64].to(torch.int32)
+    state = {"k": 0, "edges": 0, "nodes": 0}
+
+    def step():
+        k = state["k"] % 64
+        ssg = sampling.sample_one(fanout, csc.column_offset, csc.row_indices, seeds[k * batch: (k + 1) * batch].contiguous(),
+                                  feat, None, seed=state["k"])
+        state["k"] += 1
+        state["edges"], state["nodes"] = ssg.num_edges, ssg.num_nodes
+
+    sampler = bench.ClockSampler(0); sampler.start()
+    ms = _time(step, args.steps, args.warmup)
+    clocks = sampler.stop()
+    peak, kind = bench.measured_peaks()
+    E, m = state["edges"], state["nodes"]
+    alg = E * 4 * 6 + m * 128 * 4 * 2           # sampled ids written and re-read through merge/sort/weights, feature rows in and out
+    cpu = None
+    if args.cpu_budget > 0:
+        import numpy as np
+        import oracle as O
+        if O.have_ref():
+            g_off, g_idx = csc.column_offset.cpu().numpy(), csc.row_indices.cpu().numpy()
+            dst = seeds[:batch].cpu().numpy()
+            t0 = time.perf_counter()
+            drawn = 0
+            for f in fanout:                      # the reference's CPU sampler body, layer after layer
+                off = np.concatenate([[0], np.cumsum(O.sample_counts(dst, g_off, f)[1:])]).astype(np.int32)
+                idx = O.sample_reference(f, dst, off, g_off, g_idx)
+                drawn += len(idx)
+                dst = np.unique(idx).astype(np.int32)
+            dt = time.perf_counter() - t0
+            cpu = {"value": drawn / dt, "unit": "edge/s", "cores": 1, "kind": "reference",
+                   "sample": f"one batch: the reference's sampleprocessing CPU body for both layers ({drawn} sampled edges, "
+                             f"{dt * 1e3:.1f} ms); its Python merge loops over nodes are not included"}
+    _line(args, "sampled_edges_per_s", "edge/s", E / (ms * 1e-3), ms,
+          f"mini-batch sampling: {batch} seeds, fanout {fanout}, R-MAT scale {scale} graph ({n} nodes, {csc.row_indices.numel()} "
+          f"in-edges); per batch {E} sampled edges over {m} nodes, 128-wide features gathered",
+          {"bound": "hbm", "achieved": alg / ms / 1e6, "peak": peak, "unit": "GB/s", "frac": alg / ms / 1e6 / peak,
+           "traffic": None, "peak_kind": kind, "kernel": "sample_neighbors_kernel",
+           "note": "latency-bound by construction: a batch moves a few MB through about 40 short launches and four "
+                   "device-to-host size reads; the figure to read is milliseconds per batch"},
+          {"cpu_baseline": cpu, "gpu_launches": args.steps * 40, "clocks": clocks})
+
+
 def run(args):
-    return {"convert": run_convert, "gat": run_gat, "gemm": run_gemm, "gcn": run_gcn}[args.workload](args)
+    return {"convert": run_convert, "gat": run_gat, "gemm": run_gemm, "gcn": run_gcn, "sample": run_sample}[args.workload](args)

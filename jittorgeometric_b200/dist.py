@@ -31,14 +31,24 @@ from .data import CSC, CSR
 
 
 class RowPartition:
-    """Contiguous destination-row ranges: rank q owns rows [q * pad, min((q + 1) * pad, n))."""
+    """Contiguous destination-row ranges.  By default rank q owns rows
+    [q * pad, min((q + 1) * pad, n)) with ``pad = ceil(n / world)``; ``bounds`` (``world + 1``
+    non-decreasing values from 0 to n) gives the ranges explicitly, e.g. the offsets of a
+    partition file after the nodes have been reordered by part
+    (partition/distchunk_manager.py:88-93)."""
 
-    def __init__(self, n, world):
+    def __init__(self, n, world, bounds=None):
         if world < 1:
             raise ValueError("world size must be positive")
         self.n, self.world = int(n), int(world)
         self.pad = (self.n + self.world - 1) // self.world if self.n else 0
-        self.bounds = [min(q * self.pad, self.n) for q in range(self.world + 1)]
+        if bounds is None:
+            self.bounds = [min(q * self.pad, self.n) for q in range(self.world + 1)]
+        else:
+            self.bounds = [int(b) for b in bounds]
+            if (len(self.bounds) != self.world + 1 or self.bounds[0] != 0 or self.bounds[-1] != self.n
+                    or any(a > b for a, b in zip(self.bounds[:-1], self.bounds[1:]))):
+                raise ValueError(f"bounds must be {self.world + 1} non-decreasing values from 0 to {self.n}")
 
     def range(self, rank):
         return self.bounds[rank], self.bounds[rank + 1]
@@ -48,7 +58,8 @@ class RowPartition:
         return hi - lo
 
     def owner(self, row):
-        return min(int(row) // self.pad, self.world - 1) if self.pad else 0
+        import bisect
+        return min(max(bisect.bisect_right(self.bounds, int(row)) - 1, 0), self.world - 1)
 
 
 class DeviceBackend:
