@@ -212,12 +212,14 @@ def run_gcn(args):
 
     def forward():
         if world > 1:
-            z1 = torch.relu(g.aggregate(jg.linear_tf32(x, W1, weight_t=W1t)) + b1)
-            return g.aggregate(jg.linear_tf32(z1, W2, weight_t=W2t)) + b2
+            z1 = g.aggregate(jg.linear_tf32(x, W1, weight_t=W1t), bias=b1, relu=True)
+            return g.aggregate(jg.linear_tf32(z1, W2, weight_t=W2t), bias=b2)
         h1 = jg.linear_tf32(x, W1, weight_t=W1t)
-        z1 = torch.relu(jg.segment_aggregate(h1, csc.row_indices, csc.column_offset, csc.edge_weight, plan=plan) + b1)
+        z1 = jg.segment_aggregate(h1, csc.row_indices, csc.column_offset, csc.edge_weight, plan=plan, bias=b1, relu=True)
+        del h1
         h2 = jg.linear_tf32(z1, W2, weight_t=W2t)
-        return jg.segment_aggregate(h2, csc.row_indices, csc.column_offset, csc.edge_weight, plan=plan) + b2
+        del z1
+        return jg.segment_aggregate(h2, csc.row_indices, csc.column_offset, csc.edge_weight, plan=plan, bias=b2)
 
     for _ in range(args.warmup):
         forward()

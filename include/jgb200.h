@@ -85,6 +85,15 @@ int jg_aggregate_add_f32(float* out, const float* x, const int32_t* idx, const i
                          const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes,
                          jg_stream_t stream);
 
+/* The same aggregation with the layer's epilogue fused into the store of every finished row:
+ * out[v,:] = act(sum + bias), bias [f] or NULL, relu != 0 clamps at zero.  Replaces the separate
+ * elementwise passes of `out = out + self.bias` and `nn.relu(...)` that follow the aggregation in the
+ * reference layers (nn/conv/gcn_conv.py:100-101, examples/gcn_example.py:76-77), each a read and a
+ * write of the whole [n_out, f] matrix. */
+int jg_aggregate_bias_act_f32(float* out, const float* x, const int32_t* idx, const int32_t* off, const float* w,
+                              const float* bias, int relu, int64_t n_out, int64_t n_in, int64_t f, int64_t nnz,
+                              const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes, jg_stream_t stream);
+
 /* ------------------------------------------------------------------ 1-D row partition
  * Splits the in-edge structure of one shard (destination rows [lo, hi) of the graph, `idx`
  * holding GLOBAL source ids) into interior entries (source inside [lo, hi), ids rebased to the

@@ -96,6 +96,8 @@ struct AggArgs {
     float* partial;
     unsigned long long* ticket;
     int accumulate;  // 1: add the aggregated row to what `out` already holds (old + sum)
+    const float* bias;  // epilogue on finished output rows: + bias[column] (null: none) ...
+    int relu;           // ... then max(., 0)
 };
 
 
@@ -118,7 +120,8 @@ __device__ __forceinline__ void axpy4(float4& a, const float4& v, float w) {
 
 // Vector-width kernel (F = 4*G*VPL).  G lanes cover one feature row, 32/G entries are gathered
 // side by side, B steps per batch.
-template <int G, int VPL, int B, int MINB, bool EXACT>
+// EPI compiles in the bias/ReLU epilogue (a separate instantiation, so the plain kernel is untouched).
+template <int G, int VPL, int B, int MINB, bool EXACT, bool EPI>
 __global__ void __launch_bounds__(kBlock, MINB) aggregate_rows_kernel(AggArgs a) {
     constexpr int EPS = 32 / G;
     constexpr int F = 4 * G * VPL;
@@ -262,6 +265,16 @@ __global__ void __launch_bounds__(kBlock, MINB) aggregate_rows_kernel(AggArgs a)
                         acc[q].z = __fadd_rn(old.z, acc[q].z);
                         acc[q].w = __fadd_rn(old.w, acc[q].w);
                     }
+                    if (EPI && id >= n_items) {   // a finished output row (pieces of hub rows get theirs in the fix-up)
+                        if (a.bias) {
+                            const float4 b4 = __ldg(reinterpret_cast<const float4*>(a.bias) + fl + q * G);
+                            acc[q].x += b4.x; acc[q].y += b4.y; acc[q].z += b4.z; acc[q].w += b4.w;
+                        }
+                        if (a.relu) {
+                            acc[q].x = fmaxf(acc[q].x, 0.f); acc[q].y = fmaxf(acc[q].y, 0.f);
+                            acc[q].z = fmaxf(acc[q].z, 0.f); acc[q].w = fmaxf(acc[q].w, 0.f);
+                        }
+                    }
                     __stcs(o + q * G, acc[q]);
                 }
             }
@@ -270,7 +283,7 @@ __global__ void __launch_bounds__(kBlock, MINB) aggregate_rows_kernel(AggArgs a)
 }
 
 // Any feature width: lanes stride over columns with scalar loads, up to 256 columns per sweep.
-__device__ __forceinline__ void warp_segment_any(const AggArgs& a, int32_t s, int32_t e, float* dst, bool add_old) {
+__device__ __forceinline__ void warp_segment_any(const AggArgs& a, int32_t s, int32_t e, float* dst, bool add_old, bool final_row) {
     constexpr int Q = 8;
     constexpr int UNROLL = 4;
     const int lane = lane_id();
@@ -309,8 +322,14 @@ __device__ __forceinline__ void warp_segment_any(const AggArgs& a, int32_t s, in
         }
 #pragma unroll
         for (int q = 0; q < Q; q++)
-            if (c0 + q * 32 + lane < F)
-                dst[c0 + q * 32 + lane] = add_old ? __fadd_rn(dst[c0 + q * 32 + lane], acc[q]) : acc[q];
+            if (c0 + q * 32 + lane < F) {
+                float v = add_old ? __fadd_rn(dst[c0 + q * 32 + lane], acc[q]) : acc[q];
+                if (final_row) {
+                    if (a.bias) v += __ldg(a.bias + c0 + q * 32 + lane);
+                    if (a.relu) v = fmaxf(v, 0.f);
+                }
+                dst[c0 + q * 32 + lane] = v;
+            }
     }
 }
 
@@ -355,7 +374,7 @@ __global__ void __launch_bounds__(kBlock) aggregate_any_kernel(AggArgs a) {
                 if (e - s > chunk) continue;  // hub row: its pieces are separate work ids
                 dst = a.out + (size_t)row * F;
             }
-            warp_segment_any(a, s, e, dst, a.accumulate && id >= n_items);
+            warp_segment_any(a, s, e, dst, a.accumulate && id >= n_items, id >= n_items);
         }
     }
 }
@@ -375,7 +394,10 @@ __global__ void __launch_bounds__(kBlock) hub_fixup_kernel(AggArgs a) {
         float acc = p[0];
         for (int k = 1; k < pieces; k++) acc = __fadd_rn(acc, p[(size_t)k * F]);
         float* o = a.out + (size_t)row * F + c;
-        *o = a.accumulate ? __fadd_rn(*o, acc) : acc;
+        float v = a.accumulate ? __fadd_rn(*o, acc) : acc;
+        if (a.bias) v += __ldg(a.bias + c);
+        if (a.relu) v = fmaxf(v, 0.f);
+        *o = v;
     }
 }
 
@@ -393,8 +415,9 @@ static int launch_persistent(K kern, int* blocks_per_sm, const AggArgs& a, cudaS
 
 template <int G, int VPL, int B, int MINB, bool EXACT>
 static int launch_rows(const AggArgs& a, cudaStream_t st) {
-    static int blocks_per_sm = 0;
-    return launch_persistent(aggregate_rows_kernel<G, VPL, B, MINB, EXACT>, &blocks_per_sm, a, st);
+    static int blocks_per_sm = 0, blocks_per_sm_epi = 0;
+    if (a.bias || a.relu) return launch_persistent(aggregate_rows_kernel<G, VPL, B, MINB, EXACT, true>, &blocks_per_sm_epi, a, st);
+    return launch_persistent(aggregate_rows_kernel<G, VPL, B, MINB, EXACT, false>, &blocks_per_sm, a, st);
 }
 
 // Picks the kernel for a feature width: the vector kernel for the 128-bit-aligned widths it is
@@ -456,7 +479,7 @@ size_t jg_aggregate_workspace_bytes(int64_t n_out, int64_t nnz, int64_t f, int32
 static int aggregate_impl(float* out, const float* x, const int32_t* idx, const int32_t* off,
                           const float* w, int64_t n_out, int64_t n_in, int64_t f, int64_t nnz,
                           const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes,
-                          jg_stream_t stream, int accumulate) {
+                          jg_stream_t stream, int accumulate, const float* bias = nullptr, int relu = 0) {
     JG_CHECK_ARG(n_out >= 0 && n_in >= 0 && f >= 0 && nnz >= 0, JG_EINVAL, "aggregate: negative size");
     if (n_out == 0 || f == 0) return JG_OK;
     JG_CHECK_ARG(out && off, JG_EINVAL, "aggregate: null out/off");
@@ -472,6 +495,10 @@ static int aggregate_impl(float* out, const float* x, const int32_t* idx, const 
     AggArgs a = {};
     a.out = out; a.x = x; a.idx = idx; a.off = off; a.w = w; a.n_out = n_out; a.f = f;
     a.accumulate = accumulate;
+    a.bias = bias;
+    a.relu = relu;
+    JG_CHECK_ARG(!bias || f % 4 != 0 || reinterpret_cast<uintptr_t>(bias) % 16 == 0, JG_EINVAL,
+                 "aggregate: bias must be 16-byte aligned");
     Carver c(workspace);
     a.ticket = c.take<unsigned long long>(1);
     if (plan) {
@@ -504,6 +531,13 @@ int jg_aggregate_add_f32(float* out, const float* x, const int32_t* idx, const i
                          const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes,
                          jg_stream_t stream) {
     return aggregate_impl(out, x, idx, off, w, n_out, n_in, f, nnz, plan, chunk, workspace, workspace_bytes, stream, 1);
+}
+
+int jg_aggregate_bias_act_f32(float* out, const float* x, const int32_t* idx, const int32_t* off, const float* w,
+                              const float* bias, int relu, int64_t n_out, int64_t n_in, int64_t f, int64_t nnz,
+                              const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes, jg_stream_t stream) {
+    return aggregate_impl(out, x, idx, off, w, n_out, n_in, f, nnz, plan, chunk, workspace, workspace_bytes, stream, 0, bias,
+                          relu ? 1 : 0);
 }
 
 // ------------------------------------------------------------------------------------------

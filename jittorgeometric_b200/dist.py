@@ -103,8 +103,9 @@ class DeviceBackend:
     def plan(self, off, nnz):
         return ops.SpmmPlan(off, nnz)
 
-    def aggregate(self, x, idx, off, w, n_out, plan, out=None, accumulate=False):
-        return ops.segment_aggregate(x, idx, off, w, n_out=n_out, plan=plan, out=out, accumulate=accumulate)
+    def aggregate(self, x, idx, off, w, n_out, plan, out=None, accumulate=False, bias=None, relu=False):
+        return ops.segment_aggregate(x, idx, off, w, n_out=n_out, plan=plan, out=out, accumulate=accumulate, bias=bias,
+                                     relu=relu)
 
 
 class _Done:
@@ -292,17 +293,25 @@ class ShardedGraph:
             self._recv[f] = buf
         return buf
 
-    def aggregate(self, x):
+    def aggregate(self, x, bias=None, relu=False):
         """``y[v] = sum_{(u -> v)} w * x_global[u]`` for the rank's own rows ``v``; ``x`` holds the
         rank's ``n_local`` rows of the feature matrix (extra rows are ignored).  With autograd the
         gradient is the same aggregation applied to the incoming gradient, which is the true
         gradient for a symmetric matrix (the normalised adjacency of an undirected graph) - the
-        rule the reference's ``DistSpmmFunc.grad`` follows (ops/distspmm.py:42-57)."""
+        rule the reference's ``DistSpmmFunc.grad`` follows (ops/distspmm.py:42-57).  ``bias`` / ``relu``
+        apply ``act(y + bias)``; without autograd and in the merged schedule they are fused into the
+        aggregation kernel's store."""
         if torch.is_grad_enabled() and x.requires_grad:
-            return _ShardedAggregate.apply(x, self)
-        return self._aggregate(x)
+            y = _ShardedAggregate.apply(x, self)
+        elif bias is not None or relu:
+            return self._aggregate(x, bias, relu)
+        else:
+            return self._aggregate(x)
+        if bias is not None:
+            y = y + bias
+        return torch.relu(y) if relu else y
 
-    def _aggregate(self, x):
+    def _aggregate(self, x, bias=None, relu=False):
         if x.shape[0] < self.n_local:
             raise RuntimeError(f"x has {x.shape[0]} rows, the rank owns {self.n_local}")
         f = x.shape[1]
@@ -315,6 +324,9 @@ class ShardedGraph:
             if x.data_ptr() != buf.data_ptr():
                 buf[: self.n_local].copy_(x[: self.n_local])
             handle.wait()
+            if bias is not None or relu:
+                return self.backend.aggregate(buf, self.merged[0], self.merged[1], self.merged[2], self.n_local,
+                                              self.merged_plan, bias=bias, relu=relu)
             return self.backend.aggregate(buf, self.merged[0], self.merged[1], self.merged[2], self.n_local,
                                           self.merged_plan)
         recv = buf
@@ -326,7 +338,9 @@ class ShardedGraph:
         if self.halo[0].numel():
             self.backend.aggregate(recv, self.halo[0], self.halo[1], self.halo[2], self.n_local, self.halo_plan,
                                    out=y, accumulate=True)
-        return y
+        if bias is not None:
+            y += bias
+        return y.relu_() if relu else y
 
 
 class _ShardedAggregate(torch.autograd.Function):

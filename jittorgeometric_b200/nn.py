@@ -40,11 +40,13 @@ def _transform(x, weight, tf32, relu=False):
 
 class GCNConv(torch.nn.Module):
     """``out = A_hat (x W) + b`` (nn/conv/gcn_conv.py:70-112).  ``spmm`` is accepted for signature
-    compatibility; there is one backend."""
+    compatibility; there is one backend.  The bias (and, with ``relu=True``, the activation the
+    reference's models apply right after the layer) is added inside the aggregation kernel."""
 
-    def __init__(self, in_channels, out_channels, bias=True, spmm=True, tf32=False, **kwargs):
+    def __init__(self, in_channels, out_channels, bias=True, spmm=True, tf32=False, relu=False, **kwargs):
         super().__init__()
         self.in_channels, self.out_channels, self.spmm, self.tf32 = in_channels, out_channels, spmm, tf32
+        self.relu = relu
         self.weight = torch.nn.Parameter(torch.empty(in_channels, out_channels))
         self.bias = torch.nn.Parameter(torch.zeros(out_channels)) if bias else None
         self.reset_parameters()
@@ -57,10 +59,7 @@ class GCNConv(torch.nn.Module):
 
     def forward(self, x, csc, csr):
         x = _transform(x, self.weight, self.tf32)
-        out = ops.aggregateWithWeight(x, csc, csr)
-        if self.bias is not None:
-            out = out + self.bias
-        return out
+        return ops.aggregate_bias_act(x, csc, csr, self.bias, self.relu)
 
     def __repr__(self):
         return f"{self.__class__.__name__}({self.in_channels}, {self.out_channels})"

@@ -13,7 +13,7 @@ from . import _lib
 from ._lib import check, lib, ptr, stream_for, workspace
 from .data import CSC, CSR
 
-__all__ = ["aggregateWithWeight", "segment_aggregate", "SpmmPlan", "cootocsr", "cootocsc", "gcn_norm_csc_csr",
+__all__ = ["aggregateWithWeight", "aggregate_bias_act", "segment_aggregate", "SpmmPlan", "cootocsr", "cootocsc", "gcn_norm_csc_csr",
            "SpmmCsr", "SpmmCoo", "ScatterToEdge", "ScatterToVertex", "EdgeSoftmax", "gat_aggregate",
            "gat_aggregate_supported", "gcn_norm_coo", "linear_tf32", "linear_tf32_supported", "toUndirected", "validate_structure"]
 
@@ -76,12 +76,14 @@ def _plan_of(holder, off, nnz):
     return plan
 
 
-def segment_aggregate(x, idx, off, w, n_out=None, plan=None, out=None, accumulate=False):
+def segment_aggregate(x, idx, off, w, n_out=None, plan=None, out=None, accumulate=False, bias=None, relu=False):
     """out[v,:] = sum_{j in [off[v], off[v+1])} w[j] * x[idx[j],:]  (fp32).
 
     The one kernel behind aggregateWithWeight (forward over CSC, backward over
     CSR), SpmmCsr and SpmmCoo.  ``plan`` is an :class:`SpmmPlan` of ``off`` or
-    ``None`` to process every row unsplit.  ``accumulate=True`` adds the result to ``out``."""
+    ``None`` to process every row unsplit.  ``accumulate=True`` adds the result to ``out``.
+    ``bias`` / ``relu`` fuse the layer epilogue ``act(sum + bias)`` into the store of every row
+    (forward only, not together with ``accumulate``)."""
     x = _as_f32(x, "x")
     if x.dim() != 2:
         raise RuntimeError("x: expected a 2-D feature matrix")
@@ -101,6 +103,16 @@ def segment_aggregate(x, idx, off, w, n_out=None, plan=None, out=None, accumulat
         out = torch.empty((n_out, f), dtype=torch.float32, device=x.device)
     chunk = plan.chunk if plan is not None else 0
     ws = workspace(lib().jg_aggregate_workspace_bytes(n_out, nnz, f, chunk), x.device)
+    if bias is not None or relu:
+        if accumulate:
+            raise RuntimeError("segment_aggregate: the fused epilogue cannot be combined with accumulate=True")
+        b = None if bias is None else _as_f32(bias, "bias")
+        if b is not None and b.numel() != f:
+            raise RuntimeError(f"bias has {b.numel()} entries, the feature width is {f}")
+        check(lib().jg_aggregate_bias_act_f32(ptr(out), ptr(x), ptr(idx), ptr(off), ptr(w), ptr(b), 1 if relu else 0, n_out, n_in,
+                                              f, nnz, ptr(plan.buf) if plan is not None else None, chunk, ptr(ws), ws.numel(),
+                                              stream_for(x)), "jg_aggregate_bias_act_f32")
+        return out
     fn = lib().jg_aggregate_add_f32 if accumulate else lib().jg_aggregate_f32
     check(fn(ptr(out), ptr(x), ptr(idx), ptr(off), ptr(w), n_out, n_in, f, nnz,
                                  ptr(plan.buf) if plan is not None else None, chunk, ptr(ws), ws.numel(),
@@ -136,6 +148,44 @@ def aggregateWithWeight(x, csc, csr, weight=None):
     (ops/aggregateWithWeight.py:53-55).  ``weight`` overrides the containers'
     edge weights for both directions, as in the reference."""
     return _AggregateFunc.apply(x, csc, csr, weight)
+
+
+class _AggregateBiasAct(torch.autograd.Function):
+    """``act(A x + b)`` with the epilogue fused into the aggregation's store; backward masks the
+    gradient with the saved output, sums it for the bias and aggregates it over the CSR."""
+
+    @staticmethod
+    def forward(ctx, x, bias, csc, csr, relu):
+        out = segment_aggregate(x, csc.row_indices, csc.column_offset, csc.edge_weight,
+                                plan=_plan_of(csc, csc.column_offset, csc.row_indices.numel()), bias=bias, relu=relu)
+        ctx.csr, ctx.relu, ctx.has_bias = csr, relu, bias is not None
+        if relu:
+            ctx.save_for_backward(out)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        g = grad_output
+        if ctx.relu:
+            (out,) = ctx.saved_tensors
+            g = g * (out > 0)
+        g = g.contiguous()
+        csr = ctx.csr
+        gx = None
+        if ctx.needs_input_grad[0]:
+            gx = segment_aggregate(g, csr.column_indices, csr.row_offset, csr.edge_weight,
+                                   plan=_plan_of(csr, csr.row_offset, csr.column_indices.numel()))
+        gb = g.sum(0) if ctx.has_bias and ctx.needs_input_grad[1] else None
+        return gx, gb, None, None, None
+
+
+def aggregate_bias_act(x, csc, csr, bias=None, relu=False):
+    """``act(aggregateWithWeight(x, csc, csr) + bias)`` in one kernel: what the reference computes
+    with separate elementwise passes after the aggregation (nn/conv/gcn_conv.py:96-101 and the
+    ``nn.relu`` of examples/gcn_example.py:76)."""
+    if bias is None and not relu:
+        return aggregateWithWeight(x, csc, csr)
+    return _AggregateBiasAct.apply(x, bias, csc, csr, bool(relu))
 
 
 def _edge_index(edge_index):

@@ -189,3 +189,49 @@ def test_cuda_graph_replay(cuda, oracle):
         want = oracle.aggregate(xv, d["row_indices"], d["column_offset"], d["csc_weight"])
         truth, scale = oracle.aggregate_f64(xv, d["row_indices"], d["column_offset"], d["csc_weight"])
         assert rel_err(got, want, scale) <= 1e-5
+
+
+@pytest.mark.parametrize("f", [7, 32, 64, 100, 128, 256, 512])
+def test_fused_bias_and_relu_epilogue(cuda, f):
+    """act(sum + bias) written by the aggregation kernel equals the aggregation followed by the two
+    elementwise passes, bit for bit; rows split into pieces (hubs) and empty rows included."""
+    rng = np.random.default_rng(40 + f)
+    n = 900
+    idx, off, w = random_graph(rng, n, n, 12000, hubs=2, hub_deg=3000)
+    off[-1] = off[-2]                                            # make sure the last row is empty
+    idx, w = idx[: off[-1]], w[: off[-1]]
+    x = rng.standard_normal((n, f)).astype(np.float32)
+    bias = rng.standard_normal(f).astype(np.float32)
+    off_t = dev(off)
+    plan = cuda.ops.SpmmPlan(off_t, len(idx), 1024)
+    for pl in (plan, None):
+        plain = cuda.ops.segment_aggregate(dev(x), dev(idx), off_t, dev(w), plan=pl)
+        for b, relu in ((dev(bias), True), (dev(bias), False), (None, True)):
+            got = cuda.ops.segment_aggregate(dev(x), dev(idx), off_t, dev(w), plan=pl, bias=b, relu=relu)
+            want = plain if b is None else plain + b
+            want = torch.relu(want) if relu else want
+            assert torch.equal(got, want)
+    assert torch.equal(got[-1], torch.zeros(f, device="cuda"))   # empty row: relu(0) with no bias
+    with pytest.raises(RuntimeError):
+        cuda.ops.segment_aggregate(dev(x), dev(idx), off_t, dev(w), out=plain, accumulate=True, relu=True)
+
+
+def test_fused_epilogue_autograd(cuda):
+    """aggregate_bias_act against the unfused composition: outputs equal, gradients of x and bias
+    equal (the backward masks with the saved output and aggregates over the CSR)."""
+    rng = np.random.default_rng(50)
+    n, f = 600, 64
+    ei = np.unique(rng.integers(0, n, size=(7000, 2)), axis=0).T.astype(np.int32)
+    w = rng.random(ei.shape[1]).astype(np.float32)
+    csc, csr = cuda.cootocsc(dev(ei), dev(w), n), cuda.cootocsr(dev(ei), dev(w), n)
+    x0 = rng.standard_normal((n, f)).astype(np.float32)
+    b0 = rng.standard_normal(f).astype(np.float32)
+    g0 = dev(rng.standard_normal((n, f)).astype(np.float32))
+    res = []
+    for fused in (True, False):
+        x, b = dev(x0).requires_grad_(True), dev(b0).requires_grad_(True)
+        y = cuda.ops.aggregate_bias_act(x, csc, csr, b, relu=True) if fused else torch.relu(cuda.aggregateWithWeight(x, csc, csr) + b)
+        y.backward(g0)
+        res.append((y.detach(), x.grad, b.grad))
+    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
+    assert (res[0][2] - res[1][2]).abs().max().item() <= 1e-4 * res[1][2].abs().max().item()

@@ -104,6 +104,10 @@ def test_emulated_ranks_on_one_gpu(cuda, oracle, world, n, f, mode):
         assert np.array_equal(y, g.aggregate(loop.features[rank]).cpu().numpy())
         if mode == "merged":                              # every row summed exactly as the unpartitioned kernel sums it
             assert np.array_equal(y, whole[lo:hi])
+        # layer epilogue: fused into the kernel's store (merged) or applied afterwards (overlap)
+        bias = torch.linspace(-1, 1, f, device="cuda")
+        z = g.aggregate(loop.features[rank], bias=bias, relu=True)
+        assert torch.equal(z, torch.relu(torch.from_numpy(y).cuda() + bias))
 
 
 def test_accumulate_mode(cuda, oracle):
