@@ -103,7 +103,7 @@ __device__ __forceinline__ Elem load_elem(const SortSrc& s, int64_t p) {
     e.key = 0; e.idx = 0; e.w = 0.f;
     if (!e.valid) return e;
     if (s.mode == 0) {
-        e.key = s.key[p]; e.idx = s.idx[p]; e.w = s.w[p];
+        e.key = s.key[p]; e.idx = s.idx[p]; e.w = s.w ? s.w[p] : 1.f;
     } else if (s.mode == 2) {
         // mirrored list: position 2i is edge i as given, 2i + 1 the same edge reversed
         const int64_t i = p >> 1;
@@ -154,6 +154,9 @@ struct SortDst {
 
 // Stable scatter of one tile.  Element order inside the tile is (warp, round, lane), which is the
 // order of the source list because warp w reads one contiguous range of 32 * kSortItems entries.
+// HAS_W = false: every weight is 1 (no input weights), so the sort moves (key, index) pairs only and
+// the caller writes the weights afterwards; a third less traffic per pass.
+template <bool HAS_W>
 __global__ void __launch_bounds__(kSortThreads, 4) sort_scatter_kernel(SortSrc s, SortDst d, int shift, int from_idx,
                                                                     const int* __restrict__ matrix, int64_t n_tiles) {
     extern __shared__ __align__(16) unsigned char smem[];
@@ -212,7 +215,7 @@ __global__ void __launch_bounds__(kSortThreads, 4) sort_scatter_kernel(SortSrc s
             const int q = s_dstart[dig[r]] + my_hist[dig[r]] + rank[r];
             s_key[q] = el[r].key;
             s_idx[q] = el[r].idx;
-            s_w[q] = el[r].w;
+            if (HAS_W) s_w[q] = el[r].w;
             s_dig[q] = (unsigned short)dig[r];
         }
     }
@@ -222,7 +225,7 @@ __global__ void __launch_bounds__(kSortThreads, 4) sort_scatter_kernel(SortSrc s
         const int64_t g = (int64_t)s_gbase[s_dig[q]] + q;
         if (d.key) d.key[g] = s_key[q];
         d.idx[g] = s_idx[q];
-        d.w[g] = s_w[q];
+        if (HAS_W) d.w[g] = s_w[q];
     }
 }
 
@@ -290,12 +293,12 @@ __global__ void degree_kernel(const int32_t* __restrict__ off, const float* __re
 // owner, idx the other endpoint; key_is_dst tells which is which.
 __global__ void norm_weight_kernel(const int32_t* __restrict__ key, const int32_t* __restrict__ idx, float* __restrict__ w,
                                    const float* __restrict__ dis, const unsigned long long* __restrict__ dcount,
-                                   int key_is_dst) {
+                                   int key_is_dst, int unit) {
     const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= (int64_t)*dcount) return;
     const int32_t k = key[j], o = idx[j];
     const float ds = dis[key_is_dst ? o : k], dd = dis[key_is_dst ? k : o];
-    w[j] = __fmul_rn(__fmul_rn(ds, w[j]), dd);
+    w[j] = __fmul_rn(__fmul_rn(ds, unit ? 1.f : w[j]), dd);   // unit: the sort did not carry the (all-one) weights
 }
 
 // keep[i] = 1 for input entries that are not (v,v)
@@ -441,13 +444,15 @@ static ConvertWs carve_convert(void* ws, int64_t cap, int64_t n) {
 // canonical additionally orders the entries of one key by their index.  `kept` (device) is the
 // element count after a first pass that drops entries, or null when first.count is exact.
 // *sorted_key receives the buffer holding the sorted keys.
+// carry_w = false (all weights are 1): out_w is left untouched, the caller fills it.
 static int radix_sort(SortSrc first, int64_t n, int canonical, const unsigned long long* kept, ConvertWs& ws,
-                      int32_t* out_idx, float* out_w, int32_t** sorted_key, cudaStream_t st) {
+                      int32_t* out_idx, float* out_w, int32_t** sorted_key, cudaStream_t st, bool carry_w = true) {
     static bool attr_set[64] = {false};
     int dev = 0;
     JG_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        JG_CUDA(cudaFuncSetAttribute(sort_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScatterSmem));
+        JG_CUDA(cudaFuncSetAttribute(sort_scatter_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScatterSmem));
+        JG_CUDA(cudaFuncSetAttribute(sort_scatter_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScatterSmem));
         attr_set[dev] = true;
     }
     const int bits = bits_for(n);
@@ -476,8 +481,11 @@ static int radix_sort(SortSrc first, int64_t n, int canonical, const unsigned lo
         SortDst dst;
         dst.key = ws.key[cur];
         dst.idx = last ? out_idx : ws.idx[cur];
-        dst.w = last ? out_w : ws.w[cur];
-        sort_scatter_kernel<<<(unsigned)tiles, kSortThreads, kScatterSmem, st>>>(src, dst, shift, from_idx, ws.matrix, tiles);
+        dst.w = carry_w ? (last ? out_w : ws.w[cur]) : nullptr;
+        if (carry_w)
+            sort_scatter_kernel<true><<<(unsigned)tiles, kSortThreads, kScatterSmem, st>>>(src, dst, shift, from_idx, ws.matrix, tiles);
+        else
+            sort_scatter_kernel<false><<<(unsigned)tiles, kSortThreads, kScatterSmem, st>>>(src, dst, shift, from_idx, ws.matrix, tiles);
         JG_LAUNCH_CHECK();
         *sorted_key = dst.key;
         SortSrc nxt = {};
@@ -525,8 +533,13 @@ int jg_coo_to_compressed(const int32_t* edge_index, const float* w, int64_t n_ed
     first.by = by;
     first.count = n_edges;
     int32_t* skey = nullptr;
-    int rc = radix_sort(first, n_nodes, canonical, nullptr, ws, out_idx, out_w, &skey, st);
+    const bool carry_w = w != nullptr;
+    int rc = radix_sort(first, n_nodes, canonical, nullptr, ws, out_idx, out_w, &skey, st, carry_w);
     if (rc != JG_OK) return rc;
+    if (!carry_w && n_edges > 0) {   // no input weights: every output weight is 1.0f
+        fill_int_kernel<<<blocks_for(n_edges, 256), 256, 0, st>>>(reinterpret_cast<int*>(out_w), 0x3f800000, n_edges);
+        JG_LAUNCH_CHECK();
+    }
     offsets_from_sorted_keys<<<blocks_for(n_edges + 1, 256), 256, 0, st>>>(skey, n_edges, nullptr, n_nodes, out_off);
     JG_LAUNCH_CHECK();
     return JG_OK;
@@ -580,7 +593,7 @@ int jg_gcn_norm_compressed(const int32_t* edge_index, const float* w, int64_t n_
     // destination-major (CSC), raw weights; degrees and dis from its segments
     int32_t* skey = nullptr;
     first.by = 1;
-    int rc = radix_sort(first, n_nodes, canonical, ws.kept, ws, csc_idx, csc_w, &skey, st);
+    int rc = radix_sort(first, n_nodes, canonical, ws.kept, ws, csc_idx, csc_w, &skey, st, !unit);
     if (rc != JG_OK) return rc;
     offsets_from_sorted_keys<<<blocks_for(cap + 1, 256), 256, 0, st>>>(skey, 0, ws.kept, n_nodes, csc_off);
     JG_LAUNCH_CHECK();
@@ -589,17 +602,17 @@ int jg_gcn_norm_compressed(const int32_t* edge_index, const float* w, int64_t n_
         JG_LAUNCH_CHECK();
     }
     if (cap > 0) {
-        norm_weight_kernel<<<blocks_for(cap, 256), 256, 0, st>>>(skey, csc_idx, csc_w, ws.dis, ws.kept, 1);
+        norm_weight_kernel<<<blocks_for(cap, 256), 256, 0, st>>>(skey, csc_idx, csc_w, ws.dis, ws.kept, 1, unit ? 1 : 0);
         JG_LAUNCH_CHECK();
     }
     if (csr_idx) {
         first.by = 0;
-        rc = radix_sort(first, n_nodes, canonical, ws.kept, ws, csr_idx, csr_w, &skey, st);
+        rc = radix_sort(first, n_nodes, canonical, ws.kept, ws, csr_idx, csr_w, &skey, st, !unit);
         if (rc != JG_OK) return rc;
         offsets_from_sorted_keys<<<blocks_for(cap + 1, 256), 256, 0, st>>>(skey, 0, ws.kept, n_nodes, csr_off);
         JG_LAUNCH_CHECK();
         if (cap > 0) {
-            norm_weight_kernel<<<blocks_for(cap, 256), 256, 0, st>>>(skey, csr_idx, csr_w, ws.dis, ws.kept, 0);
+            norm_weight_kernel<<<blocks_for(cap, 256), 256, 0, st>>>(skey, csr_idx, csr_w, ws.dis, ws.kept, 0, unit ? 1 : 0);
             JG_LAUNCH_CHECK();
         }
     }

@@ -301,6 +301,15 @@ __global__ void __launch_bounds__(kGatBlock) gat_aggregate_kernel(GatArgs a) {
     }
 }
 
+// Persistent grid, but never more warps than segments: every warp takes at least one ticket, and on a
+// small graph (a sampled mini-batch) a full grid would mostly queue on the ticket counter.
+static unsigned gat_grid(int64_t n_segments, int blocks_per_sm) {
+    int64_t blocks = (n_segments + kGatBlock / 32 - 1) / (kGatBlock / 32);
+    const int64_t full = (int64_t)sm_count() * blocks_per_sm;
+    if (blocks > full) blocks = full;
+    return (unsigned)(blocks > 0 ? blocks : 1);
+}
+
 template <int G, int DL>
 static int launch_gat(const GatArgs& a, cudaStream_t st) {
     static int blocks_per_sm = 0;
@@ -310,7 +319,7 @@ static int launch_gat(const GatArgs& a, cudaStream_t st) {
         JG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, kern, kGatBlock, 0));
         blocks_per_sm = b > 0 ? b : 1;
     }
-    kern<<<sm_count() * blocks_per_sm, kGatBlock, 0, st>>>(a);
+    kern<<<gat_grid(a.n, blocks_per_sm), kGatBlock, 0, st>>>(a);
     JG_LAUNCH_CHECK();
     return JG_OK;
 }
@@ -761,9 +770,9 @@ static int launch_gat_bwd(const GatBwdArgs& a, cudaStream_t st) {
         JG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, k2, kGatBlock, 0));
         bps_src = b > 0 ? b : 1;
     }
-    k1<<<sm_count() * bps_dst, kGatBlock, 0, st>>>(a);
+    k1<<<gat_grid(a.n, bps_dst), kGatBlock, 0, st>>>(a);
     JG_LAUNCH_CHECK();
-    k2<<<sm_count() * bps_src, kGatBlock, 0, st>>>(a);
+    k2<<<gat_grid(a.n, bps_src), kGatBlock, 0, st>>>(a);
     JG_LAUNCH_CHECK();
     if (a.order_t) {
         gat_backward_src_fixup_kernel<<<sm_count() * 2, 128, 0, st>>>(a, 4 * G, 4 * DL);

@@ -96,6 +96,7 @@ struct AggArgs {
     float* partial;
     unsigned long long* ticket;
     int accumulate;  // 1: add the aggregated row to what `out` already holds (old + sum)
+    int64_t max_items;  // host-side upper bound on the plan's pieces (sizes the grid)
     const float* bias;  // epilogue on finished output rows: + bias[column] (null: none) ...
     int relu;           // ... then max(., 0)
 };
@@ -121,14 +122,19 @@ __device__ __forceinline__ void axpy4(float4& a, const float4& v, float w) {
 // Vector-width kernel (F = 4*G*VPL).  G lanes cover one feature row, 32/G entries are gathered
 // side by side, B steps per batch.
 // EPI compiles in the bias/ReLU epilogue (a separate instantiation, so the plain kernel is untouched).
-template <int G, int VPL, int B, int MINB, bool EXACT, bool EPI>
+// FULL: the row is exactly 4*G*VPL floats wide (everything about the width folds at compile time).
+// !FULL: any 16-byte-aligned width up to that; lanes whose columns lie beyond it sit out.
+template <int G, int VPL, int B, int MINB, bool EXACT, bool EPI, bool FULL>
 __global__ void __launch_bounds__(kBlock, MINB) aggregate_rows_kernel(AggArgs a) {
     constexpr int EPS = 32 / G;
-    constexpr int F = 4 * G * VPL;
+    const int F = FULL ? 4 * G * VPL : (int)a.f;
     __shared__ int2 s_tile[kBlock / 32][32];
     const int lane = lane_id();
     const int sub = lane / G;
     const int fl = lane % G;
+    bool qok[VPL];
+#pragma unroll
+    for (int q = 0; q < VPL; q++) qok[q] = FULL || (fl + q * G) * 4 < F;
     int2* tile = s_tile[threadIdx.x / 32];
     const char* xb = reinterpret_cast<const char*>(a.x) + fl * 16;
     const int64_t n_items = a.hdr ? a.hdr->n_items : 0;
@@ -211,9 +217,9 @@ __global__ void __launch_bounds__(kBlock, MINB) aggregate_rows_kernel(AggArgs a)
                     for (int u = 0; u < B; u++) {
                         const int2 p = tile[t + u * EPS + sub];
                         wv[u] = __int_as_float(p.y);
-                        const float4* g = reinterpret_cast<const float4*>(xb + (size_t)(unsigned)p.x * (F * 4));
+                        const float4* g = reinterpret_cast<const float4*>(xb + (size_t)(unsigned)p.x * (size_t)(F * 4));
 #pragma unroll
-                        for (int q = 0; q < VPL; q++) v[u][q] = __ldg(g + q * G);
+                        for (int q = 0; q < VPL; q++) v[u][q] = qok[q] ? __ldg(g + q * G) : make_float4(0.f, 0.f, 0.f, 0.f);
                     }
 #pragma unroll
                     for (int u = 0; u < B; u++)
@@ -232,9 +238,10 @@ __global__ void __launch_bounds__(kBlock, MINB) aggregate_rows_kernel(AggArgs a)
                         if (k < cnt) {
                             const int2 p = tile[k];
                             wv[u] = __int_as_float(p.y);
-                            const float4* g = reinterpret_cast<const float4*>(xb + (size_t)(unsigned)p.x * (F * 4));
+                            const float4* g = reinterpret_cast<const float4*>(xb + (size_t)(unsigned)p.x * (size_t)(F * 4));
 #pragma unroll
-                            for (int q = 0; q < VPL; q++) v[u][q] = __ldg(g + q * G);
+                            for (int q = 0; q < VPL; q++)
+                                if (qok[q]) v[u][q] = __ldg(g + q * G);
                         }
                     }
 #pragma unroll
@@ -258,6 +265,7 @@ __global__ void __launch_bounds__(kBlock, MINB) aggregate_rows_kernel(AggArgs a)
                 float4* o = reinterpret_cast<float4*>(dst) + fl;
 #pragma unroll
                 for (int q = 0; q < VPL; q++) {
+                    if (!qok[q]) continue;
                     if (add_old) {
                         const float4 old = o[q * G];
                         acc[q].x = __fadd_rn(old.x, acc[q].x);
@@ -283,9 +291,9 @@ __global__ void __launch_bounds__(kBlock, MINB) aggregate_rows_kernel(AggArgs a)
 }
 
 // Any feature width: lanes stride over columns with scalar loads, up to 256 columns per sweep.
+template <int Q>
 __device__ __forceinline__ void warp_segment_any(const AggArgs& a, int32_t s, int32_t e, float* dst, bool add_old, bool final_row) {
-    constexpr int Q = 8;
-    constexpr int UNROLL = 4;
+    constexpr int UNROLL = Q <= 2 ? 8 : 4;
     const int lane = lane_id();
     const int64_t F = a.f;
     for (int64_t c0 = 0; c0 < F; c0 += 32 * Q) {
@@ -333,7 +341,9 @@ __device__ __forceinline__ void warp_segment_any(const AggArgs& a, int32_t s, in
     }
 }
 
-// Any feature width: one warp per work id, column-strided scalar loads.
+// Any feature width: one warp per work id, column-strided scalar loads, Q * 32 columns per sweep
+// (Q = 2 or 4 for widths up to 64 or 128, so that narrow odd widths do not pay for empty sweeps).
+template <int Q>
 __global__ void __launch_bounds__(kBlock) aggregate_any_kernel(AggArgs a) {
     const int lane = lane_id();
     const int64_t n_items = a.hdr ? a.hdr->n_items : 0;
@@ -374,7 +384,101 @@ __global__ void __launch_bounds__(kBlock) aggregate_any_kernel(AggArgs a) {
                 if (e - s > chunk) continue;  // hub row: its pieces are separate work ids
                 dst = a.out + (size_t)row * F;
             }
-            warp_segment_any(a, s, e, dst, a.accumulate && id >= n_items, id >= n_items);
+            warp_segment_any<Q>(a, s, e, dst, a.accumulate && id >= n_items, id >= n_items);
+        }
+    }
+}
+
+// Narrow feature widths (F <= G <= 32, any alignment): G lanes own one work id (an output row or a
+// piece of a hub row), so 32/G of them are walked side by side, each in its own stored order with
+// separately rounded multiply and add - the result of a row is bit-identical to the sequential
+// reference loop.  The G lanes fetch G consecutive (index, weight) entries with one coalesced load
+// each and hand them round with width-G shuffles; lane c gathers column c of every source row.
+// All groups run the trip count of the longest of their segments, with predicates, so the shuffles
+// stay convergent.  The last layer of a GCN (a handful of classes) is this shape.
+template <int G>
+__global__ void __launch_bounds__(kBlock) aggregate_narrow_kernel(AggArgs a) {
+    constexpr int R = 32 / G;          // work ids per warp step
+    constexpr int ROUNDS = 4;          // steps per ticket
+    const int lane = lane_id();
+    const int grp = lane / G, c = lane % G;
+    const int64_t n_items = a.hdr ? a.hdr->n_items : 0;
+    const int chunk = a.hdr ? a.hdr->chunk : 0x7fffffff;
+    const int64_t total = n_items + a.n_out;
+    const int F = (int)a.f;
+    const bool col_ok = c < F;
+    for (;;) {
+        unsigned long long base = 0;
+        if (lane == 0) base = atomicAdd(a.ticket, (unsigned long long)(R * ROUNDS));
+        base = __shfl_sync(kFull, base, 0);
+        if ((int64_t)base >= total) break;
+#pragma unroll 1
+        for (int round = 0; round < ROUNDS; round++) {
+            const int64_t id = (int64_t)base + round * R + grp;
+            int32_t s = 0, e = 0;
+            float* dst = nullptr;
+            bool final_row = false;
+            if (id < total) {
+                if (id < n_items) {
+                    const int h = a.item_hub[id];
+                    const int k = a.item_k[id];
+                    const int row = a.hub_row[h];
+                    const int32_t rs = a.off[row], re = a.off[row + 1];
+                    s = rs + k * chunk;
+                    e = min(re, s + chunk);
+                    dst = a.partial + (size_t)(a.hub_first[h] + k) * F;
+                } else {
+                    const int64_t row = id - n_items;
+                    s = a.off[row];
+                    e = a.off[row + 1];
+                    if (e - s > chunk) {   // hub row: its pieces are separate work ids
+                        e = s;
+                    } else {
+                        dst = a.out + (size_t)row * F;
+                        final_row = true;
+                    }
+                }
+            }
+            const int len = e - s;
+            int maxlen = len;
+#pragma unroll
+            for (int o = G; o < 32; o <<= 1) maxlen = max(maxlen, __shfl_xor_sync(kFull, maxlen, o));
+            if (G < 32 && (int64_t)base + round * R >= total) break;   // warp-uniform: nothing left in this ticket
+            float acc = 0.f;
+            for (int j = 0; j < maxlen; j += G) {
+                int my_idx = 0;
+                float my_w = 0.f;
+                if (j + c < len) {
+                    my_idx = ld_stream(a.idx + s + j + c);
+                    my_w = ld_stream(a.w + s + j + c);
+                }
+#pragma unroll
+                for (int k0 = 0; k0 < G; k0 += 4) {
+                    float v[4], wv[4];
+                    bool ok[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int k = k0 + u;
+                        const int src = __shfl_sync(kFull, my_idx, k, G);
+                        wv[u] = __shfl_sync(kFull, my_w, k, G);
+                        ok[u] = j + k < len;
+                        v[u] = 0.f;
+                        if (ok[u] && col_ok) v[u] = __ldg(a.x + (size_t)(unsigned)src * F + c);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; u++)
+                        if (ok[u]) acc = __fadd_rn(__fmul_rn(v[u], wv[u]), acc);
+                }
+            }
+            if (dst && col_ok) {
+                float v = acc;
+                if (final_row) {
+                    if (a.accumulate) v = __fadd_rn(dst[c], v);
+                    if (a.bias) v += __ldg(a.bias + c);
+                    if (a.relu) v = fmaxf(v, 0.f);
+                }
+                dst[c] = v;
+            }
         }
     }
 }
@@ -401,6 +505,9 @@ __global__ void __launch_bounds__(kBlock) hub_fixup_kernel(AggArgs a) {
     }
 }
 
+// Persistent grid: as many CTAs as fit on the device, but no more than the work can feed.  Every warp
+// takes at least one ticket (an atomic on one address) to learn that nothing is left, so on a small
+// graph a full grid of some ten thousand warps would spend its time queueing on that counter.
 template <class K>
 static int launch_persistent(K kern, int* blocks_per_sm, const AggArgs& a, cudaStream_t st) {
     if (*blocks_per_sm == 0) {
@@ -408,16 +515,26 @@ static int launch_persistent(K kern, int* blocks_per_sm, const AggArgs& a, cudaS
         JG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, kern, kBlock, 0));
         *blocks_per_sm = b > 0 ? b : 1;
     }
-    kern<<<sm_count() * *blocks_per_sm, kBlock, 0, st>>>(a);
+    const int64_t grabs = (a.n_out + a.max_items + kGrab - 1) / kGrab;
+    int64_t blocks = (grabs + kBlock / 32 - 1) / (kBlock / 32);
+    const int64_t full = (int64_t)sm_count() * *blocks_per_sm;
+    if (blocks > full) blocks = full;
+    if (blocks < 1) blocks = 1;
+    kern<<<(unsigned)blocks, kBlock, 0, st>>>(a);
     JG_LAUNCH_CHECK();
     return JG_OK;
 }
 
 template <int G, int VPL, int B, int MINB, bool EXACT>
 static int launch_rows(const AggArgs& a, cudaStream_t st) {
-    static int blocks_per_sm = 0, blocks_per_sm_epi = 0;
-    if (a.bias || a.relu) return launch_persistent(aggregate_rows_kernel<G, VPL, B, MINB, EXACT, true>, &blocks_per_sm_epi, a, st);
-    return launch_persistent(aggregate_rows_kernel<G, VPL, B, MINB, EXACT, false>, &blocks_per_sm, a, st);
+    static int bps[4] = {0, 0, 0, 0};
+    const bool epi = a.bias || a.relu;
+    if (a.f == 4 * G * VPL) {
+        if (epi) return launch_persistent(aggregate_rows_kernel<G, VPL, B, MINB, EXACT, true, true>, &bps[0], a, st);
+        return launch_persistent(aggregate_rows_kernel<G, VPL, B, MINB, EXACT, false, true>, &bps[1], a, st);
+    }
+    // a narrower 16-byte-aligned width on the same lane layout (the epilogue variant serves both cases)
+    return launch_persistent(aggregate_rows_kernel<G, VPL, B, MINB, EXACT, true, false>, &bps[2], a, st);
 }
 
 // Picks the kernel for a feature width: the vector kernel for the 128-bit-aligned widths it is
@@ -427,12 +544,21 @@ static int dispatch_aggregate(const AggArgs& a, cudaStream_t st) {
     const bool vec_ok = (f % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.out) |
                                           reinterpret_cast<uintptr_t>(a.partial)) % 16 == 0);
     if (vec_ok && f == 32) return launch_rows<8, 1, 8, 4, true>(a, st);
-    if (vec_ok && f == 64) return launch_rows<16, 1, 8, 4, true>(a, st);
-    if (vec_ok && f == 128) return launch_rows<32, 1, 8, 4, true>(a, st);
-    if (vec_ok && f == 256) return launch_rows<32, 2, 4, 4, true>(a, st);
-    if (vec_ok && f == 512) return launch_rows<32, 4, 2, 3, true>(a, st);
-    static int any_blocks = 0;
-    return launch_persistent(aggregate_any_kernel, &any_blocks, a, st);
+    if (vec_ok && f > 32 && f <= 64) return launch_rows<16, 1, 8, 4, true>(a, st);
+    if (vec_ok && f > 64 && f <= 128) return launch_rows<32, 1, 8, 4, true>(a, st);
+    if (vec_ok && f > 128 && f <= 256) return launch_rows<32, 2, 4, 4, true>(a, st);
+    if (vec_ok && f > 256 && f <= 512) return launch_rows<32, 4, 2, 3, true>(a, st);
+    if (f <= 32) {   // narrow rows (any alignment): several rows per warp
+        static int nb4 = 0, nb8 = 0, nb16 = 0, nb32 = 0;
+        if (f <= 4) return launch_persistent(aggregate_narrow_kernel<4>, &nb4, a, st);
+        if (f <= 8) return launch_persistent(aggregate_narrow_kernel<8>, &nb8, a, st);
+        if (f <= 16) return launch_persistent(aggregate_narrow_kernel<16>, &nb16, a, st);
+        return launch_persistent(aggregate_narrow_kernel<32>, &nb32, a, st);
+    }
+    static int any2 = 0, any4 = 0, any8 = 0;
+    if (f <= 64) return launch_persistent(aggregate_any_kernel<2>, &any2, a, st);
+    if (f <= 128) return launch_persistent(aggregate_any_kernel<4>, &any4, a, st);
+    return launch_persistent(aggregate_any_kernel<8>, &any8, a, st);
 }
 
 }  // namespace jg
@@ -506,6 +632,7 @@ static int aggregate_impl(float* out, const float* x, const int32_t* idx, const 
         a.hdr = v.hdr; a.hub_row = v.hub_row; a.hub_first = v.hub_first;
         a.item_hub = v.item_hub; a.item_k = v.item_k;
         a.partial = c.take<float>((size_t)plan_max_items(nnz, chunk) * (size_t)f);
+        a.max_items = plan_max_items(nnz, chunk);
     }
     JG_CUDA(cudaMemsetAsync(a.ticket, 0, sizeof(unsigned long long), st));
 
@@ -618,6 +745,7 @@ int jg_aggregate_f32_static(float* out, const float* x, const int32_t* idx, cons
     PlanView v = plan_view(c.take<unsigned char>(plan_bytes), nnz, chunk, nullptr);
     a.hdr = v.hdr; a.hub_row = v.hub_row; a.hub_first = v.hub_first; a.item_hub = v.item_hub; a.item_k = v.item_k;
     a.partial = c.take<float>((size_t)plan_max_items(nnz, chunk) * (size_t)f);
+    a.max_items = plan_max_items(nnz, chunk);
 
     // The array keeps whatever the previous call left: the two words that must start at zero
     // (ticket, plan counters) are rewritten here; everything else is written before it is read.

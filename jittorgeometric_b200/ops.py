@@ -18,6 +18,8 @@ __all__ = ["aggregateWithWeight", "aggregate_bias_act", "segment_aggregate", "Sp
            "gat_aggregate_supported", "gcn_norm_coo", "linear_tf32", "linear_tf32_supported", "toUndirected", "validate_structure"]
 
 DEFAULT_CHUNK = int(os.environ.get("JG_SPMM_CHUNK", "1024"))
+SMALL_GRAPH_NNZ = 1 << 20
+SMALL_GRAPH_CHUNK = int(os.environ.get("JG_SPMM_SMALL_CHUNK", "64"))
 
 
 def _as_i32(t, name):
@@ -48,13 +50,20 @@ def validate_structure(idx, off, n_in):
                                      stream_for(off)), "jg_validate_segments")
 
 
+def default_chunk(nnz):
+    """Piece length for hub rows.  On a small graph the longest row is the critical path of the whole
+    aggregation (one warp walks it while the rest of the GPU idles), so rows are cut much shorter
+    there; on a large graph long pieces keep the number of partial rows small."""
+    return DEFAULT_CHUNK if nnz >= SMALL_GRAPH_NNZ else min(DEFAULT_CHUNK, SMALL_GRAPH_CHUNK)
+
+
 class SpmmPlan:
     """Hub plan of one offset array: the rows longer than ``chunk`` entries, split
     into pieces so that no warp owns more than ``chunk`` entries.  Depends only
     on the offsets; build once per graph and reuse."""
 
     def __init__(self, off, nnz, chunk=None):
-        chunk = DEFAULT_CHUNK if chunk is None else int(chunk)
+        chunk = default_chunk(nnz) if chunk is None else int(chunk)
         self.chunk = chunk
         self.n_out = off.numel() - 1
         self.nnz = int(nnz)
@@ -70,7 +79,7 @@ def _plan_of(holder, off, nnz):
     if holder is None:
         return SpmmPlan(off, nnz)
     plan = getattr(holder, "_jg_plan", None)
-    if plan is None or plan.off_ptr != off.data_ptr() or plan.nnz != nnz or plan.chunk != DEFAULT_CHUNK:
+    if plan is None or plan.off_ptr != off.data_ptr() or plan.nnz != nnz or plan.chunk != default_chunk(nnz):
         plan = SpmmPlan(off, nnz)
         holder._jg_plan = plan
     return plan
@@ -97,6 +106,14 @@ def segment_aggregate(x, idx, off, w, n_out=None, plan=None, out=None, accumulat
     n_in, f = x.shape
     if os.environ.get("JG_DEBUG_CHECKS") == "1":
         validate_structure(idx, off, n_in)
+    if f > 32 and f % 4 and out is None and not accumulate:
+        # rows that do not start on 16-byte boundaries can only be gathered with scalar loads, several
+        # times slower than the vector kernel: pad the width to a multiple of four (one extra pass over
+        # x) and hand back the first f columns of the padded result (a strided view)
+        pad = 4 - f % 4
+        xp = torch.nn.functional.pad(x, (0, pad))
+        bp = None if bias is None else torch.nn.functional.pad(_as_f32(bias, "bias"), (0, pad))
+        return segment_aggregate(xp, idx, off, w, n_out=n_out, plan=plan, bias=bp, relu=relu)[:, :f]
     if out is None:
         if accumulate:
             raise RuntimeError("accumulate=True needs the tensor to add to (out=)")

@@ -66,7 +66,7 @@ def random_graph(rng, n_out, n_in, E, hubs=0, hub_deg=0):
     return src[order].astype(np.int32), off, w
 
 
-@pytest.mark.parametrize("f", [1, 3, 7, 10, 32, 33, 64, 100, 128, 256, 260, 512])
+@pytest.mark.parametrize("f", [1, 3, 4, 7, 10, 16, 17, 31, 32, 33, 40, 47, 64, 65, 100, 128, 200, 256, 260, 512, 516])
 def test_widths_against_oracle(cuda, oracle, f):
     rng = np.random.default_rng(100 + f)
     idx, off, w = random_graph(rng, 700, 500, 9000, hubs=2, hub_deg=300)
@@ -77,7 +77,7 @@ def test_widths_against_oracle(cuda, oracle, f):
         y = run(cuda, x, idx, off, w, chunk=chunk, n_out=700)
         assert rel_err(y, truth, scale) <= 1e-5
         assert rel_err(y, want, scale) <= 1e-5
-        if f >= 128 or f % 4:   # one lane group per row: the reference's summation order
+        if f < 32 or f > 64:    # one lane group walks the row alone: the reference's summation order
             deg = np.diff(off)
             rows = deg <= (chunk or 1 << 30)
             assert np.array_equal(y[rows], want[rows])
@@ -145,7 +145,15 @@ def test_autograd_pairing(cuda, oracle):
     g = torch.from_numpy(np.random.default_rng(5).standard_normal((2708, 7)).astype(np.float32)).cuda()
     y.backward(g)
     want = oracle.aggregate(g.cpu().numpy(), d["column_indices"], d["row_offset"], d["csr_weight"])
-    assert np.array_equal(x.grad.cpu().numpy(), want)
+    got = x.grad.cpu().numpy()
+    # rows no longer than a hub piece are summed in the reference's order: bit-identical; the few
+    # longer rows of this small graph are cut into pieces (short ones, so that no warp walks a long
+    # row alone) and agree to rounding
+    whole = np.diff(d["row_offset"]) <= cuda.ops.default_chunk(len(d["column_indices"]))
+    assert whole.sum() > 2600 and not whole.all()
+    assert np.array_equal(got[whole], want[whole])
+    _, scale = oracle.aggregate_f64(g.cpu().numpy(), d["column_indices"], d["row_offset"], d["csr_weight"])
+    assert rel_err(got, want, scale) <= 1e-5
 
 
 def test_structure_validation(cuda):
