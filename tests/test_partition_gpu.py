@@ -53,3 +53,19 @@ def test_partition_to_chunks(cuda, tmp_path, n, E, P):
     assert torch.equal(back.CSC.row_indices, chunks[-1].CSC.row_indices) and back.CSC.row_indices.is_cuda
     assert torch.equal(back.local_feature, chunks[-1].local_feature)
     assert torch.equal(back.chunk_CSR[0].column_indices, chunks[-1].chunk_CSR[0].column_indices)
+
+
+def test_partition_with_an_empty_part(cuda):
+    """A part that owns no node gives a chunk with no rows and no entries; the others are unaffected."""
+    from jittorgeometric_b200.partition import partition_to_chunks
+    n, P = 40, 3
+    rng = np.random.default_rng(2)
+    pairs = np.unique(rng.integers(0, n, size=(300, 2)), axis=0).T
+    partition = np.where(rng.random(n) < 0.5, 0, 2).astype(np.int32)      # nobody in part 1
+    w = rng.random(pairs.shape[1]).astype(np.float32)
+    chunks = partition_to_chunks(partition, dev(pairs.astype(np.int32)), n, P, dev(w))
+    ref = reference_chunks(partition, pairs, n, P, w)
+    assert chunks[1].v_num == 0 and chunks[1].CSC.row_indices.numel() == 0 and host(chunks[1].CSC.column_offset).tolist() == [0]
+    for c, r in zip(chunks, ref):
+        assert np.array_equal(host(c.CSC.column_offset), r["csc"].indptr) and np.array_equal(host(c.CSC.row_indices), r["csc"].indices)
+        assert np.array_equal(host(c.CSR.row_offset), r["csr"].indptr) and np.array_equal(host(c.CSR.column_indices), r["csr"].indices)

@@ -201,3 +201,25 @@ def test_neighbor_loader_trains_a_layer(cuda):
     loss = torch.nn.functional.cross_entropy(out, ssg.target_lab)
     loss.backward()
     assert torch.isfinite(loss) and torch.isfinite(layer.weight.grad).all() and layer.weight.grad.abs().sum() > 0
+
+
+def test_sampling_edge_cases(cuda):
+    """No destinations, destinations without in-edges, fanout 0: nothing is drawn and nothing breaks."""
+    from jittorgeometric_b200 import sampling as S
+    g_off = np.array([0, 0, 3, 3, 5], np.int32)              # nodes 0 and 2 have no in-edges
+    g_idx = np.array([0, 2, 3, 1, 1], np.int32)
+    empty = dev(np.zeros(0, np.int32))
+    assert host(S.layer_offsets(3, empty, dev(g_off))).tolist() == [0]
+    assert S.sampleprocessing(3, empty, dev(np.zeros(1, np.int32)), dev(g_off), dev(g_idx)).numel() == 0
+    dst = np.array([0, 1, 2, 3], np.int32)
+    off = host(S.layer_offsets(2, dev(dst), dev(g_off)))
+    assert off.tolist() == [0, 0, 2, 2, 4]
+    got = host(S.sampleprocessing(2, dev(dst), dev(off), dev(g_off), dev(g_idx), seed=4))
+    assert set(got[:2]) <= {0, 2, 3} and len(set(got[:2])) == 2 and got[2:].tolist() == [1, 1]
+    off0 = host(S.layer_offsets(0, dev(dst), dev(g_off)))
+    assert off0.tolist() == [0, 0, 0, 0, 0]
+    assert S.sampleprocessing(0, dev(dst), dev(off0), dev(g_off), dev(g_idx)).numel() == 0
+    # a batch whose seeds have no in-edges at all: the subgraph is the seeds themselves, no entries
+    ssg = S.sample_one([5, 5], dev(g_off), dev(g_idx), dev(np.array([0, 2], np.int32)))
+    assert ssg.num_nodes == 2 and ssg.num_edges == 0 and host(ssg.column_offset).tolist() == [0, 0, 0]
+    assert host(ssg.local2global).tolist() == [0, 2]
