@@ -112,6 +112,22 @@ class _Done:
     def wait(self):
         pass
 
+    def release(self):
+        pass
+
+
+class _WorkHandle:
+    """An asynchronous ``torch.distributed`` collective."""
+
+    def __init__(self, work):
+        self.work = work
+
+    def wait(self):
+        self.work.wait()
+
+    def release(self):
+        pass
+
 
 class CollectiveTransport:
     """Row exchange with ``torch.distributed`` collectives (NCCL on GPUs, gloo on CPU ranks):
@@ -145,8 +161,9 @@ class CollectiveTransport:
             return _Done()
         send_split = [int(c) for c in g.send_counts]
         recv_split = [int(c) for c in g.recv_counts]
-        return dist.all_to_all_single(recv[: sum(recv_split)], send[: sum(send_split)], output_split_sizes=recv_split,
-                                      input_split_sizes=send_split, group=self.group, async_op=True)
+        return _WorkHandle(dist.all_to_all_single(recv[: sum(recv_split)], send[: sum(send_split)],
+                                                  output_split_sizes=recv_split, input_split_sizes=send_split,
+                                                  group=self.group, async_op=True))
 
 
 class PeerTransport(CollectiveTransport):
@@ -198,15 +215,24 @@ class PeerTransport(CollectiveTransport):
                 src0 = int(g.peer_send_offset[q])                          # where rank q packed the rows meant for this rank
                 dst0 = int(g.recv_offset[q])
                 recv[dst0:dst0 + n].copy_(peer[src0:src0 + n])
-        return _PeerHandle(self, hdl, cur)
+            landed = torch.cuda.Event()
+            landed.record(self.side)
+        return _PeerHandle(hdl, landed)
 
 
 class _PeerHandle:
-    def __init__(self, tr, hdl, cur):
-        self.tr, self.hdl, self.cur = tr, hdl, cur
+    """``wait``: the current stream waits for THIS exchange's pulls (an event, so that pulls of later
+    exchanges already queued on the side stream are not waited for).  ``release``: the barrier that
+    tells every rank its send buffer has been read and may be packed again; it is issued after the
+    aggregation has been queued, so no rank idles in it before its own kernel starts."""
+
+    def __init__(self, hdl, landed):
+        self.hdl, self.landed = hdl, landed
 
     def wait(self):
-        self.cur.wait_stream(self.tr.side)
+        torch.cuda.current_stream().wait_event(self.landed)
+
+    def release(self):
         self.hdl.barrier(channel=1, timeout_ms=PeerTransport.BARRIER_TIMEOUT_MS)   # every pull has finished
 
 
@@ -312,6 +338,12 @@ class ShardedGraph:
         return torch.relu(y) if relu else y
 
     def _aggregate(self, x, bias=None, relu=False):
+        return self.finish(self.start(x), bias, relu)
+
+    def start(self, x):
+        """First half of an aggregation: packs the rows the peers asked for and starts the exchange.
+        Several aggregations may be started before the first is finished; their exchanges then run
+        underneath the aggregation kernels of the earlier ones.  Forward only."""
         if x.shape[0] < self.n_local:
             raise RuntimeError(f"x has {x.shape[0]} rows, the rank owns {self.n_local}")
         f = x.shape[1]
@@ -323,21 +355,31 @@ class ShardedGraph:
             handle = self.transport.exchange(self, send, buf[self.n_local:], f)
             if x.data_ptr() != buf.data_ptr():
                 buf[: self.n_local].copy_(x[: self.n_local])
+        else:
+            handle = self.transport.exchange(self, send, buf, f)
+        return (x, buf, handle)
+
+    def finish(self, pending, bias=None, relu=False):
+        """Second half: waits for the halo rows of ``pending`` (from :meth:`start`) and aggregates."""
+        x, buf, handle = pending
+        if self.mode == "merged":
             handle.wait()
             if bias is not None or relu:
-                return self.backend.aggregate(buf, self.merged[0], self.merged[1], self.merged[2], self.n_local,
-                                              self.merged_plan, bias=bias, relu=relu)
-            return self.backend.aggregate(buf, self.merged[0], self.merged[1], self.merged[2], self.n_local,
-                                          self.merged_plan)
-        recv = buf
-        handle = self.transport.exchange(self, send, recv, f)
+                y = self.backend.aggregate(buf, self.merged[0], self.merged[1], self.merged[2], self.n_local,
+                                           self.merged_plan, bias=bias, relu=relu)
+            else:
+                y = self.backend.aggregate(buf, self.merged[0], self.merged[1], self.merged[2], self.n_local,
+                                           self.merged_plan)
+            handle.release()
+            return y
         # the rank's own rows while the halo rows travel
         y = self.backend.aggregate(x, self.interior[0], self.interior[1], self.interior[2], self.n_local,
                                    self.interior_plan)
         handle.wait()
         if self.halo[0].numel():
-            self.backend.aggregate(recv, self.halo[0], self.halo[1], self.halo[2], self.n_local, self.halo_plan,
+            self.backend.aggregate(buf, self.halo[0], self.halo[1], self.halo[2], self.n_local, self.halo_plan,
                                    out=y, accumulate=True)
+        handle.release()
         if bias is not None:
             y += bias
         return y.relu_() if relu else y

@@ -50,8 +50,11 @@ def run(args):
         xs[f] = x
 
     def step():
-        for f in widths:
-            g.aggregate(xs[f])
+        # the four aggregations are independent: every exchange is started first (pack + pulls on the
+        # copy engines), so the halo rows of the next width travel underneath the current kernel
+        pending = [g.start(xs[f]) for f in widths]
+        for p in pending:
+            g.finish(p)
 
     for _ in range(args.warmup):
         step()

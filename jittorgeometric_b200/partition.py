@@ -167,6 +167,8 @@ def chunks_save(chunks, output_dir):
 
 def _expand(off, total):
     out = torch.empty(total, dtype=torch.int32, device=off.device)
+    if total == 0:
+        return out
     check(lib().jg_expand_columns(ptr(off), off.numel() - 1, None, ptr(out), stream_for(off)), "jg_expand_columns")
     return out
 

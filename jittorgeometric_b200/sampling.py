@@ -121,6 +121,8 @@ def getweight(vtx_size, csc_layer_dst, csc_layer_src, csc_layer_column_offset, c
 
 def _expand(off, values, total):
     out = torch.empty(total, dtype=torch.int32, device=off.device)
+    if total == 0:
+        return out
     check(lib().jg_expand_columns(ptr(off), off.numel() - 1, ptr(values), ptr(out), stream_for(off)), "jg_expand_columns")
     return out
 

@@ -57,6 +57,9 @@ class Loopback:
         class Done:
             def wait(self):
                 pass
+
+            def release(self):
+                pass
         return Done()
 
 
@@ -141,6 +144,12 @@ def nccl_worker(rank, world, port, n, E, f, q, exchange):
         y2 = g.aggregate(t(x[lo:hi].copy()))          # second exchange reuses the shard buffers
         torch.cuda.synchronize()
         assert torch.equal(y, y2)
+        # two aggregations of different widths started before either is finished (pipelined exchanges)
+        xa, xb = t(x[lo:hi].copy()), t(np.ascontiguousarray(x[lo:hi, :64]))
+        pa, pb = g.start(xa), g.start(xb)
+        ya, yb = g.finish(pa), g.finish(pb, relu=True)
+        torch.cuda.synchronize()
+        assert torch.equal(ya, y) and torch.equal(yb, torch.relu(g.aggregate(xb)))
         # the reference-shaped API: one sub-CSR per source rank, one broadcast round each
         import oracle as O
         import jittorgeometric_b200 as jg
