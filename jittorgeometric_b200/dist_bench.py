@@ -81,15 +81,39 @@ def run(args):
         hx[f].copy_(xs[f])
     e2e_ms = float("nan")
     if not args.skip_e2e:
+        # uploads, exchanges + kernels and downloads on three event-chained streams, as in the 1-GPU leg
+        s_in, s_out, cur = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+        ev_in = {f: torch.cuda.Event() for f in widths}
+        ev_done = {f: torch.cuda.Event() for f in widths}
+        for f in widths:
+            ev_done[f].record(cur)
+
         def e2e_step():
+            pending = {}
             for f in widths:
-                xs[f].copy_(hx[f], non_blocking=True)
-                hy[f].copy_(g.aggregate(xs[f]), non_blocking=True)
+                with torch.cuda.stream(s_in):
+                    s_in.wait_event(ev_done[f])                 # last step's kernels have read xs[f]
+                    xs[f].copy_(hx[f], non_blocking=True)
+                    ev_in[f].record(s_in)
+                cur.wait_event(ev_in[f])
+                pending[f] = g.start(xs[f])
+            for f in widths:
+                y = g.finish(pending[f])
+                ev_done[f].record(cur)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_done[f])
+                    hy[f].copy_(y, non_blocking=True)
+                y.record_stream(s_out)
+
+        def e2e_join():
+            cur.wait_stream(s_in); cur.wait_stream(s_out)
+
         e2e_steps = max(1, min(args.steps, 5))
-        e2e_step(); torch.cuda.synchronize(); dist.barrier()
+        e2e_step(); e2e_join(); torch.cuda.synchronize(); dist.barrier()
         t0.record()
         for _ in range(e2e_steps):
             e2e_step()
+        e2e_join()
         t1.record(); torch.cuda.synchronize(); dist.barrier()
         e = torch.tensor([t0.elapsed_time(t1) / e2e_steps], device=dev)
         dist.all_reduce(e, op=dist.ReduceOp.MAX)

@@ -75,6 +75,11 @@ def worker(rank, world, port, n, E, f, q, mode):
         l_idx, l_off, l_w = jd.shard_rows(torch.from_numpy(idx), torch.from_numpy(off), torch.from_numpy(w), part, rank)
         g = jd.ShardedGraph(part, rank, l_idx, l_off, l_w, backend=OracleBackend(), mode=mode)
         y = g.aggregate(torch.from_numpy(x[lo:hi].copy()))
+        # two exchanges in flight before either aggregation is finished
+        xa, xb = torch.from_numpy(x[lo:hi].copy()), torch.from_numpy(np.ascontiguousarray(x[lo:hi, :2]))
+        pa, pb = g.start(xa), g.start(xb)
+        ya, yb = g.finish(pa), g.finish(pb)
+        assert torch.equal(ya, y) and torch.equal(yb, g.aggregate(xb))
         if mode == "overlap":
             # interior and halo together hold every entry of the shard exactly once
             assert g.interior[0].numel() + g.halo[0].numel() == l_idx.numel()
