@@ -1,4 +1,4 @@
-"""Secondary workloads of ``bench.py`` (``--workload convert|gat|gcn|gemm|sample|citation``): the other
+"""Secondary workloads of ``bench.py`` (``--workload convert|gat|gcn|gemm|sample|citation|edgeops``): the other
 configurations of the hot path, each printed as one JSON line in the same shape as the headline.
 They are measurement helpers for the kernels that the default SpMM sweep does not exercise."""
 import json
@@ -313,6 +313,47 @@ def run_sample(args):
           {"cpu_baseline": cpu, "gpu_launches": args.steps * 40, "clocks": clocks})
 
 
+def run_edgeops(args):
+    """The per-edge operators on a quarter-size attention graph (58 k nodes, 28.6 M in-edges, C = 64,
+    8 heads): each is a streaming kernel over ``[E, C]`` or ``[E, H]``; reported as achieved bytes per
+    second against the measured copy bandwidth, plus the op-by-op attention pipeline they form."""
+    import jittorgeometric_b200 as jg
+    from jittorgeometric_b200 import nn, synth
+    dev = torch.device("cuda", 0)
+    n, E_target, H, C = 232965 >> 2, 114_600_000 >> 2, 8, 64
+    rows, off = synth.lognormal_degree_csc(n, E_target, bench.SEED + 3, device=dev)
+    csc = jg.CSC(rows, off, None)
+    E = rows.numel()
+    g = torch.Generator(device=dev).manual_seed(21)
+    h = torch.relu(torch.randn((n, C), device=dev, generator=g))
+    msg = torch.randn((E, C), device=dev, generator=g)
+    score = torch.randn((E, H), device=dev, generator=g)
+    peak, kind = bench.measured_peaks()
+    sampler = bench.ClockSampler(0); sampler.start()
+    res = {}
+    with torch.no_grad():
+        cases = [("scatter_to_edge_src", lambda: jg.ScatterToEdge(h, csc, "src"), E * (4 + 4 * C) + 4 * n * C),
+                 ("scatter_to_edge_dst", lambda: jg.ScatterToEdge(h, csc, "dst"), E * 4 * C + 4 * n * C),
+                 ("scatter_to_vertex", lambda: jg.ScatterToVertex(msg, csc, "src"), E * 4 * C + 4 * n * C),
+                 ("edge_softmax", lambda: jg.EdgeSoftmax(score, csc), 2 * E * 4 * H)]
+        for name, fn, nbytes in cases:
+            ms = _time(fn, args.steps, args.warmup)
+            res[name] = {"ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peak}
+        layer = nn.GATConv(C, C, heads=H).to(dev)
+        ms_unfused = _time(lambda: layer.propagate_unfused(h, csc), max(2, args.steps // 4), 1)
+        a_src, a_dst = layer.attention_vectors()
+        a_src, a_dst = a_src.contiguous(), a_dst.contiguous()
+        ms_fused = _time(lambda: jg.gat_aggregate(h, a_src, a_dst, csc, H), args.steps, args.warmup)
+    clocks = sampler.stop()
+    top = res["scatter_to_vertex"]
+    _line(args, "edge_to_vertex_edges_per_s", "edge/s", E / (top["ms"] * 1e-3), top["ms"],
+          f"per-edge operators on {n} nodes, {E} in-edges, C = {C}, {H} heads (quarter-size attention graph)",
+          {"bound": "hbm", "achieved": top["gbs"], "peak": peak, "unit": "GB/s", "frac": top["frac_of_hbm_peak"], "traffic": None,
+           "peak_kind": kind, "kernel": "edge_to_vertex_kernel", "note": "bytes = the [E, C] messages read once + the [N, C] result"},
+          {"operators": res, "attention_op_by_op_ms": ms_unfused, "attention_fused_ms": ms_fused,
+           "gpu_launches": args.steps * 4, "clocks": clocks})
+
+
 def run_citation(args):
     """The citation-graph-shaped configuration: 2708 nodes, 5278 undirected edges, 1433 sparse binary
     features, 2-layer GCN 1433 -> 256 -> 7, one step = forward + loss + backward (gradients of both
@@ -397,4 +438,4 @@ def run_citation(args):
 
 
 def run(args):
-    return {"citation": run_citation, "convert": run_convert, "gat": run_gat, "gemm": run_gemm, "gcn": run_gcn, "sample": run_sample}[args.workload](args)
+    return {"citation": run_citation, "edgeops": run_edgeops, "convert": run_convert, "gat": run_gat, "gemm": run_gemm, "gcn": run_gcn, "sample": run_sample}[args.workload](args)

@@ -85,6 +85,15 @@ int jg_aggregate_add_f32(float* out, const float* x, const int32_t* idx, const i
                          const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes,
                          jg_stream_t stream);
 
+/* The same aggregation with every row that is not split by the plan summed strictly in stored order
+ * at EVERY width (jg_aggregate_f32 does so for f < 32 and f > 64 only; in between it lets lane groups
+ * take alternate entries, which is faster and differs by rounding).  With idx = 0, 1, 2, ... and
+ * unit weights over an [n_edges, f] message matrix this is the per-destination sum of
+ * edgetovertex (ops/cpp/edgetovertex_op.cc:27-57), bit-identical to its sequential loop. */
+int jg_aggregate_ordered_f32(float* out, const float* x, const int32_t* idx, const int32_t* off, const float* w,
+                             int64_t n_out, int64_t n_in, int64_t f, int64_t nnz, const void* plan, int32_t chunk,
+                             void* workspace, size_t workspace_bytes, jg_stream_t stream);
+
 /* The same aggregation with the layer's epilogue fused into the store of every finished row:
  * out[v,:] = act(sum + bias), bias [f] or NULL, relu != 0 clamps at zero.  Replaces the separate
  * elementwise passes of `out = out + self.bias` and `nn.relu(...)` that follow the aggregation in the

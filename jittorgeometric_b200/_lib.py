@@ -32,6 +32,7 @@ SIGNATURES = {
     "jg_aggregate_f32": (ctypes.c_int, [vp, vp, vp, vp, vp, i64, i64, i64, i64, vp, i32, vp, sz, vp]),
     "jg_validate_segments": (ctypes.c_int, [vp, vp, i64, i64, i64, vp, sz, vp]),
     "jg_aggregate_add_f32": (ctypes.c_int, [vp, vp, vp, vp, vp, i64, i64, i64, i64, vp, i32, vp, sz, vp]),
+    "jg_aggregate_ordered_f32": (ctypes.c_int, [vp, vp, vp, vp, vp, i64, i64, i64, i64, vp, i32, vp, sz, vp]),
     "jg_aggregate_bias_act_f32": (ctypes.c_int, [vp, vp, vp, vp, vp, vp, ctypes.c_int, i64, i64, i64, i64, vp, i32, vp, sz, vp]),
     "jg_partition_split_workspace_bytes": (sz, [i64]),
     "jg_partition_split": (ctypes.c_int, [vp, vp, vp, i64, i64, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]),

@@ -112,6 +112,10 @@ __device__ __forceinline__ float reduce_same_column_sum(float v) {
     return v;
 }
 
+// Segments of kSoftmaxHub edges or more are left to the block-per-segment kernels below: one warp
+// walking tens of thousands of entries alone would be the tail of the whole launch.
+constexpr int kSoftmaxHub = 2048;
+
 template <int HP>
 __global__ void __launch_bounds__(kEdgeBlock) edge_softmax_fwd_kernel(float* __restrict__ y, const float* __restrict__ x,
                                                                       const int32_t* __restrict__ off, int64_t n) {
@@ -119,15 +123,56 @@ __global__ void __launch_bounds__(kEdgeBlock) edge_softmax_fwd_kernel(float* __r
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     for (int64_t v = warp; v < n; v += n_warps) {
+        if (off[v + 1] - off[v] >= kSoftmaxHub) continue;
         const int64_t s = (int64_t)off[v] * HP, e = (int64_t)off[v + 1] * HP;
         if (s >= e) continue;
         float mx = -INFINITY;
-        for (int64_t i = s + lane; i < e; i += 32) mx = fmaxf(mx, x[i]);
+        int64_t i = s + lane;
+        for (; i + 96 < e; i += 128) {   // four independent loads in flight
+            const float a0 = x[i], a1 = x[i + 32], a2 = x[i + 64], a3 = x[i + 96];
+            mx = fmaxf(fmaxf(mx, fmaxf(a0, a1)), fmaxf(a2, a3));
+        }
+        for (; i < e; i += 32) mx = fmaxf(mx, x[i]);
         mx = reduce_same_column_max<HP>(mx);
         float sum = 0.f;
-        for (int64_t i = s + lane; i < e; i += 32) sum += expf(x[i] - mx);
+        for (i = s + lane; i < e; i += 32) sum += expf(x[i] - mx);
         sum = reduce_same_column_sum<HP>(sum);
-        for (int64_t i = s + lane; i < e; i += 32) y[i] = expf(x[i] - mx) / sum;
+        for (i = s + lane; i < e; i += 32) y[i] = expf(x[i] - mx) / sum;
+    }
+}
+
+// Block-wide reductions over the threads that meet the same column (thread t always meets column
+// t % HP because the block size is a multiple of HP): inside a warp by shuffles, across the warps
+// through shared memory in warp order.
+template <int HP, bool IS_MAX>
+__device__ __forceinline__ float block_same_column(float v, float* s_buf /*[kEdgeBlock]*/) {
+    v = IS_MAX ? reduce_same_column_max<HP>(v) : reduce_same_column_sum<HP>(v);
+    __syncthreads();
+    s_buf[threadIdx.x] = v;
+    __syncthreads();
+    float r = s_buf[threadIdx.x & 31];
+#pragma unroll
+    for (int w = 1; w < kEdgeBlock / 32; w++) {
+        const float o = s_buf[w * 32 + (threadIdx.x & 31)];
+        r = IS_MAX ? fmaxf(r, o) : r + o;
+    }
+    return r;
+}
+
+template <int HP>
+__global__ void __launch_bounds__(kEdgeBlock) edge_softmax_fwd_hub_kernel(float* __restrict__ y, const float* __restrict__ x,
+                                                                          const int32_t* __restrict__ off, int64_t n) {
+    __shared__ float s_buf[kEdgeBlock];
+    for (int64_t v = blockIdx.x; v < n; v += gridDim.x) {
+        if (off[v + 1] - off[v] < kSoftmaxHub) continue;   // block-uniform
+        const int64_t s = (int64_t)off[v] * HP, e = (int64_t)off[v + 1] * HP;
+        float mx = -INFINITY;
+        for (int64_t i = s + threadIdx.x; i < e; i += kEdgeBlock) mx = fmaxf(mx, x[i]);
+        mx = block_same_column<HP, true>(mx, s_buf);
+        float sum = 0.f;
+        for (int64_t i = s + threadIdx.x; i < e; i += kEdgeBlock) sum += expf(x[i] - mx);
+        sum = block_same_column<HP, false>(sum, s_buf);
+        for (int64_t i = s + threadIdx.x; i < e; i += kEdgeBlock) y[i] = expf(x[i] - mx) / sum;
     }
 }
 
@@ -160,11 +205,32 @@ __global__ void __launch_bounds__(kEdgeBlock) edge_softmax_bwd_kernel(float* __r
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     for (int64_t v = warp; v < n; v += n_warps) {
+        if (off[v + 1] - off[v] >= kSoftmaxHub) continue;
         const int64_t s = (int64_t)off[v] * HP, e = (int64_t)off[v + 1] * HP;
         float dot = 0.f;
-        for (int64_t i = s + lane; i < e; i += 32) dot += y[i] * g[i];
+        int64_t i = s + lane;
+        for (; i + 96 < e; i += 128) {   // eight independent loads in flight, added in order
+            const float p0 = y[i] * g[i], p1 = y[i + 32] * g[i + 32], p2 = y[i + 64] * g[i + 64], p3 = y[i + 96] * g[i + 96];
+            dot = (((dot + p0) + p1) + p2) + p3;
+        }
+        for (; i < e; i += 32) dot += y[i] * g[i];
         dot = reduce_same_column_sum<HP>(dot);
-        for (int64_t i = s + lane; i < e; i += 32) dx[i] = __fsub_rn(__fmul_rn(y[i], g[i]), __fmul_rn(y[i], dot));
+        for (i = s + lane; i < e; i += 32) dx[i] = __fsub_rn(__fmul_rn(y[i], g[i]), __fmul_rn(y[i], dot));
+    }
+}
+
+template <int HP>
+__global__ void __launch_bounds__(kEdgeBlock) edge_softmax_bwd_hub_kernel(float* __restrict__ dx, const float* __restrict__ g,
+                                                                          const float* __restrict__ y,
+                                                                          const int32_t* __restrict__ off, int64_t n) {
+    __shared__ float s_buf[kEdgeBlock];
+    for (int64_t v = blockIdx.x; v < n; v += gridDim.x) {
+        if (off[v + 1] - off[v] < kSoftmaxHub) continue;   // block-uniform
+        const int64_t s = (int64_t)off[v] * HP, e = (int64_t)off[v + 1] * HP;
+        float dot = 0.f;
+        for (int64_t i = s + threadIdx.x; i < e; i += kEdgeBlock) dot += y[i] * g[i];
+        dot = block_same_column<HP, false>(dot, s_buf);
+        for (int64_t i = s + threadIdx.x; i < e; i += kEdgeBlock) dx[i] = __fsub_rn(__fmul_rn(y[i], g[i]), __fmul_rn(y[i], dot));
     }
 }
 
@@ -206,6 +272,12 @@ static int grid_for_warps(int64_t warps_wanted) {
     int64_t blocks = (warps_wanted * 32 + kEdgeBlock - 1) / kEdgeBlock;
     if (blocks < 1) blocks = 1;
     return (int)(blocks < max_blocks ? blocks : max_blocks);
+}
+
+// blocks of the block-per-segment kernels: they scan all segments for the long ones
+static int hub_blocks(int64_t n_nodes) {
+    const int64_t cap = (int64_t)sm_count() * 4;
+    return (int)(n_nodes < cap ? (n_nodes > 0 ? n_nodes : 1) : cap);
 }
 
 }  // namespace jg
@@ -259,13 +331,20 @@ int jg_edge_softmax_fwd_f32(float* y, const float* x, const int32_t* off, int64_
     JG_CHECK_ARG(n_edges * h <= (int64_t)INT32_MAX * 32, JG_ESHAPE, "edge_softmax: sizes too large");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int grid = grid_for_warps(n_nodes);
+    const int hub_grid = hub_blocks(n_nodes);
     switch (h) {
-        case 1: edge_softmax_fwd_kernel<1><<<grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes); break;
-        case 2: edge_softmax_fwd_kernel<2><<<grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes); break;
-        case 4: edge_softmax_fwd_kernel<4><<<grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes); break;
-        case 8: edge_softmax_fwd_kernel<8><<<grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes); break;
-        case 16: edge_softmax_fwd_kernel<16><<<grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes); break;
-        case 32: edge_softmax_fwd_kernel<32><<<grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes); break;
+        case 1: edge_softmax_fwd_kernel<1><<<grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes);
+                edge_softmax_fwd_hub_kernel<1><<<hub_grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes); break;
+        case 2: edge_softmax_fwd_kernel<2><<<grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes);
+                edge_softmax_fwd_hub_kernel<2><<<hub_grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes); break;
+        case 4: edge_softmax_fwd_kernel<4><<<grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes);
+                edge_softmax_fwd_hub_kernel<4><<<hub_grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes); break;
+        case 8: edge_softmax_fwd_kernel<8><<<grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes);
+                edge_softmax_fwd_hub_kernel<8><<<hub_grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes); break;
+        case 16: edge_softmax_fwd_kernel<16><<<grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes);
+                edge_softmax_fwd_hub_kernel<16><<<hub_grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes); break;
+        case 32: edge_softmax_fwd_kernel<32><<<grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes);
+                edge_softmax_fwd_hub_kernel<32><<<hub_grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes); break;
         default: edge_softmax_fwd_any_kernel<<<grid_for_warps(n_nodes * h), kEdgeBlock, 0, st>>>(y, x, off, n_nodes, h);
     }
     JG_LAUNCH_CHECK();
@@ -279,13 +358,20 @@ int jg_edge_softmax_bwd_f32(float* dx, const float* grad, const float* y, const 
     JG_CHECK_ARG(dx && grad && y && off, JG_EINVAL, "edge_softmax_bwd: null pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int grid = grid_for_warps(n_nodes);
+    const int hub_grid = hub_blocks(n_nodes);
     switch (h) {
-        case 1: edge_softmax_bwd_kernel<1><<<grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes); break;
-        case 2: edge_softmax_bwd_kernel<2><<<grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes); break;
-        case 4: edge_softmax_bwd_kernel<4><<<grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes); break;
-        case 8: edge_softmax_bwd_kernel<8><<<grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes); break;
-        case 16: edge_softmax_bwd_kernel<16><<<grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes); break;
-        case 32: edge_softmax_bwd_kernel<32><<<grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes); break;
+        case 1: edge_softmax_bwd_kernel<1><<<grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes);
+                 edge_softmax_bwd_hub_kernel<1><<<hub_grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes); break;
+        case 2: edge_softmax_bwd_kernel<2><<<grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes);
+                 edge_softmax_bwd_hub_kernel<2><<<hub_grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes); break;
+        case 4: edge_softmax_bwd_kernel<4><<<grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes);
+                 edge_softmax_bwd_hub_kernel<4><<<hub_grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes); break;
+        case 8: edge_softmax_bwd_kernel<8><<<grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes);
+                 edge_softmax_bwd_hub_kernel<8><<<hub_grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes); break;
+        case 16: edge_softmax_bwd_kernel<16><<<grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes);
+                 edge_softmax_bwd_hub_kernel<16><<<hub_grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes); break;
+        case 32: edge_softmax_bwd_kernel<32><<<grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes);
+                 edge_softmax_bwd_hub_kernel<32><<<hub_grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes); break;
         default: edge_softmax_bwd_any_kernel<<<grid_for_warps(n_nodes * h), kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes, h);
     }
     JG_LAUNCH_CHECK();

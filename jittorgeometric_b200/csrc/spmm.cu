@@ -99,6 +99,7 @@ struct AggArgs {
     int64_t max_items;  // host-side upper bound on the plan's pieces (sizes the grid)
     const float* bias;  // epilogue on finished output rows: + bias[column] (null: none) ...
     int relu;           // ... then max(., 0)
+    int ordered;        // 1: every row must be summed in stored order (no lane groups taking alternate entries)
 };
 
 
@@ -543,8 +544,12 @@ static int dispatch_aggregate(const AggArgs& a, cudaStream_t st) {
     const int64_t f = a.f;
     const bool vec_ok = (f % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.out) |
                                           reinterpret_cast<uintptr_t>(a.partial)) % 16 == 0);
-    if (vec_ok && f == 32) return launch_rows<8, 1, 8, 4, true>(a, st);
-    if (vec_ok && f > 32 && f <= 64) return launch_rows<16, 1, 8, 4, true>(a, st);
+    // widths up to 64 normally put two or four entries of a row side by side in one warp and add the
+    // lane groups' partial sums at the end; an ordered sum takes the narrow kernel (F <= 32) or the
+    // 128-column layout with idle lanes (F <= 64) instead
+    if (vec_ok && f == 32 && !a.ordered) return launch_rows<8, 1, 8, 4, true>(a, st);
+    if (vec_ok && f > 32 && f <= 64 && !a.ordered) return launch_rows<16, 1, 8, 4, true>(a, st);
+    if (vec_ok && f > 32 && f <= 64) return launch_rows<32, 1, 8, 4, true>(a, st);
     if (vec_ok && f > 64 && f <= 128) return launch_rows<32, 1, 8, 4, true>(a, st);
     if (vec_ok && f > 128 && f <= 256) return launch_rows<32, 2, 4, 4, true>(a, st);
     if (vec_ok && f > 256 && f <= 512) return launch_rows<32, 4, 2, 3, true>(a, st);
@@ -605,7 +610,7 @@ size_t jg_aggregate_workspace_bytes(int64_t n_out, int64_t nnz, int64_t f, int32
 static int aggregate_impl(float* out, const float* x, const int32_t* idx, const int32_t* off,
                           const float* w, int64_t n_out, int64_t n_in, int64_t f, int64_t nnz,
                           const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes,
-                          jg_stream_t stream, int accumulate, const float* bias = nullptr, int relu = 0) {
+                          jg_stream_t stream, int accumulate, const float* bias = nullptr, int relu = 0, int ordered = 0) {
     JG_CHECK_ARG(n_out >= 0 && n_in >= 0 && f >= 0 && nnz >= 0, JG_EINVAL, "aggregate: negative size");
     if (n_out == 0 || f == 0) return JG_OK;
     JG_CHECK_ARG(out && off, JG_EINVAL, "aggregate: null out/off");
@@ -623,6 +628,7 @@ static int aggregate_impl(float* out, const float* x, const int32_t* idx, const 
     a.accumulate = accumulate;
     a.bias = bias;
     a.relu = relu;
+    a.ordered = ordered;
     JG_CHECK_ARG(!bias || f % 4 != 0 || reinterpret_cast<uintptr_t>(bias) % 16 == 0, JG_EINVAL,
                  "aggregate: bias must be 16-byte aligned");
     Carver c(workspace);
@@ -658,6 +664,13 @@ int jg_aggregate_add_f32(float* out, const float* x, const int32_t* idx, const i
                          const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes,
                          jg_stream_t stream) {
     return aggregate_impl(out, x, idx, off, w, n_out, n_in, f, nnz, plan, chunk, workspace, workspace_bytes, stream, 1);
+}
+
+int jg_aggregate_ordered_f32(float* out, const float* x, const int32_t* idx, const int32_t* off, const float* w,
+                             int64_t n_out, int64_t n_in, int64_t f, int64_t nnz, const void* plan, int32_t chunk,
+                             void* workspace, size_t workspace_bytes, jg_stream_t stream) {
+    return aggregate_impl(out, x, idx, off, w, n_out, n_in, f, nnz, plan, chunk, workspace, workspace_bytes, stream, 0, nullptr,
+                          0, 1);
 }
 
 int jg_aggregate_bias_act_f32(float* out, const float* x, const int32_t* idx, const int32_t* off, const float* w,

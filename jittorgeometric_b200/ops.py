@@ -85,14 +85,16 @@ def _plan_of(holder, off, nnz):
     return plan
 
 
-def segment_aggregate(x, idx, off, w, n_out=None, plan=None, out=None, accumulate=False, bias=None, relu=False):
+def segment_aggregate(x, idx, off, w, n_out=None, plan=None, out=None, accumulate=False, bias=None, relu=False,
+                      ordered=False):
     """out[v,:] = sum_{j in [off[v], off[v+1])} w[j] * x[idx[j],:]  (fp32).
 
     The one kernel behind aggregateWithWeight (forward over CSC, backward over
     CSR), SpmmCsr and SpmmCoo.  ``plan`` is an :class:`SpmmPlan` of ``off`` or
     ``None`` to process every row unsplit.  ``accumulate=True`` adds the result to ``out``.
     ``bias`` / ``relu`` fuse the layer epilogue ``act(sum + bias)`` into the store of every row
-    (forward only, not together with ``accumulate``)."""
+    (forward only, not together with ``accumulate``).  ``ordered=True`` sums every unsplit row
+    strictly in stored order at every width (the default does for widths below 32 and above 64)."""
     x = _as_f32(x, "x")
     if x.dim() != 2:
         raise RuntimeError("x: expected a 2-D feature matrix")
@@ -113,7 +115,7 @@ def segment_aggregate(x, idx, off, w, n_out=None, plan=None, out=None, accumulat
         pad = 4 - f % 4
         xp = torch.nn.functional.pad(x, (0, pad))
         bp = None if bias is None else torch.nn.functional.pad(_as_f32(bias, "bias"), (0, pad))
-        return segment_aggregate(xp, idx, off, w, n_out=n_out, plan=plan, bias=bp, relu=relu)[:, :f]
+        return segment_aggregate(xp, idx, off, w, n_out=n_out, plan=plan, bias=bp, relu=relu, ordered=ordered)[:, :f]
     if out is None:
         if accumulate:
             raise RuntimeError("accumulate=True needs the tensor to add to (out=)")
@@ -130,7 +132,9 @@ def segment_aggregate(x, idx, off, w, n_out=None, plan=None, out=None, accumulat
                                               f, nnz, ptr(plan.buf) if plan is not None else None, chunk, ptr(ws), ws.numel(),
                                               stream_for(x)), "jg_aggregate_bias_act_f32")
         return out
-    fn = lib().jg_aggregate_add_f32 if accumulate else lib().jg_aggregate_f32
+    if ordered and accumulate:
+        raise RuntimeError("segment_aggregate: ordered=True cannot be combined with accumulate=True")
+    fn = lib().jg_aggregate_add_f32 if accumulate else (lib().jg_aggregate_ordered_f32 if ordered else lib().jg_aggregate_f32)
     check(fn(ptr(out), ptr(x), ptr(idx), ptr(off), ptr(w), n_out, n_in, f, nnz,
                                  ptr(plan.buf) if plan is not None else None, chunk, ptr(ws), ws.numel(),
                                  stream_for(x)), "jg_aggregate_f32")
@@ -403,6 +407,19 @@ def _edge_to_vertex(msg, csc, flag):
     E, n, c = idx.numel(), off.numel() - 1, msg.shape[1]
     if msg.shape[0] != E:
         raise RuntimeError(f"edge tensor has {msg.shape[0]} rows, the graph {E} edges")
+    if flag == 1 and E > 0 and (c <= 32 or c % 4 == 0):
+        # the per-destination sum is an aggregation of the message rows with identity indices and unit
+        # weights: the aggregation kernel brings vector loads, eight rows in flight per lane and hub
+        # rows cut into pieces, and its ordered variant keeps the reference's summation order
+        ident = getattr(csc, "_jg_identity", None)
+        if ident is None or ident[0].numel() != E or ident[0].device != msg.device:
+            ident = (torch.arange(E, dtype=torch.int32, device=msg.device), torch.ones(E, dtype=torch.float32, device=msg.device))
+            csc._jg_identity = ident
+        plan = getattr(csc, "_jg_plan_ordered", None)         # long pieces: only real hubs lose the stored order
+        if plan is None or plan.off_ptr != off.data_ptr() or plan.nnz != E:
+            plan = SpmmPlan(off, E, chunk=DEFAULT_CHUNK)
+            csc._jg_plan_ordered = plan
+        return segment_aggregate(msg, ident[0], off, ident[1], n_out=n, plan=plan, ordered=True)
     out = torch.empty((n, c), dtype=torch.float32, device=msg.device)
     check(lib().jg_edge_to_vertex_f32(ptr(out), ptr(msg), ptr(idx), ptr(off), n, E, c, flag, stream_for(msg)),
           "jg_edge_to_vertex_f32")
