@@ -29,10 +29,12 @@ def gcn_norm(edge_index, edge_weight=None, num_nodes=None, improved=False, add_s
 
 
 def _transform(x, weight, tf32, relu=False):
-    """``x @ weight`` (optionally ReLU): the tcgen05 TF32 kernel when asked for and no gradient is
-    needed (it is forward-only, 2e-3 tolerance), else the fp32 matmul with autograd."""
+    """``x @ weight`` (optionally ReLU): the tcgen05 TF32 kernel when asked for (2e-3 tolerance; in
+    training its backward runs in TF32 as well), else the fp32 matmul with autograd."""
     needs_grad = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)
-    if tf32 and not needs_grad and ops.linear_tf32_supported(x.shape[0], x.shape[1], weight.shape[1]):
+    if tf32 and ops.linear_tf32_supported(x.shape[0], x.shape[1], weight.shape[1]):
+        if needs_grad:
+            return ops.linear_tf32_autograd(x, weight, relu=relu)
         return ops.linear_tf32(x, weight, relu=relu)
     h = x @ weight
     return torch.relu(h) if relu else h

@@ -15,7 +15,7 @@ from .data import CSC, CSR
 
 __all__ = ["aggregateWithWeight", "aggregate_bias_act", "segment_aggregate", "SpmmPlan", "cootocsr", "cootocsc", "gcn_norm_csc_csr",
            "SpmmCsr", "SpmmCoo", "ScatterToEdge", "ScatterToVertex", "EdgeSoftmax", "gat_aggregate",
-           "gat_aggregate_supported", "gcn_norm_coo", "linear_tf32", "linear_tf32_supported", "toUndirected", "validate_structure"]
+           "gat_aggregate_supported", "gcn_norm_coo", "linear_tf32", "linear_tf32_autograd", "linear_tf32_supported", "toUndirected", "validate_structure"]
 
 DEFAULT_CHUNK = int(os.environ.get("JG_SPMM_CHUNK", "1024"))
 SMALL_GRAPH_NNZ = 1 << 20
@@ -616,3 +616,45 @@ def linear_tf32(x, weight, bias=None, relu=False, weight_t=None, check_status=Fa
     if check_status:
         check(lib().jg_gemm_tf32_status(ptr(ws), st), "jg_gemm_tf32_status")
     return out
+
+
+class _LinearTF32(torch.autograd.Function):
+    """``act(x @ weight)`` through the tcgen05 kernel with a backward: ``grad_x = g @ weight^T`` runs
+    on the same kernel (its transposed operand is the weight itself), ``grad_weight = x^T @ g`` is a
+    reduction over the rows, a shape the row-tiled kernel does not cover, and goes to the library
+    matmul with TF32 allowed."""
+
+    @staticmethod
+    def forward(ctx, x, weight, relu):
+        out = linear_tf32(x, weight, relu=relu)
+        ctx.relu = relu
+        ctx.save_for_backward(x, weight, out if relu else None)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, weight, out = ctx.saved_tensors
+        g = grad_output
+        if ctx.relu:
+            g = g * (out > 0)
+        g = g.contiguous()
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            if linear_tf32_supported(g.shape[0], g.shape[1], weight.shape[0]):
+                gx = linear_tf32(g, weight.t(), weight_t=weight.contiguous())
+            else:
+                gx = g @ weight.t()
+        if ctx.needs_input_grad[1]:
+            before = torch.backends.cuda.matmul.allow_tf32
+            torch.backends.cuda.matmul.allow_tf32 = True
+            try:
+                gw = x.t() @ g
+            finally:
+                torch.backends.cuda.matmul.allow_tf32 = before
+        return gx, gw, None
+
+
+def linear_tf32_autograd(x, weight, relu=False):
+    """:func:`linear_tf32` usable in training (TF32 products in forward and backward)."""
+    return _LinearTF32.apply(_as_f32(x, "x"), _as_f32(weight, "weight"), bool(relu))
+

@@ -53,3 +53,49 @@ def test_unsupported_shapes_are_refused(cuda):
     assert not cuda.ops.linear_tf32_supported(100, 128, 257)
     with pytest.raises(RuntimeError):
         cuda.ops.linear_tf32(torch.zeros((10, 128), device="cuda"), torch.zeros((128, 300), device="cuda"))
+
+
+@pytest.mark.parametrize("n,k,m,relu", [(5000, 128, 64, True), (3001, 602, 64, True), (2048, 64, 128, False), (1000, 300, 16, False)])
+def test_trainable_transform(cuda, n, k, m, relu):
+    """Forward and both gradients of the TF32 transform against float64 autograd, at the TF32 bar
+    (2e-3 of the sum of absolute products); k = 300 exceeds the kernel's output width for the
+    input gradient and takes the library matmul there."""
+    g = torch.Generator(device="cuda").manual_seed(n + k)
+    x0 = torch.randn((n, k), device="cuda", generator=g)
+    w0 = torch.randn((k, m), device="cuda", generator=g) * 0.1
+    go = torch.randn((n, m), device="cuda", generator=g)
+    x, w = x0.clone().requires_grad_(True), w0.clone().requires_grad_(True)
+    y = cuda.ops.linear_tf32_autograd(x, w, relu=relu)
+    y.backward(go)
+    xd, wd = x0.double(), w0.double()
+    yd = xd @ wd
+    yd = torch.relu(yd) if relu else yd
+    # ReLU decisions differ where the pre-activation is within TF32 rounding of zero; the gradients are
+    # checked for the decisions the kernel took
+    same = ((y > 0) == (yd > 0)) if relu else torch.ones_like(y, dtype=torch.bool)
+    assert same.float().mean().item() > 0.999
+    scale_y = x0.abs().double() @ w0.abs().double()
+    assert (((y.double() - yd).abs() / (scale_y + 1e-30))[same]).max().item() <= 2e-3
+    gm = go.double() * ((y > 0) if relu else 1.0)
+    want_gx, want_gw = gm @ wd.t(), xd.t() @ gm
+    scale_x = gm.abs() @ w0.abs().double().t()
+    assert ((x.grad.double() - want_gx).abs() / (scale_x + 1e-30)).max().item() <= 2e-3
+    scale_w = x0.abs().double().t() @ gm.abs()
+    assert ((w.grad.double() - want_gw).abs() / (scale_w + 1e-30)).max().item() <= 2e-3
+
+
+def test_gcn_layer_trains_in_tf32(cuda):
+    from jittorgeometric_b200 import nn
+    torch.manual_seed(0)
+    n = 3000
+    ei = torch.randint(0, n, (2, 40000), device="cuda", dtype=torch.int32)
+    csc, csr = cuda.gcn_norm_csc_csr(ei, None, n)
+    x = torch.randn(n, 128, device="cuda")
+    a, b = nn.GCNConv(128, 64, tf32=True, relu=True).cuda(), nn.GCNConv(128, 64, relu=True).cuda()
+    with torch.no_grad():
+        b.weight.copy_(a.weight)
+    outs = []
+    for layer in (a, b):
+        layer(x, csc, csr).square().mean().backward()
+        outs.append(layer.weight.grad.clone())
+    assert (outs[0] - outs[1]).abs().max().item() <= 5e-3 * outs[1].abs().max().item()
