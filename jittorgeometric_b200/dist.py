@@ -20,14 +20,11 @@ source rank, and runs P rounds of host-staged pickled ``MPI.bcast`` + cuSPARSE. 
 One process per GPU; ``torch.distributed`` supplies the communicator.  The compute backend is
 pluggable so the partition and exchange logic can be exercised by CPU ranks over ``gloo``.
 """
-import os
-
 import torch
 import torch.distributed as dist
 
 from . import ops
 from ._lib import check, lib, ptr, stream_for, workspace
-from .data import CSC, CSR
 
 
 class RowPartition:

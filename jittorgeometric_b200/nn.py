@@ -6,7 +6,7 @@ import math
 import torch
 
 from . import ops
-from .data import CSC, CSR
+from .data import CSC, CSR  # noqa: F401  (re-exported: layers take these containers)
 
 
 def glorot_(t):

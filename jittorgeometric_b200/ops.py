@@ -9,7 +9,6 @@ import os
 
 import torch
 
-from . import _lib
 from ._lib import check, lib, ptr, stream_for, workspace
 from .data import CSC, CSR
 
