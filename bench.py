@@ -205,7 +205,7 @@ def workload_config(scale, ef, n, nnz, gpus):
             "nodes": n, "nnz": nnz, "widths": list(WIDTHS),
             "l2": "inputs larger than L2 (indices+weights %.0f MB, X %.0f-%.0f MB)" % (
                 nnz * 8 / 1e6, n * 32 * 4 / 1e6, n * 256 * 4 / 1e6),
-            "partition": "none" if gpus == 1 else f"{gpus} contiguous destination-row shards, halo exchange over NCCL"}
+            "partition": "none" if gpus == 1 else f"{gpus} contiguous destination-row shards, compact-halo exchange over NVLink"}
 
 
 def run_single(args):
