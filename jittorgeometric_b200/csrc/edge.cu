@@ -116,6 +116,36 @@ __device__ __forceinline__ float reduce_same_column_sum(float v) {
 // walking tens of thousands of entries alone would be the tail of the whole launch.
 constexpr int kSoftmaxHub = 2048;
 
+// Running (maximum, sum of exp(x - maximum)) of the elements a lane has met; merging two such states
+// rescales the one with the smaller maximum.  An empty state is (-inf, 0).
+struct MaxSum {
+    float m, s;
+    __device__ __forceinline__ void add4(float a0, float a1, float a2, float a3) {
+        const float m4 = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
+        if (m4 > m) {
+            s *= expf(m - m4);   // m = -inf at the start: the empty sum scales to 0
+            m = m4;
+        }
+        s += (expf(a0 - m) + expf(a1 - m)) + (expf(a2 - m) + expf(a3 - m));
+    }
+    __device__ __forceinline__ void add(float a) {
+        if (a > m) {
+            s *= expf(m - a);
+            m = a;
+        }
+        s += expf(a - m);
+    }
+    __device__ __forceinline__ void merge(float m2, float s2) {
+        const float mn = fmaxf(m, m2);
+        const float f1 = (m == -INFINITY) ? 0.f : expf(m - mn);
+        const float f2 = (m2 == -INFINITY) ? 0.f : expf(m2 - mn);
+        s = s * f1 + s2 * f2;
+        m = mn;
+    }
+};
+
+// Two passes per segment: (maximum, sum) in one sweep with four loads in flight per lane, then the
+// normalised values (the second sweep finds the segment in cache).
 template <int HP>
 __global__ void __launch_bounds__(kEdgeBlock) edge_softmax_fwd_kernel(float* __restrict__ y, const float* __restrict__ x,
                                                                       const int32_t* __restrict__ off, int64_t n) {
@@ -126,18 +156,29 @@ __global__ void __launch_bounds__(kEdgeBlock) edge_softmax_fwd_kernel(float* __r
         if (off[v + 1] - off[v] >= kSoftmaxHub) continue;
         const int64_t s = (int64_t)off[v] * HP, e = (int64_t)off[v + 1] * HP;
         if (s >= e) continue;
-        float mx = -INFINITY;
+        MaxSum st = {-INFINITY, 0.f};
         int64_t i = s + lane;
-        for (; i + 96 < e; i += 128) {   // four independent loads in flight
-            const float a0 = x[i], a1 = x[i + 32], a2 = x[i + 64], a3 = x[i + 96];
-            mx = fmaxf(fmaxf(mx, fmaxf(a0, a1)), fmaxf(a2, a3));
+        for (; i + 96 < e; i += 128) st.add4(x[i], x[i + 32], x[i + 64], x[i + 96]);
+        for (; i < e; i += 32) st.add(x[i]);
+#pragma unroll
+        for (int o = 16; o >= HP; o >>= 1) {   // lanes of the same column; both partners end with the same state
+            const float m2 = __shfl_xor_sync(kFull, st.m, o), s2 = __shfl_xor_sync(kFull, st.s, o);
+            if (lane & o) {
+                MaxSum other = {m2, s2};
+                other.merge(st.m, st.s);
+                st = other;
+            } else {
+                st.merge(m2, s2);
+            }
         }
-        for (; i < e; i += 32) mx = fmaxf(mx, x[i]);
-        mx = reduce_same_column_max<HP>(mx);
-        float sum = 0.f;
-        for (i = s + lane; i < e; i += 32) sum += expf(x[i] - mx);
-        sum = reduce_same_column_sum<HP>(sum);
-        for (i = s + lane; i < e; i += 32) y[i] = expf(x[i] - mx) / sum;
+        const float mx = st.m, inv = 1.f / st.s;
+        i = s + lane;
+        for (; i + 96 < e; i += 128) {
+            const float a0 = x[i], a1 = x[i + 32], a2 = x[i + 64], a3 = x[i + 96];
+            y[i] = expf(a0 - mx) * inv; y[i + 32] = expf(a1 - mx) * inv;
+            y[i + 64] = expf(a2 - mx) * inv; y[i + 96] = expf(a3 - mx) * inv;
+        }
+        for (; i < e; i += 32) y[i] = expf(x[i] - mx) * inv;
     }
 }
 
