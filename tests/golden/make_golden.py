@@ -119,5 +119,43 @@ def main():
          y256_sha256=np.frombuffer(hashlib.sha256(y256.tobytes()).digest(), np.uint8))
 
 
+def sampling():
+    """Golden vectors of the neighbour-sampling operators (compiled reference bodies)."""
+    O.build()
+    assert O.have_ref(), "reference CPU library missing: golden vectors need it"
+    ids4 = np.arange(4, dtype=np.int32)
+    # tests/test_csctocsr.py:25-35
+    co, ri = np.array([0, 0, 1, 2, 4], np.int32), np.array([0, 0, 1, 2], np.int32)
+    ro, ci = O.csc_to_csr(co, ri, ids4, ids4, I)
+    # tests/test_getweight.py:25-33
+    gco, gri = np.array([0, 1, 2, 3, 4], np.int32), np.array([0, 0, 1, 2], np.int32)
+    gw = O.get_weight(4, ids4, ids4, gco, gri, I)
+    # tests/test_sampleprocessing.py:34-40: every in-degree is at most the fanout (3), so the body copies
+    # every list in stored order; layer offsets are the running sums of the degrees
+    s_goff = np.array([0, 3, 6, 8, 10, 12, 14, 16, 17, 18, 19], np.int32)
+    s_gidx = np.array([1, 2, 3, 2, 3, 4, 0, 5, 1, 6, 2, 7, 3, 8, 4, 9, 5, 6, 7], np.int32)
+    s_dst = np.array([3, 0, 9, 5, 1], np.int32)
+    s_off = np.concatenate([[0], np.cumsum(O.sample_counts(s_dst, s_goff, 3)[1:])]).astype(np.int32)
+    s_out = O.sample_reference(3, s_dst, s_off, s_goff, s_gidx)
+    # a seeded layer over explicit id lists: 300 destinations and 1500 listed sources out of 4000 ids
+    rng = np.random.default_rng(20261125 + 7)
+    l_off = np.concatenate([[0], np.cumsum(rng.integers(0, 12, size=300))]).astype(np.int32)
+    l_idx = rng.integers(0, 4000, size=l_off[-1]).astype(np.int32)
+    l_dst = rng.permutation(4000)[:300].astype(np.int32)
+    l_src = rng.permutation(4000)[:1500].astype(np.int32)
+    l_ro, l_ci = O.csc_to_csr(l_off, l_idx, l_dst, l_src, I)
+    l_w = O.get_weight(4000, l_dst, l_src, l_off, l_idx, I)
+    save("ref_test_sampling", csr_in_column_offset=co, csr_in_row_indices=ri, csr_row_offset=ro, csr_column_indices=ci,
+         w_column_offset=gco, w_row_indices=gri, w_out=gw, counts_dst=ids4,
+         counts_global_offset=np.array([0, 1, 3, 4, 5], np.int32), counts_out=np.array([0, 1, 2, 1, 1], np.int32),
+         s_global_offset=s_goff, s_global_indices=s_gidx, s_dst=s_dst, s_layer_offset=s_off, s_out=s_out,
+         l_column_offset=l_off, l_row_indices=l_idx, l_dst=l_dst, l_src=l_src, l_row_offset=l_ro,
+         l_column_indices=l_ci, l_weight=l_w)
+
+
 if __name__ == "__main__":
-    main()
+    if sys.argv[1:] == ["sampling"]:
+        sampling()
+    else:
+        main()
+        sampling()

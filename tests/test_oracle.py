@@ -167,3 +167,24 @@ def test_sampling_checkers_on_the_reference_fixtures(oracle):
     # the property checker rejects a sample that repeats a position
     bad_off = np.array([0, 2], np.int32)
     assert oracle.check_sample(2, np.array([0]), bad_off, np.array([7, 7]), np.array([0, 3]), np.array([7, 8, 9])) is not None
+
+
+def test_sampling_golden_vectors(oracle):
+    """Committed outputs of the compiled reference bodies for the sampling operators: the C
+    restatement reproduces them (and so does the compiled reference where it is built)."""
+    d = dict(np.load(os.path.join(G, "ref_test_sampling.npz")))
+    ids4 = np.arange(4, dtype=np.int32)
+    impls = ["port", "ref"] if oracle.have_ref() else ["port"]
+    for impl in impls:
+        ro, ci = oracle.csc_to_csr(d["csr_in_column_offset"], d["csr_in_row_indices"], ids4, ids4, impl)
+        assert np.array_equal(ro, d["csr_row_offset"]) and np.array_equal(ci, d["csr_column_indices"])
+        assert np.array_equal(oracle.get_weight(4, ids4, ids4, d["w_column_offset"], d["w_row_indices"], impl), d["w_out"])
+        ro, ci = oracle.csc_to_csr(d["l_column_offset"], d["l_row_indices"], d["l_dst"], d["l_src"], impl)
+        assert np.array_equal(ro, d["l_row_offset"]) and np.array_equal(ci, d["l_column_indices"])
+        assert np.array_equal(oracle.get_weight(4000, d["l_dst"], d["l_src"], d["l_column_offset"], d["l_row_indices"], impl),
+                              d["l_weight"])
+    assert np.array_equal(oracle.sample_counts(d["counts_dst"], d["counts_global_offset"], 2), d["counts_out"])
+    # every degree is within the fanout: the sample is the in-edge lists in stored order
+    want = np.concatenate([d["s_global_indices"][d["s_global_offset"][v]: d["s_global_offset"][v + 1]] for v in d["s_dst"]])
+    assert np.array_equal(d["s_out"], want)
+    assert oracle.check_sample(3, d["s_dst"], d["s_layer_offset"], d["s_out"], d["s_global_offset"], d["s_global_indices"]) is None

@@ -223,3 +223,19 @@ def test_sampling_edge_cases(cuda):
     ssg = S.sample_one([5, 5], dev(g_off), dev(g_idx), dev(np.array([0, 2], np.int32)))
     assert ssg.num_nodes == 2 and ssg.num_edges == 0 and host(ssg.column_offset).tolist() == [0, 0, 0]
     assert host(ssg.local2global).tolist() == [0, 2]
+
+
+def test_sampling_golden_vectors(cuda):
+    """The committed outputs of the reference's own compiled CPU bodies (tests/golden/ref_test_sampling.npz)."""
+    import os
+    from jittorgeometric_b200 import sampling as S
+    d = dict(np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_test_sampling.npz")))
+    ro, ci = S.csctocsr(dev(d["l_column_offset"]), dev(d["l_row_indices"]), dev(d["l_dst"]), dev(d["l_src"]))
+    assert np.array_equal(host(ro), d["l_row_offset"]) and np.array_equal(host(ci), d["l_column_indices"])
+    w = S.getweight(4000, dev(d["l_dst"]), dev(d["l_src"]), dev(d["l_column_offset"]), dev(d["l_row_indices"]))
+    assert np.array_equal(host(w), d["l_weight"])
+    off = S.layer_offsets(3, dev(d["s_dst"]), dev(d["s_global_offset"]))
+    assert np.array_equal(host(off), d["s_layer_offset"])
+    got = S.sampleprocessing(3, dev(d["s_dst"]), off, dev(d["s_global_offset"]), dev(d["s_global_indices"]))
+    assert np.array_equal(host(got), d["s_out"])
+    assert host(S.gpuinitco(4, 2, dev(d["counts_dst"]), dev(d["counts_global_offset"]))).tolist() == d["counts_out"].tolist()
