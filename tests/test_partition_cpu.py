@@ -161,3 +161,85 @@ def test_chunks_drive_the_partitioned_aggregation(oracle):
     offset = np.concatenate([[0], np.cumsum(np.bincount(partition, minlength=world))])
     for rank, _, y, _ in got:
         assert np.abs(y - want[order][offset[rank]: offset[rank + 1]]).max() <= 1e-4
+
+
+def chunk_training_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import torch.distributed as dist
+    from jittorgeometric_b200 import dist as jd
+    from test_dist_cpu import OracleBackend
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        n, f, classes, partition, edge_index, w, feature, labels = symmetric_problem(world)
+        ref = reference_chunks(partition, edge_index, n, world, w)
+        chunk = chunk_from_reference(ref, rank, world, n, feature)
+        s, e = ref[rank]["range"]
+        local_labels = torch.from_numpy(labels[ref[rank]["order"]][s:e].copy())
+        g = chunk.sharded_graph(backend=OracleBackend())
+        mgr = jd.DistributedManager()
+        model = jd.ShardedGCN(f, 6, classes, layers=2, manager=mgr, seed=7)
+        opt = torch.optim.SGD(model.parameters(), lr=0.3)
+        mask = torch.ones(e - s, dtype=torch.bool)
+        losses = [jd.sharded_training_step(model, g, chunk.local_feature, local_labels, mask, opt, mgr) for _ in range(2)]
+        q.put((rank, 0, [p.detach().numpy().copy() for p in model.weights], losses))
+    except Exception as exc:
+        q.put((rank, -1, repr(exc), None))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+def symmetric_problem(world):
+    rng = np.random.default_rng(31)
+    n, f, classes = 70, 5, 3
+    a = rng.integers(0, n, size=260)
+    b = rng.integers(0, n, size=260)
+    keep = a != b
+    pairs = np.unique(np.stack([np.minimum(a, b)[keep], np.maximum(a, b)[keep]], 1), axis=0)
+    wv = (rng.random(len(pairs)) * 0.2).astype(np.float32)
+    edge_index = np.concatenate([pairs.T, pairs.T[::-1]], axis=1).astype(np.int64)      # both directions: a symmetric matrix
+    w = np.concatenate([wv, wv])
+    partition = rng.integers(0, world, size=n).astype(np.int32)
+    partition[:world] = np.arange(world)
+    feature = rng.standard_normal((n, f)).astype(np.float32)
+    labels = rng.integers(0, classes, size=n).astype(np.int64)
+    return n, f, classes, partition, edge_index, w, feature, labels
+
+
+@pytest.mark.timeout(180)
+def test_training_on_chunks_of_a_partition_file(oracle):
+    """Partition vector -> chunks -> compact-halo aggregation -> two SGD steps on three uneven ranks:
+    losses and weights equal dense float64 training on the whole (renumbered) graph."""
+    from jittorgeometric_b200 import dist as jd
+    world = 3
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=chunk_training_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=150) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=30)
+    assert all(g[1] == 0 for g in got), [g[2] for g in got if g[1] != 0]
+    n, f, classes, partition, edge_index, w, feature, labels = symmetric_problem(world)
+    A = np.zeros((n, n))
+    np.add.at(A, (edge_index[1], edge_index[0]), w.astype(np.float64))
+    A = torch.from_numpy(A)
+    ref = jd.ShardedGCN(f, 6, classes, layers=2, manager=None, seed=7)
+    W = [p.detach().double().requires_grad_(True) for p in ref.weights]
+    X, L = torch.from_numpy(feature).double(), torch.from_numpy(labels)
+    want_losses = []
+    for _ in range(2):
+        h = X
+        for wt in W:
+            h = (A @ h) @ wt
+        loss = torch.nn.functional.nll_loss(torch.log_softmax(h, dim=1), L)
+        grads = torch.autograd.grad(loss, W)
+        want_losses.append(float(loss.detach()))
+        W = [(wt - 0.3 * g).detach().requires_grad_(True) for wt, g in zip(W, grads)]
+    for rank, _, weights, losses in got:
+        assert np.allclose(losses, want_losses, rtol=1e-4, atol=1e-5)
+        for have, want in zip(weights, W):
+            assert np.abs(have - want.detach().numpy()).max() <= 1e-4
