@@ -362,6 +362,33 @@ def gat_unfused(h, a, idx, off, impl="port"):
     return edge_to_vertex(msg, idx, off, 1, impl)
 
 
+def gat_unfused_backward(h, a, idx, off, grad_out, impl="port"):
+    """Gradients of :func:`gat_unfused` with respect to ``h`` and ``a``, composed from the reference's
+    own backward pairings: ScatterToVertex.grad = scatter_to_edge by destination
+    (ops/scatterToVertex.py:41-45), EdgeSoftmax.grad = edgesoftmaxbackward (ops/edgesoftmax.py:69-74),
+    ScatterToEdge.grad = edge_to_vertex with the same flag (ops/scatterToEdge.py:42-46); the dense
+    steps (concat, @ a, leaky_relu, multiply) differentiated with numpy.  Returns ``(grad_h, grad_a)``."""
+    h, a, g = _f32(h), _f32(a).reshape(-1), _f32(grad_out)
+    c = h.shape[1]
+    e_s = scatter_to_edge(h, idx, off, 0, impl)
+    e_d = scatter_to_edge(h, idx, off, 1, impl)
+    cat = np.concatenate([e_s, e_d], axis=1)
+    pre = (cat @ a.reshape(-1, 1)).astype(np.float32).reshape(-1)
+    m = np.where(pre > 0, pre, np.float32(0.2) * pre).astype(np.float32)
+    alpha = edge_softmax(m, off, impl)
+    g_msg = scatter_to_edge(g, idx, off, 1, impl)                       # d out[v] / d msg[e] = 1 for e in seg(v)
+    g_alpha = (g_msg * e_s).sum(1).astype(np.float32)
+    g_es = (g_msg * alpha.reshape(-1, 1)).astype(np.float32)
+    g_m = edge_softmax_backward(g_alpha, alpha, off, impl)
+    g_pre = np.where(pre > 0, g_m, np.float32(0.2) * g_m).astype(np.float32)
+    g_cat = g_pre.reshape(-1, 1) * a.reshape(1, -1)
+    grad_a = (cat * g_pre.reshape(-1, 1)).sum(0).astype(np.float32)
+    g_es = (g_es + g_cat[:, :c]).astype(np.float32)
+    g_ed = g_cat[:, c:].astype(np.float32)
+    grad_h = edge_to_vertex(g_es, idx, off, 0, impl) + edge_to_vertex(g_ed, idx, off, 1, impl)
+    return grad_h.astype(np.float32), grad_a
+
+
 def gcn_layer(x, W, b, csc, impl="port"):
     """GCNConv.execute (nn/conv/gcn_conv.py:94-102): (x @ W) aggregated over CSC, plus bias."""
     idx, off, w = csc

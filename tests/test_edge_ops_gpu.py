@@ -176,6 +176,27 @@ def test_fused_attention_equals_reference_pipeline(cuda, oracle):
     assert np.abs(got - want).max() <= 1e-5 * (np.abs(hfeat).max() + 1)
 
 
+def test_fused_attention_backward_equals_reference_pairings(cuda, oracle):
+    """Single head: gradients of the fused kernel against the reference's own backward pairings
+    (ScatterToVertex.grad, EdgeSoftmax.grad, ScatterToEdge.grad) composed on the CPU."""
+    rng = np.random.default_rng(15)
+    n, c = 500, 8
+    ei = rng.integers(0, n, size=(2, 6000)).astype(np.int32)
+    nei, nw = oracle.gcn_norm(ei, None, n)
+    idx, off, _ = oracle.coo_to_csc(nei, nw, n)
+    hfeat = rng.standard_normal((n, c)).astype(np.float32)
+    a = (rng.standard_normal(2 * c) * 0.3).astype(np.float32)
+    g = rng.standard_normal((n, c)).astype(np.float32)
+    impl = "ref" if oracle.have_ref() else "port"
+    want_h, want_a = oracle.gat_unfused_backward(hfeat, a, idx, off, g, impl)
+    csc = cuda.CSC(dev(idx), dev(off), None)
+    h, a_s, a_d = dev(hfeat).requires_grad_(True), dev(a[:c]).requires_grad_(True), dev(a[c:]).requires_grad_(True)
+    cuda.gat_aggregate(h, a_s, a_d, csc, 1).backward(dev(g))
+    assert np.abs(host(h.grad) - want_h).max() <= 2e-5 * np.abs(want_h).max()
+    got_a = np.concatenate([host(a_s.grad).reshape(-1), host(a_d.grad).reshape(-1)])
+    assert np.abs(got_a - want_a).max() <= 2e-5 * np.abs(want_a).max()
+
+
 def test_gat_layer_fused_and_unfused_agree(cuda):
     from jittorgeometric_b200 import nn
     torch.manual_seed(0)

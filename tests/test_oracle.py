@@ -188,3 +188,35 @@ def test_sampling_golden_vectors(oracle):
     want = np.concatenate([d["s_global_indices"][d["s_global_offset"][v]: d["s_global_offset"][v + 1]] for v in d["s_dst"]])
     assert np.array_equal(d["s_out"], want)
     assert oracle.check_sample(3, d["s_dst"], d["s_layer_offset"], d["s_out"], d["s_global_offset"], d["s_global_indices"]) is None
+
+
+def test_attention_backward_composition(oracle):
+    """The reference's backward pairings composed into the gradient of its attention pipeline agree with
+    float64 autograd of the same formula (torch on the CPU)."""
+    import torch
+    rng = np.random.default_rng(12)
+    n, c = 60, 8
+    dst = rng.integers(0, n, size=500)
+    src = rng.integers(0, n, size=500)
+    order = np.argsort(dst, kind="stable")
+    idx = src[order].astype(np.int32)
+    off = np.concatenate([[0], np.cumsum(np.bincount(dst, minlength=n))]).astype(np.int32)
+    h = rng.standard_normal((n, c)).astype(np.float32)
+    a = (rng.standard_normal(2 * c) * 0.4).astype(np.float32)
+    g = rng.standard_normal((n, c)).astype(np.float32)
+    impls = ["port", "ref"] if oracle.have_ref() else ["port"]
+    ht, at = torch.from_numpy(h).double().requires_grad_(True), torch.from_numpy(a).double().requires_grad_(True)
+    seg = torch.from_numpy(np.repeat(np.arange(n), np.diff(off)))
+    e_s, e_d = ht[torch.from_numpy(idx).long()], ht[seg]
+    m = torch.nn.functional.leaky_relu(torch.cat([e_s, e_d], 1) @ at, 0.2)
+    top = torch.full((n,), -float("inf"), dtype=torch.float64).scatter_reduce(0, seg, m, "amax")
+    p = torch.exp(m - top[seg])
+    alpha = p / torch.zeros(n, dtype=torch.float64).index_add(0, seg, p)[seg]
+    out = torch.zeros((n, c), dtype=torch.float64).index_add(0, seg, e_s * alpha.unsqueeze(1))
+    out.backward(torch.from_numpy(g).double())
+    for impl in impls:
+        fwd = oracle.gat_unfused(h, a, idx, off, impl)
+        assert np.abs(fwd - out.detach().numpy()).max() <= 1e-5
+        gh, ga = oracle.gat_unfused_backward(h, a, idx, off, g, impl)
+        assert np.abs(gh - ht.grad.numpy()).max() <= 2e-5 * np.abs(ht.grad.numpy()).max()
+        assert np.abs(ga - at.grad.numpy()).max() <= 2e-5 * np.abs(at.grad.numpy()).max()
