@@ -15,7 +15,7 @@ from . import ops
 from ._lib import check, lib, ptr, stream_for, workspace
 from .data import CSC, CSR
 
-__all__ = ["gpuinitco", "sampleprocessing", "csctocsr", "getweight", "layer_offsets", "LayerSampGraph", "SampledSubgraph",
+__all__ = ["gpuinitco", "sampleprocessing", "csctocsr", "getweight", "from_nodes", "to_nodes", "layer_offsets", "LayerSampGraph", "SampledSubgraph",
            "sample_layers", "build_subgraph", "sample_one", "NeighborLoader"]
 
 _i32 = ops._as_i32
@@ -117,6 +117,23 @@ def getweight(vtx_size, csc_layer_dst, csc_layer_src, csc_layer_column_offset, c
     check(lib().jg_degree_weights(int(vtx_size), ptr(dst), dst.numel(), ptr(off), ptr(idx), E, ptr(w), ptr(ws), ws.numel(),
                                   stream_for(off)), "jg_degree_weights")
     return w
+
+
+def from_nodes(csc, nodes):
+    """In-neighbours of every node of ``nodes``, list after list, duplicates kept
+    (ops/saparse_ops.py:9-40; a Python loop over the nodes there, one full-copy sampling pass here)."""
+    if csc is None:
+        raise ValueError("CSC structure must be provided.")
+    off = layer_offsets(-1, nodes, csc.column_offset)
+    return sampleprocessing(-1, nodes, off, csc.column_offset, csc.row_indices)
+
+
+def to_nodes(csr, nodes):
+    """Out-neighbours of every node of ``nodes``, list after list (ops/saparse_ops.py:43-73)."""
+    if csr is None:
+        raise ValueError("CSR structure must be provided.")
+    off = layer_offsets(-1, nodes, csr.row_offset)
+    return sampleprocessing(-1, nodes, off, csr.row_offset, csr.column_indices)
 
 
 def _expand(off, values, total):

@@ -239,3 +239,15 @@ def test_sampling_golden_vectors(cuda):
     got = S.sampleprocessing(3, dev(d["s_dst"]), off, dev(d["s_global_offset"]), dev(d["s_global_indices"]))
     assert np.array_equal(host(got), d["s_out"])
     assert host(S.gpuinitco(4, 2, dev(d["counts_dst"]), dev(d["counts_global_offset"]))).tolist() == d["counts_out"].tolist()
+
+
+def test_from_nodes_and_to_nodes(cuda):
+    """The inputs of the reference's tests/test_fromtonodes.py:12-26: neighbour lists concatenated in the
+    order of the given nodes, duplicates kept."""
+    col_offset, row_indices = dev(np.array([0, 2, 4, 5, 6, 7], np.int32)), dev(np.array([0, 3, 1, 4, 0, 4, 2], np.int32))
+    row_offset, col_indices = dev(np.array([0, 2, 3, 4, 5, 7], np.int32)), dev(np.array([0, 2, 1, 4, 0, 1, 3], np.int32))
+    nodes = dev(np.array([1, 2, 2, 4], np.int32))
+    assert host(cuda.from_nodes(cuda.CSC(row_indices, col_offset, None), nodes)).tolist() == [1, 4, 0, 0, 2]
+    assert host(cuda.to_nodes(cuda.CSR(col_indices, row_offset, None), nodes)).tolist() == [1, 4, 4, 1, 3]
+    with pytest.raises(ValueError):
+        cuda.from_nodes(None, nodes)
