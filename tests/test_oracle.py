@@ -220,3 +220,29 @@ def test_attention_backward_composition(oracle):
         gh, ga = oracle.gat_unfused_backward(h, a, idx, off, g, impl)
         assert np.abs(gh - ht.grad.numpy()).max() <= 2e-5 * np.abs(ht.grad.numpy()).max()
         assert np.abs(ga - at.grad.numpy()).max() <= 2e-5 * np.abs(at.grad.numpy()).max()
+
+
+def test_sampling_restatement_against_reference_randomised(oracle):
+    """Property test (hypothesis): the C restatement of csctocsr / getweight equals the compiled reference
+    bodies on random small structures, including empty columns, unlisted sources and repeated ids."""
+    if not oracle.have_ref():
+        pytest.skip("compiled reference bodies not available")
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=60, deadline=None)
+    @given(st.integers(0, 2**31 - 1))
+    def run(seed):
+        rng = np.random.default_rng(seed)
+        n_dst, universe = int(rng.integers(1, 12)), int(rng.integers(1, 30))
+        off = np.concatenate([[0], np.cumsum(rng.integers(0, 5, size=n_dst))]).astype(np.int32)
+        idx = rng.integers(0, universe, size=off[-1]).astype(np.int32)
+        dst = rng.integers(0, universe, size=n_dst).astype(np.int32)
+        src = rng.permutation(universe)[: int(rng.integers(0, universe + 1))].astype(np.int32)
+        a, b = oracle.csc_to_csr(off, idx, dst, src, "port"), oracle.csc_to_csr(off, idx, dst, src, "ref")
+        assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+        if off[-1]:
+            w1 = oracle.get_weight(universe, dst, src, off, idx, "port")
+            w2 = oracle.get_weight(universe, dst, src, off, idx, "ref")
+            assert np.array_equal(w1, w2)
+
+    run()
