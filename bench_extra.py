@@ -339,7 +339,7 @@ def run_edgeops(args):
         for name, fn, nbytes in cases:
             ms = _time(fn, args.steps, args.warmup)
             res[name] = {"ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peak}
-        layer = nn.GATConv(C, C, heads=H).to(dev)
+        layer = nn.GATConv(C, C, E, heads=H).to(dev)
         ms_unfused = _time(lambda: layer.propagate_unfused(h, csc), max(2, args.steps // 4), 1)
         a_src, a_dst = layer.attention_vectors()
         a_src, a_dst = a_src.contiguous(), a_dst.contiguous()

@@ -158,10 +158,12 @@ int jg_coo_to_compressed(const int32_t* edge_index, const float* w, int64_t n_ed
  * appended in node order (weight `fill`, or the weight of the node's last (v,v) input entry),
  * deg = weighted in-degree, w' = (deg^-1/2[src] * w) * deg^-1/2[dst].  Output arrays need room for
  * n_edges + n_nodes entries; the actual entry count is written to *out_count (device, int64).
- * The CSR triple may be NULL (all three) when only the CSC is wanted. */
+ * The CSR triple may be NULL (all three) when only the CSC is wanted.  add_self_loops == 0
+ * (the reference's add_self_loops=False, nn/conv/gcn_conv.py:25) normalises the list as given:
+ * nothing is dropped or appended, and a node without in-edges has deg^-1/2 = inf, as there. */
 int jg_gcn_norm_compressed(const int32_t* edge_index, const float* w, int64_t n_edges, int64_t n_nodes, float fill,
-                           int canonical, int32_t* csc_idx, int32_t* csc_off, float* csc_w, int32_t* csr_idx,
-                           int32_t* csr_off, float* csr_w, int64_t* out_count, void* workspace,
+                           int add_self_loops, int canonical, int32_t* csc_idx, int32_t* csc_off, float* csc_w,
+                           int32_t* csr_idx, int32_t* csr_off, float* csr_w, int64_t* out_count, void* workspace,
                            size_t workspace_bytes, jg_stream_t stream);
 
 /* gcn_norm as a COO list, for callers that want the reference's intermediate
@@ -170,8 +172,8 @@ int jg_gcn_norm_compressed(const int32_t* edge_index, const float* w, int64_t n_
  * int64) the entry count.  Same weights as jg_gcn_norm_compressed. */
 size_t jg_gcn_norm_coo_workspace_bytes(int64_t n_edges, int64_t n_nodes);
 int jg_gcn_norm_coo(const int32_t* edge_index, const float* w, int64_t n_edges, int64_t n_nodes, float fill,
-                    int32_t* out_src, int32_t* out_dst, float* out_w, int64_t* out_count, void* workspace,
-                    size_t workspace_bytes, jg_stream_t stream);
+                    int add_self_loops, int32_t* out_src, int32_t* out_dst, float* out_w, int64_t* out_count,
+                    void* workspace, size_t workspace_bytes, jg_stream_t stream);
 
 /* Symmetrise and deduplicate a COO list: replaces ToundirectedOp (ops/cpp/toundirected_op.cc:33-63;
  * wrapper ops/toundirected.py:16-22).  Every edge is mirrored, the 2 * n_edges entries are sorted

@@ -41,9 +41,9 @@ SIGNATURES = {
     "jg_gather_rows_f32": (ctypes.c_int, [vp, vp, vp, i64, i64, i32, vp]),
     "jg_convert_workspace_bytes": (sz, [i64, i64]),
     "jg_coo_to_compressed": (ctypes.c_int, [vp, vp, i64, i64, ctypes.c_int, ctypes.c_int, vp, vp, vp, vp, sz, vp]),
-    "jg_gcn_norm_compressed": (ctypes.c_int, [vp, vp, i64, i64, f32, ctypes.c_int, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
+    "jg_gcn_norm_compressed": (ctypes.c_int, [vp, vp, i64, i64, f32, ctypes.c_int, ctypes.c_int, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
     "jg_gcn_norm_coo_workspace_bytes": (sz, [i64, i64]),
-    "jg_gcn_norm_coo": (ctypes.c_int, [vp, vp, i64, i64, f32, vp, vp, vp, vp, vp, sz, vp]),
+    "jg_gcn_norm_coo": (ctypes.c_int, [vp, vp, i64, i64, f32, ctypes.c_int, vp, vp, vp, vp, vp, sz, vp]),
     "jg_to_undirected_workspace_bytes": (sz, [i64, i64]),
     "jg_to_undirected": (ctypes.c_int, [vp, vp, i64, i64, vp, vp, vp, vp, vp, sz, vp]),
     "jg_scatter_to_edge_f32": (ctypes.c_int, [vp, vp, vp, vp, i64, i64, i64, ctypes.c_int, vp]),

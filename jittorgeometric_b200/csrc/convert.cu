@@ -245,6 +245,8 @@ __global__ void offsets_from_sorted_keys(const int32_t* __restrict__ key, int64_
     for (int64_t k = lo + 1; k <= hi; k++) off[k] = (int32_t)j;
 }
 
+__global__ void set_count_kernel(unsigned long long* p, unsigned long long v) { *p = v; }
+
 // Valid-entry count of the first pass (input entries that are not (v,v), plus loops).
 __global__ void count_kept_kernel(const int32_t* __restrict__ src, const int32_t* __restrict__ dst, int64_t e0,
                                   unsigned long long* __restrict__ kept) {
@@ -330,6 +332,18 @@ __global__ void write_norm_coo_kernel(const int32_t* __restrict__ src, const int
         out_dst[kept + v] = v;
         out_w[kept + v] = __fmul_rn(__fmul_rn(dis[v], loop_w ? loop_w[v] : 1.f), dis[v]);
     }
+}
+
+// add_self_loops = false: entry i keeps its place, w' = (dis[src] * w) * dis[dst]
+__global__ void norm_coo_plain_kernel(const int32_t* __restrict__ src, const int32_t* __restrict__ dst,
+                                      const float* __restrict__ w, const float* __restrict__ dis, int64_t e0,
+                                      int32_t* __restrict__ out_src, int32_t* __restrict__ out_dst, float* __restrict__ out_w) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= e0) return;
+    const int32_t a = src[i], b = dst[i];
+    out_src[i] = a;
+    out_dst[i] = b;
+    out_w[i] = __fmul_rn(__fmul_rn(dis[a], w ? w[i] : 1.f), dis[b]);
 }
 
 // ---- symmetrise + dedupe: first entry of every run of equal (row, col) pairs survives
@@ -546,8 +560,8 @@ int jg_coo_to_compressed(const int32_t* edge_index, const float* w, int64_t n_ed
 }
 
 int jg_gcn_norm_compressed(const int32_t* edge_index, const float* w, int64_t n_edges, int64_t n_nodes, float fill,
-                           int canonical, int32_t* csc_idx, int32_t* csc_off, float* csc_w, int32_t* csr_idx,
-                           int32_t* csr_off, float* csr_w, int64_t* out_count, void* workspace,
+                           int add_self_loops, int canonical, int32_t* csc_idx, int32_t* csc_off, float* csc_w,
+                           int32_t* csr_idx, int32_t* csr_off, float* csr_w, int64_t* out_count, void* workspace,
                            size_t workspace_bytes, jg_stream_t stream) {
     JG_CHECK_ARG(n_edges >= 0 && n_nodes >= 0, JG_EINVAL, "gcn_norm_compressed: negative size");
     JG_CHECK_ARG(csc_idx && csc_off && csc_w && out_count, JG_EINVAL, "gcn_norm_compressed: CSC outputs and count are required");
@@ -564,16 +578,16 @@ int jg_gcn_norm_compressed(const int32_t* edge_index, const float* w, int64_t n_
     const int32_t* dst = edge_index + n_edges;
     const int grid = sm_count() * 8;
 
-    // entries that survive: non-loop input entries + one loop per node
-    const unsigned long long loops = (unsigned long long)n_nodes;
-    JG_CUDA(cudaMemcpyAsync(ws.kept, &loops, sizeof(loops), cudaMemcpyHostToDevice, st));
-    if (n_edges > 0) {
+    // entries that survive: non-loop input entries + one loop per node; without self-loops the list as given
+    set_count_kernel<<<1, 1, 0, st>>>(ws.kept, (unsigned long long)(add_self_loops ? n_nodes : n_edges));
+    JG_LAUNCH_CHECK();
+    if (n_edges > 0 && add_self_loops) {
         count_kept_kernel<<<grid, 256, 0, st>>>(src, dst, n_edges, ws.kept);
         JG_LAUNCH_CHECK();
     }
-    const bool unit = (w == nullptr) && fill == 1.0f;
+    const bool unit = (w == nullptr) && (fill == 1.0f || !add_self_loops);
     const float* loop_w = nullptr;
-    if (!unit && n_nodes > 0) {
+    if (!unit && n_nodes > 0 && add_self_loops) {
         fill_int_kernel<<<blocks_for(n_nodes, 256), 256, 0, st>>>(ws.last_loop, -1, n_nodes);
         JG_LAUNCH_CHECK();
         if (n_edges > 0) {
@@ -587,8 +601,10 @@ int jg_gcn_norm_compressed(const int32_t* edge_index, const float* w, int64_t n_
     SortSrc first = {};
     first.mode = 1;
     first.coo_src = src; first.coo_dst = dst; first.coo_w = w; first.loop_w = loop_w;
-    first.e0 = n_edges; first.n_loops = n_nodes; first.drop_loops = 1;
-    first.count = cap;
+    first.e0 = n_edges;
+    first.n_loops = add_self_loops ? n_nodes : 0;
+    first.drop_loops = add_self_loops ? 1 : 0;
+    first.count = add_self_loops ? cap : n_edges;
 
     // destination-major (CSC), raw weights; degrees and dis from its segments
     int32_t* skey = nullptr;
@@ -654,8 +670,8 @@ size_t jg_gcn_norm_coo_workspace_bytes(int64_t n_edges, int64_t n_nodes) {
 }
 
 int jg_gcn_norm_coo(const int32_t* edge_index, const float* w, int64_t n_edges, int64_t n_nodes, float fill,
-                    int32_t* out_src, int32_t* out_dst, float* out_w, int64_t* out_count, void* workspace,
-                    size_t workspace_bytes, jg_stream_t stream) {
+                    int add_self_loops, int32_t* out_src, int32_t* out_dst, float* out_w, int64_t* out_count,
+                    void* workspace, size_t workspace_bytes, jg_stream_t stream) {
     JG_CHECK_ARG(n_edges >= 0 && n_nodes >= 0, JG_EINVAL, "gcn_norm_coo: negative size");
     JG_CHECK_ARG(out_count, JG_EINVAL, "gcn_norm_coo: null count");
     JG_CHECK_ARG(n_edges + n_nodes == 0 || (out_src && out_dst && out_w), JG_EINVAL, "gcn_norm_coo: null output");
@@ -665,11 +681,19 @@ int jg_gcn_norm_coo(const int32_t* edge_index, const float* w, int64_t n_edges, 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     NormCooWs nw = carve_norm_coo(workspace, n_edges, n_nodes);
     // degrees come from the destination-major order (sequential sums in list order); its arrays are scratch here
-    int rc = jg_gcn_norm_compressed(edge_index, w, n_edges, n_nodes, fill, 0, nw.tmp_idx, nw.tmp_off, nw.tmp_w, nullptr,
-                                    nullptr, nullptr, out_count, nw.convert, nw.convert_bytes, stream);
+    int rc = jg_gcn_norm_compressed(edge_index, w, n_edges, n_nodes, fill, add_self_loops, 0, nw.tmp_idx, nw.tmp_off,
+                                    nw.tmp_w, nullptr, nullptr, nullptr, out_count, nw.convert, nw.convert_bytes, stream);
     if (rc != JG_OK) return rc;
     ConvertWs ws = carve_convert(nw.convert, n_edges + n_nodes, n_nodes);  // dis, loop_w and kept live there
     const bool unit = (w == nullptr) && fill == 1.0f;
+    if (!add_self_loops) {   // the list as given, every weight scaled by the two degrees
+        if (n_edges > 0) {
+            norm_coo_plain_kernel<<<blocks_for(n_edges, 256), 256, 0, st>>>(edge_index, edge_index + n_edges, w, ws.dis,
+                                                                            n_edges, out_src, out_dst, out_w);
+            JG_LAUNCH_CHECK();
+        }
+        return JG_OK;
+    }
     if (n_edges > 0) {
         keep_flags_kernel<<<blocks_for(n_edges, 256), 256, 0, st>>>(edge_index, edge_index + n_edges, n_edges, nw.pos);
         JG_LAUNCH_CHECK();

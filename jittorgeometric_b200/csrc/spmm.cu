@@ -712,6 +712,14 @@ static int static_scratch(unsigned char** out) {
     return JG_OK;
 }
 
+// Start-of-call state of the shared array: ticket at zero, empty plan with this call's piece length.
+__global__ void static_scratch_init_kernel(unsigned long long* ticket, PlanHeader* hdr, int32_t chunk, int32_t max_hubs,
+                                           int32_t max_items) {
+    *ticket = 0ull;
+    PlanHeader h = {0, 0, chunk, max_hubs, max_items, {0, 0, 0}};
+    *hdr = h;
+}
+
 // Bytes of scratch one call needs when hub rows are cut into `chunk`-entry pieces.
 static size_t static_need(int64_t nnz, int64_t f, int32_t chunk) {
     size_t plan_bytes = 0;
@@ -762,9 +770,11 @@ int jg_aggregate_f32_static(float* out, const float* x, const int32_t* idx, cons
 
     // The array keeps whatever the previous call left: the two words that must start at zero
     // (ticket, plan counters) are rewritten here; everything else is written before it is read.
-    JG_CUDA(cudaMemsetAsync(a.ticket, 0, sizeof(unsigned long long), st));
-    PlanHeader h = {0, 0, chunk, (int32_t)plan_max_hubs(nnz, chunk), (int32_t)plan_max_items(nnz, chunk), {0, 0, 0}};
-    JG_CUDA(cudaMemcpyAsync(v.hdr, &h, sizeof(h), cudaMemcpyHostToDevice, st));
+    // Both are written by a one-thread kernel from its arguments: no host memory is referenced once
+    // this function has returned.
+    static_scratch_init_kernel<<<1, 1, 0, st>>>(a.ticket, v.hdr, chunk, (int32_t)plan_max_hubs(nnz, chunk),
+                                                (int32_t)plan_max_items(nnz, chunk));
+    JG_LAUNCH_CHECK();
     {
         int grid = (int)((n_out + 255) / 256);
         if (grid > sm_count() * 16) grid = sm_count() * 16;

@@ -21,11 +21,9 @@ def gcn_norm(edge_index, edge_weight=None, num_nodes=None, improved=False, add_s
     """Self-loops + symmetric normalisation as a COO list (nn/conv/gcn_conv.py:18-37).  Returned
     in the reference's order (kept entries, then one loop per node); ``ops.gcn_norm_csc_csr`` gives
     the CSC/CSR directly without materialising this list."""
-    if not add_self_loops:
-        raise RuntimeError("gcn_norm: add_self_loops=False is not implemented")
     if num_nodes is None:
         num_nodes = int(edge_index.max()) + 1 if edge_index.numel() else 0
-    return ops.gcn_norm_coo(edge_index, edge_weight, num_nodes, improved=improved)
+    return ops.gcn_norm_coo(edge_index, edge_weight, num_nodes, improved=improved, add_self_loops=add_self_loops)
 
 
 def _transform(x, weight, tf32, relu=False):
@@ -43,9 +41,11 @@ def _transform(x, weight, tf32, relu=False):
 class GCNConv(torch.nn.Module):
     """``out = A_hat (x W) + b`` (nn/conv/gcn_conv.py:70-112).  ``spmm`` is accepted for signature
     compatibility; there is one backend.  The bias (and, with ``relu=True``, the activation the
-    reference's models apply right after the layer) is added inside the aggregation kernel."""
+    reference's models apply right after the layer) is added inside the aggregation kernel.  The
+    transform runs on the tcgen05 kernel with TF32 products (results within 2e-3 of fp32);
+    ``tf32=False`` keeps it in fp32 for comparisons at 1e-5."""
 
-    def __init__(self, in_channels, out_channels, bias=True, spmm=True, tf32=False, relu=False, **kwargs):
+    def __init__(self, in_channels, out_channels, bias=True, spmm=True, tf32=True, relu=False, **kwargs):
         super().__init__()
         self.in_channels, self.out_channels, self.spmm, self.tf32 = in_channels, out_channels, spmm, tf32
         self.relu = relu
@@ -93,26 +93,31 @@ class APPNP(torch.nn.Module):
         self.K, self.alpha = K, alpha
 
     def forward(self, x, csc, csr):
-        h = x
+        ah = self.alpha * x                      # alpha * h, formed once
         for _ in range(self.K):
-            x = ops.aggregateWithWeight(x, csc, csr)
-            x = x * (1 - self.alpha)
-            x = x + self.alpha * h
+            x = torch.add(ah, ops.aggregateWithWeight(x, csc, csr), alpha=1 - self.alpha)
         return x
 
 
 class GATConv(torch.nn.Module):
-    """Attention layer (nn/conv/gat_conv.py:30-88): ``h = relu(x W)``, edge logits
+    """Attention layer (nn/conv/gat_conv.py:20-88) with the reference's constructor,
+    ``GATConv(in_channels, out_channels, e_num, improved=False, cached=False, add_self_loops=True,
+    normalize=True, bias=True)``: ``e_num`` (the edge count the reference asks for) and the four flags
+    are accepted and, as in the reference's ``execute``, unused.  ``h = relu(x W)``, edge logits
     ``leaky_relu([h_src, h_dst] a, 0.2)``, softmax over each destination's in-edges, weighted sum.
-    ``heads`` > 1 (an extension; the reference layer is single-head) splits the channels into
-    independent heads.  The edge phase runs the fused kernels (forward and backward) when the shape
-    allows, else - or with ``fused=False`` - the reference's op-by-op pipeline on the per-edge
-    operators."""
+    Keyword-only extensions: ``heads`` > 1 splits the channels into independent heads (the reference
+    layer is single-head); ``tf32=False`` runs the transform in fp32; ``fused=False`` keeps the
+    reference's op-by-op pipeline on the per-edge operators, which also serves the shapes the fused
+    kernels (forward and backward) do not take."""
 
-    def __init__(self, in_channels, out_channels, heads=1, tf32=False, fused=True, **kwargs):
+    def __init__(self, in_channels, out_channels, e_num, improved=False, cached=False, add_self_loops=True,
+                 normalize=True, bias=True, *, heads=1, tf32=True, fused=True, **kwargs):
         super().__init__()
-        assert out_channels % heads == 0
+        if out_channels % heads:
+            raise ValueError(f"out_channels ({out_channels}) must be a multiple of heads ({heads})")
         self.in_channels, self.out_channels, self.heads, self.tf32 = in_channels, out_channels, heads, tf32
+        self.e_num, self.improved, self.cached = e_num, improved, cached
+        self.add_self_loops, self.normalize = add_self_loops, normalize
         self.fused = fused
         self.weight = torch.nn.Parameter(torch.empty(in_channels, out_channels))
         self.edge_weight = torch.nn.Parameter(torch.empty(2 * out_channels, 1))

@@ -3,7 +3,7 @@
 Same names, argument order and meaning as the reference operators, with
 ``torch.Tensor`` on a CUDA device in place of ``jittor.Var``.  Every operator
 calls a hand-written sm_100a kernel through the C ABI of ``libjgb200.so``; there
-is no CPU, eager or library fallback.
+is no CPU or eager fallback for any of them.
 """
 import os
 
@@ -245,7 +245,8 @@ def cootocsc(edge_index, edge_weight, v_num, sorted=False):
     return CSC(idx, off, w)
 
 
-def gcn_norm_csc_csr(edge_index, edge_weight, num_nodes, improved=False, want_csr=True, sorted=False):
+def gcn_norm_csc_csr(edge_index, edge_weight, num_nodes, improved=False, want_csr=True, sorted=False,
+                     add_self_loops=True):
     """``gcn_norm`` (nn/conv/gcn_conv.py:18-37) fused with ``cootocsc`` / ``cootocsr``: returns
     ``(CSC, CSR)`` of the self-looped, symmetrically normalised graph without building the
     normalised COO list (``CSR`` is ``None`` when ``want_csr`` is false)."""
@@ -261,7 +262,8 @@ def gcn_norm_csc_csr(edge_index, edge_weight, num_nodes, improved=False, want_cs
     csr = (mk_i(cap), mk_i(n + 1), mk_f(cap)) if want_csr else (None, None, None)
     count = torch.zeros(1, dtype=torch.int64, device=dev)
     ws = workspace(lib().jg_convert_workspace_bytes(E0, n), dev)
-    check(lib().jg_gcn_norm_compressed(ptr(ei), ptr(w), E0, n, 2.0 if improved else 1.0, 1 if sorted else 0,
+    check(lib().jg_gcn_norm_compressed(ptr(ei), ptr(w), E0, n, 2.0 if improved else 1.0, 1 if add_self_loops else 0,
+                                       1 if sorted else 0,
                                        ptr(csc[0]), ptr(csc[1]), ptr(csc[2]), ptr(csr[0]), ptr(csr[1]), ptr(csr[2]),
                                        ptr(count), ptr(ws), ws.numel(), stream_for(ei)), "jg_gcn_norm_compressed")
     E = int(count.item())  # one synchronisation per graph: the entry count sizes the views
@@ -270,9 +272,10 @@ def gcn_norm_csc_csr(edge_index, edge_weight, num_nodes, improved=False, want_cs
     return out_csc, out_csr
 
 
-def gcn_norm_coo(edge_index, edge_weight, num_nodes, improved=False):
+def gcn_norm_coo(edge_index, edge_weight, num_nodes, improved=False, add_self_loops=True):
     """``gcn_norm`` (nn/conv/gcn_conv.py:18-37) as the reference returns it: the COO list with
-    (v,v) entries removed, one loop per node appended, and symmetric-normalised weights."""
+    (v,v) entries removed, one loop per node appended, and symmetric-normalised weights;
+    ``add_self_loops=False`` normalises the list as given."""
     ei = _edge_index(edge_index)
     E0, n, dev = ei.shape[1], int(num_nodes), ei.device
     w = None if edge_weight is None else _as_f32(edge_weight, "edge_weight")
@@ -281,7 +284,8 @@ def gcn_norm_coo(edge_index, edge_weight, num_nodes, improved=False):
     ow = torch.empty(cap, dtype=torch.float32, device=dev)
     count = torch.zeros(1, dtype=torch.int64, device=dev)
     ws = workspace(lib().jg_gcn_norm_coo_workspace_bytes(E0, n), dev)
-    check(lib().jg_gcn_norm_coo(ptr(ei), ptr(w), E0, n, 2.0 if improved else 1.0, ptr(out[0]), ptr(out[1]), ptr(ow),
+    check(lib().jg_gcn_norm_coo(ptr(ei), ptr(w), E0, n, 2.0 if improved else 1.0, 1 if add_self_loops else 0,
+                                ptr(out[0]), ptr(out[1]), ptr(ow),
                                 ptr(count), ptr(ws), ws.numel(), stream_for(ei)), "jg_gcn_norm_coo")
     E = int(count.item())
     return out[:, :E].contiguous(), ow[:E]
@@ -309,9 +313,12 @@ def toUndirected(edge_index, edge_attr, num_nodes):
 # ------------------------------------------------------------------------------ SpMM front ends
 def _csr_rows(csr):
     """Source of every CSR entry (row ids expanded from the offsets)."""
-    n = csr.row_offset.numel() - 1
-    counts = (csr.row_offset[1:] - csr.row_offset[:-1]).long()
-    return torch.repeat_interleave(torch.arange(n, dtype=torch.int32, device=counts.device), counts)
+    off = _as_i32(csr.row_offset, "row_offset")
+    n = off.numel() - 1
+    out = torch.empty(csr.column_indices.numel(), dtype=torch.int32, device=off.device)
+    if out.numel():
+        check(lib().jg_expand_columns(ptr(off), n, None, ptr(out), stream_for(off)), "jg_expand_columns")
+    return out
 
 
 def _transposed_of(csr, n_cols=None):

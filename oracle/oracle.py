@@ -295,16 +295,18 @@ def check_sample(fanout, dst, layer_off, layer_idx, g_off, g_idx):
 
 
 # --------------------------------------------------------------------- gcn_norm
-def gcn_norm(edge_index, w, n):
+def gcn_norm(edge_index, w, n, add_self_loops=True):
     """C restatement of gcn_norm + add_remaining_self_loops
-    (nn/conv/gcn_conv.py:18-37, utils/loop.py:120-134) -> (edge_index[2,E], w[E])."""
+    (nn/conv/gcn_conv.py:18-37, utils/loop.py:120-134) -> (edge_index[2,E], w[E]).  A node without
+    in-edges has degree 0 and deg^-1/2 = inf there, as in the reference (its ``masked_fill`` result
+    is discarded, nn/conv/gcn_conv.py:36); this only arises with ``add_self_loops=False``."""
     ei = _i32(edge_index)
     E0 = ei.shape[1]
     s, d = _i32(ei[0]), _i32(ei[1])
     w = None if w is None else _f32(w)
     os_, od, ow = np.zeros(E0 + n, np.int32), np.zeros(E0 + n, np.int32), np.zeros(E0 + n, np.float32)
     E = port_lib().orc_gcn_norm(_ip(s), _ip(d), _fp(w), L(E0), ctypes.c_int32(n), _ip(os_), _ip(od),
-                                _fp(ow))
+                                _fp(ow), ctypes.c_int(1 if add_self_loops else 0))
     return np.stack([os_[:E], od[:E]]), ow[:E].copy()
 
 

@@ -179,23 +179,34 @@ void orc_gat_aggregate(float* out, const float* h, const float* a_src, const flo
  * (capacity E0 + n).  deg[dst] accumulates in list order; weights are
  * (dis[src] * w) * dis[dst] with dis = deg^-1/2 in fp32.  Returns E. */
 int64_t orc_gcn_norm(const int32_t* src, const int32_t* dst, const float* w, int64_t E0, int32_t n,
-                     int32_t* out_src, int32_t* out_dst, float* out_w) {
+                     int32_t* out_src, int32_t* out_dst, float* out_w, int add_self_loops) {
     int64_t m = 0;
-    for (int64_t i = 0; i < E0; i++)
-        if (src[i] != dst[i]) {
-            out_src[m] = src[i];
-            out_dst[m] = dst[i];
-            out_w[m] = w ? w[i] : 1.0f;
-            m++;
+    int64_t E;
+    if (add_self_loops) {
+        for (int64_t i = 0; i < E0; i++)
+            if (src[i] != dst[i]) {
+                out_src[m] = src[i];
+                out_dst[m] = dst[i];
+                out_w[m] = w ? w[i] : 1.0f;
+                m++;
+            }
+        for (int32_t v = 0; v < n; v++) {
+            out_src[m + v] = v;
+            out_dst[m + v] = v;
+            out_w[m + v] = 1.0f;
         }
-    for (int32_t v = 0; v < n; v++) {
-        out_src[m + v] = v;
-        out_dst[m + v] = v;
-        out_w[m + v] = 1.0f;
+        for (int64_t i = 0; i < E0; i++)
+            if (src[i] == dst[i]) out_w[m + src[i]] = w ? w[i] : 1.0f;
+        E = m + n;
+    } else {
+        /* add_self_loops=False (nn/conv/gcn_conv.py:25): the list is normalised as given */
+        for (int64_t i = 0; i < E0; i++) {
+            out_src[i] = src[i];
+            out_dst[i] = dst[i];
+            out_w[i] = w ? w[i] : 1.0f;
+        }
+        E = E0;
     }
-    for (int64_t i = 0; i < E0; i++)
-        if (src[i] == dst[i]) out_w[m + src[i]] = w ? w[i] : 1.0f;
-    int64_t E = m + n;
     float* deg = (float*)calloc((size_t)(n > 0 ? n : 1), sizeof(float));
     for (int64_t i = 0; i < E; i++) deg[out_dst[i]] += out_w[i];
     for (int32_t v = 0; v < n; v++) deg[v] = powf(deg[v], -0.5f);

@@ -204,7 +204,7 @@ def test_gat_layer_fused_and_unfused_agree(cuda):
     n = 500
     idx, off = random_csc(rng, n, 6000)
     csc = cuda.CSC(dev(idx), dev(off), None)
-    layer = nn.GATConv(40, 64, heads=8).cuda()
+    layer = nn.GATConv(40, 64, 0, heads=8, tf32=False).cuda()
     x = torch.randn(n, 40, device="cuda")
     with torch.no_grad():
         fused = layer(x, csc)
@@ -299,42 +299,130 @@ def test_gcn_norm_coo_list(cuda, oracle):
         assert np.abs(host(gw).view(np.int32).astype(np.int64) - ww.view(np.int32).astype(np.int64)).max() <= 4
 
 
+def test_gcn_norm_without_self_loops(cuda, oracle):
+    """``gcn_norm(add_self_loops=False)`` (nn/conv/gcn_conv.py:18-37): the list as given, weights scaled by
+    the weighted in-degrees; also through the fused conversion."""
+    from jittorgeometric_b200 import nn
+    rng = np.random.default_rng(9)
+    n, E = 2000, 30000
+    ei = np.minimum((rng.random((2, E)) ** 2 * n).astype(np.int32), n - 1)
+    ei[1, :n] = np.arange(n)                                   # every node has an in-edge: finite weights
+    for w in (None, rng.random(E).astype(np.float32) + 0.1):
+        gei, gw = nn.gcn_norm(dev(ei), None if w is None else dev(w), n, add_self_loops=False)
+        wei, ww = oracle.gcn_norm(ei, w, n, add_self_loops=False)
+        assert np.array_equal(host(gei), ei) and np.array_equal(wei, ei)
+        assert np.abs(host(gw).view(np.int32).astype(np.int64) - ww.view(np.int32).astype(np.int64)).max() <= 4
+        csc, csr = cuda.gcn_norm_csc_csr(dev(ei), None if w is None else dev(w), n, add_self_loops=False)
+        ri, co, cw = oracle.coo_to_csc(wei, ww, n)
+        assert np.array_equal(host(csc.row_indices), ri) and np.array_equal(host(csc.column_offset), co)
+        assert np.abs(host(csc.edge_weight).view(np.int32).astype(np.int64) - cw.view(np.int32).astype(np.int64)).max() <= 4
+        ci, ro, rw = oracle.coo_to_csr(wei, ww, n)
+        assert np.array_equal(host(csr.column_indices), ci) and np.array_equal(host(csr.row_offset), ro)
+
+
 def test_gcn_layers_on_citation_graph(cuda, oracle):
-    """Two-layer GCN forward + backward on the 2708-node instance against numpy with the checker's
-    aggregation; SGConv and APPNP against their compositions."""
+    """Two-layer GCN forward + loss + backward on the 2708-node instance (layers 1433 -> 256 -> 7, fp32
+    transform): the forward and all five gradients (both weights, both biases, the input) against
+    float64 and against the reference recipe (numpy fp32 products + the checker's aggregation)."""
     from jittorgeometric_b200 import nn, synth
     d = load("citation_2708")
     n = 2708
     csc, csr = cuda.gcn_norm_csc_csr(dev(d["edge_index"]), None, n)
     x = synth.sparse_binary_features(n, 1433, 18, seed=3).numpy()
     torch.manual_seed(1)
-    c1, c2 = nn.GCNConv(1433, 256).cuda(), nn.GCNConv(256, 7).cuda()
+    c1, c2 = nn.GCNConv(1433, 256, tf32=False).cuda(), nn.GCNConv(256, 7, tf32=False).cuda()
+    with torch.no_grad():                                       # non-zero biases, so that their path is exercised
+        c1.bias.copy_(torch.linspace(-0.05, 0.05, 256)); c2.bias.copy_(torch.linspace(-0.1, 0.1, 7))
     labels = torch.randint(7, (n,), generator=torch.Generator().manual_seed(2)).cuda()
     xt = dev(x).requires_grad_(True)
     out = c2(torch.relu(c1(xt, csc, csr)), csc, csr)
     loss = torch.nn.functional.cross_entropy(out, labels)
     loss.backward()
-    # numpy forward with the checker's aggregation on the library's own CSC (weights within ulps of the checker's)
     ci, co, cw = host(csc.row_indices), host(csc.column_offset), host(csc.edge_weight)
     ri, ro, rw = host(csr.column_indices), host(csr.row_offset), host(csr.edge_weight)
-    W1, W2 = host(c1.weight), host(c2.weight)
-    h1 = oracle.aggregate((x @ W1).astype(np.float32), ci, co, cw)
-    z = oracle.aggregate((np.maximum(h1, 0) @ W2).astype(np.float32), ci, co, cw)
-    assert np.abs(host(out) - z).max() <= 2e-3 * (np.abs(z).max() + 1)     # dense products: TF32-free fp32 matmul vs numpy
-    # backward through the aggregation: dL/d(xW) = A^T-aggregate of dL/dout, i.e. the CSR pass
+    W1, b1, W2, b2, lab = host(c1.weight), host(c1.bias), host(c2.weight), host(c2.bias), host(labels)
+
+    # float64 truth by dense autograd
+    A = torch.zeros((n, n), dtype=torch.float64)
+    A.index_put_((torch.from_numpy(np.repeat(np.arange(n), np.diff(co))), torch.from_numpy(ci.astype(np.int64))),
+                 torch.from_numpy(cw.astype(np.float64)), accumulate=True)
+    P = [torch.from_numpy(a.astype(np.float64)).requires_grad_(True) for a in (x, W1, b1, W2, b2)]
+    h64 = torch.relu(A @ (P[0] @ P[1]) + P[2])
+    z64 = A @ (h64 @ P[3]) + P[4]
+    l64 = torch.nn.functional.cross_entropy(z64, torch.from_numpy(lab))
+    g64 = [g.numpy() for g in torch.autograd.grad(l64, P)]
+    # error scale of the forward: the same network on absolute values
+    Aabs = A.abs()
+    s1 = Aabs @ (torch.from_numpy(np.abs(x).astype(np.float64)) @ P[1].detach().abs()) + P[2].detach().abs()
+    s2 = (Aabs @ (s1 @ P[3].detach().abs()) + P[4].detach().abs()).numpy()
+    assert (np.abs(host(out) - z64.detach().numpy()) / s2).max() <= 1e-5
+    assert abs(float(loss) - float(l64)) <= 1e-5 * abs(float(l64))
+
+    # the reference recipe in fp32: numpy products, the checker's aggregation (CSC forward, CSR backward)
+    h1 = oracle.aggregate((x @ W1).astype(np.float32), ci, co, cw) + b1
+    hr = np.maximum(h1, 0)
+    z = oracle.aggregate((hr @ W2).astype(np.float32), ci, co, cw) + b2
     p = np.exp(z - z.max(1, keepdims=True)); p /= p.sum(1, keepdims=True)
-    gz = p.copy(); gz[np.arange(n), host(labels)] -= 1; gz /= n
-    g_hw2 = oracle.aggregate(gz.astype(np.float32), ri, ro, rw)
-    gW2 = np.maximum(h1, 0).T @ g_hw2
-    assert np.abs(host(c2.weight.grad) - gW2).max() <= 2e-3 * (np.abs(gW2).max() + 1e-6)
-    assert xt.grad is not None and torch.isfinite(xt.grad).all()
+    gz = p.copy(); gz[np.arange(n), lab] -= 1; gz /= n
+    g2 = oracle.aggregate(gz.astype(np.float32), ri, ro, rw)
+    gh1 = ((g2 @ W2.T) * (h1 > 0)).astype(np.float32)
+    g1 = oracle.aggregate(gh1, ri, ro, rw)
+    want = {"x": g1 @ W1.T, "W1": x.T @ g1, "b1": gh1.sum(0), "W2": hr.T @ g2, "b2": gz.sum(0)}
+    have = {"x": host(xt.grad), "W1": host(c1.weight.grad), "b1": host(c1.bias.grad), "W2": host(c2.weight.grad),
+            "b2": host(c2.bias.grad)}
+    truth = dict(zip(("x", "W1", "b1", "W2", "b2"), g64))
+    assert np.abs(host(out) - z).max() <= 1e-5 * np.abs(z).max()
+    for name in ("x", "W1", "b1", "W2", "b2"):
+        top = np.abs(truth[name]).max()
+        assert have[name].shape == truth[name].shape, name
+        assert np.abs(have[name] - truth[name]).max() <= 1e-5 * top, (name, "vs float64")
+        assert np.abs(have[name] - want[name]).max() <= 2e-5 * top, (name, "vs the reference recipe in fp32")
+
+
+def test_sgconv_appnp_against_checker(cuda, oracle):
+    """``SGConv`` (nn/conv/sg_conv.py:62-70) and ``APPNP`` (nn/conv/appnp_conv.py:42-52) against the same
+    compositions built from the CPU checker's aggregation."""
+    from jittorgeometric_b200 import nn
+    d = load("citation_2708")
+    n = 2708
+    csc, csr = cuda.gcn_norm_csc_csr(dev(d["edge_index"]), None, n)
+    ci, co, cw = host(csc.row_indices), host(csc.column_offset), host(csc.edge_weight)
+    f = np.random.default_rng(4).standard_normal((n, 16)).astype(np.float32)
+    _, scale = oracle.aggregate_f64(np.abs(f), ci, co, cw)
     with torch.no_grad():
-        f = torch.randn(n, 16, device="cuda")
+        torch.manual_seed(3)
         sg = nn.SGConv(16, 5, K=2).cuda()
-        a1 = cuda.aggregateWithWeight(cuda.aggregateWithWeight(f, csc, csr), csc, csr)
-        assert torch.allclose(sg(f, csc, csr), sg.lin(a1))
+        a2 = oracle.aggregate(oracle.aggregate(f, ci, co, cw), ci, co, cw)
+        want = a2 @ host(sg.lin.weight).T + host(sg.lin.bias)
+        assert np.abs(host(sg(dev(f), csc, csr)) - want).max() <= 1e-5 * (np.abs(a2).max() * 16 + 1)
         ap = nn.APPNP(K=3, alpha=0.1)
         want = f
         for _ in range(3):
-            want = cuda.aggregateWithWeight(want, csc, csr) * 0.9 + 0.1 * f
-        assert torch.allclose(ap(f, csc, csr), want)
+            want = oracle.aggregate(want, ci, co, cw) * np.float32(0.9) + np.float32(0.1) * f
+        assert (np.abs(host(ap(dev(f), csc, csr)) - want) / (scale + np.abs(f) + 1e-30)).max() <= 1e-5
+
+
+def test_gatconv_takes_the_reference_constructor_call(cuda, oracle):
+    """The reference's own call, ``GATConv(num_features, 128, e_num, cached=True, normalize=...)``
+    (examples/gat_example.py:96-99, nn/conv/gat_conv.py:27-30): ``e_num`` is accepted and unused, the
+    layer is single-head, and its forward equals the reference's op-by-op pipeline."""
+    from jittorgeometric_b200 import nn
+    d = load("citation_2708")
+    n = 2708
+    csc = cuda.cootocsc(dev(d["edge_index"]), None, n)
+    e_num = d["edge_index"].shape[1]
+    torch.manual_seed(5)
+    conv1 = nn.GATConv(64, 128, e_num, cached=True, normalize=True).cuda()
+    conv2 = nn.GATConv(128, 7, e_num, cached=True, normalize=True).cuda()
+    assert conv1.heads == 1 and conv2.heads == 1
+    x = np.random.default_rng(6).standard_normal((n, 64)).astype(np.float32)
+    with torch.no_grad():
+        y1 = conv1(dev(x), csc)
+        y2 = conv2(torch.relu(y1), csc)
+    assert y1.shape == (n, 128) and y2.shape == (n, 7)
+    ri, co = host(csc.row_indices), host(csc.column_offset)
+    h = np.maximum(x @ host(conv1.weight), 0).astype(np.float32)
+    want = oracle.gat_unfused(h, host(conv1.edge_weight)[:, 0], ri, co)
+    assert np.abs(host(y1) - want).max() <= 1e-5 * (np.abs(want).max() + 1e-30) + 1e-6
+    with pytest.raises(TypeError):
+        nn.GATConv(64, 128)                                    # e_num is positional and required, as in the reference

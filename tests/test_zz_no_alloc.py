@@ -47,9 +47,13 @@ def test_static_scratch_matches_workspace_entry_point_twice(cuda, oracle, f):
         got, want = got.cpu().numpy(), want.cpu().numpy()
         _, scale = oracle.aggregate_f64(x, idx, off, w, n_out=n_out)
         assert float((np.abs(got - want) / (scale + 1e-30)).max()) <= 1e-5, f"call {call}"
+        # and against the CPU checker itself (the reference's sequential loop), not only the sibling entry point
+        ref = oracle.aggregate(x, idx, off, w, n_out=n_out)
+        assert float((np.abs(got - ref) / (scale + 1e-30)).max()) <= 1e-5, f"call {call} vs the CPU checker"
         short = np.diff(off) <= 1024                      # unsplit rows: identical summation order
         if f >= 128 or f % 4:
             assert np.array_equal(got[short], want[short]), f"call {call}"
+            assert np.array_equal(got[short], ref[short]), f"call {call} vs the CPU checker"
 
 
 def test_static_scratch_rejects_sizes_beyond_its_capacity(cuda):
