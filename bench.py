@@ -46,7 +46,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(self.index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
             self.t.start()
@@ -98,13 +98,28 @@ def build_graph(device, scale=21, edge_factor=32):
     return jg.CSC(src.contiguous(), off, w.contiguous()), n
 
 
-def measured_traffic(args, nnz):
-    """DRAM bytes (read + write) of the four aggregation launches of one default step, from the ncu
-    capture summarised in profiles/aggregate_rows_kernel_spmm_sweep_scale21.md; None for any other
-    workload size."""
-    if args.scale == 21 and args.edge_factor == 32 and tuple(WIDTHS) == (32, 64, 128, 256) and nnz == 125548660:
-        return 2757975808 + 273128704 + 6993170176 + 572856320 + 19284060160 + 1193964288 + 51131966464 + 2204640768
-    return None
+def measured_traffic(nnz, widths):
+    """DRAM bytes (read + write) per aggregation launch at each width, from the committed table of ncu
+    counters (``dram__bytes_read.sum + dram__bytes_write.sum``, one capture at full size).  The record is
+    used only for the workload it was taken on (same nonzero count) and only while the kernel source
+    it was taken with is unchanged; otherwise there is no traffic figure (``None``)."""
+    import hashlib
+    table = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    src = os.path.join(ROOT, "jittorgeometric_b200", "csrc", "spmm.cu")
+    try:
+        rec = json.load(open(table))["aggregate_rows_kernel"]["spmm_sweep"]
+        sha = hashlib.sha256(open(src, "rb").read()).hexdigest()
+    except (OSError, KeyError, ValueError):
+        return None
+    if rec.get("nnz") != nnz or rec.get("source_sha256") != sha:
+        return None
+    out = {}
+    for f in widths:
+        b = rec.get("bytes", {}).get(str(f))
+        if b is None:
+            return None
+        out[f] = int(b)
+    return out
 
 
 def alg_bytes(nnz, n, f):
@@ -113,7 +128,12 @@ def alg_bytes(nnz, n, f):
     return nnz * (4 + 4 + 4 * f) + 4 * (n + 1) + 4 * n * f
 
 
-def cpu_reference_sample(csc, n, widths, budget_s):
+def min_bytes(nnz, n, f):
+    """Compulsory bytes: every index and weight once, X read once, Y written once."""
+    return 8 * nnz + 4 * (n + 1) + 8 * n * f
+
+
+def cpu_reference_sample(csc, n, widths, budget_s, xs=None, ys=None):
     """Times the reference's own CPU aggregation (compiled reference body when present,
     else the C restatement) on the first rows of the same CSC: a bounded sample."""
     import numpy as np
@@ -125,8 +145,10 @@ def cpu_reference_sample(csc, n, widths, budget_s):
     rng = np.random.default_rng(SEED)
     per_width = budget_s / len(widths)
     done_ef, done_t, rows_used = 0.0, 0.0, []
+    parity = {}
     for f in widths:
-        x = rng.standard_normal((n, f), dtype=np.float32)
+        # the GPU run's own X when there is one, so that the two results can be compared
+        x = rng.standard_normal((n, f), dtype=np.float32) if xs is None else xs[f].cpu().numpy()
         # calibrate on 20k rows, then size the sample for the per-width budget
         r0 = min(n, 20000)
         t0 = time.perf_counter()
@@ -137,12 +159,29 @@ def cpu_reference_sample(csc, n, widths, budget_s):
         r = int(np.searchsorted(off, min(target, int(off[-1])), side="left"))
         r = max(min(r, n), r0)
         t0 = time.perf_counter()
-        _sample_aggregate(O, impl, x, idx_all, off, w_all, r)
+        want = _sample_aggregate(O, impl, x, idx_all, off, w_all, r)
         dt = time.perf_counter() - t0
         done_ef += float(off[r]) * f
         done_t += dt
         rows_used.append(r)
-    return {"value": done_ef / done_t, "unit": "edge*feat/s", "cores": 1,
+        if ys is not None:
+            # full-size parity: the GPU's rows [0, r) of this width against the CPU result on the same X;
+            # error scale = sum |w x| per element (float64 on the GPU, sampled rows only)
+            got = ys[f][:r].cpu().numpy()
+            e = int(off[r])
+            dev = ys[f].device
+            seg = torch.repeat_interleave(torch.arange(r, device=dev), (csc.column_offset[1:r + 1] - csc.column_offset[:r]).long())
+            scale = torch.zeros((r, f), dtype=torch.float64, device=dev)
+            step = (1 << 27) // f
+            for a in range(0, e, step):
+                b = min(e, a + step)
+                term = (xs[f][csc.row_indices[a:b].long()].double() * csc.edge_weight[a:b].double().unsqueeze(1)).abs()
+                scale.index_add_(0, seg[a:b], term)
+            err = np.abs(got - want) / (scale.cpu().numpy() + 1e-30)
+            parity[str(f)] = {"rows": r, "max_rel_err": float(err.max()),
+                              "bit_identical_rows": int((got == want).all(axis=1).sum())}
+            del scale, seg
+    return {"value": done_ef / done_t, "unit": "edge*feat/s", "cores": 1, "parity": parity or None,
             "kind": "reference" if impl == "ref" else "port",
             "sample": f"first {rows_used} destination rows of the same CSC at widths {list(widths)}; "
                       f"{done_t:.1f} s of single-thread CPU work (the reference loop is single-threaded)",
@@ -246,14 +285,23 @@ def run_single(args):
     per_f = {f: sum(e[f][0].elapsed_time(e[f][1]) for e in evs) / args.steps for f in WIDTHS}
 
     peak, peak_kind = measured_peaks()
+    traffic = measured_traffic(nnz, WIDTHS)
     sweep = {}
     for f in WIDTHS:
-        b = alg_bytes(nnz, n, f)
-        sweep[str(f)] = {"ms": per_f[f], "gflops": 2.0 * nnz * f / per_f[f] / 1e6,
-                         "alg_gbs": b / per_f[f] / 1e6, "frac_of_hbm_peak": b / per_f[f] / 1e6 / peak}
+        b, bm = alg_bytes(nnz, n, f), min_bytes(nnz, n, f)
+        t = per_f[f]
+        sweep[str(f)] = {"ms": t, "gflops": 2.0 * nnz * f / t / 1e6,
+                         "dram_gbs": traffic[f] / t / 1e6 if traffic else None,
+                         "frac": traffic[f] / t / 1e6 / peak if traffic else None,
+                         "traffic": traffic[f] if traffic else None,
+                         "traffic_over_compulsory": traffic[f] / bm if traffic else None,
+                         "model_gbs": b / t / 1e6, "model_frac": b / t / 1e6 / peak,
+                         "min_gbs": bm / t / 1e6, "min_frac": bm / t / 1e6 / peak}
     total_bytes = sum(alg_bytes(nnz, n, f) for f in WIDTHS)
+    total_min = sum(min_bytes(nnz, n, f) for f in WIDTHS)
+    total_traffic = sum(traffic.values()) if traffic else None
     kernel_ms = sum(per_f.values())
-    achieved = total_bytes / kernel_ms / 1e6
+    achieved = total_traffic / kernel_ms / 1e6 if traffic else None
     value = nnz * sum(WIDTHS) / (ms_step * 1e-3)
 
     # end to end through the public API with host buffers: X from pinned host memory, Y back to pinned host memory
@@ -305,7 +353,8 @@ def run_single(args):
         e2e_ms = t0.elapsed_time(t1) / e2e_steps
     io_bytes = sum(n * f * 4 for f in WIDTHS)
 
-    cpu = cpu_reference_sample(csc, n, WIDTHS, budget_s=args.cpu_budget) if args.cpu_budget > 0 else None
+    cpu = cpu_reference_sample(csc, n, WIDTHS, budget_s=args.cpu_budget, xs=xs, ys=ys) if args.cpu_budget > 0 else None
+    parity = cpu.pop("parity") if cpu else None
     line = {
         "metric": "spmm_edge_feat_per_s", "value": value, "unit": "edge*feat/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -313,19 +362,34 @@ def run_single(args):
         "config": workload_config(args.scale, args.edge_factor, n, nnz, 1),
         "gflops": 2.0 * value / 1e9,
         "sweep": sweep,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": measured_traffic(args, nnz), "peak_kind": peak_kind, "kernel": "aggregate_rows_kernel",
-                     "note": "algorithmic bytes = no-reuse gather model (index + weight + one source row per nonzero, "
-                             "output written once) summed over the four widths / summed launch time; hub source rows "
-                             "hit in L2, so real DRAM traffic (`traffic`, ncu, summed over the same four launches) is "
-                             "lower and the model figure can exceed the HBM peak",
-                     "dram_gbs": (measured_traffic(args, nnz) or 0) / kernel_ms / 1e6 or None},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak if achieved else None, "traffic": total_traffic, "peak_kind": peak_kind,
+                     "kernel": "aggregate_rows_kernel",
+                     "model_gbs": total_bytes / kernel_ms / 1e6, "model_frac": total_bytes / kernel_ms / 1e6 / peak,
+                     "min_gbs": total_min / kernel_ms / 1e6, "min_frac": total_min / kernel_ms / 1e6 / peak,
+                     "note": "achieved / frac = DRAM bytes the four aggregation launches really move (ncu dram__bytes read + "
+                             "write, one capture at full size, kept as a table beside the ncu summaries and dropped when the "
+                             "kernel source changes) / CUDA-event time of the same launches, summed over the widths; model_* = "
+                             "no-reuse gather model (index + weight + one source row per nonzero, output written once), which "
+                             "counts L2 hits as DRAM bytes and can exceed the peak; min_* = compulsory bytes"},
         "cpu_baseline": cpu,
-        "e2e": {"value": nnz * sum(WIDTHS) / (e2e_ms * 1e-3), "unit": "edge*feat/s", "ms_per_step": e2e_ms,
+        "parity": parity,
+        "parity_ok": bool(parity) and all(v["max_rel_err"] <= 1e-5 for v in parity.values()),
+        "e2e": {"value": nnz * sum(WIDTHS) / (e2e_ms * 1e-3), "unit": "edge*feat/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
                 "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes},
         "gpu_launches": args.steps * len(WIDTHS) * 2,
         "clocks": clocks,
     }
+    # free the sweep before the other workloads are built
+    del xs, ys, dx, hx, hy, csc, plan
+    torch.cuda.empty_cache()
+    if not args.skip_secondary:
+        import bench_extra
+        line["secondary"] = bench_extra.secondary(args)
+    if args.gcn_scale > 0:
+        import bench_dist
+        torch.cuda.empty_cache()
+        line["gcn_forward"] = bench_dist.gcn_forward_record(args, dev, 0, 1, ClockSampler)
     print(json.dumps(line))
 
 
@@ -342,6 +406,12 @@ def main():
                     help="spmm (default, the headline) or one of the other hot-path workloads (1 GPU; gcn also N > 1)")
     ap.add_argument("--widths", default=None, help="comma-separated subset of the sweep (profiling runs)")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--skip-secondary", action="store_true", help="skip the secondary workloads of the default line")
+    ap.add_argument("--exchange", default="direct", choices=["direct", "nccl"],
+                    help="N > 1: halo rows pulled out of peer memory (default) or packed + one NCCL all-to-all")
+    ap.add_argument("--gcn-scale", type=int, default=26, help="R-MAT scale of the gcn_forward sub-record (0 = skip)")
+    ap.add_argument("--gcn-steps", type=int, default=5)
+    ap.add_argument("--gcn-warmup", type=int, default=3)
     args = ap.parse_args()
     global WIDTHS
     if args.widths:
@@ -357,8 +427,8 @@ def main():
         return bench_extra.run(args)
     if args.gpus == 1:
         return run_single(args)
-    from jittorgeometric_b200 import dist_bench
-    return dist_bench.run(args)
+    import bench_dist
+    return bench_dist.run(args)
 
 
 if __name__ == "__main__":

@@ -33,7 +33,7 @@ def _line(args, metric, unit, value, ms, workload, roofline, extra):
             "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": workload},
             "roofline": roofline}
     line.update(extra)
-    print(json.dumps(line))
+    return line
 
 
 def run_convert(args):
@@ -70,7 +70,7 @@ def run_convert(args):
         cpu = {"value": sub / dt, "unit": "edge/s", "cores": 1, "kind": "reference" if impl == "ref" else "port",
                "sample": f"first {sub} input edges of the same list, gcn_norm (C restatement) + the reference's "
                          f"cootocsc and cootocsr bodies, {dt:.1f} s, single thread"}
-    _line(args, "coo_to_csc_csr_edges_per_s", "edge/s", E0 / (ms * 1e-3), ms,
+    return _line(args, "coo_to_csc_csr_edges_per_s", "edge/s", E0 / (ms * 1e-3), ms,
           f"gcn_norm + COO->CSC + COO->CSR: R-MAT scale {scale}, edge factor 16, {E0} shuffled input edges, "
           f"{n} nodes, unit weights, int32; entry order bit-exact with the reference",
           {"bound": "hbm", "achieved": alg / ms / 1e6, "peak": peak, "unit": "GB/s", "frac": alg / ms / 1e6 / peak,
@@ -141,7 +141,7 @@ def run_gat(args):
         cpu = {"value": int(off[r]) / dt, "unit": "edge/s", "cores": 1, "kind": "reference" if O.have_ref() else "port",
                "sample": f"in-edges of the first {r} destinations ({int(off[r])} edges), ONE head of width 8 through the "
                          f"reference's unfused op-by-op pipeline, {dt:.1f} s, single thread (x8 heads for the full layer)"}
-    _line(args, "gat_edge_phase_edges_per_s", "edge/s", E / (ms_edge * 1e-3), ms_edge,
+    return _line(args, "gat_edge_phase_edges_per_s", "edge/s", E / (ms_edge * 1e-3), ms_edge,
           f"attention layer 8 heads x 8, LeakyReLU 0.2: {n} nodes, {E} in-edges (log-normal degrees, mean "
           f"{E / n:.0f}), input width {fin}; fused logits + softmax + aggregation over CSC",
           {"bound": "hbm", "achieved": alg / ms_edge / 1e6, "peak": peak, "unit": "GB/s", "frac": alg / ms_edge / 1e6 / peak,
@@ -171,7 +171,7 @@ def run_gemm(args):
                            "tflops": 2.0 * n * k * m / ms / 1e9, "library_fp32_ms": ms_lib}
         del x
     first = res["128x128"]
-    _line(args, "dense_transform_rows_per_s", "row/s", n / (first["ms"] * 1e-3), first["ms"],
+    return _line(args, "dense_transform_rows_per_s", "row/s", n / (first["ms"] * 1e-3), first["ms"],
           f"dense feature transform H = X W, {n} rows, TF32 products with fp32 accumulation on tcgen05; shapes 128->128, "
           "128->64, 256->64",
           {"bound": "hbm", "achieved": first["gbs"], "peak": peak, "unit": "GB/s", "frac": first["frac_of_hbm_peak"],
@@ -181,79 +181,26 @@ def run_gemm(args):
 
 
 def run_gcn(args):
-    """Two-layer GCN forward (width 128 -> 128 -> 64) on one GPU or row-partitioned over N GPUs."""
+    """Two-layer GCN forward (width 128 -> 128 -> 64) on one GPU or row-partitioned over N GPUs, at
+    ``--scale`` (22 when left at the default): the ``gcn_forward`` record of the default line, alone."""
     import torch.distributed as dist
-    import jittorgeometric_b200 as jg
-    from jittorgeometric_b200 import dist as jd, synth
+    import bench_dist
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
     if world > 1:
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
-    scale = 22 if args.scale == 21 else args.scale
-    ei, n = synth.rmat_graph(scale, 8, bench.SEED + 4, device=dev)      # 8 undirected pairs per node -> factor 16 directed
-    csc, _ = jg.gcn_norm_csc_csr(ei, None, n, want_csr=False)
-    del ei
-    csc = jg.CSC(csc.row_indices.clone(), csc.column_offset, csc.edge_weight.clone())   # drop the capacity-sized buffers
-    torch.cuda.empty_cache()
-    nnz = csc.row_indices.numel()
-    part = jd.RowPartition(n, world)
-    W1, W2 = synth.glorot((128, 128), 1, dev), synth.glorot((128, 64), 2, dev)
-    W1t, W2t = W1.t().contiguous(), W2.t().contiguous()
-    b1, b2 = torch.zeros(128, device=dev), torch.zeros(64, device=dev)
-    if world > 1:
-        g = jd.ShardedGraph(part, rank, *jd.shard_rows(csc.row_indices, csc.column_offset, csc.edge_weight, part, rank),
-                            exchange=os.environ.get("JG_EXCHANGE", "peer"), mode=os.environ.get("JG_DIST_MODE", "merged"))
-        del csc
-        n_local = g.n_local
-    else:
-        plan = jg.SpmmPlan(csc.column_offset, nnz)
-        n_local = n
-    x = torch.randn((n_local, 128), device=dev, generator=torch.Generator(device=dev).manual_seed(9 + rank))
-
-    def forward():
-        if world > 1:
-            z1 = g.aggregate(jg.linear_tf32(x, W1, weight_t=W1t), bias=b1, relu=True)
-            return g.aggregate(jg.linear_tf32(z1, W2, weight_t=W2t), bias=b2)
-        h1 = jg.linear_tf32(x, W1, weight_t=W1t)
-        z1 = jg.segment_aggregate(h1, csc.row_indices, csc.column_offset, csc.edge_weight, plan=plan, bias=b1, relu=True)
-        del h1
-        h2 = jg.linear_tf32(z1, W2, weight_t=W2t)
-        del z1
-        return jg.segment_aggregate(h2, csc.row_indices, csc.column_offset, csc.edge_weight, plan=plan, bias=b2)
-
-    for _ in range(args.warmup):
-        forward()
-    torch.cuda.synchronize()
+        args.exchange = bench_dist.pick_exchange(args, dev)
+    args.gcn_scale = 22 if args.scale == 21 else args.scale
+    args.gcn_steps, args.gcn_warmup = args.steps, args.warmup
+    rec = bench_dist.gcn_forward_record(args, dev, rank, world, bench.ClockSampler)
     if world > 1:
         dist.barrier()
-    a, b = _events()
-    torch.cuda.synchronize()
-    a.record()
-    for _ in range(args.steps):
-        forward()
-    b.record()
-    torch.cuda.synchronize()
-    ms = torch.tensor([a.elapsed_time(b) / args.steps], device=dev)
-    if world > 1:
-        dist.barrier()
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms = float(ms.item())
-    if rank == 0:
-        peak, kind = bench.measured_peaks()
-        alg = sum(nnz * (8 + 4 * f) + 4 * (n + 1) + 4 * n * f for f in (128, 64)) + 4 * n * (128 + 128) + 4 * n * (128 + 64)
-        args.gpus = world
-        _line(args, "gcn_forward_edge_feat_per_s", "edge*feat/s", nnz * (128 + 64) / (ms * 1e-3), ms,
-              f"2-layer GCN forward 128->128->64 (TF32 transform, fp32 aggregation): R-MAT scale {scale}, {n} nodes, "
-              f"{nnz} directed edges incl. self-loops, gcn_norm weights; {world} destination-row shard(s)",
-              {"bound": "hbm", "achieved": alg / world / ms / 1e6, "peak": peak, "unit": "GB/s",
-               "frac": alg / world / ms / 1e6 / peak, "traffic": None, "peak_kind": kind, "kernel": "aggregate_rows_kernel",
-               "note": "per-GPU algorithmic bytes of both aggregations and both transforms over the whole forward"},
-              {"gpu_launches": args.steps * (6 if world == 1 else 10),
-               "peak_device_memory_gb": torch.cuda.max_memory_allocated(dev) / 1e9})
-    if world > 1:
         dist.destroy_process_group()
+    return rec
 
 
 def run_sample(args):
@@ -303,7 +250,7 @@ def run_sample(args):
             cpu = {"value": drawn / dt, "unit": "edge/s", "cores": 1, "kind": "reference",
                    "sample": f"one batch: the reference's sampleprocessing CPU body for both layers ({drawn} sampled edges, "
                              f"{dt * 1e3:.1f} ms); its Python merge loops over nodes are not included"}
-    _line(args, "sampled_edges_per_s", "edge/s", E / (ms * 1e-3), ms,
+    return _line(args, "sampled_edges_per_s", "edge/s", E / (ms * 1e-3), ms,
           f"mini-batch sampling: {batch} seeds, fanout {fanout}, R-MAT scale {scale} graph ({n} nodes, {csc.row_indices.numel()} "
           f"in-edges); per batch {E} sampled edges over {m} nodes, 128-wide features gathered",
           {"bound": "hbm", "achieved": alg / ms / 1e6, "peak": peak, "unit": "GB/s", "frac": alg / ms / 1e6 / peak,
@@ -346,7 +293,7 @@ def run_edgeops(args):
         ms_fused = _time(lambda: jg.gat_aggregate(h, a_src, a_dst, csc, H), args.steps, args.warmup)
     clocks = sampler.stop()
     top = res["scatter_to_vertex"]
-    _line(args, "edge_to_vertex_edges_per_s", "edge/s", E / (top["ms"] * 1e-3), top["ms"],
+    return _line(args, "edge_to_vertex_edges_per_s", "edge/s", E / (top["ms"] * 1e-3), top["ms"],
           f"per-edge operators on {n} nodes, {E} in-edges, C = {C}, {H} heads (quarter-size attention graph)",
           {"bound": "hbm", "achieved": top["gbs"], "peak": peak, "unit": "GB/s", "frac": top["frac_of_hbm_peak"], "traffic": None,
            "peak_kind": kind, "kernel": "edge_to_vertex_kernel", "note": "bytes = the [E, C] messages read once + the [N, C] result"},
@@ -428,7 +375,7 @@ def run_citation(args):
                "sample": f"the whole step, {reps} repetitions: numpy (BLAS threads) for the dense products, the reference's "
                          f"single-threaded aggregation body for the four aggregations; {dt * 1e3:.1f} ms per step"}
     best = min(ms, graph_ms) if graph_ms else ms
-    _line(args, "citation_gcn_train_steps_per_s", "step/s", 1e3 / best, best,
+    return _line(args, "citation_gcn_train_steps_per_s", "step/s", 1e3 / best, best,
           f"2-layer GCN 1433->256->7 forward + cross-entropy + backward on a preferential-attachment graph with the citation "
           f"benchmark's shape ({n} nodes, {E} directed edges incl. self-loops, 18 ones per feature row, row-normalised)",
           {"bound": "hbm", "achieved": None, "peak": None, "unit": "GB/s", "frac": None, "traffic": None,
@@ -438,4 +385,29 @@ def run_citation(args):
 
 
 def run(args):
-    return {"citation": run_citation, "edgeops": run_edgeops, "convert": run_convert, "gat": run_gat, "gemm": run_gemm, "gcn": run_gcn, "sample": run_sample}[args.workload](args)
+    line = {"citation": run_citation, "edgeops": run_edgeops, "convert": run_convert, "gat": run_gat, "gemm": run_gemm,
+            "gcn": run_gcn, "sample": run_sample}[args.workload](args)
+    if line is not None:
+        print(json.dumps(line))
+
+
+def secondary(args):
+    """The other configurations of the hot path, time-boxed (3 warm-up + 5 timed steps each, a few seconds
+    of CPU baseline), as sub-records of the default benchmark line: conversion at scale 24, the attention
+    layer at full size (forward and forward + backward), the dense transform's three shapes, and the
+    citation-graph training step."""
+    import copy
+    out = {}
+    for name, fn in (("convert", run_convert), ("gat", run_gat), ("gemm", run_gemm), ("citation", run_citation)):
+        a = copy.copy(args)
+        a.steps, a.warmup, a.workload, a.scale, a.gpus = 5, 3, name, 21, 1
+        a.cpu_budget = min(args.cpu_budget, 4.0)
+        try:
+            rec = fn(a)
+            for k in ("n_gpus", "higher_is_better", "scaling", "vs_baseline", "data"):
+                rec.pop(k, None)
+            out[name] = rec
+        except Exception as exc:                      # a secondary workload never takes the headline down with it
+            out[name] = {"error": repr(exc)}
+        torch.cuda.empty_cache()
+    return out

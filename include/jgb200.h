@@ -107,6 +107,16 @@ int jg_aggregate_bias_act_f32(float* out, const float* x, const int32_t* idx, co
                               const float* bias, int relu, int64_t n_out, int64_t n_in, int64_t f, int64_t nnz,
                               const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes, jg_stream_t stream);
 
+/* The aggregation with every option of the entry points above in one call (bias/relu epilogue,
+ * accumulate, ordered) plus `reserve_ctas`: that many CTA slots of the persistent grid are left free, so
+ * that a small kernel on another stream - the halo pull of the next exchange, jg_halo_pull - finds room
+ * to run beside it.  The reference runs its P exchange rounds and SpMMs strictly one after another
+ * (ops/distspmm.py:31-39). */
+int jg_aggregate_opts_f32(float* out, const float* x, const int32_t* idx, const int32_t* off, const float* w,
+                          const float* bias, int relu, int accumulate, int ordered, int reserve_ctas, int64_t n_out,
+                          int64_t n_in, int64_t f, int64_t nnz, const void* plan, int32_t chunk, void* workspace,
+                          size_t workspace_bytes, jg_stream_t stream);
+
 /* ------------------------------------------------------------------ 1-D row partition
  * Splits the in-edge structure of one shard (destination rows [lo, hi) of the graph, `idx`
  * holding GLOBAL source ids) into interior entries (source inside [lo, hi), ids rebased to the
@@ -138,6 +148,41 @@ int jg_halo_map_build(const int32_t* halo_idx, int64_t nnz, int64_t n_global, in
                       jg_stream_t stream);
 int jg_gather_rows_f32(float* out, const float* x, const int32_t* rows, int64_t n_rows, int64_t f, int32_t rebase,
                        jg_stream_t stream);
+
+/* Halo exchange by direct loads from peer memory (one process per GPU, NVLink).  Replaces the P
+ * rounds of host-staged MPI.bcast of whole feature blocks (ops/distspmm.py:31-39,
+ * utils/distributed_utils.py:66-74): every rank keeps its feature rows in a buffer all ranks have
+ * mapped and pulls the distinct remote rows it references (`needed`, from jg_halo_map_build) out of
+ * their owners' buffers into its own halo rows.
+ *
+ * Flag block: jg_halo_flag_bytes() bytes per rank, zeroed once, mapped by every rank; it holds one
+ * "ready" (kind 0) and one "done" (kind 1) epoch word per buffer slot (< jg_halo_flag_slots()) and
+ * rank (< jg_halo_max_ranks()).  Arrays named *_host are HOST arrays of `world` device pointers (the
+ * peers' buffers as mapped in this process, this rank's own included) or of per-rank values.
+ *   jg_halo_post   writes `epoch` into word (slot, kind, rank) of EVERY rank's flag block, after all
+ *                  earlier work of `stream` (kind 0: "my rows of this slot are written").
+ *   jg_halo_pull   for every peer q waits (at most wait_ns) for ready word (slot, q) >= epoch in this
+ *                  rank's flag block, then copies rows needed[seg_begin[q] .. seg_begin[q+1]) -
+ *                  global ids, row id - lo[q] inside peer q's buffer - to halo rows of the same
+ *                  positions; when everything has landed it posts done word (slot, rank) = epoch to
+ *                  every rank.  Rows are row_bytes long (a multiple of 4; multiples of 16 use bulk
+ *                  asynchronous copies through shared memory, one warp per CTA, at most max_ctas
+ *                  CTAs; plain != 0 forces the plain-load kernel).  `counter` is 4 zeroed bytes of
+ *                  device memory owned by the caller, zero again when the call has finished.
+ *   jg_halo_wait   waits (at most wait_ns) until word (slot, kind, q) >= epoch for every peer q in
+ *                  this rank's flag block (kind 1: "every peer has read my rows, I may overwrite them").
+ * A wait that runs out stores a code in *error (a device-accessible int32, e.g. pinned host memory:
+ * 0x100 + q ready word of rank q, 0x200 + q done word of rank q, 0x300 a copy that never landed) and the
+ * kernel returns; nothing traps and the context stays usable.  No load uses cluster multicast. */
+size_t jg_halo_flag_bytes(void);
+int jg_halo_max_ranks(void);
+int jg_halo_flag_slots(void);
+int jg_halo_post(void* const* peer_flags_host, int world, int rank, int slot, int kind, uint32_t epoch, jg_stream_t stream);
+int jg_halo_wait(const void* my_flags, int world, int rank, int slot, int kind, uint32_t epoch, int32_t* error,
+                 int64_t wait_ns, jg_stream_t stream);
+int jg_halo_pull(void* halo, const int32_t* needed, void* const* peer_x_host, void* const* peer_flags_host,
+                 const int64_t* seg_begin_host, const int32_t* lo_host, int world, int rank, int64_t row_bytes, int slot,
+                 uint32_t epoch, void* counter, int32_t* error, int64_t wait_ns, int max_ctas, int plain, jg_stream_t stream);
 
 /* ------------------------------------------------------------------ conversion
  * COO -> CSR (by = 0, rows keyed by source) or CSC (by = 1, columns keyed by destination).

@@ -34,6 +34,15 @@ SIGNATURES = {
     "jg_aggregate_add_f32": (ctypes.c_int, [vp, vp, vp, vp, vp, i64, i64, i64, i64, vp, i32, vp, sz, vp]),
     "jg_aggregate_ordered_f32": (ctypes.c_int, [vp, vp, vp, vp, vp, i64, i64, i64, i64, vp, i32, vp, sz, vp]),
     "jg_aggregate_bias_act_f32": (ctypes.c_int, [vp, vp, vp, vp, vp, vp, ctypes.c_int, i64, i64, i64, i64, vp, i32, vp, sz, vp]),
+    "jg_aggregate_opts_f32": (ctypes.c_int, [vp, vp, vp, vp, vp, vp, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                             i64, i64, i64, i64, vp, i32, vp, sz, vp]),
+    "jg_halo_flag_bytes": (sz, []),
+    "jg_halo_max_ranks": (ctypes.c_int, []),
+    "jg_halo_flag_slots": (ctypes.c_int, []),
+    "jg_halo_post": (ctypes.c_int, [vp, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_uint32, vp]),
+    "jg_halo_wait": (ctypes.c_int, [vp, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_uint32, vp, i64, vp]),
+    "jg_halo_pull": (ctypes.c_int, [vp, vp, vp, vp, vp, vp, ctypes.c_int, ctypes.c_int, i64, ctypes.c_int, ctypes.c_uint32,
+                                    vp, vp, i64, ctypes.c_int, ctypes.c_int, vp]),
     "jg_partition_split_workspace_bytes": (sz, [i64]),
     "jg_partition_split": (ctypes.c_int, [vp, vp, vp, i64, i64, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
     "jg_halo_map_workspace_bytes": (sz, [i64]),

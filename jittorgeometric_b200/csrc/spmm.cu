@@ -100,6 +100,7 @@ struct AggArgs {
     const float* bias;  // epilogue on finished output rows: + bias[column] (null: none) ...
     int relu;           // ... then max(., 0)
     int ordered;        // 1: every row must be summed in stored order (no lane groups taking alternate entries)
+    int reserve_ctas;   // CTA slots of the persistent grid left free for a kernel that runs beside this one
 };
 
 
@@ -518,7 +519,8 @@ static int launch_persistent(K kern, int* blocks_per_sm, const AggArgs& a, cudaS
     }
     const int64_t grabs = (a.n_out + a.max_items + kGrab - 1) / kGrab;
     int64_t blocks = (grabs + kBlock / 32 - 1) / (kBlock / 32);
-    const int64_t full = (int64_t)sm_count() * *blocks_per_sm;
+    int64_t full = (int64_t)sm_count() * *blocks_per_sm;
+    if (a.reserve_ctas > 0) full = full - a.reserve_ctas > sm_count() ? full - a.reserve_ctas : sm_count();
     if (blocks > full) blocks = full;
     if (blocks < 1) blocks = 1;
     kern<<<(unsigned)blocks, kBlock, 0, st>>>(a);
@@ -610,7 +612,8 @@ size_t jg_aggregate_workspace_bytes(int64_t n_out, int64_t nnz, int64_t f, int32
 static int aggregate_impl(float* out, const float* x, const int32_t* idx, const int32_t* off,
                           const float* w, int64_t n_out, int64_t n_in, int64_t f, int64_t nnz,
                           const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes,
-                          jg_stream_t stream, int accumulate, const float* bias = nullptr, int relu = 0, int ordered = 0) {
+                          jg_stream_t stream, int accumulate, const float* bias = nullptr, int relu = 0, int ordered = 0,
+                          int reserve_ctas = 0) {
     JG_CHECK_ARG(n_out >= 0 && n_in >= 0 && f >= 0 && nnz >= 0, JG_EINVAL, "aggregate: negative size");
     if (n_out == 0 || f == 0) return JG_OK;
     JG_CHECK_ARG(out && off, JG_EINVAL, "aggregate: null out/off");
@@ -629,6 +632,7 @@ static int aggregate_impl(float* out, const float* x, const int32_t* idx, const 
     a.bias = bias;
     a.relu = relu;
     a.ordered = ordered;
+    a.reserve_ctas = reserve_ctas;
     JG_CHECK_ARG(!bias || f % 4 != 0 || reinterpret_cast<uintptr_t>(bias) % 16 == 0, JG_EINVAL,
                  "aggregate: bias must be 16-byte aligned");
     Carver c(workspace);
@@ -678,6 +682,17 @@ int jg_aggregate_bias_act_f32(float* out, const float* x, const int32_t* idx, co
                               const void* plan, int32_t chunk, void* workspace, size_t workspace_bytes, jg_stream_t stream) {
     return aggregate_impl(out, x, idx, off, w, n_out, n_in, f, nnz, plan, chunk, workspace, workspace_bytes, stream, 0, bias,
                           relu ? 1 : 0);
+}
+
+int jg_aggregate_opts_f32(float* out, const float* x, const int32_t* idx, const int32_t* off, const float* w,
+                          const float* bias, int relu, int accumulate, int ordered, int reserve_ctas, int64_t n_out,
+                          int64_t n_in, int64_t f, int64_t nnz, const void* plan, int32_t chunk, void* workspace,
+                          size_t workspace_bytes, jg_stream_t stream) {
+    JG_CHECK_ARG(!(accumulate && (bias || relu)), JG_EINVAL, "aggregate_opts: the epilogue cannot be combined with accumulate");
+    JG_CHECK_ARG(!(accumulate && ordered), JG_EINVAL, "aggregate_opts: ordered cannot be combined with accumulate");
+    JG_CHECK_ARG(reserve_ctas >= 0, JG_EINVAL, "aggregate_opts: negative reserve");
+    return aggregate_impl(out, x, idx, off, w, n_out, n_in, f, nnz, plan, chunk, workspace, workspace_bytes, stream,
+                          accumulate ? 1 : 0, bias, relu ? 1 : 0, ordered ? 1 : 0, reserve_ctas);
 }
 
 // ------------------------------------------------------------------------------------------

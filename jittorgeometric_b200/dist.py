@@ -7,19 +7,27 @@ source rank, and runs P rounds of host-staged pickled ``MPI.bcast`` + cuSPARSE. 
 * owns a contiguous range of destination rows and the matching rows of the feature matrix
   (:class:`RowPartition`; equal ranges of ``ceil(N / P)`` rows, which balances edges when vertex
   ids carry no degree order),
-* splits its in-edges on device into interior entries (source row owned, read from the rank's own
-  shard) and halo entries (source row remote),
-* finds, once per graph, the distinct remote rows its halo entries reference (with skewed degrees
-  a minority of all remote rows) and tells their owners; per aggregation every rank packs the rows
-  its peers asked for and the packed segments travel over NVLink into a local halo buffer -
-  copy-engine pulls from peer memory (:class:`PeerTransport`) or one NCCL all-to-all
-  (:class:`CollectiveTransport`) - while the interior aggregation runs; the halo entries are then
-  aggregated from that buffer and added to the same output rows (fixed order: interior, then
-  halo, so results are run-to-run identical).  Kernels only ever gather from local memory.
+* finds, once per graph, the distinct remote rows its in-edges reference (with skewed degrees a
+  minority of all remote rows) and re-addresses its entries into one buffer ``[own rows | halo rows]``,
+* per aggregation fetches those rows into the halo part and runs ONE aggregation over the buffer,
+  every row summed exactly as the unpartitioned kernel sums it (``mode="merged"``); or aggregates
+  the entries with owned sources while the halo rows travel and adds the rest afterwards
+  (``mode="overlap"``).
+
+Transports.  :class:`DirectTransport` (GPUs): every rank keeps its feature rows in a buffer all
+ranks have mapped and PULLS the rows it needs straight out of their owners' buffers with a small
+kernel of bulk asynchronous copies over NVLink - no pack step, no send buffer, no barrier; epoch
+words with bounded waits order producers and readers, and the pull of one feature width runs beside
+the aggregation of another.  :class:`CollectiveTransport`: owners pack the requested rows and one
+``all_to_all_single`` moves them (NCCL, or gloo for CPU ranks in tests).
 
 One process per GPU; ``torch.distributed`` supplies the communicator.  The compute backend is
 pluggable so the partition and exchange logic can be exercised by CPU ranks over ``gloo``.
 """
+import os
+
+import ctypes
+
 import torch
 import torch.distributed as dist
 
@@ -100,9 +108,14 @@ class DeviceBackend:
     def plan(self, off, nnz):
         return ops.SpmmPlan(off, nnz)
 
-    def aggregate(self, x, idx, off, w, n_out, plan, out=None, accumulate=False, bias=None, relu=False):
+    def aggregate(self, x, idx, off, w, n_out, plan, out=None, accumulate=False, bias=None, relu=False, reserve_ctas=0):
         return ops.segment_aggregate(x, idx, off, w, n_out=n_out, plan=plan, out=out, accumulate=accumulate, bias=bias,
-                                     relu=relu)
+                                     relu=relu, reserve_ctas=reserve_ctas)
+
+
+class ExchangeTimeout(RuntimeError):
+    """A bounded wait of the halo exchange ran out (``JG_ETIMEOUT``): a peer never posted its rows,
+    never finished reading this rank's, or never joined the collective."""
 
 
 class _Done:
@@ -114,13 +127,22 @@ class _Done:
 
 
 class _WorkHandle:
-    """An asynchronous ``torch.distributed`` collective."""
+    """An asynchronous ``torch.distributed`` collective; ``timeout_s`` bounds the wait."""
 
-    def __init__(self, work):
-        self.work = work
+    def __init__(self, work, timeout_s=None):
+        self.work, self.timeout_s = work, timeout_s
 
     def wait(self):
-        self.work.wait()
+        if self.timeout_s is None:
+            self.work.wait()
+            return
+        import datetime
+        try:
+            done = self.work.wait(datetime.timedelta(seconds=self.timeout_s))
+        except RuntimeError as exc:
+            raise ExchangeTimeout(f"halo exchange: a peer did not take part within {self.timeout_s} s ({exc})") from exc
+        if done is False:
+            raise ExchangeTimeout(f"halo exchange: a peer did not take part within {self.timeout_s} s")
 
     def release(self):
         pass
@@ -130,8 +152,9 @@ class CollectiveTransport:
     """Row exchange with ``torch.distributed`` collectives (NCCL on GPUs, gloo on CPU ranks):
     one ``all_to_all_single`` with per-peer row counts."""
 
-    def __init__(self, group=None):
+    def __init__(self, group=None, timeout_s=None):
         self.group = group
+        self.timeout_s = timeout_s       # None: the process group's own timeout
 
     def send_buffer(self, rows, f, like):
         return torch.empty((max(rows, 1), f), dtype=like.dtype, device=like.device)
@@ -160,77 +183,219 @@ class CollectiveTransport:
         recv_split = [int(c) for c in g.recv_counts]
         return _WorkHandle(dist.all_to_all_single(recv[: sum(recv_split)], send[: sum(send_split)],
                                                   output_split_sizes=recv_split, input_split_sizes=send_split,
-                                                  group=self.group, async_op=True))
+                                                  group=self.group, async_op=True), self.timeout_s)
 
 
-class PeerTransport(CollectiveTransport):
-    """Row exchange by peer-to-peer copies over NVLink, driven by the copy engines.
+class _Slot:
+    """One feature width's buffer ``[own rows | halo rows]`` as every rank has mapped it."""
 
-    An NCCL collective runs as a kernel, and the aggregation kernels are persistent grids that
-    fill every SM: whichever starts first keeps the other waiting, so nothing overlaps.  Here every
-    rank packs the rows its peers asked for into a buffer the peers can map (``torch.distributed``
-    symmetric memory) and each rank pulls its segments with plain device-to-device copies on a side
-    stream; those are DMA transfers that need no SM, so they proceed underneath the interior
-    aggregation.  Two small barriers order the exchange: one after the buffers are packed (before
-    anyone pulls), one after the pulls (before a buffer may be packed again).
+    def __init__(self, index, buf, ptrs):
+        self.index, self.buf = index, buf
+        self.ptrs = (ctypes.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+        self.epoch = 0           # exchanges started on this buffer
+        self.acquired = 0        # epoch whose readers have been waited for
+
+
+class DirectTransport(CollectiveTransport):
+    """Halo rows pulled straight out of their owners' feature buffers over NVLink.
+
+    Every rank writes its feature rows into the head of a buffer that all ranks have mapped
+    (``torch.distributed`` symmetric memory is only the allocator and the address exchange) and
+    fetches the remote rows it references with ``jg_halo_pull``: bulk asynchronous copies, one warp
+    per CTA, no SM time to speak of, so the pull of the next feature width runs beside the current
+    aggregation kernel (which leaves ``pull_ctas`` CTA slots free for it).  Producers and readers are
+    ordered by epoch words in a mapped flag block: ``post`` after the rows are written, the pull
+    acquires its owners' words before the first load and reports back when everything has landed,
+    and ``acquire`` makes a rank wait for its readers before it overwrites its rows.  Every wait
+    is bounded (``wait_ms``); one that runs out is reported through an error word in pinned host
+    memory and raised as :class:`ExchangeTimeout` at the next call - nothing traps or hangs.
+    No NCCL kernel is involved and nothing uses multicast.
     """
 
-    BARRIER_TIMEOUT_MS = 20000
+    direct = True
 
-    def __init__(self, group=None):
+    def __init__(self, group=None, pull_ctas=48, wait_ms=2000.0, plain=False, device=None):
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
         self._symm = symm
-        self.group = group                                                # set-up collectives
+        self.group = group
         self.symm_group = group if group is not None else dist.group.WORLD
-        self.side = torch.cuda.Stream()
-        self._bufs = {}
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > lib().jg_halo_max_ranks():
+            raise RuntimeError(f"DirectTransport serves at most {lib().jg_halo_max_ranks()} ranks")
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        self.pull_ctas, self.wait_ns, self.plain = int(pull_ctas), int(wait_ms * 1e6), bool(plain)
+        self.side = torch.cuda.Stream(device=self.device, priority=-1)
+        self._slots = {}
+        words = lib().jg_halo_flag_bytes() // 4
+        self._flags = symm.empty((words,), dtype=torch.int32, device=self.device)
+        self._flags.zero_()
+        hdl = symm.rendezvous(self._flags, self.symm_group.group_name)
+        self._flag_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs])
+        self._counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._error = torch.zeros(1, dtype=torch.int32).pin_memory()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)                     # every flag block is zero before anyone posts
 
-    def send_buffer(self, rows, f, like):
-        """Symmetric buffer of ``rows`` x ``f`` (the same shape on every rank)."""
-        rows = max(rows, 1)
-        entry = self._bufs.get((rows, f))
-        if entry is None:
-            t = self._symm.empty((rows, f), dtype=torch.float32, device=like.device)
-            hdl = self._symm.rendezvous(t, self.symm_group.group_name)
-            entry = (t, hdl)
-            self._bufs[(rows, f)] = entry
-        return entry[0]
+    # ---- errors
+    def check(self):
+        """Raises :class:`ExchangeTimeout` if a bounded wait of an earlier exchange ran out."""
+        code = int(self._error[0])
+        if code:
+            self._error[0] = 0
+            what = {0x100: "never posted its rows", 0x200: "never finished reading this rank's rows"}.get(code & 0xf00,
+                                                                                                      "a row copy never landed")
+            raise ExchangeTimeout(f"halo exchange on rank {self.rank}: rank {code & 0xff} {what} "
+                                  f"within {self.wait_ns / 1e6:.0f} ms [JG_ETIMEOUT, code {code:#x}]")
 
-    def exchange(self, g, send, recv, f):
-        hdl = self._bufs[(send.shape[0], f)][1]
-        hdl.barrier(channel=0, timeout_ms=self.BARRIER_TIMEOUT_MS)       # every send buffer is packed
-        cur = torch.cuda.current_stream()
+    # ---- buffers
+    def _slot(self, g, f):
+        slot = self._slots.get(f)
+        if slot is None:
+            if len(self._slots) >= lib().jg_halo_flag_slots():
+                raise RuntimeError(f"DirectTransport holds at most {lib().jg_halo_flag_slots()} feature widths")
+            buf = self._symm.empty((max(g.buffer_rows, 1), f), dtype=torch.float32, device=self.device)
+            hdl = self._symm.rendezvous(buf, self.symm_group.group_name)
+            slot = _Slot(len(self._slots), buf, hdl.buffer_ptrs)
+            self._slots[f] = slot
+        return slot
+
+    def feature_buffer(self, g, f):
+        """The rank's buffer for width ``f`` (``[own rows | halo rows]``; collective on first use:
+        every rank must ask for its widths in the same order)."""
+        return self._slot(g, f).buf
+
+    def acquire(self, g, f):
+        """Queues, on the current stream, the wait for every peer to have finished reading the rows
+        of the last exchange of width ``f``: call it before overwriting the head of the buffer."""
+        slot = self._slot(g, f)
+        if slot.epoch > slot.acquired and self.world > 1:
+            check(lib().jg_halo_wait(ptr(self._flags), self.world, self.rank, slot.index, 1, slot.epoch, self._eptr(),
+                                     self.wait_ns, stream_for(slot.buf)), "jg_halo_wait")
+        slot.acquired = slot.epoch
+
+    def _eptr(self):
+        return ctypes.c_void_p(self._error.data_ptr())
+
+    def begin(self, g, f):
+        """The rank's rows of width ``f`` are in place (written by work already queued on the current
+        stream): tells the peers and starts pulling this rank's halo rows on the side stream."""
+        self.check()
+        slot = self._slot(g, f)
+        slot.epoch += 1
+        st = stream_for(slot.buf)
+        check(lib().jg_halo_post(self._flag_ptrs, self.world, self.rank, slot.index, 0, slot.epoch, st), "jg_halo_post")
+        cur = torch.cuda.current_stream(self.device)
         self.side.wait_stream(cur)
-        world, rank = g.part.world, g.rank
+        seg = (ctypes.c_int64 * (self.world + 1))(*([int(v) for v in g.recv_offset] + [int(g.n_halo)]))
+        los = (ctypes.c_int32 * self.world)(*[int(g.part.bounds[q]) for q in range(self.world)])
+        halo = slot.buf[g.n_local:]
         with torch.cuda.stream(self.side):
-            for step in range(1, world):
-                q = (rank + step) % world                                  # staggered: no two ranks start on the same peer
-                n = int(g.recv_counts[q])
-                if n == 0:
-                    continue
-                peer = hdl.get_buffer(q, tuple(send.shape), torch.float32)
-                src0 = int(g.peer_send_offset[q])                          # where rank q packed the rows meant for this rank
-                dst0 = int(g.recv_offset[q])
-                recv[dst0:dst0 + n].copy_(peer[src0:src0 + n])
+            check(lib().jg_halo_pull(ptr(halo), ptr(g.needed), slot.ptrs, self._flag_ptrs, seg, los, self.world, self.rank,
+                                     4 * f, slot.index, slot.epoch, ptr(self._counter), self._eptr(), self.wait_ns,
+                                     self.pull_ctas, 1 if self.plain else 0,
+                                     ctypes.c_void_p(self.side.cuda_stream)), "jg_halo_pull")
             landed = torch.cuda.Event()
             landed.record(self.side)
-        return _PeerHandle(hdl, landed)
+        return _DirectHandle(self, landed)
 
 
-class _PeerHandle:
-    """``wait``: the current stream waits for THIS exchange's pulls (an event, so that pulls of later
-    exchanges already queued on the side stream are not waited for).  ``release``: the barrier that
-    tells every rank its send buffer has been read and may be packed again; it is issued after the
-    aggregation has been queued, so no rank idles in it before its own kernel starts."""
+class EmulatedRanks:
+    """The direct exchange with every rank of a partition living on ONE GPU in one process (no
+    process group): each emulated rank has its own flag block and feature buffers in local memory,
+    and the "peer" pointers are simply the other ranks' buffers.  It runs the real kernels
+    (``jg_halo_post`` / ``jg_halo_pull``, epoch words included) where only one GPU is available.
+    Kernels that wait for one another must not run as separate launches on one GPU, so a rank's
+    exchange first posts the ready words of ALL emulated ranks (their rows must already be in their
+    buffers: write every rank's ``feature_buffer`` before the first ``start``); ``acquire`` does not
+    wait.  ``transport(rank)`` is what ``ShardedGraph(transport=...)`` takes."""
 
-    def __init__(self, hdl, landed):
-        self.hdl, self.landed = hdl, landed
+    def __init__(self, world, device=None, wait_ms=1000.0, plain=False, pull_ctas=48):
+        self.world = int(world)
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        words = lib().jg_halo_flag_bytes() // 4
+        self.flags = [torch.zeros(words, dtype=torch.int32, device=self.device) for _ in range(self.world)]
+        self.flag_ptrs = (ctypes.c_void_p * self.world)(*[t.data_ptr() for t in self.flags])
+        self.buffers = {}            # f -> [tensor per rank]
+        self.rows = [0] * self.world
+        self.views = [_EmulatedRank(self, r, wait_ms, plain, pull_ctas) for r in range(self.world)]
+
+    def transport(self, rank):
+        return self.views[rank]
+
+    def wire(self, graphs):
+        """What the set-up collectives do between real ranks: every emulated rank learns the matrix of
+        request counts (``graphs[r]`` built with ``transport=self.transport(r), setup=False``)."""
+        matrix = [list(g.recv_counts) for g in graphs]
+        for r, g in enumerate(graphs):
+            g.apply_setup(matrix, None)
+            self.rows[r] = g.n_local + g.n_halo
+
+    def buffer(self, f, rank):
+        bufs = self.buffers.get(f)
+        if bufs is None:
+            if len(self.buffers) >= lib().jg_halo_flag_slots():
+                raise RuntimeError("too many feature widths")
+            bufs = [torch.zeros((max(self.rows[r], 1), f), dtype=torch.float32, device=self.device) for r in range(self.world)]
+            self.buffers[f] = bufs
+        return bufs[rank]
+
+    def slot_index(self, f):
+        return list(self.buffers).index(f)
+
+
+class _EmulatedRank(CollectiveTransport):
+    direct = True
+
+    def __init__(self, owner, rank, wait_ms, plain, pull_ctas):
+        self.owner, self.rank, self.world = owner, rank, owner.world
+        self.group = None
+        self.wait_ns, self.plain, self.pull_ctas = int(wait_ms * 1e6), bool(plain), int(pull_ctas)
+        self.epochs = {}
+        self.post_for_peers = True       # tests of the time-out path switch this off: nobody posts, the wait runs out
+        self._counter = torch.zeros(1, dtype=torch.int32, device=owner.device)
+        self._error = torch.zeros(1, dtype=torch.int32).pin_memory()
+
+    check = DirectTransport.check
+    _eptr = DirectTransport._eptr
+
+    def all_gather_counts(self, g, counts):
+        raise RuntimeError("emulated ranks are wired by hand: ShardedGraph(setup=False) + apply_setup")
+
+    def feature_buffer(self, g, f):
+        return self.owner.buffer(f, self.rank)
+
+    def acquire(self, g, f):
+        pass
+
+    def begin(self, g, f):
+        self.check()
+        buf = self.feature_buffer(g, f)
+        slot = self.owner.slot_index(f)
+        epoch = self.epochs.get(f, 0) + 1
+        self.epochs[f] = epoch
+        st = stream_for(buf)
+        posters = range(self.world) if self.post_for_peers else [self.rank]
+        for q in posters:
+            check(lib().jg_halo_post(self.owner.flag_ptrs, self.world, q, slot, 0, epoch, st), "jg_halo_post")
+        ptrs = (ctypes.c_void_p * self.world)(*[self.owner.buffer(f, q).data_ptr() for q in range(self.world)])
+        seg = (ctypes.c_int64 * (self.world + 1))(*([int(v) for v in g.recv_offset] + [int(g.n_halo)]))
+        los = (ctypes.c_int32 * self.world)(*[int(g.part.bounds[q]) for q in range(self.world)])
+        check(lib().jg_halo_pull(ptr(buf[g.n_local:]), ptr(g.needed), ptrs, self.owner.flag_ptrs, seg, los, self.world,
+                                 self.rank, 4 * f, slot, epoch, ptr(self._counter), self._eptr(), self.wait_ns,
+                                 self.pull_ctas, 1 if self.plain else 0, st), "jg_halo_pull")
+        return _Done()
+
+
+class _DirectHandle:
+    def __init__(self, transport, landed):
+        self.transport, self.landed = transport, landed
 
     def wait(self):
         torch.cuda.current_stream().wait_event(self.landed)
 
     def release(self):
-        self.hdl.barrier(channel=1, timeout_ms=PeerTransport.BARRIER_TIMEOUT_MS)   # every pull has finished
+        pass
 
 
 class ShardedGraph:
@@ -238,7 +403,9 @@ class ShardedGraph:
 
     ``idx`` holds GLOBAL source ids, ``off`` the offsets of the rank's own rows (CSC of the shard).
     Construction is collective (every rank of the group builds its graph at the same time): the
-    ranks tell each other which rows they need.
+    ranks tell each other which rows they need.  ``exchange``: ``"direct"`` (alias ``"peer"``) pulls
+    halo rows out of peer memory (:class:`DirectTransport`), ``"nccl"`` packs and runs one all-to-all
+    (:class:`CollectiveTransport`, also what CPU ranks use over gloo).
     """
 
     def __init__(self, part, rank, idx, off, w, backend=None, group=None, exchange="nccl", transport=None,
@@ -250,8 +417,9 @@ class ShardedGraph:
         if off.numel() != self.n_local + 1:
             raise RuntimeError(f"offsets describe {off.numel() - 1} rows, the rank owns {self.n_local}")
         if transport is None:
-            transport = PeerTransport(group) if exchange == "peer" else CollectiveTransport(group)
+            transport = DirectTransport(group) if exchange in ("direct", "peer") else CollectiveTransport(group)
         self.transport = transport
+        self.direct = bool(getattr(transport, "direct", False))
         if mode not in ("merged", "overlap"):
             raise ValueError("mode must be 'merged' or 'overlap'")
         self.mode = mode
@@ -274,7 +442,9 @@ class ShardedGraph:
             self.merged_plan = self.backend.plan(off, idx.numel())
         self.recv_offset = [sum(self.recv_counts[:q]) for q in range(part.world)]
         self.n_halo = sum(self.recv_counts)
+        self.buffer_rows = self.n_local + self.n_halo
         self._recv = {}
+        self._inflight = set()
         if setup:
             self._setup_requests()
 
@@ -284,12 +454,14 @@ class ShardedGraph:
         counts = torch.tensor(self.recv_counts, dtype=torch.int64, device=dev)
         matrix = self.transport.all_gather_counts(self, counts)           # matrix[r][q] = rows rank r needs from rank q
         send_counts = [int(matrix[r][self.rank]) for r in range(self.part.world)]
-        send_rows = self.transport.all_to_all_ids(self, self.needed, self.recv_counts, send_counts)
+        # the owners only need the requested ids when they pack rows for their readers
+        send_rows = None if self.direct else self.transport.all_to_all_ids(self, self.needed, self.recv_counts, send_counts)
         self.apply_setup(matrix, send_rows)
 
     def apply_setup(self, matrix, send_rows):
         """``matrix[r][q]`` = rows rank r needs from rank q; ``send_rows`` = the global ids of this
-        rank's rows its peers asked for, grouped by requesting rank in rank order."""
+        rank's rows its peers asked for, grouped by requesting rank in rank order (``None`` when
+        readers fetch rows themselves)."""
         world = self.part.world
         self.count_matrix = matrix
         self.send_counts = [int(matrix[r][self.rank]) for r in range(world)]
@@ -299,11 +471,18 @@ class ShardedGraph:
         self.n_send = sum(self.send_counts)
         self.max_send = max(sum(int(matrix[r][q]) for r in range(world)) for q in range(world))
         self.send_rows = send_rows
+        # one mapped buffer shape for every rank: its own rows followed by its halo rows
+        self.buffer_rows = max(self.part.n_local(r) + sum(int(c) for c in matrix[r]) for r in range(world))
 
     # ---- per aggregation
-    def feature_buffer(self, f, like):
-        """Where a caller should write the rank's feature rows to save a copy per aggregation (the
-        head of the buffer the merged aggregation reads); any tensor with ``n_local`` rows works."""
+    def feature_buffer(self, f, like=None):
+        """Where a caller should write the rank's ``n_local`` feature rows of width ``f`` to save a copy
+        per aggregation: the head of the buffer the aggregation reads (and, with the direct transport,
+        the peers read).  Ask for it EVERY time before writing: with the direct transport the call
+        also queues the wait for the readers of the previous exchange of this width."""
+        if self.direct:
+            self.transport.acquire(self, f)
+            return self.transport.feature_buffer(self, f)[: self.n_local]
         if self.mode == "merged":
             return self._recv_buffer(f, like)[: self.n_local]
         return torch.empty((self.n_local, f), dtype=like.dtype, device=like.device)
@@ -338,12 +517,24 @@ class ShardedGraph:
         return self.finish(self.start(x), bias, relu)
 
     def start(self, x):
-        """First half of an aggregation: packs the rows the peers asked for and starts the exchange.
-        Several aggregations may be started before the first is finished; their exchanges then run
-        underneath the aggregation kernels of the earlier ones.  Forward only."""
+        """First half of an aggregation: starts the exchange of the halo rows.  Aggregations of
+        DIFFERENT widths may be started before the first is finished; their exchanges then run
+        underneath the aggregation kernels of the earlier ones.  A second ``start`` of a width whose
+        aggregation has not been finished raises: the two would share one buffer.  Forward only."""
         if x.shape[0] < self.n_local:
             raise RuntimeError(f"x has {x.shape[0]} rows, the rank owns {self.n_local}")
         f = x.shape[1]
+        if f in self._inflight:
+            raise RuntimeError(f"an aggregation of width {f} is already in flight on this graph: finish() it first "
+                               "(aggregations of one width share their exchange buffers)")
+        if self.direct:
+            buf = self.transport.feature_buffer(self, f)
+            if x.data_ptr() != buf.data_ptr():
+                self.transport.acquire(self, f)
+                buf[: self.n_local].copy_(x[: self.n_local])
+            handle = self.transport.begin(self, f)
+            self._inflight.add(f)
+            return (buf[: self.n_local], buf if self.mode == "merged" else buf[self.n_local:], handle)
         buf = self._recv_buffer(f, x)
         send = self.transport.send_buffer(self.max_send, f, x)
         if self.n_send:
@@ -354,29 +545,37 @@ class ShardedGraph:
                 buf[: self.n_local].copy_(x[: self.n_local])
         else:
             handle = self.transport.exchange(self, send, buf, f)
+        self._inflight.add(f)
         return (x, buf, handle)
 
     def finish(self, pending, bias=None, relu=False):
         """Second half: waits for the halo rows of ``pending`` (from :meth:`start`) and aggregates."""
         x, buf, handle = pending
+        f = x.shape[1]
+        # other exchanges still travelling: leave their pull kernels room beside this aggregation
+        extra = {}
+        if self.direct and len(self._inflight) > 1:
+            extra = {"reserve_ctas": self.transport.pull_ctas}
         if self.mode == "merged":
             handle.wait()
             if bias is not None or relu:
                 y = self.backend.aggregate(buf, self.merged[0], self.merged[1], self.merged[2], self.n_local,
-                                           self.merged_plan, bias=bias, relu=relu)
+                                           self.merged_plan, bias=bias, relu=relu, **extra)
             else:
                 y = self.backend.aggregate(buf, self.merged[0], self.merged[1], self.merged[2], self.n_local,
-                                           self.merged_plan)
+                                           self.merged_plan, **extra)
             handle.release()
+            self._inflight.discard(f)
             return y
         # the rank's own rows while the halo rows travel
         y = self.backend.aggregate(x, self.interior[0], self.interior[1], self.interior[2], self.n_local,
-                                   self.interior_plan)
+                                   self.interior_plan, **extra)
         handle.wait()
         if self.halo[0].numel():
             self.backend.aggregate(buf, self.halo[0], self.halo[1], self.halo[2], self.n_local, self.halo_plan,
                                    out=y, accumulate=True)
         handle.release()
+        self._inflight.discard(f)
         if bias is not None:
             y += bias
         return y.relu_() if relu else y
@@ -534,10 +733,11 @@ class ShardedGCN(torch.nn.Module):
     ``layers`` rounds of ``h <- (A_hat h) W`` with Glorot weights drawn on rank 0 and broadcast, then
     ``log_softmax``.  ``A_hat h`` is :meth:`ShardedGraph.aggregate` (one compact halo exchange per
     layer) instead of ``P`` broadcast rounds.  ``relu=True`` adds the activation between layers that
-    the single-GPU example has and the graph-parallel one omits."""
+    the single-GPU example has and the graph-parallel one omits.  ``tf32=False`` keeps the transform
+    in fp32 (comparisons at 1e-5)."""
 
     def __init__(self, in_channels, hidden_channels, out_channels, layers=2, manager=None, relu=False,
-                 device=None, seed=0):
+                 device=None, seed=0, tf32=True):
         super().__init__()
         widths = [in_channels] + [hidden_channels] * (layers - 1) + [out_channels]
         gen = torch.Generator().manual_seed(seed)
@@ -547,6 +747,7 @@ class ShardedGCN(torch.nn.Module):
             w = (torch.rand((a, b), generator=gen) * 2 - 1) * bound
             self.weights.append(torch.nn.Parameter(w.to(device) if device is not None else w))
         self.relu = relu
+        self.tf32 = tf32
         self.manager = manager
         self.sync_parameters()
 
@@ -562,9 +763,14 @@ class ShardedGCN(torch.nn.Module):
         h = x
         last = len(self.weights) - 1
         for i, w in enumerate(self.weights):
-            h = graph.aggregate(h) @ w
-            if self.relu and i != last:
-                h = torch.relu(h)
+            z = graph.aggregate(h)
+            act = self.relu and i != last
+            if self.tf32 and z.is_cuda:      # the tcgen05 transform, forward and backward (CPU ranks of the tests: matmul)
+                h = ops.linear_tf32_autograd(z, w, relu=act)
+            else:
+                h = z @ w
+                if act:
+                    h = torch.relu(h)
         return torch.log_softmax(h, dim=1)
 
 

@@ -85,7 +85,7 @@ def _plan_of(holder, off, nnz):
 
 
 def segment_aggregate(x, idx, off, w, n_out=None, plan=None, out=None, accumulate=False, bias=None, relu=False,
-                      ordered=False):
+                      ordered=False, reserve_ctas=0):
     """out[v,:] = sum_{j in [off[v], off[v+1])} w[j] * x[idx[j],:]  (fp32).
 
     The one kernel behind aggregateWithWeight (forward over CSC, backward over
@@ -93,7 +93,9 @@ def segment_aggregate(x, idx, off, w, n_out=None, plan=None, out=None, accumulat
     ``None`` to process every row unsplit.  ``accumulate=True`` adds the result to ``out``.
     ``bias`` / ``relu`` fuse the layer epilogue ``act(sum + bias)`` into the store of every row
     (forward only, not together with ``accumulate``).  ``ordered=True`` sums every unsplit row
-    strictly in stored order at every width (the default does for widths below 32 and above 64)."""
+    strictly in stored order at every width (the default does for widths below 32 and above 64).
+    ``reserve_ctas`` leaves that many CTA slots of the persistent grid free for a kernel on another
+    stream (the halo pull of the next exchange)."""
     x = _as_f32(x, "x")
     if x.dim() != 2:
         raise RuntimeError("x: expected a 2-D feature matrix")
@@ -114,13 +116,23 @@ def segment_aggregate(x, idx, off, w, n_out=None, plan=None, out=None, accumulat
         pad = 4 - f % 4
         xp = torch.nn.functional.pad(x, (0, pad))
         bp = None if bias is None else torch.nn.functional.pad(_as_f32(bias, "bias"), (0, pad))
-        return segment_aggregate(xp, idx, off, w, n_out=n_out, plan=plan, bias=bp, relu=relu, ordered=ordered)[:, :f]
+        return segment_aggregate(xp, idx, off, w, n_out=n_out, plan=plan, bias=bp, relu=relu, ordered=ordered,
+                                 reserve_ctas=reserve_ctas)[:, :f]
     if out is None:
         if accumulate:
             raise RuntimeError("accumulate=True needs the tensor to add to (out=)")
         out = torch.empty((n_out, f), dtype=torch.float32, device=x.device)
     chunk = plan.chunk if plan is not None else 0
     ws = workspace(lib().jg_aggregate_workspace_bytes(n_out, nnz, f, chunk), x.device)
+    if reserve_ctas:
+        b = None if bias is None else _as_f32(bias, "bias")
+        if b is not None and b.numel() != f:
+            raise RuntimeError(f"bias has {b.numel()} entries, the feature width is {f}")
+        check(lib().jg_aggregate_opts_f32(ptr(out), ptr(x), ptr(idx), ptr(off), ptr(w), ptr(b), 1 if relu else 0,
+                                          1 if accumulate else 0, 1 if ordered else 0, int(reserve_ctas), n_out, n_in, f, nnz,
+                                          ptr(plan.buf) if plan is not None else None, chunk, ptr(ws), ws.numel(),
+                                          stream_for(x)), "jg_aggregate_opts_f32")
+        return out
     if bias is not None or relu:
         if accumulate:
             raise RuntimeError("segment_aggregate: the fused epilogue cannot be combined with accumulate=True")
@@ -603,18 +615,22 @@ def linear_tf32_supported(n_rows, k, m):
     return bool(lib().jg_gemm_tf32_supported(int(n_rows), int(k), int(m)))
 
 
-def linear_tf32(x, weight, bias=None, relu=False, weight_t=None, check_status=False):
+def linear_tf32(x, weight, bias=None, relu=False, weight_t=None, check_status=False, out=None):
     """``act(x @ weight + bias)`` on the tcgen05 tensor cores (TF32 products, fp32 accumulation):
     the dense feature transform of the layers (nn/conv/gcn_conv.py:95, nn/conv/gat_conv.py:86).
     ``weight`` is ``[k, m]`` as the layers store it; ``weight_t`` may carry its cached transpose.
-    Forward only.  ``check_status=True`` synchronises and raises if a bounded wait in the kernel
+    Forward only.  ``out`` receives the result in place (e.g. the feature buffer of a partitioned
+    aggregation).  ``check_status=True`` synchronises and raises if a bounded wait in the kernel
     ran out."""
     x = _as_f32(x, "x")
     n, k = x.shape
     m = weight.shape[1]
     wt = weight_t if weight_t is not None else _as_f32(weight, "weight").t().contiguous()
     b = None if bias is None else _as_f32(bias, "bias")
-    out = torch.empty((n, m), dtype=torch.float32, device=x.device)
+    if out is None:
+        out = torch.empty((n, m), dtype=torch.float32, device=x.device)
+    elif out.shape != (n, m) or out.dtype != torch.float32 or not out.is_contiguous():
+        raise RuntimeError(f"out: expected a contiguous float32 [{n}, {m}] tensor")
     ws = workspace(lib().jg_gemm_tf32_workspace_bytes(), x.device)
     st = stream_for(x)
     check(lib().jg_gemm_tf32(ptr(out), ptr(x), ptr(wt), ptr(b), n, k, m, 1 if relu else 0, ptr(ws), ws.numel(), st),

@@ -17,12 +17,12 @@ def _gen(seed, device):
     return g
 
 
-def rmat_edges(scale, n_edges, seed, device="cpu", a=0.57, b=0.19, c=0.19, batch=1 << 24):
-    """R-MAT edge list: each edge picks one quadrant per bit level with
+def rmat_edge_batches(scale, n_edges, seed, device="cpu", a=0.57, b=0.19, c=0.19, batch=1 << 24):
+    """R-MAT edge list in batches: each edge picks one quadrant per bit level with
     probabilities (a, b, c, d); bit k of (src, dst) is the (row, column) half
-    chosen at level k.  No noise.  Returns int64 ``src, dst`` of length n_edges."""
+    chosen at level k.  No noise.  Yields int64 ``(src, dst)`` pairs of tensors; the stream depends
+    only on (seed, device type, batch), so every rank of a job can regenerate it."""
     g = _gen(seed, device)
-    srcs, dsts = [], []
     ab, abc = a + b, a + b + c
     for start in range(0, n_edges, batch):
         m = min(batch, n_edges - start)
@@ -34,9 +34,65 @@ def rmat_edges(scale, n_edges, seed, device="cpu", a=0.57, b=0.19, c=0.19, batch
             col_bit = ((r >= a) & (r < ab) | (r >= abc)).to(torch.int64)  # quadrants b, d
             src |= row_bit << level
             dst |= col_bit << level
-        srcs.append(src)
-        dsts.append(dst)
+        yield src, dst
+
+
+def rmat_edges(scale, n_edges, seed, device="cpu", a=0.57, b=0.19, c=0.19, batch=1 << 24):
+    """All batches of :func:`rmat_edge_batches` as one int64 ``src, dst`` pair of length n_edges."""
+    srcs, dsts = zip(*rmat_edge_batches(scale, n_edges, seed, device, a, b, c, batch))
     return torch.cat(srcs), torch.cat(dsts)
+
+
+def rmat_shard_csc(scale, edge_factor, seed, lo, hi, device="cpu", relabel=True, degrees=None):
+    """Destination rows ``[lo, hi)`` of the gcn-normalised graph of :func:`rmat_graph` (symmetrised,
+    deduplicated, relabelled, one self-loop per node), built WITHOUT materialising the whole graph:
+    the edge stream is regenerated batch by batch and only the entries whose destination lies in
+    the range are kept.  Returns ``(row_indices int32 [global source ids], column_offset int32,
+    in_degree int32 [hi - lo])`` in the layout ``gcn_norm`` + ``cootocsc`` give for those rows
+    (sources ascending within a column, the loop last); weights follow from the degrees of both
+    endpoints (:func:`gcn_weights`), the remote ones gathered from their owners."""
+    n = 1 << scale
+    perm = torch.randperm(n, generator=_gen(seed + 1, device), device=device) if relabel else None
+    keys = []
+    held = 0
+    for src, dst in rmat_edge_batches(scale, edge_factor * n, seed, device):
+        if perm is not None:
+            src, dst = perm[src], perm[dst]
+        keep = src != dst
+        src, dst = src[keep], dst[keep]
+        for a, b in ((src, dst), (dst, src)):                    # the edge and its mirror image
+            m = (b >= lo) & (b < hi)
+            keys.append((b[m] - lo) * n + a[m])                  # (destination, source): CSC order when sorted
+            held += int(keys[-1].numel())
+        if held > (1 << 28):                                     # bound the working set: merge what has been collected
+            keys = [torch.unique(torch.cat(keys))]
+            held = int(keys[0].numel())
+    key = torch.unique(torch.cat(keys)) if keys else torch.empty(0, dtype=torch.int64, device=device)
+    del keys
+    col = key // n
+    src = (key - col * n).to(torch.int32)
+    counts = torch.bincount(col, minlength=hi - lo)
+    del key
+    deg = (counts + 1).to(torch.int32)                           # in-edges + the loop
+    off = torch.zeros(hi - lo + 1, dtype=torch.int64, device=device)
+    off[1:] = torch.cumsum(counts + 1, 0)
+    # entries shift right by one place per earlier column (its loop); the loop closes each column
+    idx = torch.empty(int(off[-1]), dtype=torch.int32, device=device)
+    pos = torch.arange(src.numel(), device=device, dtype=torch.int64) + col
+    idx[pos] = src
+    idx[off[1:] - 1] = torch.arange(lo, hi, device=device, dtype=torch.int32)
+    assert int(off[-1]) < 2**31
+    return idx, off.to(torch.int32), deg
+
+
+def gcn_weights(idx, off, deg_global, lo):
+    """``gcn_norm`` weights of a CSC shard with unit input weights: ``(dis[src] * 1) * dis[dst]``,
+    ``dis = deg^-1/2`` rounded to fp32 from double (nn/conv/gcn_conv.py:35-37), bit for bit what the
+    fused conversion kernel writes."""
+    dis = (1.0 / deg_global.double().sqrt()).float()
+    n_rows = off.numel() - 1
+    col = torch.repeat_interleave(torch.arange(lo, lo + n_rows, device=idx.device), (off[1:] - off[:-1]).long())
+    return dis[idx.long()] * dis[col]
 
 
 def symmetrise_dedupe(src, dst, n, relabel_seed=None):

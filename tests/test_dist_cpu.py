@@ -78,6 +78,11 @@ def worker(rank, world, port, n, E, f, q, mode):
         # two exchanges in flight before either aggregation is finished
         xa, xb = torch.from_numpy(x[lo:hi].copy()), torch.from_numpy(np.ascontiguousarray(x[lo:hi, :2]))
         pa, pb = g.start(xa), g.start(xb)
+        try:                                                    # a second exchange of a width still in flight would share its buffers
+            g.start(xa)
+            raise AssertionError("a second start of the same width must raise")
+        except RuntimeError as exc:
+            assert "already in flight" in str(exc)
         ya, yb = g.finish(pa), g.finish(pb)
         assert torch.equal(ya, y) and torch.equal(yb, g.aggregate(xb))
         if mode == "overlap":
@@ -342,3 +347,55 @@ def test_row_partition_bounds():
     assert [p.n_local(r) for r in range(4)] == [1, 1, 1, 0]
     with pytest.raises(ValueError):
         RowPartition(5, 0)
+
+
+def silent_worker(rank, world, port, n, E, f, q):
+    """Rank ``world - 1`` builds its graph and then never starts the exchange."""
+    sys.path.insert(0, ROOT)
+    import time
+    import torch.distributed as dist
+    from jittorgeometric_b200 import dist as jd
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        idx, off, w, x = make_graph(7, n, E, f)
+        part = jd.RowPartition(n, world)
+        lo, hi = part.range(rank)
+        shard = jd.shard_rows(torch.from_numpy(idx), torch.from_numpy(off), torch.from_numpy(w), part, rank)
+        g = jd.ShardedGraph(part, rank, *shard, backend=OracleBackend(), transport=jd.CollectiveTransport(timeout_s=3.0))
+        if rank == world - 1:
+            time.sleep(8.0)                                     # the failure: this rank never posts its halo rows
+            q.put((rank, "silent", 0.0))
+            return
+        t0 = time.perf_counter()
+        try:
+            g.aggregate(torch.from_numpy(x[lo:hi].copy()))
+            q.put((rank, "finished", time.perf_counter() - t0))
+        except jd.ExchangeTimeout as exc:
+            q.put((rank, "timeout", time.perf_counter() - t0))
+    except Exception as exc:
+        q.put((rank, repr(exc), -1.0))
+    finally:
+        # no destroy_process_group: its shutdown handshake would wait for the ranks that gave up
+        q.close()
+        q.join_thread()
+        os._exit(0)
+
+
+@pytest.mark.timeout(120)
+def test_a_rank_that_never_posts_its_halo_ends_in_a_timeout_not_a_hang(oracle):
+    """Failure detection on the host (three gloo ranks, one silent): the others' bounded wait for
+    the exchange raises ``ExchangeTimeout`` after the transport's limit instead of hanging."""
+    world, n, E, f = 3, 64, 1500, 5
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=silent_worker, args=(r, world, port, n, E, f, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = sorted(q.get(timeout=60) for _ in range(world))
+    for p in procs:
+        p.join(timeout=30)
+    assert got[world - 1][1] == "silent"
+    for rank, what, secs in got[: world - 1]:
+        assert what == "timeout", got
+        assert 2.0 <= secs <= 7.5, got

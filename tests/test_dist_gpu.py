@@ -113,6 +113,94 @@ def test_emulated_ranks_on_one_gpu(cuda, oracle, world, n, f, mode):
         assert torch.equal(z, torch.relu(torch.from_numpy(y).cuda() + bias))
 
 
+def build_emulated(jd, world, n, f, E=60000, seed=None, mode="merged", **kw):
+    idx, off, w, x = make_graph(world if seed is None else seed, n, E, f)
+    part = jd.RowPartition(n, world)
+    t = lambda a: torch.from_numpy(a).cuda()
+    idx_t, off_t, w_t = t(idx), t(off), t(w)
+    emu = jd.EmulatedRanks(world, **kw)
+    graphs = [jd.ShardedGraph(part, r, *jd.shard_rows(idx_t, off_t, w_t, part, r), transport=emu.transport(r), setup=False,
+                              mode=mode) for r in range(world)]
+    emu.wire(graphs)
+    for r, g in enumerate(graphs):                       # every rank's rows are in place before the first exchange
+        lo, hi = part.range(r)
+        g.feature_buffer(f).copy_(t(x[lo:hi].copy()))
+    return (idx, off, w, x), part, emu, graphs
+
+
+@pytest.mark.parametrize("mode", ["merged", "overlap"])
+@pytest.mark.parametrize("world,n,f,plain", [(2, 5001, 128, False), (4, 4096, 32, False), (8, 3000, 7, False), (3, 2500, 256, False),
+                                             (4, 4096, 64, True), (2, 40000, 512, False)])
+def test_direct_exchange_with_emulated_ranks(cuda, oracle, world, n, f, plain, mode):
+    """The peer-load exchange (epoch words, bulk-copy pull kernel, plain-load pull kernel for rows that
+    are not multiples of 16 bytes) with all ranks of the partition on one GPU, against the CPU checker
+    and bit for bit against the unpartitioned kernel."""
+    from jittorgeometric_b200 import dist as jd
+    (idx, off, w, x), part, emu, graphs = build_emulated(jd, world, n, f, E=20 * n, mode=mode, plain=plain)
+    want = oracle.aggregate(x, idx, off, w)
+    _, scale = oracle.aggregate_f64(x, idx, off, w)
+    t = lambda a: torch.from_numpy(a).cuda()
+    whole = cuda.ops.segment_aggregate(t(x), t(idx), t(off), t(w), plan=cuda.ops.SpmmPlan(t(off), len(idx))).cpu().numpy()
+    for r, g in enumerate(graphs):
+        lo, hi = part.range(r)
+        xr = g.feature_buffer(f)
+        y = g.aggregate(xr).cpu().numpy()
+        emu.transport(r).check()
+        # the halo rows that landed are exactly the referenced remote rows
+        halo = emu.buffer(f, r)[g.n_local: g.n_local + g.n_halo].cpu().numpy()
+        assert np.array_equal(halo, x[g.needed.cpu().numpy()])
+        assert (np.abs(y - want[lo:hi]) / (scale[lo:hi] + 1e-30)).max() <= 1e-5
+        if mode == "merged":
+            assert np.array_equal(y, whole[lo:hi])
+        y2 = g.aggregate(t(x[lo:hi].copy())).cpu().numpy()          # rows handed over in another tensor: copied in, next epoch
+        assert np.array_equal(y, y2)
+    # two widths in flight on one rank; the same width twice raises
+    g = graphs[0]
+    lo, hi = part.range(0)
+    f2 = 16 if f > 16 else 4
+    for r, h in enumerate(graphs):
+        a, b = part.range(r)
+        h.feature_buffer(f2).copy_(t(np.ascontiguousarray(x[a:b, :f2])))
+    pa, pb = g.start(g.feature_buffer(f)), g.start(g.feature_buffer(f2))
+    with pytest.raises(RuntimeError, match="already in flight"):
+        g.start(g.feature_buffer(f))
+    ya, yb = g.finish(pa), g.finish(pb, relu=True)
+    torch.cuda.synchronize()
+    want2 = oracle.aggregate(np.ascontiguousarray(x[:, :f2]), idx, off, w)
+    _, scale2 = oracle.aggregate_f64(np.ascontiguousarray(x[:, :f2]), idx, off, w)
+    assert (np.abs(ya.cpu().numpy() - want[lo:hi]) / (scale[lo:hi] + 1e-30)).max() <= 1e-5
+    assert (np.abs(yb.cpu().numpy() - np.maximum(want2[lo:hi], 0)) / (scale2[lo:hi] + 1e-30)).max() <= 1e-5
+
+
+def test_exchange_wait_runs_out_and_reports(cuda):
+    """Failure path of the exchange without any fault: a peer that never posts its rows.  The pull's
+    bounded wait runs out after the (short) limit, the kernel returns, the host raises ExchangeTimeout
+    with the silent rank's number, and the same context then runs a normal exchange."""
+    from jittorgeometric_b200 import dist as jd
+    (idx, off, w, x), part, emu, graphs = build_emulated(jd, 2, 3000, 64, wait_ms=20.0)
+    g, tr = graphs[0], emu.transport(0)
+    tr.post_for_peers = False                      # rank 1 stays silent
+    y = g.aggregate(g.feature_buffer(64))
+    torch.cuda.synchronize()                       # returns: the kernel gave up after 20 ms instead of spinning on
+    with pytest.raises(jd.ExchangeTimeout, match="rank 1 never posted"):
+        tr.check()
+    tr.post_for_peers = True
+    y = g.aggregate(g.feature_buffer(64))
+    torch.cuda.synchronize()
+    tr.check()
+    t = lambda a: torch.from_numpy(a).cuda()
+    whole = cuda.ops.segment_aggregate(t(x), t(idx), t(off), t(w), plan=cuda.ops.SpmmPlan(t(off), len(idx)))
+    assert torch.equal(y, whole[: g.n_local])
+    # the done-word wait of an owner whose reader never reports
+    lib = __import__("jittorgeometric_b200._lib", fromlist=["lib"])
+    err = torch.zeros(1, dtype=torch.int32).pin_memory()
+    import ctypes
+    lib.check(lib.lib().jg_halo_wait(lib.ptr(emu.flags[0]), 2, 0, 5, 1, 7, ctypes.c_void_p(err.data_ptr()), 5_000_000,
+                                     lib.stream_for(emu.flags[0])), "jg_halo_wait")
+    torch.cuda.synchronize()
+    assert int(err[0]) == 0x200 + 1
+
+
 def test_accumulate_mode(cuda, oracle):
     idx, off, w, x = make_graph(1, 2000, 30000, 64)
     t = lambda a: torch.from_numpy(a).cuda()
@@ -131,8 +219,10 @@ def nccl_worker(rank, world, port, n, E, f, q, exchange):
     from jittorgeometric_b200 import dist as jd
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
+    import datetime
+    os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"
     dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
-                            device_id=torch.device("cuda", rank))
+                            device_id=torch.device("cuda", rank), timeout=datetime.timedelta(seconds=90))
     try:
         idx, off, w, x = make_graph(11, n, E, f)
         part = jd.RowPartition(n, world)
@@ -218,8 +308,10 @@ def train_worker(rank, world, port, n, f, hidden, classes, steps, q):
     from jittorgeometric_b200 import dist as jd
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
+    import datetime
+    os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"
     dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
-                            device_id=torch.device("cuda", rank))
+                            device_id=torch.device("cuda", rank), timeout=datetime.timedelta(seconds=90))
     try:
         idx, off, w, x = make_symmetric(21, n, f)
         rng = np.random.default_rng(22)
@@ -229,7 +321,7 @@ def train_worker(rank, world, port, n, f, hidden, classes, steps, q):
         t = lambda a: torch.from_numpy(a).cuda()
         g = jd.ShardedGraph(part, rank, *jd.shard_rows(t(idx), t(off), t(w), part, rank), exchange="nccl", mode="merged")
         mgr = jd.DistributedManager()
-        model = jd.ShardedGCN(f, hidden, classes, layers=2, manager=mgr, device="cuda", seed=300 + rank)
+        model = jd.ShardedGCN(f, hidden, classes, layers=2, manager=mgr, device="cuda", seed=300 + rank, tf32=False)
         opt = torch.optim.SGD(model.parameters(), lr=0.5)
         losses = [jd.sharded_training_step(model, g, t(x[lo:hi].copy()), t(labels[lo:hi].copy()), t(mask[lo:hi].copy()), opt, mgr)
                   for _ in range(steps)]
@@ -284,3 +376,46 @@ def test_nccl_training_step(cuda):
         assert np.allclose(losses, want_losses, rtol=1e-4, atol=1e-5)
         for have, want in zip(weights, W):
             assert np.abs(have - want.detach().numpy()).max() <= 1e-4
+
+
+def test_training_step_on_one_gpu(cuda):
+    """``ShardedGCN`` + ``sharded_training_step`` on the device kernels with a one-rank process group
+    (the whole graph is the rank's shard): three SGD steps equal dense float64 training.  The
+    multi-rank version of the same check needs two GPUs (``test_nccl_training_step``) or CPU ranks
+    (tests/test_dist_cpu.py)."""
+    import torch.distributed as dist
+    from jittorgeometric_b200 import dist as jd
+    n, f, hidden, classes, steps = 3000, 32, 16, 5, 3
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1)
+    try:
+        idx, off, w, x = make_symmetric(21, n, f)
+        rng = np.random.default_rng(22)
+        labels, mask = rng.integers(0, classes, size=n).astype(np.int64), rng.random(n) < 0.5
+        t = lambda a: torch.from_numpy(a).cuda()
+        part = jd.RowPartition(n, 1)
+        g = jd.ShardedGraph(part, 0, t(idx), t(off), t(w), exchange="nccl", mode="merged")
+        mgr = jd.DistributedManager()
+        model = jd.ShardedGCN(f, hidden, classes, layers=2, manager=mgr, device="cuda", seed=300, tf32=False)
+        opt = torch.optim.SGD(model.parameters(), lr=0.5)
+        losses = [jd.sharded_training_step(model, g, t(x), t(labels), t(mask), opt, mgr) for _ in range(steps)]
+        torch.cuda.synchronize()
+        weights = [p.detach().cpu().numpy() for p in model.weights]
+    finally:
+        dist.destroy_process_group()
+    A = np.zeros((n, n))
+    np.add.at(A, (np.repeat(np.arange(n), np.diff(off)), idx), w.astype(np.float64))
+    A = torch.from_numpy(A)
+    ref = jd.ShardedGCN(f, hidden, classes, layers=2, manager=None, seed=300)
+    W = [p.detach().double().requires_grad_(True) for p in ref.weights]
+    X, L, M = torch.from_numpy(x).double(), torch.from_numpy(labels), torch.from_numpy(mask)
+    for k in range(steps):
+        h = X
+        for wt in W:
+            h = (A @ h) @ wt
+        loss = torch.nn.functional.nll_loss(torch.log_softmax(h, dim=1)[M], L[M])
+        grads = torch.autograd.grad(loss, W)
+        assert abs(losses[k] - float(loss.detach())) <= 1e-4 * abs(float(loss.detach())) + 1e-5
+        W = [(wt - 0.5 * gr).detach().requires_grad_(True) for wt, gr in zip(W, grads)]
+    for have, want in zip(weights, W):
+        assert np.abs(have - want.detach().numpy()).max() <= 1e-4
