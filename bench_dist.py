@@ -92,11 +92,12 @@ def gcn_forward_record(args, dev, rank, world, sampler_cls=None):
     b1 = torch.linspace(-0.1, 0.1, 128, device=dev)
     b2 = torch.linspace(-0.1, 0.1, 64, device=dev)
     x = torch.randn((n_local, 128), device=dev, generator=torch.Generator(device=dev).manual_seed(feature_seed(seed, rank, 128)))
-    halo_rows = 0
+    halo_rows, halo_half = 0, False
     if world > 1:
         g = jd.ShardedGraph(part, rank, idx, off, w, exchange=args.exchange, mode="merged")
         if g.direct:
             g.transport.pull_ctas = 0            # nothing runs beside a layer's exchange: the pull may take every SM
+            g.halo_half = halo_half = args.gcn_halo == "fp16"
         halo_rows = g.n_halo
         del idx, w
 
@@ -175,7 +176,8 @@ def gcn_forward_record(args, dev, rank, world, sampler_cls=None):
                        f"scale {scale}, {n} nodes, {nnz} directed edges incl. self-loops, gcn_norm weights; {world} contiguous "
                        f"destination-row shard(s), each generated and converted by its own rank",
            "alg_gbs_per_gpu": alg / world / ms / 1e6, "frac_of_hbm_peak_per_gpu": alg / world / ms / 1e6 / peak, "peak_kind": kind,
-           "halo_rows_rank0": halo_rows, "halo_bytes_per_forward_rank0": halo_rows * (128 + 64) * 4,
+           "halo_payload": None if world == 1 else ("fp16 (rows widened to fp32 on arrival; own rows fp32)" if halo_half else "fp32"),
+           "halo_rows_rank0": halo_rows, "halo_bytes_per_forward_rank0": halo_rows * (128 + 64) * (2 if halo_half else 4),
            "remote_rows_rank0": n - n_local, "phases_ms_max_over_ranks": phases or None,
            "output_finite": finite, "peak_device_memory_gb": peak_mem, "graph_build_s": t_build, "clocks": clocks}
     return rec
@@ -214,6 +216,8 @@ def run(args):
     part = jd.RowPartition(n, world)
     idx, off, w, nnz = build_shard(args.scale, args.edge_factor, bench.SEED, part, rank, world, dev)
     g = jd.ShardedGraph(part, rank, idx, off, w, exchange=args.exchange, mode=os.environ.get("JG_DIST_MODE", "merged"))
+    if g.direct and "JG_PULL_CTAS" in os.environ:
+        g.transport.pull_ctas = int(os.environ["JG_PULL_CTAS"])
     local_nnz = idx.numel()
     halo_rows, remote_rows = g.n_halo, n - g.n_local
 
@@ -252,6 +256,25 @@ def run(args):
     ms = torch.tensor([t0.elapsed_time(t1) / args.steps], device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms_step = float(ms.item())
+
+    # where the time of a step goes (one extra, untimed step; events around every aggregation)
+    breakdown = None
+    if g.direct:
+        ev = {f: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for f in widths}
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+        e0.record()
+        pending = [g.start(xs[f]) for f in widths]
+        for f, p in zip(widths, pending):
+            p[2].wait()
+            ev[f][0].record()
+            g.finish(p)
+            ev[f][1].record()
+        e1.record()
+        torch.cuda.synchronize()
+        breakdown = {"step_ms": e0.elapsed_time(e1),
+                     "aggregate_ms": {str(f): ev[f][0].elapsed_time(ev[f][1]) for f in widths},
+                     "start_of_aggregate_ms": {str(f): e0.elapsed_time(ev[f][0]) for f in widths}}
 
     # parity after the timed region: this rank's rows against the reference's CPU aggregation
     pf = 128 if 128 in widths else widths[-1]
@@ -349,6 +372,7 @@ def run(args):
                      "bytes_per_step_rank0": halo_rows * 4 * sum(widths)},
             "exchange": "referenced remote rows only (%.0f %% of the remote rows on rank 0), " % (
                 100.0 * halo_rows / max(remote_rows, 1)) + exchange_text,
+            "breakdown_rank0": breakdown,
             "parity": par, "parity_ok": bool(float(okmin[0]) == 1.0),
             "gcn_forward": gcn,
             "clocks": clocks,

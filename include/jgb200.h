@@ -182,7 +182,15 @@ int jg_halo_wait(const void* my_flags, int world, int rank, int slot, int kind, 
                  int64_t wait_ns, jg_stream_t stream);
 int jg_halo_pull(void* halo, const int32_t* needed, void* const* peer_x_host, void* const* peer_flags_host,
                  const int64_t* seg_begin_host, const int32_t* lo_host, int world, int rank, int64_t row_bytes, int slot,
-                 uint32_t epoch, void* counter, int32_t* error, int64_t wait_ns, int max_ctas, int plain, jg_stream_t stream);
+                 uint32_t epoch, void* counter, int32_t* error, int64_t wait_ns, int max_ctas, int plain, int src_half,
+                 jg_stream_t stream);
+/* Half-width payload of the exchange: jg_rows_to_half rounds n_values fp32 values (a multiple of 4) to
+ * fp16 (values beyond +-65504 saturate), the copy of its rows an owner offers; jg_halo_pull with
+ * src_half != 0 then reads rows of row_bytes = 2 * width bytes (a multiple of 16) from the peers' fp16
+ * buffers and widens them to fp32 halo rows of 2 * row_bytes.  Every aggregated element stays within
+ * 5e-4 of the fp32 exchange relative to its sum of absolute terms: for the workloads whose tolerance is
+ * 2e-3 (a TF32/bf16 transform feeds the aggregation).  The fp32 exchange is bit-exact. */
+int jg_rows_to_half(void* out, const float* x, int64_t n_values, jg_stream_t stream);
 
 /* ------------------------------------------------------------------ conversion
  * COO -> CSR (by = 0, rows keyed by source) or CSC (by = 1, columns keyed by destination).

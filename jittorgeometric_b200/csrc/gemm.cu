@@ -47,6 +47,8 @@ struct GemmParams {
     const float* wt;
     int32_t plain_loads;
     int32_t tma_store;   // epilogue stages 32x32 blocks in shared memory and stores them by TMA
+    int32_t ldo;         // row pitch of the output in floats (the full width when m is one column tile of it)
+    int32_t col_base;    // first output column of this tile (out, bias and wt already point at it)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -79,6 +81,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 // 4-byte asynchronous global->shared copy; valid == false writes zeros.
 __device__ __forceinline__ void cp_async4(uint32_t smem_dst, const float* src, bool valid) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_dst), "l"(src), "r"(valid ? 4 : 0) : "memory");
+}
+
+// 8-byte variant (row pitch and base a multiple of 8 bytes): half the requests per tile.
+__device__ __forceinline__ void cp_async8(uint32_t smem_dst, const float* src, bool valid) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(smem_dst), "l"(src), "r"(valid ? 8 : 0) : "memory");
 }
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -205,9 +212,34 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 const uint32_t round = it / kStages;
                 if (round > 0 && !mbar_wait(&ctl->empty[s], (round - 1) & 1)) { ok = false; break; }
                 const uint32_t a_dst = smem_u32(ring + s * stage_bytes);
+                const int64_t row0 = (int64_t)tile * kTileM;
+                if (p.plain_loads == 2) {
+                    // even K: a lane copies two neighbouring values, a half-warp one 128-byte row segment, a
+                    // warp two rows per instruction
+                    const uint32_t half = (uint32_t)lane >> 4, hl = (uint32_t)lane & 15u;
+                    const int kc = kb * kTileK + 2 * (int)hl;
+                    const bool kin2 = kc < p.k;
+                    const uint32_t col_off = (hl & 1u) * 8u;
+                    const float* src2 = p.x + row0 * p.k + kc;
+#pragma unroll 8
+                    for (uint32_t rr = pw; rr < (uint32_t)kTileM / 2; rr += kPlainWarps) {
+                        const uint32_t r = 2 * rr + half;
+                        const bool in = kin2 && row0 + r < p.n_rows;
+                        cp_async8(a_dst + r * 128 + (((hl >> 1) ^ (r & 7)) << 4) + col_off, in ? src2 + (int64_t)r * p.k : p.x, in);
+                    }
+                    const uint32_t b_dst2 = a_dst + a_bytes;
+                    const float* wsrc2 = p.wt + kc;
+#pragma unroll 8
+                    for (uint32_t rr = pw; rr < b_rows / 2; rr += kPlainWarps) {
+                        const uint32_t r = 2 * rr + half;
+                        const bool in = kin2 && (int)r < p.m;
+                        cp_async8(b_dst2 + r * 128 + (((hl >> 1) ^ (r & 7)) << 4) + col_off, in ? wsrc2 + (int64_t)r * p.k : p.wt, in);
+                    }
+                    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&ctl->full[s])) : "memory");
+                    continue;
+                }
                 const int kcol = kb * kTileK + lane;
                 const bool kin = kcol < p.k;
-                const int64_t row0 = (int64_t)tile * kTileM;
                 // asynchronous 4-byte copies straight into shared memory (zero-filled outside the
                 // matrix): nothing waits here, the barrier counts the copies as they land
                 const float* src = p.x + row0 * p.k + kcol;
@@ -280,7 +312,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         // alternate 32-column chunks.
         const int quad = warp & 3;
         const int half = (warp - 2) >> 2;
-        const bool full_chunks = (p.m % 32) == 0;
+        const bool full_chunks = (p.m % 32) == 0 && (p.ldo % 4) == 0;   // 16-byte stores need 16-byte aligned row starts
         uint32_t local_tile = 0;
         for (int tile = blockIdx.x; tile < p.n_tiles && !*abort_flag; tile += gridDim.x, local_tile++) {
             const int b = local_tile & 1;
@@ -315,11 +347,11 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     __syncwarp();
                     if (lane == 0) {
                         asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
-                                     ::"l"(&map_out), "r"(c0), "r"(tile * kTileM + quad * 32), "r"(smem_u32(slab)) : "memory");
+                                     ::"l"(&map_out), "r"(p.col_base + c0), "r"(tile * kTileM + quad * 32), "r"(smem_u32(slab)) : "memory");
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
                 } else if (row < p.n_rows) {
-                    float* o = p.out + row * p.m + c0;
+                    float* o = p.out + row * p.ldo + c0;
                     if (p.bias) {
 #pragma unroll
                         for (int i = 0; i < 32; i++)
@@ -396,25 +428,16 @@ using namespace jg;
 extern "C" {
 
 int jg_gemm_tf32_supported(int64_t n_rows, int64_t k, int64_t m) {
-    return n_rows > 0 && k > 0 && m > 0 && m <= 256 && n_rows < ((int64_t)1 << 31) * 64;
+    return n_rows > 0 && k > 0 && m > 0 && m <= 4096 && k < (1 << 20) && n_rows < ((int64_t)1 << 31) * 64;
 }
 
 size_t jg_gemm_tf32_workspace_bytes(void) { return 256; }
 
-int jg_gemm_tf32(float* out, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k, int64_t m,
-                 int relu, void* workspace, size_t workspace_bytes, jg_stream_t stream) {
-    JG_CHECK_ARG(n_rows >= 0 && k > 0 && m > 0, JG_EINVAL, "gemm_tf32: bad size");
-    if (n_rows == 0) return JG_OK;
-    JG_CHECK_ARG(out && x && wt, JG_EINVAL, "gemm_tf32: null pointer");
-    if (!jg_gemm_tf32_supported(n_rows, k, m)) {
-        set_error("gemm_tf32: needs m <= 256 (got k=%lld, m=%lld)", (long long)k, (long long)m);
-        return JG_EUNSUPPORTED;
-    }
-    JG_CHECK_ARG(reinterpret_cast<uintptr_t>(out) % 16 == 0, JG_EINVAL, "gemm_tf32: out must be 16-byte aligned");
+// One column tile (at most 256 output columns) of the product.
+static int gemm_tile(float* out, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k, int64_t m,
+                     int64_t m_total, int64_t col_base, int relu, int32_t* error, cudaStream_t st) {
     // TMA needs 16-byte aligned bases and row pitches; anything else goes through the plain-load producer
     const bool plain = (k % 4 != 0) || ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wt)) % 16 != 0);
-    JG_CHECK_ARG(workspace && workspace_bytes >= 256, JG_EWORKSPACE, "gemm_tf32: workspace missing");
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int b_rows = (int)((m + 15) / 16 * 16);
     CUtensorMap map_x, map_w;
     memset(&map_x, 0, sizeof(map_x));
@@ -426,23 +449,25 @@ int jg_gemm_tf32(float* out, const float* x, const float* wt, const float* bias,
         if (rc != JG_OK) return rc;
     }
     GemmParams p = {};
-    p.x = x; p.wt = wt; p.plain_loads = plain ? 1 : 0;
+    // plain loads: 8-byte copies when every row starts on an 8-byte boundary, else 4-byte copies
+    const bool pairs = (k % 2 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wt)) % 8 == 0);
+    p.x = x; p.wt = wt; p.plain_loads = plain ? (pairs ? 2 : 1) : 0;
     // TMA store needs a 16-byte row pitch for the output
-    p.tma_store = (m % 4 == 0) ? 1 : 0;
+    p.tma_store = (m_total % 4 == 0 && m % 4 == 0) ? 1 : 0;
     CUtensorMap map_out;
     memset(&map_out, 0, sizeof(map_out));
     if (p.tma_store) {
-        int rc2 = make_map(&map_out, out, n_rows, m, 32);
+        int rc2 = make_map(&map_out, out - col_base, n_rows, m_total, 32);
         if (rc2 != JG_OK) return rc2;
     }
     p.out = out; p.bias = bias; p.n_rows = n_rows; p.k = (int32_t)k; p.m = (int32_t)m; p.relu = relu;
+    p.ldo = (int32_t)m_total; p.col_base = (int32_t)col_base;
     int pad = 32;
     while (pad < b_rows) pad *= 2;
     p.m_pad = pad;
     p.n_tiles = (int32_t)((n_rows + kTileM - 1) / kTileM);
     p.k_blocks = (int32_t)((k + kTileK - 1) / kTileK);
-    p.error = static_cast<int32_t*>(workspace);
-    JG_CUDA(cudaMemsetAsync(p.error, 0, sizeof(int32_t), st));
+    p.error = error;
     const size_t a_bytes = kTileM * kTileK * 4;
     const size_t b_bytes = ((size_t)b_rows * kTileK * 4 + 1023) / 1024 * 1024;
     const size_t smem = 1024 + kStages * (a_bytes + b_bytes) + (p.tma_store ? kEpiWarps * 4096 : 0) + sizeof(GemmSmem) + 64;
@@ -457,6 +482,29 @@ int jg_gemm_tf32(float* out, const float* x, const float* wt, const float* bias,
     if (grid > p.n_tiles) grid = p.n_tiles;
     gemm_tf32_kernel<<<grid, kGemmThreads, smem, st>>>(map_x, map_w, map_out, p);
     JG_LAUNCH_CHECK();
+    return JG_OK;
+}
+
+int jg_gemm_tf32(float* out, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k, int64_t m,
+                 int relu, void* workspace, size_t workspace_bytes, jg_stream_t stream) {
+    JG_CHECK_ARG(n_rows >= 0 && k > 0 && m > 0, JG_EINVAL, "gemm_tf32: bad size");
+    if (n_rows == 0) return JG_OK;
+    JG_CHECK_ARG(out && x && wt, JG_EINVAL, "gemm_tf32: null pointer");
+    if (!jg_gemm_tf32_supported(n_rows, k, m)) {
+        set_error("gemm_tf32: needs m <= 4096 (got k=%lld, m=%lld)", (long long)k, (long long)m);
+        return JG_EUNSUPPORTED;
+    }
+    JG_CHECK_ARG(reinterpret_cast<uintptr_t>(out) % 16 == 0, JG_EINVAL, "gemm_tf32: out must be 16-byte aligned");
+    JG_CHECK_ARG(workspace && workspace_bytes >= 256, JG_EWORKSPACE, "gemm_tf32: workspace missing");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int32_t* error = static_cast<int32_t*>(workspace);
+    JG_CUDA(cudaMemsetAsync(error, 0, sizeof(int32_t), st));
+    // wider outputs: one launch per tile of 256 columns (x is read once per tile)
+    for (int64_t cb = 0; cb < m; cb += 256) {
+        const int64_t mt = m - cb < 256 ? m - cb : 256;
+        int rc = gemm_tile(out + cb, x, wt + cb * k, bias ? bias + cb : nullptr, n_rows, k, mt, m, cb, relu, error, st);
+        if (rc != JG_OK) return rc;
+    }
     return JG_OK;
 }
 

@@ -172,6 +172,30 @@ def test_direct_exchange_with_emulated_ranks(cuda, oracle, world, n, f, plain, m
     assert (np.abs(yb.cpu().numpy() - np.maximum(want2[lo:hi], 0)) / (scale2[lo:hi] + 1e-30)).max() <= 1e-5
 
 
+@pytest.mark.parametrize("world,n,f", [(2, 5001, 128), (4, 4096, 64), (8, 3000, 8)])
+def test_half_width_halo_payload(cuda, oracle, world, n, f):
+    """fp16 halo payload: what lands is the fp16 rounding of the remote rows, the rank's own rows stay
+    fp32, the aggregation equals the unpartitioned kernel on exactly that mixed input and stays within
+    5e-4 (fp16 unit roundoff 2^-11) of the fp32 result."""
+    from jittorgeometric_b200 import dist as jd
+    (idx, off, w, x), part, emu, graphs = build_emulated(jd, world, n, f, E=20 * n)
+    t = lambda a: torch.from_numpy(a).cuda()
+    x16 = t(x).to(torch.float16).float().cpu().numpy()          # round to nearest even
+    _, scale = oracle.aggregate_f64(x, idx, off, w)
+    want_full = oracle.aggregate(x, idx, off, w)
+    for r, g in enumerate(graphs):
+        g.halo_half = True
+        lo, hi = part.range(r)
+        y = g.aggregate(g.feature_buffer(f)).cpu().numpy()
+        emu.transport(r).check()
+        halo = emu.buffer(f, r)[g.n_local: g.n_local + g.n_halo].cpu().numpy()
+        assert np.array_equal(halo, x16[g.needed.cpu().numpy()])
+        mixed = x16.copy(); mixed[lo:hi] = x[lo:hi]
+        whole = cuda.ops.segment_aggregate(t(mixed), t(idx), t(off), t(w), plan=cuda.ops.SpmmPlan(t(off), len(idx))).cpu().numpy()
+        assert np.array_equal(y, whole[lo:hi])
+        assert (np.abs(y - want_full[lo:hi]) / (scale[lo:hi] + 1e-30)).max() <= 5e-4
+
+
 def test_exchange_wait_runs_out_and_reports(cuda):
     """Failure path of the exchange without any fault: a peer that never posts its rows.  The pull's
     bounded wait runs out after the (short) limit, the kernel returns, the host raises ExchangeTimeout

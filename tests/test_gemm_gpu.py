@@ -24,7 +24,8 @@ def run(cuda, n, k, m, bias, relu, seed=0):
 
 @pytest.mark.parametrize("n,k,m", [(128, 32, 16), (1000, 128, 128), (5000, 256, 64), (3000, 128, 7), (777, 64, 256),
                                    (20000, 128, 64), (129, 36, 24), (40000, 604, 64),
-                                   (5000, 602, 64), (2708, 1433, 256), (300, 7, 5), (1000, 33, 16)])
+                                   (5000, 602, 64), (2708, 1433, 256), (300, 7, 5), (1000, 33, 16),
+                                   (3000, 128, 300), (2000, 64, 512), (1500, 1433, 600), (900, 602, 1030), (233000, 602, 64)])
 def test_against_float64(cuda, n, k, m):
     assert cuda.ops.linear_tf32_supported(n, k, m)
     got, want, scale = run(cuda, n, k, m, bias=False, relu=False, seed=n + k + m)
@@ -50,9 +51,10 @@ def test_runs_are_identical_and_large(cuda):
 
 def test_unsupported_shapes_are_refused(cuda):
     assert cuda.ops.linear_tf32_supported(100, 602, 64)          # row pitch not a multiple of 16 bytes: plain-load producer
-    assert not cuda.ops.linear_tf32_supported(100, 128, 257)
+    assert cuda.ops.linear_tf32_supported(100, 128, 257)          # wider than one accumulator: 256-column tiles
+    assert not cuda.ops.linear_tf32_supported(100, 128, 5000)
     with pytest.raises(RuntimeError):
-        cuda.ops.linear_tf32(torch.zeros((10, 128), device="cuda"), torch.zeros((128, 300), device="cuda"))
+        cuda.ops.linear_tf32(torch.zeros((10, 128), device="cuda"), torch.zeros((128, 5000), device="cuda"))
 
 
 @pytest.mark.parametrize("n,k,m,relu", [(5000, 128, 64, True), (3001, 602, 64, True), (2048, 64, 128, False), (1000, 300, 16, False)])
@@ -91,7 +93,7 @@ def test_gcn_layer_trains_in_tf32(cuda):
     ei = torch.randint(0, n, (2, 40000), device="cuda", dtype=torch.int32)
     csc, csr = cuda.gcn_norm_csc_csr(ei, None, n)
     x = torch.randn(n, 128, device="cuda")
-    a, b = nn.GCNConv(128, 64, tf32=True, relu=True).cuda(), nn.GCNConv(128, 64, relu=True).cuda()
+    a, b = nn.GCNConv(128, 64, tf32=True, relu=True).cuda(), nn.GCNConv(128, 64, tf32=False, relu=True).cuda()
     with torch.no_grad():
         b.weight.copy_(a.weight)
     outs = []
