@@ -101,13 +101,16 @@ def gcn_forward_record(args, dev, rank, world, sampler_cls=None):
         halo_rows = g.n_halo
         del idx, w
 
+        fused_half = g.direct and halo_half       # the transform's epilogue also writes the fp16 rows the peers read
+
+        def transform(src, W, Wt, f):
+            h = g.feature_buffer(f, x)
+            jg.linear_tf32(src, W, weight_t=Wt, out=h, out_half=g.half_buffer(f) if fused_half else None)
+            return h
+
         def forward():
-            h1 = g.feature_buffer(128, x)
-            jg.linear_tf32(x, W1, weight_t=W1t, out=h1)
-            z1 = g.aggregate(h1, bias=b1, relu=True)
-            h2 = g.feature_buffer(64, x)
-            jg.linear_tf32(z1, W2, weight_t=W2t, out=h2)
-            return g.aggregate(h2, bias=b2)
+            z1 = g.aggregate(transform(x, W1, W1t, 128), bias=b1, relu=True, half_ready=fused_half)
+            return g.aggregate(transform(z1, W2, W2t, 64), bias=b2, half_ready=fused_half)
     else:
         plan = jg.SpmmPlan(off, nnz)
         h1 = torch.empty((n, 128), device=dev)
@@ -149,13 +152,11 @@ def gcn_forward_record(args, dev, rank, world, sampler_cls=None):
             torch.cuda.synchronize()
             phases[name] = phases.get(name, 0.0) + (time.perf_counter() - t0) * 1e3
             return r
-        h1 = g.feature_buffer(128, x)
-        timed("transform_ms", lambda: jg.linear_tf32(x, W1, weight_t=W1t, out=h1))
-        p = timed("exchange_ms", lambda: (lambda q: (q[2].wait(), q)[1])(g.start(h1)))
+        h1 = timed("transform_ms", lambda: transform(x, W1, W1t, 128))
+        p = timed("exchange_ms", lambda: (lambda q: (q[2].wait(), q)[1])(g.start(h1, fused_half)))
         z1 = timed("aggregate_ms", lambda: g.finish(p, b1, True))
-        h2 = g.feature_buffer(64, x)
-        timed("transform_ms", lambda: jg.linear_tf32(z1, W2, weight_t=W2t, out=h2))
-        p = timed("exchange_ms", lambda: (lambda q: (q[2].wait(), q)[1])(g.start(h2)))
+        h2 = timed("transform_ms", lambda: transform(z1, W2, W2t, 64))
+        p = timed("exchange_ms", lambda: (lambda q: (q[2].wait(), q)[1])(g.start(h2, fused_half)))
         out = timed("aggregate_ms", lambda: g.finish(p, b2))
         if g.direct:
             g.transport.check()
@@ -234,6 +235,7 @@ def run(args):
     def step():
         # the aggregations of a step are independent: every exchange is started first, so the halo rows of
         # the next width travel beside the current aggregation kernel
+        # (a start queued after an aggregation would wait for it in stream order, so all starts come first)
         pending = [g.start(xs[f]) for f in widths]
         return [g.finish(p) for p in pending]
 
@@ -260,21 +262,30 @@ def run(args):
     # where the time of a step goes (one extra, untimed step; events around every aggregation)
     breakdown = None
     if g.direct:
+        g.transport.profile = True
         ev = {f: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for f in widths}
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        handles = {}
         torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
         e0.record()
-        pending = [g.start(xs[f]) for f in widths]
-        for f, p in zip(widths, pending):
+
+        def fin(f, p):
             p[2].wait()
             ev[f][0].record()
             g.finish(p)
             ev[f][1].record()
+        pending = [(f, g.start(xs[f])) for f in widths]
+        for f, p in pending:
+            handles[f] = p[2]
+            fin(f, p)
         e1.record()
         torch.cuda.synchronize()
+        g.transport.profile = False
         breakdown = {"step_ms": e0.elapsed_time(e1),
                      "aggregate_ms": {str(f): ev[f][0].elapsed_time(ev[f][1]) for f in widths},
-                     "start_of_aggregate_ms": {str(f): e0.elapsed_time(ev[f][0]) for f in widths}}
+                     "aggregate_starts_at_ms": {str(f): e0.elapsed_time(ev[f][0]) for f in widths},
+                     "pull_ms": {str(f): h.begun.elapsed_time(h.landed) for f, h in handles.items() if h is not None},
+                     "pull_starts_at_ms": {str(f): e0.elapsed_time(h.begun) for f, h in handles.items() if h is not None}}
 
     # parity after the timed region: this rank's rows against the reference's CPU aggregation
     pf = 128 if 128 in widths else widths[-1]

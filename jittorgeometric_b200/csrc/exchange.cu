@@ -143,6 +143,48 @@ __device__ __forceinline__ bool decode_block(const PullArgs& a, int64_t v, int& 
     return true;
 }
 
+// The next block a producer warp will request, with this lane's row ids already loaded: the ids of
+// block b + 1 are fetched while the copies of block b are being issued, so a lane never sits through a
+// dependent id load per row (that chain, about 2 us per row and lane, was the limit of the first version).
+constexpr int kMaxIdsPerLane = 8;   // rows_per_block <= 256
+struct BlockCursor {
+    int64_t v;
+    bool have;
+    int q, cnt;
+    int64_t r0;
+    int32_t ids[kMaxIdsPerLane];
+};
+__device__ __forceinline__ void cursor_advance(const PullArgs& a, BlockCursor& c, int64_t total_v, int lane) {
+    c.have = false;
+    while (c.v < total_v && !c.have) {
+        c.have = decode_block(a, c.v, c.q, c.r0, c.cnt);
+        c.v += gridDim.x;
+    }
+    if (c.have) {
+#pragma unroll
+        for (int j = 0; j < kMaxIdsPerLane; j++) {
+            const int i = lane + 32 * j;
+            c.ids[j] = i < c.cnt ? __ldg(a.needed + c.r0 + i) : 0;
+        }
+    }
+}
+// Requests the rows of the cursor's block: one bulk copy per row, completing on `bar`.
+__device__ __forceinline__ void cursor_issue(const PullArgs& a, const BlockCursor& c, uint32_t dst0, uint32_t bar, int lane) {
+    if (lane == 0)
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)c.cnt * a.row_bytes) : "memory");
+    const unsigned char* base = static_cast<const unsigned char*>(a.t.x[c.q]);
+    const int32_t lo = a.t.lo[c.q];
+#pragma unroll
+    for (int j = 0; j < kMaxIdsPerLane; j++) {
+        const int i = lane + 32 * j;
+        if (i < c.cnt) {
+            const unsigned char* src = base + (size_t)(c.ids[j] - lo) * a.row_bytes;
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(dst0 + (uint32_t)i * a.row_bytes), "l"(src), "r"(a.row_bytes), "r"(bar) : "memory");
+        }
+    }
+}
+
 // When the last CTA of a pull has finished, every owner learns that this rank has read its rows.
 __device__ __forceinline__ void finish_pull(const PullArgs& a, bool ok) {
     __syncthreads();
@@ -171,19 +213,16 @@ __global__ void __launch_bounds__(32) halo_pull_bulk_kernel(PullArgs a, uint32_t
     }
     __syncwarp();
     const int64_t total_v = (int64_t)a.max_blocks * (a.world - 1);
-    int64_t v_load = blockIdx.x, v_cons = blockIdx.x;
+    int64_t v_cons = blockIdx.x;
     uint32_t it_load = 0, it_cons = 0, ready_mask = 0;
     bool ok = true;
+    BlockCursor cur;
+    cur.v = blockIdx.x;
+    cursor_advance(a, cur, total_v, lane);
 
     auto issue_next = [&]() -> bool {
-        int q = 0, cnt = 0;
-        int64_t r0 = 0;
-        bool found = false;
-        while (v_load < total_v && !found) {
-            found = decode_block(a, v_load, q, r0, cnt);
-            v_load += gridDim.x;
-        }
-        if (!found) return false;
+        if (!cur.have) return false;
+        const int q = cur.q;
         if (!((ready_mask >> q) & 1u)) {   // first touch of this owner: its rows must have been posted
             int r = 1;
             if (lane == 0) r = wait_epoch(a.my_flags + flag_index(a.slot, 0, q), a.epoch, a.wait_ns) ? 1 : 0;
@@ -197,19 +236,9 @@ __global__ void __launch_bounds__(32) halo_pull_bulk_kernel(PullArgs a, uint32_t
             asm volatile("fence.proxy.async;" ::: "memory");   // the acquire orders generic accesses; the copies below are asynchronous-proxy reads
         }
         const int s = (int)(it_load % (uint32_t)n_stages);
-        const uint32_t bar = xsmem_u32(&full[s]);
-        if (lane == 0)
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)cnt * a.row_bytes) : "memory");
-        const unsigned char* base = static_cast<const unsigned char*>(a.t.x[q]);
-        const int32_t lo = a.t.lo[q];
-        const uint32_t dst0 = xsmem_u32(smem + (size_t)s * stage_bytes);
-        for (int i = lane; i < cnt; i += 32) {
-            const int32_t id = __ldg(a.needed + r0 + i);
-            const unsigned char* src = base + (size_t)(id - lo) * a.row_bytes;
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                         ::"r"(dst0 + (uint32_t)i * a.row_bytes), "l"(src), "r"(a.row_bytes), "r"(bar) : "memory");
-        }
+        cursor_issue(a, cur, xsmem_u32(smem + (size_t)s * stage_bytes), xsmem_u32(&full[s]), lane);
         it_load++;
+        cursor_advance(a, cur, total_v, lane);
         return true;
     };
 
@@ -283,18 +312,13 @@ __global__ void __launch_bounds__(160) halo_pull_half_kernel(PullArgs a, uint32_
     const int64_t total_v = (int64_t)a.max_blocks * (a.world - 1);
     const uint32_t dst_row_bytes = a.row_bytes * 2;     // fp32 rows on this side
     if (warp == 0) {
-        int64_t v = blockIdx.x;
         uint32_t it = 0, ready_mask = 0;
         bool ok = true;
-        while (ok) {
-            int q = 0, cnt = 0;
-            int64_t r0 = 0;
-            bool found = false;
-            while (v < total_v && !found) {
-                found = decode_block(a, v, q, r0, cnt);
-                v += gridDim.x;
-            }
-            if (!found) break;
+        BlockCursor cur;
+        cur.v = blockIdx.x;
+        cursor_advance(a, cur, total_v, lane);
+        while (ok && cur.have) {
+            const int q = cur.q;
             if (!((ready_mask >> q) & 1u)) {
                 int r = 1;
                 if (lane == 0) r = wait_epoch(a.my_flags + flag_index(a.slot, 0, q), a.epoch, a.wait_ns) ? 1 : 0;
@@ -313,19 +337,9 @@ __global__ void __launch_bounds__(160) halo_pull_half_kernel(PullArgs a, uint32_
                 ok = false;
                 break;
             }
-            const uint32_t bar = xsmem_u32(&full[s]);
-            if (lane == 0)
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)cnt * a.row_bytes) : "memory");
-            const unsigned char* base = static_cast<const unsigned char*>(a.t.x[q]);
-            const int32_t lo = a.t.lo[q];
-            const uint32_t dst0 = xsmem_u32(smem + (size_t)s * stage_bytes);
-            for (int i = lane; i < cnt; i += 32) {
-                const int32_t id = __ldg(a.needed + r0 + i);
-                const unsigned char* src = base + (size_t)(id - lo) * a.row_bytes;
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                             ::"r"(dst0 + (uint32_t)i * a.row_bytes), "l"(src), "r"(a.row_bytes), "r"(bar) : "memory");
-            }
+            cursor_issue(a, cur, xsmem_u32(smem + (size_t)s * stage_bytes), xsmem_u32(&full[s]), lane);
             it++;
+            cursor_advance(a, cur, total_v, lane);
         }
         if (!ok && lane == 0) {
             ctl->issued = it;
@@ -396,15 +410,22 @@ __global__ void __launch_bounds__(256) rows_to_half_kernel(__half* __restrict__ 
     }
 }
 
-// Any row size that is a multiple of 4 bytes: one warp per row, plain loads from peer memory.
-__global__ void __launch_bounds__(256) halo_pull_rows_kernel(PullArgs a) {
+// Plain loads from peer memory.  Bulk copies are issued at a fixed rate per SM whatever their size (about
+// 18 million a second on this part), so rows shorter than 1 KB are fetched faster by ordinary
+// 16-byte loads with many of them in flight: G lanes share a row (G * 16 bytes per step), 32 / G rows are
+// walked side by side, four steps unrolled.  HALF: the source rows are fp16 and are widened to fp32 here.
+// Rows that are not multiples of 16 bytes fall back to 4-byte loads, one warp per row.
+template <bool HALF>
+__global__ void __launch_bounds__(256) halo_pull_rows_kernel(PullArgs a, int lanes_per_row) {
     __shared__ int s_ok;
     const int lane = lane_id(), warp = threadIdx.x / 32;
     const int64_t total_v = (int64_t)a.max_blocks * (a.world - 1);
     uint32_t ready_mask = 0;
     bool ok = true;
-    const uint32_t words = a.row_bytes / 4;
-    const bool vec = (a.row_bytes % 16 == 0);
+    const bool vec = lanes_per_row > 0;       // 0: rows or pointers that 16-byte accesses cannot take
+    const uint32_t dst_row_bytes = HALF ? a.row_bytes * 2 : a.row_bytes;
+    const int G = vec ? lanes_per_row : 32, sub = lane / G, gl = lane % G, rows_per_step = 32 / G;
+    const uint32_t chunks = a.row_bytes / 16;     // 16-byte pieces of a source row
     for (int64_t v = blockIdx.x; v < total_v && ok; v += gridDim.x) {
         int q = 0, cnt = 0;
         int64_t r0 = 0;
@@ -422,14 +443,47 @@ __global__ void __launch_bounds__(256) halo_pull_rows_kernel(PullArgs a) {
         }
         const unsigned char* base = static_cast<const unsigned char*>(a.t.x[q]);
         const int32_t lo = a.t.lo[q];
-        for (int i = warp; i < cnt; i += 8) {
-            const int32_t id = __ldg(a.needed + r0 + i);
-            const unsigned char* src = base + (size_t)(id - lo) * a.row_bytes;
-            unsigned char* dst = a.halo + (size_t)(r0 + i) * a.row_bytes;
-            if (vec) {
-                for (uint32_t c = lane; c < words / 4; c += 32)
-                    reinterpret_cast<float4*>(dst)[c] = reinterpret_cast<const float4*>(src)[c];
-            } else {
+        if (vec) {
+            constexpr int U = 4;
+            for (int i0 = warp * rows_per_step * U; i0 < cnt; i0 += 8 * rows_per_step * U) {
+                int32_t id[U];
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    const int i = i0 + u * rows_per_step + sub;
+                    id[u] = i < cnt ? __ldg(a.needed + r0 + i) : lo;
+                }
+                for (uint32_t c = gl; c < chunks; c += G) {
+                    uint4 val[U];
+#pragma unroll
+                    for (int u = 0; u < U; u++) {
+                        const int i = i0 + u * rows_per_step + sub;
+                        val[u] = make_uint4(0, 0, 0, 0);
+                        if (i < cnt) val[u] = *reinterpret_cast<const uint4*>(base + (size_t)(id[u] - lo) * a.row_bytes + (size_t)c * 16);
+                    }
+#pragma unroll
+                    for (int u = 0; u < U; u++) {
+                        const int i = i0 + u * rows_per_step + sub;
+                        if (i >= cnt) continue;
+                        unsigned char* dst = a.halo + (size_t)(r0 + i) * dst_row_bytes;
+                        if (HALF) {
+                            const float2 p0 = __half22float2(*reinterpret_cast<const __half2*>(&val[u].x));
+                            const float2 p1 = __half22float2(*reinterpret_cast<const __half2*>(&val[u].y));
+                            const float2 p2 = __half22float2(*reinterpret_cast<const __half2*>(&val[u].z));
+                            const float2 p3 = __half22float2(*reinterpret_cast<const __half2*>(&val[u].w));
+                            reinterpret_cast<float4*>(dst)[2 * c] = make_float4(p0.x, p0.y, p1.x, p1.y);
+                            reinterpret_cast<float4*>(dst)[2 * c + 1] = make_float4(p2.x, p2.y, p3.x, p3.y);
+                        } else {
+                            reinterpret_cast<uint4*>(dst)[c] = val[u];
+                        }
+                    }
+                }
+            }
+        } else {
+            const uint32_t words = a.row_bytes / 4;
+            for (int i = warp; i < cnt; i += 8) {
+                const int32_t id = __ldg(a.needed + r0 + i);
+                const unsigned char* src = base + (size_t)(id - lo) * a.row_bytes;
+                unsigned char* dst = a.halo + (size_t)(r0 + i) * a.row_bytes;
                 for (uint32_t c = lane; c < words; c += 32)
                     reinterpret_cast<float*>(dst)[c] = reinterpret_cast<const float*>(src)[c];
             }
@@ -512,6 +566,7 @@ int jg_halo_pull(void* halo, const int32_t* needed, void* const* peer_x_host, vo
     // about 16 KB per stage, whole multiples of 32 rows
     int64_t rpb = (16384 / row_bytes) / 32 * 32;
     if (rpb < 32) rpb = 32;
+    if (rpb > 32 * kMaxIdsPerLane) rpb = 32 * kMaxIdsPerLane;
     a.rows_per_block = (int32_t)rpb;
     int64_t total_blocks = 0;
     a.max_blocks = 0;
@@ -530,10 +585,27 @@ int jg_halo_pull(void* halo, const int32_t* needed, void* const* peer_x_host, vo
     const bool bulk = !plain && row_bytes % 16 == 0 && (size_t)n_stages * stage_bytes <= 200 * 1024 &&
                       (reinterpret_cast<uintptr_t>(halo) % 16 == 0);
     int64_t grid = total_blocks;
-    if (max_ctas <= 0) max_ctas = sm_count();
+    if (max_ctas <= 0) max_ctas = 2 * sm_count();   // nothing runs beside this pull: two warps' worth of requests per SM
     if (max_ctas > 0xffff) max_ctas = 0xffff;
+    // bulk copies pay off from 1 KB rows on; shorter rows take the plain-load kernel
+    const bool use_bulk = bulk && row_bytes >= 1024;
+    int lanes_per_row = 1;
+    while (lanes_per_row < 32 && lanes_per_row * 16 < row_bytes) lanes_per_row *= 2;
+    {
+        uintptr_t bits = reinterpret_cast<uintptr_t>(halo) | (uintptr_t)row_bytes;
+        for (int q = 0; q < world; q++) bits |= reinterpret_cast<uintptr_t>(peer_x_host[q]);
+        if (bits % 16 != 0) lanes_per_row = 0;
+    }
+    if (grid > 0xffff) grid = 0xffff;
     if (src_half) {
-        JG_CHECK_ARG(bulk, JG_EUNSUPPORTED, "halo_pull: the fp16 payload needs rows that are multiples of 16 bytes (width %% 8 == 0)");
+        JG_CHECK_ARG(lanes_per_row > 0, JG_EUNSUPPORTED,
+                     "halo_pull: the fp16 payload needs rows that are multiples of 16 bytes (width %% 8 == 0)");
+        if (!use_bulk) {
+            if (grid > 4 * (int64_t)max_ctas) grid = 4 * (int64_t)max_ctas;
+            halo_pull_rows_kernel<true><<<(unsigned)grid, 256, 0, st>>>(a, lanes_per_row);
+            JG_LAUNCH_CHECK();
+            return JG_OK;
+        }
         if (grid > max_ctas) grid = max_ctas;
         const size_t smem = (size_t)n_stages * stage_bytes + sizeof(uint64_t) * 2 * kPullStages + sizeof(HalfCtl) + 128;
         static size_t attr_half[64] = {0};
@@ -547,7 +619,7 @@ int jg_halo_pull(void* halo, const int32_t* needed, void* const* peer_x_host, vo
         JG_LAUNCH_CHECK();
         return JG_OK;
     }
-    if (bulk) {
+    if (use_bulk) {
         bool aligned = true;
         for (int q = 0; q < world; q++) aligned = aligned && (reinterpret_cast<uintptr_t>(peer_x_host[q]) % 16 == 0);
         JG_CHECK_ARG(aligned, JG_EINVAL, "halo_pull: peer buffers must be 16-byte aligned");
@@ -562,8 +634,9 @@ int jg_halo_pull(void* halo, const int32_t* needed, void* const* peer_x_host, vo
         }
         halo_pull_bulk_kernel<<<(unsigned)grid, 32, smem, st>>>(a, (uint32_t)stage_bytes, n_stages);
     } else {
-        if (grid > max_ctas) grid = max_ctas;
-        halo_pull_rows_kernel<<<(unsigned)grid, 256, 0, st>>>(a);
+        // 256-thread CTAs: up to four per SM slot the caller granted
+        if (grid > 4 * (int64_t)max_ctas) grid = 4 * (int64_t)max_ctas;
+        halo_pull_rows_kernel<false><<<(unsigned)grid, 256, 0, st>>>(a, lanes_per_row);
     }
     JG_LAUNCH_CHECK();
     return JG_OK;

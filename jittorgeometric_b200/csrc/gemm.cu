@@ -22,6 +22,7 @@
 #include "common.cuh"
 
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <cstring>
 
 namespace jg {
@@ -49,6 +50,7 @@ struct GemmParams {
     int32_t tma_store;   // epilogue stages 32x32 blocks in shared memory and stores them by TMA
     int32_t ldo;         // row pitch of the output in floats (the full width when m is one column tile of it)
     int32_t col_base;    // first output column of this tile (out, bias and wt already point at it)
+    __half* out_half;    // optional second copy of the result in fp16 (same shape and pitch in elements), or null
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -336,6 +338,24 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
                         for (int i = 0; i < 32; i++) v[i] = fmaxf(v[i], 0.f);
                     }
+                    if (p.out_half && row < p.n_rows) {
+                        // the fp16 copy a partitioned aggregation offers to its peers: this lane's 32 values as
+                        // 64 contiguous bytes of its row (values beyond the fp16 range saturate)
+                        uint4* oh = reinterpret_cast<uint4*>(p.out_half + row * p.ldo + c0);
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            if (c0 + 8 * i < p.m) {
+                                uint4 pk;
+                                __half2 h0 = __floats2half2_rn(fminf(fmaxf(v[8 * i], -65504.f), 65504.f), fminf(fmaxf(v[8 * i + 1], -65504.f), 65504.f));
+                                __half2 h1 = __floats2half2_rn(fminf(fmaxf(v[8 * i + 2], -65504.f), 65504.f), fminf(fmaxf(v[8 * i + 3], -65504.f), 65504.f));
+                                __half2 h2 = __floats2half2_rn(fminf(fmaxf(v[8 * i + 4], -65504.f), 65504.f), fminf(fmaxf(v[8 * i + 5], -65504.f), 65504.f));
+                                __half2 h3 = __floats2half2_rn(fminf(fmaxf(v[8 * i + 6], -65504.f), 65504.f), fminf(fmaxf(v[8 * i + 7], -65504.f), 65504.f));
+                                pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                                pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                                __stcs(oh + i, pk);
+                            }
+                        }
+                    }
                     unsigned char* slab = slabs + (warp - 2) * 4096;
                     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // previous store has read the slab
                     __syncwarp();
@@ -435,7 +455,7 @@ size_t jg_gemm_tf32_workspace_bytes(void) { return 256; }
 
 // One column tile (at most 256 output columns) of the product.
 static int gemm_tile(float* out, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k, int64_t m,
-                     int64_t m_total, int64_t col_base, int relu, int32_t* error, cudaStream_t st) {
+                     int64_t m_total, int64_t col_base, int relu, int32_t* error, cudaStream_t st, __half* out_half = nullptr) {
     // TMA needs 16-byte aligned bases and row pitches; anything else goes through the plain-load producer
     const bool plain = (k % 4 != 0) || ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wt)) % 16 != 0);
     const int b_rows = (int)((m + 15) / 16 * 16);
@@ -462,6 +482,7 @@ static int gemm_tile(float* out, const float* x, const float* wt, const float* b
     }
     p.out = out; p.bias = bias; p.n_rows = n_rows; p.k = (int32_t)k; p.m = (int32_t)m; p.relu = relu;
     p.ldo = (int32_t)m_total; p.col_base = (int32_t)col_base;
+    p.out_half = out_half;
     int pad = 32;
     while (pad < b_rows) pad *= 2;
     p.m_pad = pad;
@@ -485,9 +506,11 @@ static int gemm_tile(float* out, const float* x, const float* wt, const float* b
     return JG_OK;
 }
 
-int jg_gemm_tf32(float* out, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k, int64_t m,
-                 int relu, void* workspace, size_t workspace_bytes, jg_stream_t stream) {
+static int gemm_impl(float* out, void* out_half, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k,
+                     int64_t m, int relu, void* workspace, size_t workspace_bytes, jg_stream_t stream) {
     JG_CHECK_ARG(n_rows >= 0 && k > 0 && m > 0, JG_EINVAL, "gemm_tf32: bad size");
+    JG_CHECK_ARG(!out_half || (m % 8 == 0 && reinterpret_cast<uintptr_t>(out_half) % 16 == 0), JG_ESHAPE,
+                 "gemm_tf32: the fp16 copy needs a width that is a multiple of 8 and a 16-byte aligned buffer");
     if (n_rows == 0) return JG_OK;
     JG_CHECK_ARG(out && x && wt, JG_EINVAL, "gemm_tf32: null pointer");
     if (!jg_gemm_tf32_supported(n_rows, k, m)) {
@@ -502,10 +525,22 @@ int jg_gemm_tf32(float* out, const float* x, const float* wt, const float* bias,
     // wider outputs: one launch per tile of 256 columns (x is read once per tile)
     for (int64_t cb = 0; cb < m; cb += 256) {
         const int64_t mt = m - cb < 256 ? m - cb : 256;
-        int rc = gemm_tile(out + cb, x, wt + cb * k, bias ? bias + cb : nullptr, n_rows, k, mt, m, cb, relu, error, st);
+        int rc = gemm_tile(out + cb, x, wt + cb * k, bias ? bias + cb : nullptr, n_rows, k, mt, m, cb, relu, error, st,
+                           out_half ? static_cast<__half*>(out_half) + cb : nullptr);
         if (rc != JG_OK) return rc;
     }
     return JG_OK;
+}
+
+int jg_gemm_tf32(float* out, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k, int64_t m,
+                 int relu, void* workspace, size_t workspace_bytes, jg_stream_t stream) {
+    return gemm_impl(out, nullptr, x, wt, bias, n_rows, k, m, relu, workspace, workspace_bytes, stream);
+}
+
+int jg_gemm_tf32_dual(float* out, void* out_half, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k,
+                      int64_t m, int relu, void* workspace, size_t workspace_bytes, jg_stream_t stream) {
+    JG_CHECK_ARG(out_half, JG_EINVAL, "gemm_tf32_dual: null fp16 buffer");
+    return gemm_impl(out, out_half, x, wt, bias, n_rows, k, m, relu, workspace, workspace_bytes, stream);
 }
 
 /* Reads the error word a finished jg_gemm_tf32 call left in its workspace (synchronises the

@@ -228,6 +228,7 @@ class DirectTransport(CollectiveTransport):
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.pull_ctas, self.wait_ns, self.plain = int(pull_ctas), int(wait_ms * 1e6), bool(plain)
         self.side = torch.cuda.Stream(device=self.device, priority=-1)
+        self.profile = False
         self._slots = {}
         words = lib().jg_halo_flag_bytes() // 4
         self._flags = symm.empty((words,), dtype=torch.int32, device=self.device)
@@ -279,7 +280,18 @@ class DirectTransport(CollectiveTransport):
     def _eptr(self):
         return ctypes.c_void_p(self._error.data_ptr())
 
-    def begin(self, g, f):
+    def half_buffer(self, g, f):
+        """The fp16 copy of the rank's rows that the peers read when ``g.halo_half`` is set (collective on
+        first use).  A producer that writes it together with the fp32 rows (``ops.linear_tf32(out_half=)``)
+        passes ``half_ready=True`` to ``start`` and saves the conversion pass."""
+        slot = self._slot(g, f)
+        if slot.buf16 is None:
+            slot.buf16 = self._symm.empty((max(g.part.pad, 1), f), dtype=torch.float16, device=self.device)
+            hdl = self._symm.rendezvous(slot.buf16, self.symm_group.group_name)
+            slot.ptrs16 = (ctypes.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs])
+        return slot.buf16
+
+    def begin(self, g, f, half_ready=False):
         """The rank's rows of width ``f`` are in place (written by work already queued on the current
         stream): tells the peers and starts pulling this rank's halo rows on the side stream."""
         self.check()
@@ -288,25 +300,31 @@ class DirectTransport(CollectiveTransport):
         st = stream_for(slot.buf)
         half = bool(getattr(g, "halo_half", False))
         if half:
-            if slot.buf16 is None:              # collective on first use, like the buffer itself
-                slot.buf16 = self._symm.empty((max(g.part.pad, 1), f), dtype=torch.float16, device=self.device)
-                hdl = self._symm.rendezvous(slot.buf16, self.symm_group.group_name)
-                slot.ptrs16 = (ctypes.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs])
-            check(lib().jg_rows_to_half(ptr(slot.buf16), ptr(slot.buf), g.n_local * f, st), "jg_rows_to_half")
+            self.half_buffer(g, f)
+            if not half_ready:
+                check(lib().jg_rows_to_half(ptr(slot.buf16), ptr(slot.buf), g.n_local * f, st), "jg_rows_to_half")
         check(lib().jg_halo_post(self._flag_ptrs, self.world, self.rank, slot.index, 0, slot.epoch, st), "jg_halo_post")
         cur = torch.cuda.current_stream(self.device)
         self.side.wait_stream(cur)
-        seg = (ctypes.c_int64 * (self.world + 1))(*([int(v) for v in g.recv_offset] + [int(g.n_halo)]))
-        los = (ctypes.c_int32 * self.world)(*[int(g.part.bounds[q]) for q in range(self.world)])
+        tables = getattr(g, "_pull_tables", None)
+        if tables is None:                       # per-graph constants of the pull, built once
+            tables = ((ctypes.c_int64 * (self.world + 1))(*([int(v) for v in g.recv_offset] + [int(g.n_halo)])),
+                      (ctypes.c_int32 * self.world)(*[int(g.part.bounds[q]) for q in range(self.world)]))
+            g._pull_tables = tables
+        seg, los = tables
         halo = slot.buf[g.n_local:]
         with torch.cuda.stream(self.side):
+            begun = None
+            if self.profile:                      # timing events around the pull (benchmarks: where a step's time goes)
+                begun = torch.cuda.Event(enable_timing=True)
+                begun.record(self.side)
             check(lib().jg_halo_pull(ptr(halo), ptr(g.needed), slot.ptrs16 if half else slot.ptrs, self._flag_ptrs, seg, los,
                                      self.world, self.rank, (2 if half else 4) * f, slot.index, slot.epoch, ptr(self._counter),
                                      self._eptr(), self.wait_ns, self.pull_ctas, 1 if self.plain else 0, 1 if half else 0,
                                      ctypes.c_void_p(self.side.cuda_stream)), "jg_halo_pull")
-            landed = torch.cuda.Event()
+            landed = torch.cuda.Event(enable_timing=self.profile)
             landed.record(self.side)
-        return _DirectHandle(self, landed)
+        return _DirectHandle(self, landed, begun)
 
 
 class EmulatedRanks:
@@ -377,7 +395,10 @@ class _EmulatedRank(CollectiveTransport):
     def acquire(self, g, f):
         pass
 
-    def begin(self, g, f):
+    def half_buffer(self, g, f):
+        raise RuntimeError("emulated ranks convert on every exchange: no persistent fp16 buffer")
+
+    def begin(self, g, f, half_ready=False):
         self.check()
         buf = self.feature_buffer(g, f)
         slot = self.owner.slot_index(f)
@@ -409,8 +430,8 @@ class _EmulatedRank(CollectiveTransport):
 
 
 class _DirectHandle:
-    def __init__(self, transport, landed):
-        self.transport, self.landed = transport, landed
+    def __init__(self, transport, landed, begun=None):
+        self.transport, self.landed, self.begun = transport, landed, begun
 
     def wait(self):
         torch.cuda.current_stream().wait_event(self.landed)
@@ -512,6 +533,14 @@ class ShardedGraph:
             return self._recv_buffer(f, like)[: self.n_local]
         return torch.empty((self.n_local, f), dtype=like.dtype, device=like.device)
 
+    def half_buffer(self, f):
+        """Direct transport with ``halo_half``: the fp16 buffer ``[>= n_local, f]`` the peers read.  Fill it
+        together with :meth:`feature_buffer` (e.g. ``ops.linear_tf32(out=..., out_half=...)``) and call
+        ``start`` / ``aggregate`` with ``half_ready=True``."""
+        if not (self.direct and self.halo_half):
+            raise RuntimeError("half_buffer: needs the direct transport with halo_half set")
+        return self.transport.half_buffer(self, f)
+
     def _recv_buffer(self, f, like):
         buf = self._recv.get(f)
         if buf is None:
@@ -520,7 +549,7 @@ class ShardedGraph:
             self._recv[f] = buf
         return buf
 
-    def aggregate(self, x, bias=None, relu=False):
+    def aggregate(self, x, bias=None, relu=False, half_ready=False):
         """``y[v] = sum_{(u -> v)} w * x_global[u]`` for the rank's own rows ``v``; ``x`` holds the
         rank's ``n_local`` rows of the feature matrix (extra rows are ignored).  With autograd the
         gradient is the same aggregation applied to the incoming gradient, which is the true
@@ -531,9 +560,9 @@ class ShardedGraph:
         if torch.is_grad_enabled() and x.requires_grad:
             y = _ShardedAggregate.apply(x, self)
         elif bias is not None or relu:
-            return self._aggregate(x, bias, relu)
+            return self.finish(self.start(x, half_ready), bias, relu)
         else:
-            return self._aggregate(x)
+            return self.finish(self.start(x, half_ready))
         if bias is not None:
             y = y + bias
         return torch.relu(y) if relu else y
@@ -541,7 +570,7 @@ class ShardedGraph:
     def _aggregate(self, x, bias=None, relu=False):
         return self.finish(self.start(x), bias, relu)
 
-    def start(self, x):
+    def start(self, x, half_ready=False):
         """First half of an aggregation: starts the exchange of the halo rows.  Aggregations of
         DIFFERENT widths may be started before the first is finished; their exchanges then run
         underneath the aggregation kernels of the earlier ones.  A second ``start`` of a width whose
@@ -557,7 +586,7 @@ class ShardedGraph:
             if x.data_ptr() != buf.data_ptr():
                 self.transport.acquire(self, f)
                 buf[: self.n_local].copy_(x[: self.n_local])
-            handle = self.transport.begin(self, f)
+            handle = self.transport.begin(self, f, half_ready)
             self._inflight.add(f)
             return (buf[: self.n_local], buf if self.mode == "merged" else buf[self.n_local:], handle)
         buf = self._recv_buffer(f, x)

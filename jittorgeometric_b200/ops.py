@@ -615,12 +615,13 @@ def linear_tf32_supported(n_rows, k, m):
     return bool(lib().jg_gemm_tf32_supported(int(n_rows), int(k), int(m)))
 
 
-def linear_tf32(x, weight, bias=None, relu=False, weight_t=None, check_status=False, out=None):
+def linear_tf32(x, weight, bias=None, relu=False, weight_t=None, check_status=False, out=None, out_half=None):
     """``act(x @ weight + bias)`` on the tcgen05 tensor cores (TF32 products, fp32 accumulation):
     the dense feature transform of the layers (nn/conv/gcn_conv.py:95, nn/conv/gat_conv.py:86).
     ``weight`` is ``[k, m]`` as the layers store it; ``weight_t`` may carry its cached transpose.
     Forward only.  ``out`` receives the result in place (e.g. the feature buffer of a partitioned
-    aggregation).  ``check_status=True`` synchronises and raises if a bounded wait in the kernel
+    aggregation); ``out_half`` additionally receives an fp16 copy from the same epilogue (the half-width
+    halo payload of :class:`dist.ShardedGraph`).  ``check_status=True`` synchronises and raises if a bounded wait in the kernel
     ran out."""
     x = _as_f32(x, "x")
     n, k = x.shape
@@ -633,8 +634,14 @@ def linear_tf32(x, weight, bias=None, relu=False, weight_t=None, check_status=Fa
         raise RuntimeError(f"out: expected a contiguous float32 [{n}, {m}] tensor")
     ws = workspace(lib().jg_gemm_tf32_workspace_bytes(), x.device)
     st = stream_for(x)
-    check(lib().jg_gemm_tf32(ptr(out), ptr(x), ptr(wt), ptr(b), n, k, m, 1 if relu else 0, ptr(ws), ws.numel(), st),
-          "jg_gemm_tf32")
+    if out_half is not None:
+        if out_half.dtype != torch.float16 or out_half.shape[1] != m or out_half.shape[0] < n or not out_half.is_contiguous():
+            raise RuntimeError(f"out_half: expected a contiguous float16 tensor of at least [{n}, {m}]")
+        check(lib().jg_gemm_tf32_dual(ptr(out), ptr(out_half), ptr(x), ptr(wt), ptr(b), n, k, m, 1 if relu else 0, ptr(ws),
+                                      ws.numel(), st), "jg_gemm_tf32_dual")
+    else:
+        check(lib().jg_gemm_tf32(ptr(out), ptr(x), ptr(wt), ptr(b), n, k, m, 1 if relu else 0, ptr(ws), ws.numel(), st),
+              "jg_gemm_tf32")
     if check_status:
         check(lib().jg_gemm_tf32_status(ptr(ws), st), "jg_gemm_tf32_status")
     return out

@@ -172,7 +172,7 @@ def test_direct_exchange_with_emulated_ranks(cuda, oracle, world, n, f, plain, m
     assert (np.abs(yb.cpu().numpy() - np.maximum(want2[lo:hi], 0)) / (scale2[lo:hi] + 1e-30)).max() <= 1e-5
 
 
-@pytest.mark.parametrize("world,n,f", [(2, 5001, 128), (4, 4096, 64), (8, 3000, 8)])
+@pytest.mark.parametrize("world,n,f", [(2, 5001, 128), (4, 4096, 64), (8, 3000, 8), (2, 6000, 256), (2, 4000, 512)])
 def test_half_width_halo_payload(cuda, oracle, world, n, f):
     """fp16 halo payload: what lands is the fp16 rounding of the remote rows, the rank's own rows stay
     fp32, the aggregation equals the unpartitioned kernel on exactly that mixed input and stays within

@@ -101,3 +101,19 @@ def test_gcn_layer_trains_in_tf32(cuda):
         layer(x, csc, csr).square().mean().backward()
         outs.append(layer.weight.grad.clone())
     assert (outs[0] - outs[1]).abs().max().item() <= 5e-3 * outs[1].abs().max().item()
+
+
+@pytest.mark.parametrize("n,k,m", [(5000, 128, 128), (3001, 128, 64), (777, 96, 8), (2000, 64, 512)])
+def test_second_output_in_fp16(cuda, n, k, m):
+    """The fp16 copy written from the same epilogue is the round-to-nearest fp16 of the fp32 result."""
+    g = torch.Generator(device="cuda").manual_seed(n + m)
+    x = torch.randn((n, k), device="cuda", generator=g)
+    w = torch.randn((k, m), device="cuda", generator=g) / k ** 0.5
+    b = torch.randn(m, device="cuda", generator=g)
+    out = torch.empty((n, m), device="cuda")
+    half = torch.full((n + 3, m), float("nan"), dtype=torch.float16, device="cuda")
+    y = cuda.ops.linear_tf32(x, w, b, relu=True, out=out, out_half=half, check_status=True)
+    assert y.data_ptr() == out.data_ptr()
+    assert torch.equal(half[:n], out.to(torch.float16))
+    assert torch.isnan(half[n:]).all()                       # rows beyond n are not touched
+    assert torch.equal(out, cuda.ops.linear_tf32(x, w, b, relu=True))
