@@ -359,10 +359,13 @@ size_t jg_gemm_tf32_workspace_bytes(void);
 int jg_gemm_tf32(float* out, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k, int64_t m,
                  int relu, void* workspace, size_t workspace_bytes, jg_stream_t stream);
 int jg_gemm_tf32_status(const void* workspace, jg_stream_t stream);
-/* The same transform writing a second copy of the result in fp16 (out_half [n_rows, m], m % 8 == 0, values
- * beyond +-65504 saturate) from the same epilogue: the copy a row-partitioned aggregation offers to its
- * peers (jg_halo_pull with src_half), without a separate conversion pass over the result.  The
- * reference broadcasts the fp32 product itself (ops/distspmm.py:31-39). */
+/* The same transform, optionally writing a second copy of the result in fp16 (out_half [n_rows, m] or NULL;
+ * m % 8 == 0, values beyond +-65504 saturate) from the same epilogue: the copy a row-partitioned
+ * aggregation offers to its peers (jg_halo_pull with src_half), without a separate conversion pass over
+ * the result.  The reference broadcasts the fp32 product itself (ops/distspmm.py:31-39).
+ * The error word (first 4 bytes of `workspace`) is STICKY here: the call does not clear it, a kernel whose
+ * bounded wait ran out stores 1 with a plain store, so the word may live in pinned host memory that the
+ * host polls without synchronising (and clears itself). */
 int jg_gemm_tf32_dual(float* out, void* out_half, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k,
                       int64_t m, int relu, void* workspace, size_t workspace_bytes, jg_stream_t stream);
 

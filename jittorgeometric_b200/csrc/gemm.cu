@@ -404,7 +404,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         const uint32_t cols = (uint32_t)(2 * p.m_pad);
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(cols) : "memory");
     }
-    if (threadIdx.x == 0 && *abort_flag) atomicExch(p.error, 1);
+    if (threadIdx.x == 0 && *abort_flag) {   // plain store: the word may live in pinned host memory
+        *reinterpret_cast<volatile int32_t*>(p.error) = 1;
+        __threadfence_system();
+    }
 }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point lookup: no link-time
@@ -507,7 +510,7 @@ static int gemm_tile(float* out, const float* x, const float* wt, const float* b
 }
 
 static int gemm_impl(float* out, void* out_half, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k,
-                     int64_t m, int relu, void* workspace, size_t workspace_bytes, jg_stream_t stream) {
+                     int64_t m, int relu, void* workspace, size_t workspace_bytes, jg_stream_t stream, bool clear_error = true) {
     JG_CHECK_ARG(n_rows >= 0 && k > 0 && m > 0, JG_EINVAL, "gemm_tf32: bad size");
     JG_CHECK_ARG(!out_half || (m % 8 == 0 && reinterpret_cast<uintptr_t>(out_half) % 16 == 0), JG_ESHAPE,
                  "gemm_tf32: the fp16 copy needs a width that is a multiple of 8 and a 16-byte aligned buffer");
@@ -521,7 +524,7 @@ static int gemm_impl(float* out, void* out_half, const float* x, const float* wt
     JG_CHECK_ARG(workspace && workspace_bytes >= 256, JG_EWORKSPACE, "gemm_tf32: workspace missing");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int32_t* error = static_cast<int32_t*>(workspace);
-    JG_CUDA(cudaMemsetAsync(error, 0, sizeof(int32_t), st));
+    if (clear_error) JG_CUDA(cudaMemsetAsync(error, 0, sizeof(int32_t), st));
     // wider outputs: one launch per tile of 256 columns (x is read once per tile)
     for (int64_t cb = 0; cb < m; cb += 256) {
         const int64_t mt = m - cb < 256 ? m - cb : 256;
@@ -539,8 +542,7 @@ int jg_gemm_tf32(float* out, const float* x, const float* wt, const float* bias,
 
 int jg_gemm_tf32_dual(float* out, void* out_half, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k,
                       int64_t m, int relu, void* workspace, size_t workspace_bytes, jg_stream_t stream) {
-    JG_CHECK_ARG(out_half, JG_EINVAL, "gemm_tf32_dual: null fp16 buffer");
-    return gemm_impl(out, out_half, x, wt, bias, n_rows, k, m, relu, workspace, workspace_bytes, stream);
+    return gemm_impl(out, out_half, x, wt, bias, n_rows, k, m, relu, workspace, workspace_bytes, stream, false);
 }
 
 /* Reads the error word a finished jg_gemm_tf32 call left in its workspace (synchronises the

@@ -5,6 +5,7 @@ Same names, argument order and meaning as the reference operators, with
 calls a hand-written sm_100a kernel through the C ABI of ``libjgb200.so``; there
 is no CPU or eager fallback for any of them.
 """
+import ctypes
 import os
 
 import torch
@@ -14,7 +15,7 @@ from .data import CSC, CSR
 
 __all__ = ["aggregateWithWeight", "aggregate_bias_act", "segment_aggregate", "SpmmPlan", "cootocsr", "cootocsc", "gcn_norm_csc_csr",
            "SpmmCsr", "SpmmCoo", "ScatterToEdge", "ScatterToVertex", "EdgeSoftmax", "gat_aggregate",
-           "gat_aggregate_supported", "gcn_norm_coo", "linear_tf32", "linear_tf32_autograd", "linear_tf32_supported", "toUndirected", "validate_structure"]
+           "gat_aggregate_supported", "gcn_norm_coo", "linear_tf32", "check_transform_status", "linear_tf32_autograd", "linear_tf32_supported", "toUndirected", "validate_structure"]
 
 DEFAULT_CHUNK = int(os.environ.get("JG_SPMM_CHUNK", "1024"))
 SMALL_GRAPH_NNZ = 1 << 20
@@ -615,6 +616,33 @@ def linear_tf32_supported(n_rows, k, m):
     return bool(lib().jg_gemm_tf32_supported(int(n_rows), int(k), int(m)))
 
 
+_tf32_status = {}      # device index -> pinned host word a transform kernel sets when a bounded wait ran out
+
+
+def _tf32_status_word(device):
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    word = _tf32_status.get(idx)
+    if word is None:
+        word = torch.zeros(64, dtype=torch.int32).pin_memory()
+        _tf32_status[idx] = word
+    return word
+
+
+def check_transform_status(device=None, synchronize=False):
+    """Raises if a ``linear_tf32`` kernel on ``device`` gave up on a bounded wait (its output is then
+    not valid).  The kernels report through a word in pinned host memory, so the check costs nothing;
+    it runs at the start of every ``linear_tf32`` call, and a training loop may call it (with
+    ``synchronize=True`` for a definitive answer) before the optimiser step."""
+    words = _tf32_status.items() if device is None else [(None, _tf32_status_word(torch.device(device)))]
+    if synchronize:
+        torch.cuda.synchronize()
+    for _, word in list(words):
+        if int(word[0]):
+            word[0] = 0
+            raise RuntimeError("jg_gemm_tf32: a bounded wait inside the kernel ran out [JG_ETIMEOUT]; the result of "
+                               "that transform is not valid")
+
+
 def linear_tf32(x, weight, bias=None, relu=False, weight_t=None, check_status=False, out=None, out_half=None):
     """``act(x @ weight + bias)`` on the tcgen05 tensor cores (TF32 products, fp32 accumulation):
     the dense feature transform of the layers (nn/conv/gcn_conv.py:95, nn/conv/gat_conv.py:86).
@@ -632,18 +660,17 @@ def linear_tf32(x, weight, bias=None, relu=False, weight_t=None, check_status=Fa
         out = torch.empty((n, m), dtype=torch.float32, device=x.device)
     elif out.shape != (n, m) or out.dtype != torch.float32 or not out.is_contiguous():
         raise RuntimeError(f"out: expected a contiguous float32 [{n}, {m}] tensor")
-    ws = workspace(lib().jg_gemm_tf32_workspace_bytes(), x.device)
+    word = _tf32_status_word(x.device)
+    if int(word[0]):                       # an earlier transform on this device gave up: its consumers must not carry on
+        check_transform_status(x.device)
     st = stream_for(x)
-    if out_half is not None:
-        if out_half.dtype != torch.float16 or out_half.shape[1] != m or out_half.shape[0] < n or not out_half.is_contiguous():
-            raise RuntimeError(f"out_half: expected a contiguous float16 tensor of at least [{n}, {m}]")
-        check(lib().jg_gemm_tf32_dual(ptr(out), ptr(out_half), ptr(x), ptr(wt), ptr(b), n, k, m, 1 if relu else 0, ptr(ws),
-                                      ws.numel(), st), "jg_gemm_tf32_dual")
-    else:
-        check(lib().jg_gemm_tf32(ptr(out), ptr(x), ptr(wt), ptr(b), n, k, m, 1 if relu else 0, ptr(ws), ws.numel(), st),
-              "jg_gemm_tf32")
+    if out_half is not None and (out_half.dtype != torch.float16 or out_half.shape[1] != m or out_half.shape[0] < n
+                                 or not out_half.is_contiguous()):
+        raise RuntimeError(f"out_half: expected a contiguous float16 tensor of at least [{n}, {m}]")
+    check(lib().jg_gemm_tf32_dual(ptr(out), ptr(out_half), ptr(x), ptr(wt), ptr(b), n, k, m, 1 if relu else 0,
+                                  ctypes.c_void_p(word.data_ptr()), 256, st), "jg_gemm_tf32_dual")
     if check_status:
-        check(lib().jg_gemm_tf32_status(ptr(ws), st), "jg_gemm_tf32_status")
+        check_transform_status(x.device, synchronize=True)
     return out
 
 

@@ -153,9 +153,97 @@ def sampling():
          l_column_indices=l_ci, l_weight=l_w)
 
 
+def partition():
+    """Golden vectors of the offline partitioner: the reference's OWN ``DistChunkManager.partition_to_chunk``
+    (partition/distchunk_manager.py:47-157) and ``set_chunks_csrs`` (examples/dist_gcn/dist_partition.py:122-158),
+    loaded from the checkout and run on numpy inputs.  Their modules import Jittor and pymetis at the
+    top, which are not installed; both are replaced by stand-ins that only hold attributes (the two
+    functions themselves use numpy and scipy), so what runs is the reference's code unmodified."""
+    import ast
+    import importlib.util
+    import pickle
+    import tempfile
+    import types
+    ref_root = os.environ.get("JG_REFERENCE_ROOT", "/root/reference")
+
+    class Holder:                       # stands in for DistChunk / CSR: keeps what it is given
+        def __init__(self, *a, **kw):
+            self.__dict__.update(kw)
+            self.chunk_CSR = []
+
+        def set_csr(self, column_indices, row_offset, edge_weight=None):
+            self.CSR = Holder(column_indices=column_indices, row_offset=row_offset, edge_weight=edge_weight)
+
+        def set_csc(self, row_indices, column_offset, edge_weight=None):
+            self.CSC = Holder(row_indices=row_indices, column_offset=column_offset, edge_weight=edge_weight)
+
+    jt = types.ModuleType("jittor")
+    jt.Var = type("Var", (), {})
+    jt.array = lambda a: np.asarray(a)
+    jt.gc = lambda: None
+    data_mod = types.ModuleType("jittor_geometric.data")
+    data_mod.DistChunk, data_mod.CSR, data_mod.CSC = Holder, Holder, Holder
+    pkg = types.ModuleType("jittor_geometric")
+    pkg.data = data_mod
+    metis = types.ModuleType("pymetis")
+    metis.part_graph = None
+    saved = {k: sys.modules.get(k) for k in ("jittor", "jittor_geometric", "jittor_geometric.data", "pymetis")}
+    sys.modules.update({"jittor": jt, "jittor_geometric": pkg, "jittor_geometric.data": data_mod, "pymetis": metis})
+    try:
+        spec = importlib.util.spec_from_file_location(
+            "ref_distchunk_manager", os.path.join(ref_root, "jittor_geometric", "partition", "distchunk_manager.py"))
+        mgr_mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mgr_mod)
+        # the two functions of the example script, without running the script itself
+        src = open(os.path.join(ref_root, "examples", "dist_gcn", "dist_partition.py")).read()
+        tree = ast.parse(src)
+        keep = [n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name in ("compute_chunk_id", "set_chunks_csrs")]
+        ns = {"np": np, "jt": jt, "tqdm": lambda it, **kw: it, "CSR": Holder}
+        exec(compile(ast.Module(body=keep, type_ignores=[]), "dist_partition.py", "exec"), ns)
+    finally:
+        for k, v in saved.items():
+            if v is None:
+                sys.modules.pop(k, None)
+            else:
+                sys.modules[k] = v
+
+    rng = np.random.default_rng(41)
+    n, P, E = 60, 3, 400
+    pairs = np.unique(rng.integers(0, n, size=(E, 2)), axis=0)          # distinct edges: scipy would add duplicates up
+    edge_index = pairs.T.astype(np.int64)
+    w = rng.random(edge_index.shape[1]).astype(np.float32)
+    part = rng.integers(0, P, size=n).astype(np.int64)
+    part[:P] = np.arange(P)
+    feature = rng.standard_normal((n, 5)).astype(np.float32)
+    label = np.arange(n)                                                # the local labels reveal the node order inside a part
+    with tempfile.TemporaryDirectory() as tmp:
+        pf = os.path.join(tmp, "partition.bin")
+        with open(pf, "wb") as f:
+            pickle.dump(part, f)
+        chunks = mgr_mod.DistChunkManager().partition_to_chunk(pf, edge_index.copy(), n, P, edge_weight=w.copy(),
+                                                               global_feature=feature, global_masks=[None, None, None],
+                                                               global_label=label, num_classes=3)
+    ns["set_chunks_csrs"](chunks, P)
+    out = dict(edge_index=edge_index, edge_weight=w, partition=part, feature=feature, n=np.int64(n), parts=np.int64(P))
+    for p, c in enumerate(chunks):
+        out.update({f"p{p}_edge_index": np.asarray(c.edge_index), f"p{p}_edge_weight": np.asarray(c.edge_weight),
+                    f"p{p}_offset": np.asarray(c.offset), f"p{p}_label": np.asarray(c.local_label),
+                    f"p{p}_feature": np.asarray(c.local_feature),
+                    f"p{p}_csr_indices": np.asarray(c.CSR.column_indices), f"p{p}_csr_indptr": np.asarray(c.CSR.row_offset),
+                    f"p{p}_csr_data": np.asarray(c.CSR.edge_weight),
+                    f"p{p}_csc_indices": np.asarray(c.CSC.row_indices), f"p{p}_csc_indptr": np.asarray(c.CSC.column_offset),
+                    f"p{p}_csc_data": np.asarray(c.CSC.edge_weight)})
+        for q, sub in enumerate(c.chunk_CSR):
+            out.update({f"p{p}_chunk{q}_indices": np.asarray(sub.column_indices), f"p{p}_chunk{q}_indptr": np.asarray(sub.row_offset),
+                        f"p{p}_chunk{q}_data": np.asarray(sub.edge_weight)})
+    save("ref_partition", **out)
+
+
 if __name__ == "__main__":
     if sys.argv[1:] == ["sampling"]:
         sampling()
+    elif sys.argv[1:] == ["partition"]:
+        partition()
     else:
         main()
         sampling()

@@ -117,3 +117,22 @@ def test_second_output_in_fp16(cuda, n, k, m):
     assert torch.equal(half[:n], out.to(torch.float16))
     assert torch.isnan(half[n:]).all()                       # rows beyond n are not touched
     assert torch.equal(out, cuda.ops.linear_tf32(x, w, b, relu=True))
+
+
+def test_status_word_is_polled_without_a_synchronisation(cuda):
+    """The transform reports a bounded wait that ran out through a pinned host word.  After normal runs it is
+    zero; once set (here by hand: nothing on the device is made to fail) the next call refuses to carry on
+    and clears it."""
+    from jittorgeometric_b200 import ops
+    x = torch.randn((4096, 128), device="cuda")
+    w = torch.randn((128, 64), device="cuda")
+    for _ in range(3):
+        ops.linear_tf32(x, w)
+    ops.check_transform_status(x.device, synchronize=True)          # nothing to report
+    word = ops._tf32_status_word(x.device)
+    assert int(word[0]) == 0
+    word[0] = 1
+    with pytest.raises(RuntimeError, match="JG_ETIMEOUT"):
+        ops.linear_tf32(x, w)
+    assert int(word[0]) == 0
+    ops.linear_tf32(x, w, check_status=True)                         # and the path works again

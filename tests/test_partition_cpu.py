@@ -13,11 +13,13 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def reference_chunks(partition, edge_index, n, P, w):
+def reference_chunks(partition, edge_index, n, P, w, order=None):
     """Restatement of the reference partitioner (partition/distchunk_manager.py:63-157) with numpy and
-    scipy, the node order inside a part pinned to the original order (``kind="stable"``)."""
+    scipy, the node order inside a part pinned to the original order (``kind="stable"``) unless
+    ``order`` gives it.  Pinned against the reference's own function by
+    ``test_restatement_equals_the_reference_partitioner``."""
     from scipy.sparse import csc_matrix, csr_matrix
-    order = np.argsort(partition, kind="stable")
+    order = np.argsort(partition, kind="stable") if order is None else order
     remap = np.zeros(n, np.int64)
     remap[order] = np.arange(n)
     ei = np.stack([remap[edge_index[0]], remap[edge_index[1]]])
@@ -243,3 +245,35 @@ def test_training_on_chunks_of_a_partition_file(oracle):
         assert np.allclose(losses, want_losses, rtol=1e-4, atol=1e-5)
         for have, want in zip(weights, W):
             assert np.abs(have - want.detach().numpy()).max() <= 1e-4
+
+
+def test_restatement_equals_the_reference_partitioner():
+    """``tests/golden/ref_partition.npz`` holds what the reference's own ``partition_to_chunk`` and
+    ``set_chunks_csrs`` produced (run from the checkout by tests/golden/make_golden.py).  The numpy
+    restatement above, given the node order the reference's ``argsort`` chose, reproduces every array;
+    and ``DistChunk.set_chunk_csrs`` (slices) equals the reference's per-node loop."""
+    from jittorgeometric_b200.partition import DistChunk
+    g = dict(np.load(os.path.join(ROOT, "tests", "golden", "ref_partition.npz")))
+    n, P = int(g["n"]), int(g["parts"])
+    order = np.concatenate([g[f"p{p}_label"] for p in range(P)])         # labels were arange(n): the order the reference chose
+    assert np.array_equal(np.sort(order), np.arange(n))
+    assert np.array_equal(g["partition"][order], np.sort(g["partition"]))
+    ref = reference_chunks(g["partition"], g["edge_index"], n, P, g["edge_weight"], order=order)
+    t = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a).astype(dt))
+    for p in range(P):
+        r = ref[p]
+        assert np.array_equal(r["edge_index"], g[f"p{p}_edge_index"])
+        assert np.array_equal(r["edge_weight"], g[f"p{p}_edge_weight"])
+        assert np.array_equal(r["offset"], g[f"p{p}_offset"])
+        assert np.array_equal(g["feature"][order][r["range"][0]: r["range"][1]], g[f"p{p}_feature"])
+        for kind in ("csr", "csc"):
+            assert np.array_equal(r[kind].indices, g[f"p{p}_{kind}_indices"])
+            assert np.array_equal(r[kind].indptr, g[f"p{p}_{kind}_indptr"])
+            assert np.array_equal(r[kind].data, g[f"p{p}_{kind}_data"])
+        s, e = r["range"]
+        c = DistChunk(P, p, e - s, n, t(r["edge_index"], np.int32), t(r["offset"], np.int32), t(r["edge_weight"], np.float32))
+        c.set_csr(t(g[f"p{p}_csr_indices"], np.int32), t(g[f"p{p}_csr_indptr"], np.int32), t(g[f"p{p}_csr_data"], np.float32))
+        for q, sub in enumerate(c.set_chunk_csrs()):
+            assert np.array_equal(sub.column_indices.numpy(), g[f"p{p}_chunk{q}_indices"])
+            assert np.array_equal(sub.row_offset.numpy(), g[f"p{p}_chunk{q}_indptr"])
+            assert np.array_equal(sub.edge_weight.numpy(), g[f"p{p}_chunk{q}_data"])
