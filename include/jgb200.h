@@ -369,6 +369,17 @@ int jg_gemm_tf32_status(const void* workspace, jg_stream_t stream);
 int jg_gemm_tf32_dual(float* out, void* out_half, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k,
                       int64_t m, int relu, void* workspace, size_t workspace_bytes, jg_stream_t stream);
 
+/* Dense product in full fp32 on the CUDA cores: c[M, N] (row pitch ldc) = op(A) * op(B) (+ bias[N], ReLU),
+ * operands addressed by strides, A(i,l) = a[i*sa0 + l*sa1], B(l,j) = b[l*sb0 + j*sb1], so that x @ W,
+ * g @ W^T and x^T @ g are one kernel.  Serves what the tensor-core transform does not: the fp32 opt-out of
+ * the layers (the reference's `x @ self.weight` in fp32, nn/conv/gcn_conv.py:95), the weight gradient
+ * x^T g of its backward, and shapes jg_gemm_tf32 refuses.  A long reduction is cut into slices whose
+ * partial results are added in a fixed order (workspace from jg_gemm_f32_workspace_bytes; may be 0). */
+size_t jg_gemm_f32_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int jg_gemm_f32(float* c, const float* a, const float* b, const float* bias, int64_t M, int64_t N, int64_t K, int64_t sa0,
+                int64_t sa1, int64_t sb0, int64_t sb1, int64_t ldc, int relu, void* workspace, size_t workspace_bytes,
+                jg_stream_t stream);
+
 /* Aggregation for callers that cannot allocate.  No counterpart in the reference: this entry
  * point exists for hosts that must not call cudaMalloc (or any allocating routine) once they
  * run - a serving process with a memory pool fixed at start-up, a plugin inside a process that

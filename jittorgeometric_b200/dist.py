@@ -819,9 +819,9 @@ class ShardedGCN(torch.nn.Module):
         for i, w in enumerate(self.weights):
             z = graph.aggregate(h)
             act = self.relu and i != last
-            if self.tf32 and z.is_cuda:      # the tcgen05 transform, forward and backward (CPU ranks of the tests: matmul)
-                h = ops.linear_tf32_autograd(z, w, relu=act)
-            else:
+            if z.is_cuda:                    # the library's own transforms: tcgen05 TF32, or fp32 on the CUDA cores
+                h = ops.linear_tf32_autograd(z, w, relu=act) if self.tf32 else ops.linear_f32_autograd(z, w, relu=act)
+            else:                            # CPU ranks of the tests
                 h = z @ w
                 if act:
                     h = torch.relu(h)

@@ -27,15 +27,17 @@ def gcn_norm(edge_index, edge_weight=None, num_nodes=None, improved=False, add_s
 
 
 def _transform(x, weight, tf32, relu=False):
-    """``x @ weight`` (optionally ReLU): the tcgen05 TF32 kernel when asked for (2e-3 tolerance; in
-    training its backward runs in TF32 as well), else the fp32 matmul with autograd."""
+    """``x @ weight`` (optionally ReLU): the tcgen05 TF32 kernel (2e-3 tolerance; in training its input
+    gradient runs in TF32 as well), or with ``tf32=False`` the library's fp32 CUDA-core kernel.  Neither
+    path calls a vendor GEMM."""
     needs_grad = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)
     if tf32 and ops.linear_tf32_supported(x.shape[0], x.shape[1], weight.shape[1]):
         if needs_grad:
             return ops.linear_tf32_autograd(x, weight, relu=relu)
         return ops.linear_tf32(x, weight, relu=relu)
-    h = x @ weight
-    return torch.relu(h) if relu else h
+    if needs_grad:
+        return ops.linear_f32_autograd(x, weight, relu=relu)
+    return ops.matmul_f32(x, weight, relu=relu)
 
 
 class GCNConv(torch.nn.Module):
@@ -67,17 +69,28 @@ class GCNConv(torch.nn.Module):
         return f"{self.__class__.__name__}({self.in_channels}, {self.out_channels})"
 
 
+class Linear(torch.nn.Module):
+    """``x W^T + b`` with ``weight`` stored ``[out, in]`` like the reference's ``Linear`` (nn/dense/linear.py),
+    on the library's own kernels (TF32 tensor-core transform, or fp32 with ``tf32=False``)."""
+
+    def __init__(self, in_channels, out_channels, bias=True, tf32=True):
+        super().__init__()
+        self.tf32 = tf32
+        self.weight = torch.nn.Parameter(torch.empty(out_channels, in_channels))
+        self.bias = torch.nn.Parameter(torch.zeros(out_channels)) if bias else None
+        glorot_(self.weight)
+
+    def forward(self, x):
+        return ops.linear_nt(x, self.weight, self.bias, tf32=self.tf32)
+
+
 class SGConv(torch.nn.Module):
     """``lin(A_hat^K x)`` (nn/conv/sg_conv.py:43-70)."""
 
-    def __init__(self, in_channels, out_channels, K=1, bias=True, spmm=True, **kwargs):
+    def __init__(self, in_channels, out_channels, K=1, bias=True, spmm=True, tf32=True, **kwargs):
         super().__init__()
         self.K = K
-        self.lin = torch.nn.Linear(in_channels, out_channels, bias=bias)
-        glorot_(self.lin.weight)
-        if bias:
-            with torch.no_grad():
-                self.lin.bias.zero_()
+        self.lin = Linear(in_channels, out_channels, bias=bias, tf32=tf32)
 
     def forward(self, x, csc, csr):
         for _ in range(self.K):

@@ -15,7 +15,7 @@ from .data import CSC, CSR
 
 __all__ = ["aggregateWithWeight", "aggregate_bias_act", "segment_aggregate", "SpmmPlan", "cootocsr", "cootocsc", "gcn_norm_csc_csr",
            "SpmmCsr", "SpmmCoo", "ScatterToEdge", "ScatterToVertex", "EdgeSoftmax", "gat_aggregate",
-           "gat_aggregate_supported", "gcn_norm_coo", "linear_tf32", "check_transform_status", "linear_tf32_autograd", "linear_tf32_supported", "toUndirected", "validate_structure"]
+           "gat_aggregate_supported", "gcn_norm_coo", "linear_tf32", "check_transform_status", "linear_tf32_autograd", "linear_tf32_supported", "matmul_f32", "linear_f32_autograd", "linear_nt", "toUndirected", "validate_structure"]
 
 DEFAULT_CHUNK = int(os.environ.get("JG_SPMM_CHUNK", "1024"))
 SMALL_GRAPH_NNZ = 1 << 20
@@ -674,11 +674,96 @@ def linear_tf32(x, weight, bias=None, relu=False, weight_t=None, check_status=Fa
     return out
 
 
+def matmul_f32(a, b, trans_a=False, trans_b=False, bias=None, relu=False):
+    """``act(op(a) @ op(b) + bias)`` in full fp32 on the library's own CUDA-core kernel (no vendor GEMM):
+    the fp32 opt-out of the layers' transform, the weight gradient ``x^T g`` and the shapes
+    ``linear_tf32`` does not take.  ``a`` and ``b`` are 2-D and contiguous; the transposes are taken by
+    stride, nothing is copied."""
+    a, b = _as_f32(a, "a"), _as_f32(b, "b")
+    M, K = (a.shape[1], a.shape[0]) if trans_a else a.shape
+    K2, N = (b.shape[1], b.shape[0]) if trans_b else b.shape
+    if K != K2:
+        raise RuntimeError(f"matmul_f32: inner sizes differ ({K} and {K2})")
+    sa0, sa1 = (1, a.shape[1]) if trans_a else (a.shape[1], 1)
+    sb0, sb1 = (1, b.shape[1]) if trans_b else (b.shape[1], 1)
+    bb = None if bias is None else _as_f32(bias, "bias")
+    out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    ws = workspace(lib().jg_gemm_f32_workspace_bytes(M, N, K), a.device)
+    check(lib().jg_gemm_f32(ptr(out), ptr(a), ptr(b), ptr(bb), M, N, K, sa0, sa1, sb0, sb1, N, 1 if relu else 0, ptr(ws),
+                            ws.numel(), stream_for(a)), "jg_gemm_f32")
+    return out
+
+
+class _LinearF32(torch.autograd.Function):
+    """``act(x @ weight)`` in fp32 with its backward, every product on :func:`matmul_f32`."""
+
+    @staticmethod
+    def forward(ctx, x, weight, relu):
+        out = matmul_f32(x, weight, relu=relu)
+        ctx.relu = relu
+        ctx.save_for_backward(x, weight, out if relu else None)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, weight, out = ctx.saved_tensors
+        g = _relu_mask(grad_output, out) if ctx.relu else grad_output.contiguous()
+        gx = matmul_f32(g, weight, trans_b=True) if ctx.needs_input_grad[0] else None
+        gw = matmul_f32(x, g, trans_a=True) if ctx.needs_input_grad[1] else None
+        return gx, gw, None
+
+
+def linear_f32_autograd(x, weight, relu=False):
+    """The layers' transform in fp32 (``tf32=False``), usable in training."""
+    return _LinearF32.apply(_as_f32(x, "x"), _as_f32(weight, "weight"), bool(relu))
+
+
+class _LinearNT(torch.autograd.Function):
+    """``x @ weight^T + bias`` for a weight stored ``[out, in]`` (the layout of a ``Linear`` layer):
+    TF32 forward and input gradient on the tensor-core kernel when asked for, everything else on the fp32
+    kernel; the bias gradient is a column sum."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, tf32):
+        ctx.tf32 = tf32
+        ctx.has_bias = bias is not None
+        ctx.save_for_backward(x, weight)
+        if tf32 and linear_tf32_supported(x.shape[0], x.shape[1], weight.shape[0]):
+            return linear_tf32(x, weight.t(), bias=bias, weight_t=weight.contiguous())
+        return matmul_f32(x, weight, trans_b=True, bias=bias)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, weight = ctx.saved_tensors
+        g = grad_output.contiguous()
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            if ctx.tf32 and linear_tf32_supported(g.shape[0], g.shape[1], weight.shape[1]):
+                gx = linear_tf32(g, weight, weight_t=weight.t().contiguous())
+            else:
+                gx = matmul_f32(g, weight)
+        if ctx.needs_input_grad[1]:
+            gw = matmul_f32(g, x, trans_a=True)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = g.sum(0)
+        return gx, gw, gb, None
+
+
+def linear_nt(x, weight, bias=None, tf32=True):
+    """``x @ weight^T + bias`` with ``weight`` stored ``[out, in]``; differentiable."""
+    return _LinearNT.apply(_as_f32(x, "x"), _as_f32(weight, "weight"), bias, bool(tf32))
+
+
+def _relu_mask(grad, out):
+    """``grad * (out > 0)``: the gradient through a fused ReLU, from the saved output."""
+    return (grad * (out > 0)).contiguous()
+
+
 class _LinearTF32(torch.autograd.Function):
     """``act(x @ weight)`` through the tcgen05 kernel with a backward: ``grad_x = g @ weight^T`` runs
-    on the same kernel (its transposed operand is the weight itself), ``grad_weight = x^T @ g`` is a
-    reduction over the rows, a shape the row-tiled kernel does not cover, and goes to the library
-    matmul with TF32 allowed."""
+    on the same kernel (its transposed operand is the weight itself); ``grad_weight = x^T @ g`` is a
+    reduction over the rows, an operand layout the row-tiled kernel does not take, and runs on the fp32
+    CUDA-core kernel (sliced over the rows, fixed-order sum of the slices)."""
 
     @staticmethod
     def forward(ctx, x, weight, relu):
@@ -690,23 +775,15 @@ class _LinearTF32(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         x, weight, out = ctx.saved_tensors
-        g = grad_output
-        if ctx.relu:
-            g = g * (out > 0)
-        g = g.contiguous()
+        g = _relu_mask(grad_output, out) if ctx.relu else grad_output.contiguous()
         gx = gw = None
         if ctx.needs_input_grad[0]:
             if linear_tf32_supported(g.shape[0], g.shape[1], weight.shape[0]):
                 gx = linear_tf32(g, weight.t(), weight_t=weight.contiguous())
             else:
-                gx = g @ weight.t()
+                gx = matmul_f32(g, weight, trans_b=True)
         if ctx.needs_input_grad[1]:
-            before = torch.backends.cuda.matmul.allow_tf32
-            torch.backends.cuda.matmul.allow_tf32 = True
-            try:
-                gw = x.t() @ g
-            finally:
-                torch.backends.cuda.matmul.allow_tf32 = before
+            gw = matmul_f32(x, g, trans_a=True)
         return gx, gw, None
 
 

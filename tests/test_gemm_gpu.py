@@ -136,3 +136,47 @@ def test_status_word_is_polled_without_a_synchronisation(cuda):
         ops.linear_tf32(x, w)
     assert int(word[0]) == 0
     ops.linear_tf32(x, w, check_status=True)                         # and the path works again
+
+
+@pytest.mark.parametrize("M,N,K,ta,tb", [(300, 70, 45, False, False), (64, 64, 16, False, False), (2708, 256, 1433, False, False),
+                                        (1433, 256, 2708, True, False), (5000, 1433, 256, False, True), (128, 64, 300000, True, False),
+                                        (7, 5, 100000, True, False), (1, 1, 1, False, False)])
+def test_fp32_product_on_the_cuda_cores(cuda, M, N, K, ta, tb):
+    """``matmul_f32`` (x @ W, g @ W^T, x^T @ g by strides; long reductions sliced) against float64 at the
+    fp32 bar, and run-to-run identical."""
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn((K, M) if ta else (M, K), device="cuda", generator=g)
+    b = torch.randn((N, K) if tb else (K, N), device="cuda", generator=g)
+    bias = torch.randn(N, device="cuda", generator=g)
+    got = cuda.ops.matmul_f32(a, b, trans_a=ta, trans_b=tb, bias=bias, relu=True)
+    A, B = (a.t() if ta else a).double(), (b.t() if tb else b).double()
+    want = torch.relu(A @ B + bias.double())
+    scale = A.abs() @ B.abs() + bias.abs().double()
+    assert ((got.double() - want).abs() / scale).max().item() <= 1e-5
+    assert torch.equal(got, cuda.ops.matmul_f32(a, b, trans_a=ta, trans_b=tb, bias=bias, relu=True))
+
+
+def test_no_vendor_gemm_in_the_layers(cuda):
+    """GCNConv in both precisions trains without any library matmul: forward and all gradients agree with
+    float64 autograd at the bar of the precision chosen."""
+    from jittorgeometric_b200 import nn
+    torch.manual_seed(0)
+    n = 2000
+    ei = torch.randint(0, n, (2, 30000), device="cuda", dtype=torch.int32)
+    csc, csr = cuda.gcn_norm_csc_csr(ei, None, n)
+    x0 = torch.randn(n, 96, device="cuda")
+    A = torch.zeros((n, n), dtype=torch.float64, device="cuda")
+    seg = torch.repeat_interleave(torch.arange(n, device="cuda"), (csc.column_offset[1:] - csc.column_offset[:-1]).long())
+    A.index_put_((seg, csc.row_indices.long()), csc.edge_weight.double(), accumulate=True)
+    for tf32, bar in ((False, 1e-5), (True, 2e-3)):
+        layer = nn.GCNConv(96, 40, tf32=tf32, relu=True).cuda()
+        x = x0.clone().requires_grad_(True)
+        y = layer(x, csc, csr)
+        y.square().sum().backward()
+        xd = x0.double().requires_grad_(True)
+        wd = layer.weight.detach().double().requires_grad_(True)
+        bd = layer.bias.detach().double().requires_grad_(True)
+        yd = torch.relu(A @ (xd @ wd) + bd)
+        yd.square().sum().backward()
+        for have, want in ((y, yd), (x.grad, xd.grad), (layer.weight.grad, wd.grad), (layer.bias.grad, bd.grad)):
+            assert (have.double() - want).abs().max().item() <= 20 * bar * want.abs().max().item()
