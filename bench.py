@@ -402,7 +402,7 @@ def main():
     ap.add_argument("--scale", type=int, default=21)
     ap.add_argument("--edge-factor", type=int, default=32)
     ap.add_argument("--cpu-budget", type=float, default=16.0, help="seconds of CPU-baseline work (0 = skip)")
-    ap.add_argument("--workload", default="spmm", choices=["spmm", "convert", "gat", "gcn", "gemm", "sample", "citation", "edgeops"],
+    ap.add_argument("--workload", default="spmm", choices=["spmm", "convert", "gat", "gcn", "gemm", "sample", "citation", "edgeops", "exchange"],
                     help="spmm (default, the headline) or one of the other hot-path workloads (1 GPU; gcn also N > 1)")
     ap.add_argument("--widths", default=None, help="comma-separated subset of the sweep (profiling runs)")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")

@@ -384,8 +384,60 @@ def run_citation(args):
            "gpu_launches": args.steps * 8, "clocks": clocks})
 
 
+def run_exchange(args):
+    """The halo exchange kernels with the ranks of a 4-way partition emulated on ONE GPU (peers are local
+    buffers, so the figures show the kernels' own limits, not NVLink): the bulk-copy pull (1 KB rows), the
+    plain-load pull (512-byte rows), the fp16-payload pull, and the row-packing kernel of the collective
+    transport.  For profiling; multi-GPU numbers come from ``bench.py --gpus N``."""
+    import jittorgeometric_b200 as jg
+    from jittorgeometric_b200 import dist as jd, synth
+    from jittorgeometric_b200._lib import check, lib, ptr, stream_for
+    dev = torch.device("cuda", 0)
+    world, scale = 4, (20 if args.scale == 21 else args.scale)
+    n = 1 << scale
+    part = jd.RowPartition(n, world)
+    emu = jd.EmulatedRanks(world, pull_ctas=0)
+    graphs = []
+    for r in range(world):
+        lo, hi = part.range(r)
+        idx, off, deg = synth.rmat_shard_csc(scale, 16, bench.SEED, lo, hi, device=dev)
+        w = torch.ones(idx.numel(), device=dev)
+        graphs.append(jd.ShardedGraph(part, r, idx, off, w, transport=emu.transport(r), setup=False, mode="merged"))
+    emu.wire(graphs)
+    g = graphs[0]
+    peak, kind = bench.measured_peaks()
+    res = {}
+    for name, f, half in (("pull_bulk_f256", 256, False), ("pull_plain_f128", 128, False), ("pull_half_f128", 128, True)):
+        for h in graphs:
+            h.feature_buffer(f).normal_()
+            h.halo_half = half
+        pend = {}
+
+        def step():
+            pend["p"] = g.start(g.feature_buffer(f))
+            g._inflight.discard(f)
+        ms = _time(step, args.steps, args.warmup)
+        nbytes = g.n_halo * f * (2 if half else 4) + g.n_halo * f * 4       # rows read + fp32 rows written
+        res[name] = {"ms": ms, "halo_rows": g.n_halo, "gbs": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peak,
+                     "note": "includes the flag posts" + (" and the fp16 conversion of every emulated owner's rows" if half else "")}
+    x = g.feature_buffer(128)
+    rows = torch.randperm(g.n_local, device=dev)[: g.n_local // 2].sort().values.to(torch.int32) + g.lo
+    out = torch.empty((rows.numel(), 128), device=dev)
+    ms = _time(lambda: check(lib().jg_gather_rows_f32(ptr(out), ptr(x), ptr(rows), rows.numel(), 128, g.lo, stream_for(x)),
+                             "jg_gather_rows_f32"), args.steps, args.warmup)
+    res["gather_rows_f128"] = {"ms": ms, "rows": rows.numel(), "gbs": 2 * rows.numel() * 512 / ms / 1e6,
+                               "frac_of_hbm_peak": 2 * rows.numel() * 512 / ms / 1e6 / peak}
+    top = res["pull_bulk_f256"]
+    return _line(args, "halo_rows_per_s", "row/s", g.n_halo / (top["ms"] * 1e-3), top["ms"],
+                 f"halo exchange kernels, 4 ranks emulated on one GPU: R-MAT scale {scale}, rank 0 fetches {g.n_halo} of "
+                 f"{n - g.n_local} remote rows",
+                 {"bound": "hbm", "achieved": top["gbs"], "peak": peak, "unit": "GB/s", "frac": top["frac_of_hbm_peak"], "traffic": None,
+                  "peak_kind": kind, "kernel": "halo_pull_bulk_kernel", "note": "bytes = halo rows read once + written once"},
+                 {"kernels": res, "gpu_launches": args.steps * 2})
+
+
 def run(args):
-    line = {"citation": run_citation, "edgeops": run_edgeops, "convert": run_convert, "gat": run_gat, "gemm": run_gemm,
+    line = {"exchange": run_exchange, "citation": run_citation, "edgeops": run_edgeops, "convert": run_convert, "gat": run_gat, "gemm": run_gemm,
             "gcn": run_gcn, "sample": run_sample}[args.workload](args)
     if line is not None:
         print(json.dumps(line))

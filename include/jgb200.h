@@ -50,11 +50,11 @@ int jg_set_device(int device);
  * ops/aggregateWithWeight.py:19-41): called with the CSC arrays it is the forward
  * pass, with the CSR arrays the backward pass.  It is also the kernel behind the
  * cuSPARSE-backed SpmmCsr/SpmmCoo (ops/spmmcsr.py:21-44, ops/spmmcoo.py:19-45).
- * Multiply and add are rounded separately.  For f < 32 and f > 64 the terms of a row
+ * For f < 32 and f > 64 multiply and add are rounded separately and the terms of a row
  * are added in ascending j, so rows of at most `chunk` entries reproduce the
  * reference CPU loop bit for bit; for 32 <= f <= 64 two or four entries are taken side
- * by side and their partial sums added at the end (rounding-level difference; use
- * jg_aggregate_ordered_f32 where the order matters).  Longer rows are split into
+ * by side with fused multiply-adds and their partial sums added at the end
+ * (rounding-level difference; use jg_aggregate_ordered_f32 where the order matters).  Longer rows are split into
  * `chunk`-sized pieces whose partial sums are added in piece order.  No atomics touch
  * `out`.  Any f >= 1 is accepted: f <= 32 runs several rows per warp, 16-byte-aligned
  * widths up to 512 use 128-bit gathers, other widths column-strided scalar loads.

@@ -22,15 +22,18 @@ __device__ __forceinline__ int32_t owner_of(const int32_t* __restrict__ off, int
     return lo;
 }
 
-// One warp copies node rows onto 32 consecutive edges at a time.
+// One warp copies node rows onto 32 consecutive edges at a time.  G lanes share a row (G * 16 bytes per
+// step), 32 / G rows are copied side by side and four such steps are in flight, so a 256-byte row does
+// not leave half the warp idle behind one dependent load.
 __global__ void __launch_bounds__(kEdgeBlock) scatter_to_edge_kernel(float* __restrict__ out, const float* __restrict__ x,
                                                                      const int32_t* __restrict__ idx,
                                                                      const int32_t* __restrict__ off, int64_t n, int64_t E,
-                                                                     int64_t C, int flag) {
+                                                                     int64_t C, int flag, int lanes_per_row) {
     const int lane = lane_id();
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    const bool vec = (C % 4 == 0) && ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x)) % 16 == 0);
+    const bool vec = lanes_per_row > 0;   // 0: width or pointers that 16-byte accesses cannot take
+    const int G = vec ? lanes_per_row : 32, sub = lane / G, gl = lane % G, R = 32 / G;
     for (int64_t e0 = warp * 32; e0 < E; e0 += n_warps * 32) {
         const int64_t e = e0 + lane;
         int32_t node = 0;
@@ -44,14 +47,33 @@ __global__ void __launch_bounds__(kEdgeBlock) scatter_to_edge_kernel(float* __re
             if (e < E) node = owner_of(off, r_first, r_last, (int32_t)e);
         }
         const int cnt = (E - e0) < 32 ? (int)(E - e0) : 32;
-        for (int k = 0; k < cnt; k++) {
-            const int32_t src = __shfl_sync(kFull, node, k);
-            const float* xr = x + (size_t)src * C;
-            float* o = out + (size_t)(e0 + k) * C;
-            if (vec) {
-                for (int64_t c = lane; c < C / 4; c += 32)
-                    __stcs(reinterpret_cast<float4*>(o) + c, __ldg(reinterpret_cast<const float4*>(xr) + c));
-            } else {
+        if (vec) {
+            constexpr int U = 4;
+            const int64_t chunks = C / 4;
+            for (int k0 = 0; k0 < cnt; k0 += R * U) {
+                int32_t src[U];
+#pragma unroll
+                for (int u = 0; u < U; u++) src[u] = __shfl_sync(kFull, node, (k0 + u * R + sub) & 31);
+                for (int64_t c = gl; c < chunks; c += G) {
+                    float4 v[U];
+#pragma unroll
+                    for (int u = 0; u < U; u++) {
+                        const int k = k0 + u * R + sub;
+                        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (k < cnt) v[u] = __ldg(reinterpret_cast<const float4*>(x + (size_t)src[u] * C) + c);
+                    }
+#pragma unroll
+                    for (int u = 0; u < U; u++) {
+                        const int k = k0 + u * R + sub;
+                        if (k < cnt) __stcs(reinterpret_cast<float4*>(out + (size_t)(e0 + k) * C) + c, v[u]);
+                    }
+                }
+            }
+        } else {
+            for (int k = 0; k < cnt; k++) {
+                const int32_t src = __shfl_sync(kFull, node, k);
+                const float* xr = x + (size_t)src * C;
+                float* o = out + (size_t)(e0 + k) * C;
                 for (int64_t c = lane; c < C; c += 32) o[c] = __ldg(xr + c);
             }
         }
@@ -200,20 +222,47 @@ __device__ __forceinline__ float block_same_column(float v, float* s_buf /*[kEdg
     return r;
 }
 
+// One block per long segment, the same two sweeps as the warp kernel: running (maximum, sum) with four
+// loads in flight per thread, merged across the block in thread order, then the normalised values.
 template <int HP>
 __global__ void __launch_bounds__(kEdgeBlock) edge_softmax_fwd_hub_kernel(float* __restrict__ y, const float* __restrict__ x,
                                                                           const int32_t* __restrict__ off, int64_t n) {
-    __shared__ float s_buf[kEdgeBlock];
+    __shared__ float s_m[kEdgeBlock], s_s[kEdgeBlock];
+    const int lane = threadIdx.x & 31;
     for (int64_t v = blockIdx.x; v < n; v += gridDim.x) {
         if (off[v + 1] - off[v] < kSoftmaxHub) continue;   // block-uniform
         const int64_t s = (int64_t)off[v] * HP, e = (int64_t)off[v + 1] * HP;
-        float mx = -INFINITY;
-        for (int64_t i = s + threadIdx.x; i < e; i += kEdgeBlock) mx = fmaxf(mx, x[i]);
-        mx = block_same_column<HP, true>(mx, s_buf);
-        float sum = 0.f;
-        for (int64_t i = s + threadIdx.x; i < e; i += kEdgeBlock) sum += expf(x[i] - mx);
-        sum = block_same_column<HP, false>(sum, s_buf);
-        for (int64_t i = s + threadIdx.x; i < e; i += kEdgeBlock) y[i] = expf(x[i] - mx) / sum;
+        MaxSum st = {-INFINITY, 0.f};
+        int64_t i = s + threadIdx.x;
+        for (; i + 3 * kEdgeBlock < e; i += 4 * kEdgeBlock)
+            st.add4(x[i], x[i + kEdgeBlock], x[i + 2 * kEdgeBlock], x[i + 3 * kEdgeBlock]);
+        for (; i < e; i += kEdgeBlock) st.add(x[i]);
+#pragma unroll
+        for (int o = 16; o >= HP; o >>= 1) {   // lanes of the same column inside the warp
+            const float m2 = __shfl_xor_sync(kFull, st.m, o), s2 = __shfl_xor_sync(kFull, st.s, o);
+            if (lane & o) {
+                MaxSum other = {m2, s2};
+                other.merge(st.m, st.s);
+                st = other;
+            } else {
+                st.merge(m2, s2);
+            }
+        }
+        __syncthreads();
+        s_m[threadIdx.x] = st.m;
+        s_s[threadIdx.x] = st.s;
+        __syncthreads();
+        MaxSum all = {s_m[lane], s_s[lane]};     // warps in order: every thread ends with the same state per column
+#pragma unroll
+        for (int w = 1; w < kEdgeBlock / 32; w++) all.merge(s_m[w * 32 + lane], s_s[w * 32 + lane]);
+        const float mx = all.m, inv = 1.f / all.s;
+        i = s + threadIdx.x;
+        for (; i + 3 * kEdgeBlock < e; i += 4 * kEdgeBlock) {
+            const float a0 = x[i], a1 = x[i + kEdgeBlock], a2 = x[i + 2 * kEdgeBlock], a3 = x[i + 3 * kEdgeBlock];
+            y[i] = expf(a0 - mx) * inv; y[i + kEdgeBlock] = expf(a1 - mx) * inv;
+            y[i + 2 * kEdgeBlock] = expf(a2 - mx) * inv; y[i + 3 * kEdgeBlock] = expf(a3 - mx) * inv;
+        }
+        for (; i < e; i += kEdgeBlock) y[i] = expf(x[i] - mx) * inv;
     }
 }
 
@@ -269,9 +318,23 @@ __global__ void __launch_bounds__(kEdgeBlock) edge_softmax_bwd_hub_kernel(float*
         if (off[v + 1] - off[v] < kSoftmaxHub) continue;   // block-uniform
         const int64_t s = (int64_t)off[v] * HP, e = (int64_t)off[v + 1] * HP;
         float dot = 0.f;
-        for (int64_t i = s + threadIdx.x; i < e; i += kEdgeBlock) dot += y[i] * g[i];
+        int64_t i = s + threadIdx.x;
+        for (; i + 3 * kEdgeBlock < e; i += 4 * kEdgeBlock) {   // eight independent loads in flight, added in order
+            const float p0 = y[i] * g[i], p1 = y[i + kEdgeBlock] * g[i + kEdgeBlock];
+            const float p2 = y[i + 2 * kEdgeBlock] * g[i + 2 * kEdgeBlock], p3 = y[i + 3 * kEdgeBlock] * g[i + 3 * kEdgeBlock];
+            dot = (((dot + p0) + p1) + p2) + p3;
+        }
+        for (; i < e; i += kEdgeBlock) dot += y[i] * g[i];
         dot = block_same_column<HP, false>(dot, s_buf);
-        for (int64_t i = s + threadIdx.x; i < e; i += kEdgeBlock) dx[i] = __fsub_rn(__fmul_rn(y[i], g[i]), __fmul_rn(y[i], dot));
+        i = s + threadIdx.x;
+        for (; i + 3 * kEdgeBlock < e; i += 4 * kEdgeBlock) {
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const float yy = y[i + u * kEdgeBlock], gg = g[i + u * kEdgeBlock];
+                dx[i + u * kEdgeBlock] = __fsub_rn(__fmul_rn(yy, gg), __fmul_rn(yy, dot));
+            }
+        }
+        for (; i < e; i += kEdgeBlock) dx[i] = __fsub_rn(__fmul_rn(y[i], g[i]), __fmul_rn(y[i], dot));
     }
 }
 
@@ -335,8 +398,13 @@ int jg_scatter_to_edge_f32(float* out, const float* x, const int32_t* idx, const
     JG_CHECK_ARG(out && x && idx && off, JG_EINVAL, "scatter_to_edge: null pointer");
     JG_CHECK_ARG(n_nodes > 0, JG_ESHAPE, "scatter_to_edge: edges without nodes");
     JG_CHECK_ARG(n_edges <= INT32_MAX && n_nodes < INT32_MAX, JG_ESHAPE, "scatter_to_edge: sizes beyond int32");
+    int lanes_per_row = 0;
+    if (c % 4 == 0 && (reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x)) % 16 == 0) {
+        lanes_per_row = 1;
+        while (lanes_per_row < 32 && lanes_per_row * 4 < c) lanes_per_row *= 2;
+    }
     scatter_to_edge_kernel<<<grid_for_warps((n_edges + 31) / 32), kEdgeBlock, 0, static_cast<cudaStream_t>(stream)>>>(
-        out, x, idx, off, n_nodes, n_edges, c, flag);
+        out, x, idx, off, n_nodes, n_edges, c, flag, lanes_per_row);
     JG_LAUNCH_CHECK();
     return JG_OK;
 }

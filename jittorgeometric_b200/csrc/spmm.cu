@@ -549,8 +549,11 @@ static int dispatch_aggregate(const AggArgs& a, cudaStream_t st) {
     // widths up to 64 normally put two or four entries of a row side by side in one warp and add the
     // lane groups' partial sums at the end; an ordered sum takes the narrow kernel (F <= 32) or the
     // 128-column layout with idle lanes (F <= 64) instead
-    if (vec_ok && f == 32 && !a.ordered) return launch_rows<8, 1, 8, 4, true>(a, st);
-    if (vec_ok && f > 32 && f <= 64 && !a.ordered) return launch_rows<16, 1, 8, 4, true>(a, st);
+    // (the lane groups' partial sums are added at the end, so these two layouts differ from the sequential
+    // sum by rounding anyway: they use one fused multiply-add per term, half the arithmetic instructions
+    // of the separately rounded form, in a kernel that is bound by instruction issue at these widths)
+    if (vec_ok && f == 32 && !a.ordered) return launch_rows<8, 1, 8, 4, false>(a, st);
+    if (vec_ok && f > 32 && f <= 64 && !a.ordered) return launch_rows<16, 1, 8, 4, false>(a, st);
     if (vec_ok && f > 32 && f <= 64) return launch_rows<32, 1, 8, 4, true>(a, st);
     if (vec_ok && f > 64 && f <= 128) return launch_rows<32, 1, 8, 4, true>(a, st);
     if (vec_ok && f > 128 && f <= 256) return launch_rows<32, 2, 4, 4, true>(a, st);

@@ -487,7 +487,7 @@ def _edge_softmax(x, off, bwd_y=None):
     x2 = _as_f32(x, "x").reshape(shape[0], -1)
     E, h = x2.shape
     n = off.numel() - 1
-    out = torch.zeros_like(x2)     # empty segments write nothing, like the reference
+    out = torch.empty_like(x2)     # every edge lies in exactly one segment, so every element is written
     if bwd_y is None:
         check(lib().jg_edge_softmax_fwd_f32(ptr(out), ptr(x2), ptr(off), n, E, h, stream_for(x2)), "jg_edge_softmax_fwd_f32")
     else:
