@@ -232,12 +232,22 @@ def run(args):
         x.copy_(x_of(rank, f))
         xs[f] = x
 
+    ahead = max(1, int(os.environ.get("JG_SWEEP_AHEAD", str(len(widths)))))
+
     def step():
         # the aggregations of a step are independent: every exchange is started first, so the halo rows of
         # the next width travel beside the current aggregation kernel
-        # (a start queued after an aggregation would wait for it in stream order, so all starts come first)
-        pending = [g.start(xs[f]) for f in widths]
-        return [g.finish(p) for p in pending]
+        # (a start queued after an aggregation waits for it in stream order, so by default all starts come first;
+        # JG_SWEEP_AHEAD = k keeps only k exchanges ahead of the aggregation being queued)
+        if ahead >= len(widths):
+            pending = [g.start(xs[f]) for f in widths]
+            return [g.finish(p) for p in pending]
+        pending, ys = [g.start(xs[f]) for f in widths[:ahead]], []
+        for f in widths[ahead:]:
+            ys.append(g.finish(pending.pop(0)))
+            pending.append(g.start(xs[f]))
+        ys.extend(g.finish(p) for p in pending)
+        return ys
 
     for _ in range(args.warmup):
         step()

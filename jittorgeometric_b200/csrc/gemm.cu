@@ -160,7 +160,7 @@ struct GemmSmem {
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                 const __grid_constant__ CUtensorMap map_out, GemmParams p) {
+                 const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_half, GemmParams p) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // ring first (1024-byte aligned stages), control block after it
     unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -169,7 +169,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const uint32_t b_bytes = ((b_rows * kTileK * 4) + 1023) / 1024 * 1024;
     const uint32_t stage_bytes = a_bytes + b_bytes;
     unsigned char* slabs = ring + kStages * stage_bytes;                 // 4 KB per epilogue warp (TMA-store epilogue)
-    GemmSmem* ctl = reinterpret_cast<GemmSmem*>(slabs + (p.tma_store ? kEpiWarps * 4096 : 0));
+    unsigned char* hslabs = slabs + (p.tma_store ? kEpiWarps * 4096 : 0);   // 2 KB per epilogue warp (fp16 copy)
+    GemmSmem* ctl = reinterpret_cast<GemmSmem*>(hslabs + (p.out_half ? kEpiWarps * 2048 : 0));
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
 
     if (threadIdx.x == 0) {
@@ -338,24 +339,6 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
                         for (int i = 0; i < 32; i++) v[i] = fmaxf(v[i], 0.f);
                     }
-                    if (p.out_half && row < p.n_rows) {
-                        // the fp16 copy a partitioned aggregation offers to its peers: this lane's 32 values as
-                        // 64 contiguous bytes of its row (values beyond the fp16 range saturate)
-                        uint4* oh = reinterpret_cast<uint4*>(p.out_half + row * p.ldo + c0);
-#pragma unroll
-                        for (int i = 0; i < 4; i++) {
-                            if (c0 + 8 * i < p.m) {
-                                uint4 pk;
-                                __half2 h0 = __floats2half2_rn(fminf(fmaxf(v[8 * i], -65504.f), 65504.f), fminf(fmaxf(v[8 * i + 1], -65504.f), 65504.f));
-                                __half2 h1 = __floats2half2_rn(fminf(fmaxf(v[8 * i + 2], -65504.f), 65504.f), fminf(fmaxf(v[8 * i + 3], -65504.f), 65504.f));
-                                __half2 h2 = __floats2half2_rn(fminf(fmaxf(v[8 * i + 4], -65504.f), 65504.f), fminf(fmaxf(v[8 * i + 5], -65504.f), 65504.f));
-                                __half2 h3 = __floats2half2_rn(fminf(fmaxf(v[8 * i + 6], -65504.f), 65504.f), fminf(fmaxf(v[8 * i + 7], -65504.f), 65504.f));
-                                pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
-                                pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                                __stcs(oh + i, pk);
-                            }
-                        }
-                    }
                     unsigned char* slab = slabs + (warp - 2) * 4096;
                     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // previous store has read the slab
                     __syncwarp();
@@ -363,11 +346,31 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     for (int c = 0; c < 8; c++)
                         *reinterpret_cast<float4*>(slab + lane * 128 + ((c ^ (lane & 7)) << 4)) =
                             make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+                    unsigned char* hslab = hslabs + (warp - 2) * 2048;
+                    if (p.out_half) {
+                        // the fp16 copy a partitioned aggregation offers to its peers: the same 32x32 block as 64-byte
+                        // rows in the 64-byte swizzle (16-byte chunk c of row r at chunk c ^ ((r >> 1) & 3)), stored
+                        // by a second bulk tensor store; values beyond the fp16 range saturate
+#pragma unroll
+                        for (int c = 0; c < 4; c++) {
+                            uint4 pk;
+                            __half2 h0 = __floats2half2_rn(fminf(fmaxf(v[8 * c], -65504.f), 65504.f), fminf(fmaxf(v[8 * c + 1], -65504.f), 65504.f));
+                            __half2 h1 = __floats2half2_rn(fminf(fmaxf(v[8 * c + 2], -65504.f), 65504.f), fminf(fmaxf(v[8 * c + 3], -65504.f), 65504.f));
+                            __half2 h2 = __floats2half2_rn(fminf(fmaxf(v[8 * c + 4], -65504.f), 65504.f), fminf(fmaxf(v[8 * c + 5], -65504.f), 65504.f));
+                            __half2 h3 = __floats2half2_rn(fminf(fmaxf(v[8 * c + 6], -65504.f), 65504.f), fminf(fmaxf(v[8 * c + 7], -65504.f), 65504.f));
+                            pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                            pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                            *reinterpret_cast<uint4*>(hslab + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)) = pk;
+                        }
+                    }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {
                         asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
                                      ::"l"(&map_out), "r"(p.col_base + c0), "r"(tile * kTileM + quad * 32), "r"(smem_u32(slab)) : "memory");
+                        if (p.out_half)
+                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                                         ::"l"(&map_half), "r"(p.col_base + c0), "r"(tile * kTileM + quad * 32), "r"(smem_u32(hslab)) : "memory");
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
                 } else if (row < p.n_rows) {
@@ -428,6 +431,21 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// 2-D fp16 tensor [rows, cols] row-major, box [32 rows, 32 columns] = 64-byte rows, 64-byte swizzle (stores only).
+static int make_map_half(CUtensorMap* map, const void* base, int64_t rows, int64_t cols) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    JG_CHECK_ARG(enc, JG_ECUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    JG_CHECK_ARG(r == CUDA_SUCCESS, JG_ECUDA, "cuTensorMapEncodeTiled (fp16) failed with code %d", (int)r);
+    return JG_OK;
+}
+
 // 2-D fp32 tensor [rows, cols] row-major, box [box_rows, 32 columns], 128-byte swizzle, zero fill
 // on loads / clipping on stores outside the tensor.
 static int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t cols, int box_rows) {
@@ -486,6 +504,13 @@ static int gemm_tile(float* out, const float* x, const float* wt, const float* b
     p.out = out; p.bias = bias; p.n_rows = n_rows; p.k = (int32_t)k; p.m = (int32_t)m; p.relu = relu;
     p.ldo = (int32_t)m_total; p.col_base = (int32_t)col_base;
     p.out_half = out_half;
+    CUtensorMap map_half;
+    memset(&map_half, 0, sizeof(map_half));
+    if (out_half) {
+        JG_CHECK_ARG(p.tma_store, JG_ESHAPE, "gemm_tf32: the fp16 copy needs an output width that is a multiple of 8");
+        int rc3 = make_map_half(&map_half, out_half - col_base, n_rows, m_total);
+        if (rc3 != JG_OK) return rc3;
+    }
     int pad = 32;
     while (pad < b_rows) pad *= 2;
     p.m_pad = pad;
@@ -494,7 +519,8 @@ static int gemm_tile(float* out, const float* x, const float* wt, const float* b
     p.error = error;
     const size_t a_bytes = kTileM * kTileK * 4;
     const size_t b_bytes = ((size_t)b_rows * kTileK * 4 + 1023) / 1024 * 1024;
-    const size_t smem = 1024 + kStages * (a_bytes + b_bytes) + (p.tma_store ? kEpiWarps * 4096 : 0) + sizeof(GemmSmem) + 64;
+    const size_t smem = 1024 + kStages * (a_bytes + b_bytes) + (p.tma_store ? kEpiWarps * 4096 : 0) +
+                        (out_half ? kEpiWarps * 2048 : 0) + sizeof(GemmSmem) + 64;
     static size_t attr_done[64] = {0};
     int dev = 0;
     JG_CUDA(cudaGetDevice(&dev));
@@ -504,7 +530,7 @@ static int gemm_tile(float* out, const float* x, const float* wt, const float* b
     }
     int grid = sm_count();
     if (grid > p.n_tiles) grid = p.n_tiles;
-    gemm_tf32_kernel<<<grid, kGemmThreads, smem, st>>>(map_x, map_w, map_out, p);
+    gemm_tf32_kernel<<<grid, kGemmThreads, smem, st>>>(map_x, map_w, map_out, map_half, p);
     JG_LAUNCH_CHECK();
     return JG_OK;
 }
@@ -525,9 +551,11 @@ static int gemm_impl(float* out, void* out_half, const float* x, const float* wt
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int32_t* error = static_cast<int32_t*>(workspace);
     if (clear_error) JG_CUDA(cudaMemsetAsync(error, 0, sizeof(int32_t), st));
-    // wider outputs: one launch per tile of 256 columns (x is read once per tile)
-    for (int64_t cb = 0; cb < m; cb += 256) {
-        const int64_t mt = m - cb < 256 ? m - cb : 256;
+    // wider outputs: one launch per tile of 256 columns (x is read once per tile); 128 columns when the fp16
+    // copy needs its own staging slabs in shared memory
+    const int64_t tile_w = out_half ? 128 : 256;
+    for (int64_t cb = 0; cb < m; cb += tile_w) {
+        const int64_t mt = m - cb < tile_w ? m - cb : tile_w;
         int rc = gemm_tile(out + cb, x, wt + cb * k, bias ? bias + cb : nullptr, n_rows, k, mt, m, cb, relu, error, st,
                            out_half ? static_cast<__half*>(out_half) + cb : nullptr);
         if (rc != JG_OK) return rc;

@@ -312,18 +312,17 @@ class DirectTransport(CollectiveTransport):
                       (ctypes.c_int32 * self.world)(*[int(g.part.bounds[q]) for q in range(self.world)]))
             g._pull_tables = tables
         seg, los = tables
-        halo = slot.buf[g.n_local:]
-        with torch.cuda.stream(self.side):
-            begun = None
-            if self.profile:                      # timing events around the pull (benchmarks: where a step's time goes)
-                begun = torch.cuda.Event(enable_timing=True)
-                begun.record(self.side)
-            check(lib().jg_halo_pull(ptr(halo), ptr(g.needed), slot.ptrs16 if half else slot.ptrs, self._flag_ptrs, seg, los,
-                                     self.world, self.rank, (2 if half else 4) * f, slot.index, slot.epoch, ptr(self._counter),
-                                     self._eptr(), self.wait_ns, self.pull_ctas, 1 if self.plain else 0, 1 if half else 0,
-                                     ctypes.c_void_p(self.side.cuda_stream)), "jg_halo_pull")
-            landed = torch.cuda.Event(enable_timing=self.profile)
-            landed.record(self.side)
+        halo_ptr = ctypes.c_void_p(slot.buf.data_ptr() + g.n_local * f * 4)
+        begun = None
+        if self.profile:                      # timing events around the pull (benchmarks: where a step's time goes)
+            begun = torch.cuda.Event(enable_timing=True)
+            begun.record(self.side)
+        check(lib().jg_halo_pull(halo_ptr, ptr(g.needed), slot.ptrs16 if half else slot.ptrs, self._flag_ptrs, seg, los,
+                                 self.world, self.rank, (2 if half else 4) * f, slot.index, slot.epoch, ptr(self._counter),
+                                 self._eptr(), self.wait_ns, self.pull_ctas, 1 if self.plain else 0, 1 if half else 0,
+                                 ctypes.c_void_p(self.side.cuda_stream)), "jg_halo_pull")
+        landed = torch.cuda.Event(enable_timing=self.profile)
+        landed.record(self.side)
         return _DirectHandle(self, landed, begun)
 
 
