@@ -77,7 +77,7 @@ __global__ void plan_build_kernel(const int32_t* __restrict__ off, int64_t n, Pl
     }
 }
 
-constexpr int kGrab = 8;      // work ids taken per ticket
+constexpr int kGrab = 8;      // most work ids taken per ticket (AggArgs::grab: fewer when the work is short)
 constexpr int kBlock = 256;   // threads per CTA
 
 struct AggArgs {
@@ -101,6 +101,7 @@ struct AggArgs {
     int relu;           // ... then max(., 0)
     int ordered;        // 1: every row must be summed in stored order (no lane groups taking alternate entries)
     int reserve_ctas;   // CTA slots of the persistent grid left free for a kernel that runs beside this one
+    int grab;           // work ids per ticket, 1..kGrab (set by the launcher from the amount of work)
 };
 
 
@@ -142,23 +143,24 @@ __global__ void __launch_bounds__(kBlock, MINB) aggregate_rows_kernel(AggArgs a)
     const int64_t n_items = a.hdr ? a.hdr->n_items : 0;
     const int chunk = a.hdr ? a.hdr->chunk : 0x7fffffff;
     const int64_t total = n_items + a.n_out;
+    const int grab = a.grab;
     for (;;) {
         unsigned long long base = 0;
-        if (lane == 0) base = atomicAdd(a.ticket, (unsigned long long)kGrab);
+        if (lane == 0) base = atomicAdd(a.ticket, (unsigned long long)grab);
         base = __shfl_sync(kFull, base, 0);
         if ((int64_t)base >= total) break;
         const int64_t row0 = (int64_t)base - n_items;
         int32_t offv = 0;
         {
             const int64_t r = row0 + lane;
-            if (lane <= kGrab && r >= 0 && r <= a.n_out) offv = a.off[r];
+            if (lane <= grab && r >= 0 && r <= a.n_out) offv = a.off[r];
         }
         int32_t pf_pos = -1;  // position of the prefetched tile
         int32_t pf_lim = -1;  // ... which holds entries below this bound only
         int pf_idx = 0;
         float pf_w = 0.f;
 #pragma unroll 1
-        for (int i = 0; i < kGrab; i++) {
+        for (int i = 0; i < grab; i++) {
             const int64_t id = (int64_t)base + i;
             if (id >= total) break;
             int32_t s, e, lim;
@@ -179,7 +181,7 @@ __global__ void __launch_bounds__(kBlock, MINB) aggregate_rows_kernel(AggArgs a)
                 if (e - s > chunk) continue;  // hub row: its pieces are separate work ids
                 // entries of the following rows of this grab are contiguous with this row's
                 const int64_t left = a.n_out - row0;
-                const int last = left < kGrab ? (int)left : kGrab;
+                const int last = left < grab ? (int)left : grab;
                 lim = __shfl_sync(kFull, offv, last);
                 dst = a.out + (size_t)(id - n_items) * F;
             }
@@ -352,9 +354,10 @@ __global__ void __launch_bounds__(kBlock) aggregate_any_kernel(AggArgs a) {
     const int chunk = a.hdr ? a.hdr->chunk : 0x7fffffff;
     const int64_t total = n_items + a.n_out;
     const int64_t F = a.f;
+    const int grab = a.grab;
     for (;;) {
         unsigned long long base = 0;
-        if (lane == 0) base = atomicAdd(a.ticket, (unsigned long long)kGrab);
+        if (lane == 0) base = atomicAdd(a.ticket, (unsigned long long)grab);
         base = __shfl_sync(kFull, base, 0);
         if ((int64_t)base >= total) break;
         // offsets of up to kGrab consecutive ordinary rows with one coalesced read
@@ -362,10 +365,10 @@ __global__ void __launch_bounds__(kBlock) aggregate_any_kernel(AggArgs a) {
         int32_t offv = 0;
         {
             const int64_t r = row0 + lane;
-            if (lane <= kGrab && r >= 0 && r <= a.n_out) offv = a.off[r];
+            if (lane <= grab && r >= 0 && r <= a.n_out) offv = a.off[r];
         }
 #pragma unroll 1
-        for (int i = 0; i < kGrab; i++) {
+        for (int i = 0; i < grab; i++) {
             const int64_t id = (int64_t)base + i;
             if (id >= total) break;
             int32_t s, e;
@@ -517,13 +520,21 @@ static int launch_persistent(K kern, int* blocks_per_sm, const AggArgs& a, cudaS
         JG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, kern, kBlock, 0));
         *blocks_per_sm = b > 0 ? b : 1;
     }
-    const int64_t grabs = (a.n_out + a.max_items + kGrab - 1) / kGrab;
-    int64_t blocks = (grabs + kBlock / 32 - 1) / (kBlock / 32);
     int64_t full = (int64_t)sm_count() * *blocks_per_sm;
     if (a.reserve_ctas > 0) full = full - a.reserve_ctas > sm_count() ? full - a.reserve_ctas : sm_count();
+    // Tickets of eight ids keep the atomic rare on a large graph; when a warp would see fewer than about
+    // two dozen tickets the tail (the last warps still walking their eight rows while the rest of the
+    // device idles) dominates, so the tickets get smaller: a shard of 262 k rows ran at half the per-entry
+    // speed of the whole graph with eight ids per ticket.
+    AggArgs b = a;
+    const int64_t ids = a.n_out + a.max_items;
+    int64_t g = ids / (full * (kBlock / 32) * 24);
+    b.grab = g < 1 ? 1 : (g > kGrab ? kGrab : (int)g);
+    const int64_t grabs = (ids + b.grab - 1) / b.grab;
+    int64_t blocks = (grabs + kBlock / 32 - 1) / (kBlock / 32);
     if (blocks > full) blocks = full;
     if (blocks < 1) blocks = 1;
-    kern<<<(unsigned)blocks, kBlock, 0, st>>>(a);
+    kern<<<(unsigned)blocks, kBlock, 0, st>>>(b);
     JG_LAUNCH_CHECK();
     return JG_OK;
 }

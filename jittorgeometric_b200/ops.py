@@ -20,6 +20,8 @@ __all__ = ["aggregateWithWeight", "aggregate_bias_act", "segment_aggregate", "Sp
 DEFAULT_CHUNK = int(os.environ.get("JG_SPMM_CHUNK", "1024"))
 SMALL_GRAPH_NNZ = 1 << 20
 SMALL_GRAPH_CHUNK = int(os.environ.get("JG_SPMM_SMALL_CHUNK", "64"))
+FEW_ROWS = 1 << 19
+FEW_ROWS_CHUNK = int(os.environ.get("JG_SPMM_FEW_ROWS_CHUNK", "256"))
 
 
 def _as_i32(t, name):
@@ -50,11 +52,17 @@ def validate_structure(idx, off, n_in):
                                      stream_for(off)), "jg_validate_segments")
 
 
-def default_chunk(nnz):
+def default_chunk(nnz, n_out=None):
     """Piece length for hub rows.  On a small graph the longest row is the critical path of the whole
     aggregation (one warp walks it while the rest of the GPU idles), so rows are cut much shorter
-    there; on a large graph long pieces keep the number of partial rows small."""
-    return DEFAULT_CHUNK if nnz >= SMALL_GRAPH_NNZ else min(DEFAULT_CHUNK, SMALL_GRAPH_CHUNK)
+    there; on a large graph long pieces keep the number of partial rows small.  In between - many
+    nonzeros but few output rows, e.g. one shard of an 8-way partition - a 1024-entry row is still a
+    quarter of a millisecond of one warp's time against a kernel of a millisecond or two: 256."""
+    if nnz < SMALL_GRAPH_NNZ:
+        return min(DEFAULT_CHUNK, SMALL_GRAPH_CHUNK)
+    if n_out is not None and n_out < FEW_ROWS:
+        return min(DEFAULT_CHUNK, FEW_ROWS_CHUNK)
+    return DEFAULT_CHUNK
 
 
 class SpmmPlan:
@@ -63,9 +71,9 @@ class SpmmPlan:
     on the offsets; build once per graph and reuse."""
 
     def __init__(self, off, nnz, chunk=None):
-        chunk = default_chunk(nnz) if chunk is None else int(chunk)
-        self.chunk = chunk
         self.n_out = off.numel() - 1
+        chunk = default_chunk(nnz, self.n_out) if chunk is None else int(chunk)
+        self.chunk = chunk
         self.nnz = int(nnz)
         self.off_ptr = off.data_ptr()
         nbytes = lib().jg_spmm_plan_bytes(self.n_out, self.nnz, chunk)
@@ -79,7 +87,7 @@ def _plan_of(holder, off, nnz):
     if holder is None:
         return SpmmPlan(off, nnz)
     plan = getattr(holder, "_jg_plan", None)
-    if plan is None or plan.off_ptr != off.data_ptr() or plan.nnz != nnz or plan.chunk != default_chunk(nnz):
+    if plan is None or plan.off_ptr != off.data_ptr() or plan.nnz != nnz or plan.chunk != default_chunk(nnz, off.numel() - 1):
         plan = SpmmPlan(off, nnz)
         holder._jg_plan = plan
     return plan
