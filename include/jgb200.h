@@ -369,6 +369,17 @@ int jg_gemm_tf32_status(const void* workspace, jg_stream_t stream);
 int jg_gemm_tf32_dual(float* out, void* out_half, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k,
                       int64_t m, int relu, void* workspace, size_t workspace_bytes, jg_stream_t stream);
 
+/* Weight gradient gw[k, m] = x^T * g (x [n_rows, k], g [n_rows, m], both row-major) on the tensor cores, TF32
+ * products: the product Jittor's autograd forms for `x @ self.weight` (nn/conv/gcn_conv.py:95).  The
+ * reduction runs over the rows, so both operands are MN-major for tcgen05; the rows are cut into slices,
+ * one CTA per (slice, 128 features), and the slices' partial results are added in a fixed order.
+ * Supported when k % 4 == 0, m % 4 == 0 and m <= 256 (jg_gemm_tn_tf32_supported); other shapes take
+ * jg_gemm_f32.  `error` is a sticky word as in jg_gemm_tf32_dual. */
+int jg_gemm_tn_tf32_supported(int64_t n_rows, int64_t k, int64_t m);
+size_t jg_gemm_tn_tf32_workspace_bytes(int64_t n_rows, int64_t k, int64_t m);
+int jg_gemm_tn_tf32(float* gw, const float* x, const float* g, int64_t n_rows, int64_t k, int64_t m, int32_t* error,
+                    void* workspace, size_t workspace_bytes, jg_stream_t stream);
+
 /* Dense product in full fp32 on the CUDA cores: c[M, N] (row pitch ldc) = op(A) * op(B) (+ bias[N], ReLU),
  * operands addressed by strides, A(i,l) = a[i*sa0 + l*sa1], B(l,j) = b[l*sb0 + j*sb1], so that x @ W,
  * g @ W^T and x^T @ g are one kernel.  Serves what the tensor-core transform does not: the fp32 opt-out of

@@ -462,6 +462,145 @@ static int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t c
     return JG_OK;
 }
 
+// ------------------------------------------------------------------------------------------
+// Weight gradient  gw[K, M] = x^T * g = sum over the rows n of x[n, :]^T g[n, :]  on the tensor cores.
+//
+// The reduction runs over the ROWS, so both operands are "MN-major" for the MMA: in x [n, K] the
+// feature index (the M of the instruction) is the contiguous one, in g [n, M] the output column (its
+// N).  A TMA box of 64 rows x 32 columns with the 128-byte swizzle lands as 64 lines of 128 bytes; for
+// an MN-major operand that is exactly the canonical layout (32 consecutive MN elements per line, 8
+// lines = one K step of 8, groups of 8 lines 1024 bytes apart), and the 32-column blocks that make
+// up the 128 features (or the M columns) sit one box (8192 bytes) apart: leading byte offset 8192,
+// stride byte offset 1024 in the shared-memory descriptor, both major bits set in the instruction
+// descriptor.  One CTA owns a tile of 128 features and one slice of the rows, accumulates
+// [128, M] in TMEM over its slice and writes it to partial[slice]; a second kernel adds the slices in
+// order (no atomics: results repeat exactly).  Same bounded mbarrier waits as the transform.
+constexpr int kTnRows = 64;          // rows (the reduction dimension) per stage
+constexpr int kTnThreads = 192;      // warp 0: TMA producer, warp 1: MMA, warps 2-5: epilogue
+
+struct TnParams {
+    float* partial;      // [slices][k][m]
+    int64_t n_rows;
+    int32_t k, m;        // features (rows of gw), columns of g and gw
+    int32_t m_blocks;    // 32-column boxes of g per stage
+    int32_t n_pad;       // MMA N (m rounded up to 16) and TMEM columns (power of two >= 32)
+    int32_t tmem_cols;
+    int32_t blocks_per_slice;   // stages of kTnRows rows per slice
+    int32_t stages;
+    int32_t* error;
+};
+
+__device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr, uint32_t lbo_bytes) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) | (64ull << 32) | (1ull << 46) |
+           (2ull << 61);
+}
+
+__global__ void __launch_bounds__(kTnThreads, 1)
+gemm_tn_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_g, TnParams p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t box_bytes = kTnRows * 128;                         // 8 KB
+    const uint32_t a_bytes = 4 * box_bytes;                           // 128 features
+    const uint32_t stage_bytes = a_bytes + (uint32_t)p.m_blocks * box_bytes;
+    GemmSmem* ctl = reinterpret_cast<GemmSmem*>(ring + (size_t)p.stages * stage_bytes);
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int slice = blockIdx.x, ftile = blockIdx.y;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(&ctl->full[s], 1);
+            mbar_init(&ctl->empty[s], 1);
+        }
+        mbar_init(&ctl->acc_full[0], 1);
+        ctl->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)), "r"((uint32_t)p.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctl->tmem_base;
+    volatile int32_t* abort_flag = &ctl->abort;
+    const int64_t blk0 = (int64_t)slice * p.blocks_per_slice;
+    const int64_t n_blocks_total = (p.n_rows + kTnRows - 1) / kTnRows;
+    int64_t my_blocks = n_blocks_total - blk0;
+    if (my_blocks > p.blocks_per_slice) my_blocks = p.blocks_per_slice;
+    if (my_blocks < 0) my_blocks = 0;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int64_t it = 0; it < my_blocks && !*abort_flag; it++) {
+                const int s = (int)(it % p.stages);
+                const uint32_t round = (uint32_t)(it / p.stages);
+                if (round > 0 && !mbar_wait(&ctl->empty[s], (round - 1) & 1)) { *abort_flag = 1; break; }
+                unsigned char* dst = ring + (size_t)s * stage_bytes;
+                mbar_expect_tx(&ctl->full[s], stage_bytes);
+                const int row = (int)((blk0 + it) * kTnRows);
+                for (int j = 0; j < 4; j++) tma_load_2d(dst + j * box_bytes, &map_x, ftile * 128 + j * 32, row, &ctl->full[s]);
+                for (int j = 0; j < p.m_blocks; j++) tma_load_2d(dst + a_bytes + j * box_bytes, &map_g, j * 32, row, &ctl->full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && my_blocks > 0) {
+            // D fp32, A/B tf32, both MN-major, N = n_pad, M = 128
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | (1u << 16) | (((uint32_t)p.n_pad >> 3) << 17) | ((128u >> 4) << 24);
+            bool ok = true;
+            for (int64_t it = 0; it < my_blocks; it++) {
+                const int s = (int)(it % p.stages);
+                if (!mbar_wait(&ctl->full[s], (uint32_t)(it / p.stages) & 1)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(ring + (size_t)s * stage_bytes);
+                const uint64_t da = umma_desc_mn(a_addr, box_bytes), db = umma_desc_mn(a_addr + a_bytes, box_bytes);
+#pragma unroll
+                for (int ks = 0; ks < kTnRows / 8; ks++)   // 8 rows = 1024 bytes per K step: +64 in 16-byte units
+                    umma_tf32(tmem_base, da + 64 * ks, db + 64 * ks, idesc, (it > 0 || ks > 0) ? 1u : 0u);
+                umma_commit(&ctl->empty[s]);
+            }
+            if (!ok) *abort_flag = 1;
+            umma_commit(&ctl->acc_full[0]);
+        }
+    } else {
+        // epilogue: warp w reads TMEM lanes 32*(w % 4) .. +31 = features ftile*128 + 32*(w % 4) + lane
+        const int quad = warp & 3;
+        const int64_t feat = (int64_t)ftile * 128 + quad * 32 + lane;
+        float* out = p.partial + ((size_t)slice * p.k + (size_t)feat) * p.m;
+        if (my_blocks > 0) {
+            if (!mbar_wait(&ctl->acc_full[0], 0)) *abort_flag = 1;
+            tc_fence_after();
+            if (!*abort_flag) {
+                for (int c0 = 0; c0 < p.m; c0 += 32) {
+                    float v[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v, c0 + 16 < p.n_pad);
+                    if (feat < p.k) {
+#pragma unroll
+                        for (int i = 0; i < 32; i++)
+                            if (c0 + i < p.m) out[c0 + i] = v[i];
+                    }
+                }
+            }
+        } else if (feat < p.k) {
+            for (int c = 0; c < p.m; c++) out[c] = 0.f;   // a slice beyond the last row contributes nothing
+        }
+        tc_fence_before();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols) : "memory");
+    if (threadIdx.x == 0 && *abort_flag) {
+        *reinterpret_cast<volatile int32_t*>(p.error) = 1;
+        __threadfence_system();
+    }
+}
+
+// 2-D fp32 tensor [rows, cols] row-major, box [kTnRows rows, 32 columns], 128-byte swizzle, zero fill.
+static int make_map_rows(CUtensorMap* map, const float* base, int64_t rows, int64_t cols) { return make_map(map, base, rows, cols, kTnRows); }
+
+// gw[k, m] = sum_s partial[s]: defined with the fp32 product (gemm_f32.cu).
+int reduce_slices(float* c, const float* partial, int64_t M, int64_t N, int slices, cudaStream_t st);
+
 }  // namespace jg
 
 using namespace jg;
@@ -571,6 +710,71 @@ int jg_gemm_tf32(float* out, const float* x, const float* wt, const float* bias,
 int jg_gemm_tf32_dual(float* out, void* out_half, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k,
                       int64_t m, int relu, void* workspace, size_t workspace_bytes, jg_stream_t stream) {
     return gemm_impl(out, out_half, x, wt, bias, n_rows, k, m, relu, workspace, workspace_bytes, stream, false);
+}
+
+static int tn_slices(int64_t n_rows, int64_t k) {
+    const int64_t tiles = (k + 127) / 128;
+    const int64_t blocks = (n_rows + kTnRows - 1) / kTnRows;
+    int64_t s = (sm_count() + tiles - 1) / tiles;        // about one CTA per SM
+    if (s > (blocks + 3) / 4) s = (blocks + 3) / 4;      // at least four stages of rows per slice
+    return s < 1 ? 1 : (int)s;
+}
+
+int jg_gemm_tn_tf32_supported(int64_t n_rows, int64_t k, int64_t m) {
+    return n_rows > 0 && k > 0 && m > 0 && m <= 256 && k % 4 == 0 && m % 4 == 0 && n_rows < ((int64_t)1 << 31) - kTnRows;
+}
+
+size_t jg_gemm_tn_tf32_workspace_bytes(int64_t n_rows, int64_t k, int64_t m) {
+    if (!jg_gemm_tn_tf32_supported(n_rows, k, m)) return 0;
+    return 256 + align_up((size_t)tn_slices(n_rows, k) * (size_t)k * (size_t)m * sizeof(float), 256);
+}
+
+int jg_gemm_tn_tf32(float* gw, const float* x, const float* g, int64_t n_rows, int64_t k, int64_t m, int32_t* error,
+                    void* workspace, size_t workspace_bytes, jg_stream_t stream) {
+    JG_CHECK_ARG(gw && x && g && error, JG_EINVAL, "gemm_tn_tf32: null pointer");
+    if (!jg_gemm_tn_tf32_supported(n_rows, k, m)) {
+        set_error("gemm_tn_tf32: needs k %% 4 == 0, m %% 4 == 0, m <= 256 (got k=%lld, m=%lld)", (long long)k, (long long)m);
+        return JG_EUNSUPPORTED;
+    }
+    JG_CHECK_ARG((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(g)) % 16 == 0, JG_EINVAL, "gemm_tn_tf32: operands must be 16-byte aligned");
+    const size_t need = jg_gemm_tn_tf32_workspace_bytes(n_rows, k, m);
+    JG_CHECK_ARG(workspace && workspace_bytes >= need, JG_EWORKSPACE, "gemm_tn_tf32: workspace %zu < %zu", workspace_bytes, need);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    CUtensorMap map_x, map_g;
+    memset(&map_x, 0, sizeof(map_x));
+    memset(&map_g, 0, sizeof(map_g));
+    int rc = make_map_rows(&map_x, x, n_rows, k);
+    if (rc != JG_OK) return rc;
+    rc = make_map_rows(&map_g, g, n_rows, m);
+    if (rc != JG_OK) return rc;
+    TnParams p = {};
+    p.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + 256);
+    p.n_rows = n_rows; p.k = (int32_t)k; p.m = (int32_t)m;
+    p.m_blocks = (int32_t)((m + 31) / 32);
+    p.n_pad = (int32_t)((m + 15) / 16 * 16);
+    int cols = 32;
+    while (cols < p.n_pad) cols *= 2;
+    p.tmem_cols = cols;
+    const int slices = tn_slices(n_rows, k);
+    const int64_t blocks = (n_rows + kTnRows - 1) / kTnRows;
+    p.blocks_per_slice = (int32_t)((blocks + slices - 1) / slices);
+    const size_t stage_bytes = (size_t)(4 + p.m_blocks) * kTnRows * 128;
+    int stages = kStages;
+    while (stages > 2 && (size_t)stages * stage_bytes > 200 * 1024) stages--;
+    p.stages = stages;
+    p.error = error;
+    const size_t smem = 1024 + (size_t)stages * stage_bytes + sizeof(GemmSmem) + 64;
+    static size_t attr_done[64] = {0};
+    int dev = 0;
+    JG_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && attr_done[dev] < smem) {
+        JG_CUDA(cudaFuncSetAttribute(gemm_tn_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024)));
+        attr_done[dev] = 227 * 1024;
+    }
+    dim3 grid((unsigned)slices, (unsigned)((k + 127) / 128));
+    gemm_tn_tf32_kernel<<<grid, kTnThreads, smem, st>>>(map_x, map_g, p);
+    JG_LAUNCH_CHECK();
+    return reduce_slices(gw, p.partial, k, m, slices, st);
 }
 
 /* Reads the error word a finished jg_gemm_tf32 call left in its workspace (synchronises the

@@ -106,6 +106,16 @@ __global__ void __launch_bounds__(256) sgemm_reduce_kernel(float* __restrict__ c
     }
 }
 
+// Used by the tensor-core weight gradient as well: c[M, N] = sum of `slices` partial results, in order.
+int reduce_slices(float* c, const float* partial, int64_t M, int64_t N, int slices, cudaStream_t st) {
+    int64_t blocks = (M * N + 255) / 256;
+    if (blocks > (int64_t)sm_count() * 8) blocks = (int64_t)sm_count() * 8;
+    if (blocks < 1) blocks = 1;
+    sgemm_reduce_kernel<<<(unsigned)blocks, 256, 0, st>>>(c, partial, M, N, N, slices, nullptr, 0);
+    JG_LAUNCH_CHECK();
+    return JG_OK;
+}
+
 static int sgemm_slices(int64_t M, int64_t N, int64_t K) {
     const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
     int64_t want = (2 * (int64_t)sm_count() + tiles - 1) / tiles;      // enough CTAs to fill the device twice

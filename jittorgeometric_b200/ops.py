@@ -15,7 +15,7 @@ from .data import CSC, CSR
 
 __all__ = ["aggregateWithWeight", "aggregate_bias_act", "segment_aggregate", "SpmmPlan", "cootocsr", "cootocsc", "gcn_norm_csc_csr",
            "SpmmCsr", "SpmmCoo", "ScatterToEdge", "ScatterToVertex", "EdgeSoftmax", "gat_aggregate",
-           "gat_aggregate_supported", "gcn_norm_coo", "linear_tf32", "check_transform_status", "linear_tf32_autograd", "linear_tf32_supported", "matmul_f32", "linear_f32_autograd", "linear_nt", "toUndirected", "validate_structure"]
+           "gat_aggregate_supported", "gcn_norm_coo", "linear_tf32", "check_transform_status", "linear_tf32_autograd", "linear_tf32_supported", "matmul_f32", "linear_f32_autograd", "linear_nt", "weight_grad_tf32", "toUndirected", "validate_structure"]
 
 DEFAULT_CHUNK = int(os.environ.get("JG_SPMM_CHUNK", "1024"))
 SMALL_GRAPH_NNZ = 1 << 20
@@ -726,6 +726,26 @@ def linear_f32_autograd(x, weight, relu=False):
     return _LinearF32.apply(_as_f32(x, "x"), _as_f32(weight, "weight"), bool(relu))
 
 
+def weight_grad_tf32(x, g):
+    """``x^T @ g`` (the weight gradient of ``x @ W``) on the tensor cores with TF32 products when the shape
+    allows (widths multiples of 4, at most 256 output columns), else in fp32 on the CUDA cores."""
+    x, g = _as_f32(x, "x"), _as_f32(g, "g")
+    n, k = x.shape
+    m = g.shape[1]
+    if g.shape[0] != n:
+        raise RuntimeError("weight_grad_tf32: x and g need the same number of rows")
+    if not lib().jg_gemm_tn_tf32_supported(n, k, m) or (x.data_ptr() | g.data_ptr()) % 16:
+        return matmul_f32(x, g, trans_a=True)
+    word = _tf32_status_word(x.device)
+    if int(word[0]):
+        check_transform_status(x.device)
+    out = torch.empty((k, m), dtype=torch.float32, device=x.device)
+    ws = workspace(lib().jg_gemm_tn_tf32_workspace_bytes(n, k, m), x.device)
+    check(lib().jg_gemm_tn_tf32(ptr(out), ptr(x), ptr(g), n, k, m, ctypes.c_void_p(word.data_ptr()), ptr(ws), ws.numel(),
+                                stream_for(x)), "jg_gemm_tn_tf32")
+    return out
+
+
 class _LinearNT(torch.autograd.Function):
     """``x @ weight^T + bias`` for a weight stored ``[out, in]`` (the layout of a ``Linear`` layer):
     TF32 forward and input gradient on the tensor-core kernel when asked for, everything else on the fp32
@@ -751,7 +771,7 @@ class _LinearNT(torch.autograd.Function):
             else:
                 gx = matmul_f32(g, weight)
         if ctx.needs_input_grad[1]:
-            gw = matmul_f32(g, x, trans_a=True)
+            gw = weight_grad_tf32(g, x) if ctx.tf32 else matmul_f32(g, x, trans_a=True)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             gb = g.sum(0)
         return gx, gw, gb, None
@@ -770,8 +790,8 @@ def _relu_mask(grad, out):
 class _LinearTF32(torch.autograd.Function):
     """``act(x @ weight)`` through the tcgen05 kernel with a backward: ``grad_x = g @ weight^T`` runs
     on the same kernel (its transposed operand is the weight itself); ``grad_weight = x^T @ g`` is a
-    reduction over the rows, an operand layout the row-tiled kernel does not take, and runs on the fp32
-    CUDA-core kernel (sliced over the rows, fixed-order sum of the slices)."""
+    reduction over the rows and runs on its own tensor-core kernel (MN-major operands, sliced over the
+    rows, fixed-order sum of the slices) or, for widths that are not multiples of 4, on the fp32 kernel."""
 
     @staticmethod
     def forward(ctx, x, weight, relu):
@@ -791,7 +811,7 @@ class _LinearTF32(torch.autograd.Function):
             else:
                 gx = matmul_f32(g, weight, trans_b=True)
         if ctx.needs_input_grad[1]:
-            gw = matmul_f32(x, g, trans_a=True)
+            gw = weight_grad_tf32(x, g)
         return gx, gw, None
 
 

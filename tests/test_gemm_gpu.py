@@ -180,3 +180,20 @@ def test_no_vendor_gemm_in_the_layers(cuda):
         yd.square().sum().backward()
         for have, want in ((y, yd), (x.grad, xd.grad), (layer.weight.grad, wd.grad), (layer.bias.grad, bd.grad)):
             assert (have.double() - want).abs().max().item() <= 20 * bar * want.abs().max().item()
+
+
+@pytest.mark.parametrize("n,k,m", [(64, 128, 128), (5000, 128, 64), (300000, 128, 128), (4097, 256, 64), (1000, 64, 16),
+                                   (20000, 132, 36), (777, 4, 4), (50000, 512, 256), (63, 32, 32)])
+def test_weight_gradient_on_the_tensor_cores(cuda, n, k, m):
+    """``x^T g`` with MN-major tcgen05 operands against float64 at the TF32 bar, identical run to run."""
+    assert cuda.ops.lib().jg_gemm_tn_tf32_supported(n, k, m)
+    gen = torch.Generator(device="cuda").manual_seed(n + k + m)
+    x = torch.randn((n, k), device="cuda", generator=gen)
+    g = torch.randn((n, m), device="cuda", generator=gen)
+    got = cuda.ops.weight_grad_tf32(x, g)
+    cuda.ops.check_transform_status(x.device, synchronize=True)
+    want = x.double().t() @ g.double()
+    scale = x.abs().double().t() @ g.abs().double()
+    assert got.shape == (k, m) and torch.isfinite(got).all()
+    assert ((got.double() - want).abs() / scale).max().item() <= 2e-3
+    assert torch.equal(got, cuda.ops.weight_grad_tf32(x, g))
