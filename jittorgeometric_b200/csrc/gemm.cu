@@ -448,7 +448,7 @@ static int make_map_half(CUtensorMap* map, const void* base, int64_t rows, int64
 
 // 2-D fp32 tensor [rows, cols] row-major, box [box_rows, 32 columns], 128-byte swizzle, zero fill
 // on loads / clipping on stores outside the tensor.
-static int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t cols, int box_rows) {
+static int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t cols, int box_rows, int atom32 = 0) {
     EncodeTiledFn enc = encode_tiled_fn();
     JG_CHECK_ARG(enc, JG_ECUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -456,7 +456,7 @@ static int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t c
     cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows};
     cuuint32_t elem[2] = {1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, elem,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     JG_CHECK_ARG(r == CUDA_SUCCESS, JG_ECUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
     return JG_OK;
@@ -467,12 +467,13 @@ static int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t c
 //
 // The reduction runs over the ROWS, so both operands are "MN-major" for the MMA: in x [n, K] the
 // feature index (the M of the instruction) is the contiguous one, in g [n, M] the output column (its
-// N).  A TMA box of 64 rows x 32 columns with the 128-byte swizzle lands as 64 lines of 128 bytes; for
-// an MN-major operand that is exactly the canonical layout (32 consecutive MN elements per line, 8
-// lines = one K step of 8, groups of 8 lines 1024 bytes apart), and the 32-column blocks that make
-// up the 128 features (or the M columns) sit one box (8192 bytes) apart: leading byte offset 8192,
-// stride byte offset 1024 in the shared-memory descriptor, both major bits set in the instruction
-// descriptor.  One CTA owns a tile of 128 features and one slice of the rows, accumulates
+// N).  32-bit MN-major operands take the 128-byte swizzle with 32-byte atoms (the plain 128-byte
+// swizzle with both major bits set returned all zeros on a B200), so the TMA maps of this kernel use
+// CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B.  A box of 64 rows x 32 columns lands as 64 lines of 128 bytes:
+// 32 consecutive MN elements per line, 4 lines per K atom, two atoms (512 bytes apart: the stride
+// byte offset) per K = 8 instruction, and the 32-column blocks that make up the 128 features (or the
+// M columns) one box (8192 bytes: the leading byte offset) apart; both major bits set in the
+// instruction descriptor.  One CTA owns a tile of 128 features and one slice of the rows, accumulates
 // [128, M] in TMEM over its slice and writes it to partial[slice]; a second kernel adds the slices in
 // order (no atomics: results repeat exactly).  Same bounded mbarrier waits as the transform.
 constexpr int kTnRows = 64;          // rows (the reduction dimension) per stage
@@ -490,9 +491,11 @@ struct TnParams {
     int32_t* error;
 };
 
+// MN-major operand of 32-bit elements: 128-byte swizzle with 32-byte atoms (layout type 1), whose K atom
+// is 4 lines: stride byte offset 512 between the two atoms of one K = 8 step.
 __device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr, uint32_t lbo_bytes) {
-    return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) | (64ull << 32) | (1ull << 46) |
-           (2ull << 61);
+    return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) | (32ull << 32) | (1ull << 46) |
+           (1ull << 61);
 }
 
 __global__ void __launch_bounds__(kTnThreads, 1)
@@ -596,7 +599,7 @@ gemm_tn_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 }
 
 // 2-D fp32 tensor [rows, cols] row-major, box [kTnRows rows, 32 columns], 128-byte swizzle, zero fill.
-static int make_map_rows(CUtensorMap* map, const float* base, int64_t rows, int64_t cols) { return make_map(map, base, rows, cols, kTnRows); }
+static int make_map_rows(CUtensorMap* map, const float* base, int64_t rows, int64_t cols) { return make_map(map, base, rows, cols, kTnRows, 1); }
 
 // gw[k, m] = sum_s partial[s]: defined with the fp32 product (gemm_f32.cu).
 int reduce_slices(float* c, const float* partial, int64_t M, int64_t N, int slices, cudaStream_t st);
