@@ -359,6 +359,14 @@ size_t jg_gemm_tf32_workspace_bytes(void);
 int jg_gemm_tf32(float* out, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k, int64_t m,
                  int relu, void* workspace, size_t workspace_bytes, jg_stream_t stream);
 int jg_gemm_tf32_status(const void* workspace, jg_stream_t stream);
+/* Failure-path self-test of the transform (no counterpart in the reference, whose kernels have no waits):
+ * the same kernel, but every CTA's producer leaves out ring fill number `withhold` and every wait gives
+ * up after `wait_spins` polls (128 .. 2^22).  The consumer's bounded wait runs out, the CTAs free their
+ * TMEM and return, and jg_gemm_tf32_status on the same workspace reports JG_ETIMEOUT; nothing traps
+ * and the next call on the device runs normally.  `out` is left partly written.  Needs k % 4 == 0 and
+ * 16-byte aligned x, wt. */
+int jg_gemm_tf32_timeout_selftest(float* out, const float* x, const float* wt, int64_t n_rows, int64_t k, int64_t m,
+                                  int32_t withhold, uint32_t wait_spins, void* workspace, size_t workspace_bytes, jg_stream_t stream);
 /* The same transform, optionally writing a second copy of the result in fp16 (out_half [n_rows, m] or NULL;
  * m % 8 == 0, values beyond +-65504 saturate) from the same epilogue: the copy a row-partitioned
  * aggregation offers to its peers (jg_halo_pull with src_half), without a separate conversion pass over

@@ -80,6 +80,7 @@ SIGNATURES = {
     "jg_gemm_tf32": (ctypes.c_int, [vp, vp, vp, vp, i64, i64, i64, ctypes.c_int, vp, sz, vp]),
     "jg_gemm_tf32_dual": (ctypes.c_int, [vp, vp, vp, vp, vp, i64, i64, i64, ctypes.c_int, vp, sz, vp]),
     "jg_gemm_tf32_status": (ctypes.c_int, [vp, vp]),
+    "jg_gemm_tf32_timeout_selftest": (ctypes.c_int, [vp, vp, vp, i64, i64, i64, ctypes.c_int32, ctypes.c_uint32, vp, sz, vp]),
     "jg_gemm_tn_tf32_supported": (ctypes.c_int, [i64, i64, i64]),
     "jg_gemm_tn_tf32_workspace_bytes": (sz, [i64, i64, i64]),
     "jg_gemm_tn_tf32": (ctypes.c_int, [vp, vp, vp, i64, i64, i64, vp, vp, sz, vp]),

@@ -51,6 +51,8 @@ struct GemmParams {
     int32_t ldo;         // row pitch of the output in floats (the full width when m is one column tile of it)
     int32_t col_base;    // first output column of this tile (out, bias and wt already point at it)
     __half* out_half;    // optional second copy of the result in fp16 (same shape and pitch in elements), or null
+    uint32_t wait_spins; // limit of every mbarrier wait (kWaitSpins; the time-out test entry shortens it)
+    int32_t withhold;    // time-out test entry only: the producer skips this fill of the ring (-1: none)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -65,9 +67,9 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // Bounded wait for the phase with the given parity; false when it ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t spins = kWaitSpins) {
     const uint32_t addr = smem_u32(bar);
-    for (uint32_t spin = 0; spin < kWaitSpins; spin++) {
+    for (uint32_t spin = 0; spin < spins; spin++) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -213,7 +215,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             for (int kb = 0; kb < p.k_blocks; kb++, it++) {
                 const int s = it % kStages;
                 const uint32_t round = it / kStages;
-                if (round > 0 && !mbar_wait(&ctl->empty[s], (round - 1) & 1)) { ok = false; break; }
+                if (round > 0 && !mbar_wait(&ctl->empty[s], (round - 1) & 1, p.wait_spins)) { ok = false; break; }
                 const uint32_t a_dst = smem_u32(ring + s * stage_bytes);
                 const int64_t row0 = (int64_t)tile * kTileM;
                 if (p.plain_loads == 2) {
@@ -270,7 +272,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 for (int kb = 0; kb < p.k_blocks; kb++, it++) {
                     const int s = it % kStages;
                     const uint32_t round = it / kStages;
-                    if (round > 0 && !mbar_wait(&ctl->empty[s], (round - 1) & 1)) { *abort_flag = 1; break; }
+                    if (round > 0 && !mbar_wait(&ctl->empty[s], (round - 1) & 1, p.wait_spins)) { *abort_flag = 1; break; }
+                    if ((int32_t)it == p.withhold) continue;   // test entry: this fill never arrives, its consumer's wait runs out
                     unsigned char* a_dst = ring + s * stage_bytes;
                     mbar_expect_tx(&ctl->full[s], a_bytes + b_rows * kTileK * 4);
                     tma_load_2d(a_dst, &map_x, kb * kTileK, tile * kTileM, &ctl->full[s]);
@@ -289,13 +292,13 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             for (int tile = blockIdx.x; tile < p.n_tiles && !*abort_flag; tile += gridDim.x, local_tile++) {
                 const int b = local_tile & 1;
                 const uint32_t use = local_tile >> 1;
-                if (use > 0 && !mbar_wait(&ctl->acc_empty[b], (use - 1) & 1)) { *abort_flag = 1; break; }
+                if (use > 0 && !mbar_wait(&ctl->acc_empty[b], (use - 1) & 1, p.wait_spins)) { *abort_flag = 1; break; }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(b * p.m_pad);
                 bool ok = true;
                 for (int kb = 0; kb < p.k_blocks; kb++, it++) {
                     const int s = it % kStages;
-                    if (!mbar_wait(&ctl->full[s], (it / kStages) & 1)) { ok = false; break; }
+                    if (!mbar_wait(&ctl->full[s], (it / kStages) & 1, p.wait_spins)) { ok = false; break; }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // plain-load producer: generic-proxy writes
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(ring + s * stage_bytes);
@@ -319,7 +322,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         uint32_t local_tile = 0;
         for (int tile = blockIdx.x; tile < p.n_tiles && !*abort_flag; tile += gridDim.x, local_tile++) {
             const int b = local_tile & 1;
-            if (!mbar_wait(&ctl->acc_full[b], (local_tile >> 1) & 1)) { *abort_flag = 1; break; }
+            if (!mbar_wait(&ctl->acc_full[b], (local_tile >> 1) & 1, p.wait_spins)) { *abort_flag = 1; break; }
             tc_fence_after();
             const int64_t row = (int64_t)tile * kTileM + quad * 32 + lane;
             const uint32_t taddr = tmem_base + (uint32_t)(b * p.m_pad) + ((uint32_t)(quad * 32) << 16);
@@ -616,6 +619,10 @@ int jg_gemm_tf32_supported(int64_t n_rows, int64_t k, int64_t m) {
 
 size_t jg_gemm_tf32_workspace_bytes(void) { return 256; }
 
+// Set only inside jg_gemm_tf32_timeout_selftest (one thread, for the duration of its call).
+static thread_local uint32_t g_test_wait_spins = kWaitSpins;
+static thread_local int32_t g_test_withhold = -1;
+
 // One column tile (at most 256 output columns) of the product.
 static int gemm_tile(float* out, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k, int64_t m,
                      int64_t m_total, int64_t col_base, int relu, int32_t* error, cudaStream_t st, __half* out_half = nullptr) {
@@ -659,6 +666,8 @@ static int gemm_tile(float* out, const float* x, const float* wt, const float* b
     p.n_tiles = (int32_t)((n_rows + kTileM - 1) / kTileM);
     p.k_blocks = (int32_t)((k + kTileK - 1) / kTileK);
     p.error = error;
+    p.wait_spins = g_test_wait_spins;
+    p.withhold = g_test_withhold;
     const size_t a_bytes = kTileM * kTileK * 4;
     const size_t b_bytes = ((size_t)b_rows * kTileK * 4 + 1023) / 1024 * 1024;
     const size_t smem = 1024 + kStages * (a_bytes + b_bytes) + (p.tma_store ? kEpiWarps * 4096 : 0) +
@@ -713,6 +722,24 @@ int jg_gemm_tf32(float* out, const float* x, const float* wt, const float* bias,
 int jg_gemm_tf32_dual(float* out, void* out_half, const float* x, const float* wt, const float* bias, int64_t n_rows, int64_t k,
                       int64_t m, int relu, void* workspace, size_t workspace_bytes, jg_stream_t stream) {
     return gemm_impl(out, out_half, x, wt, bias, n_rows, k, m, relu, workspace, workspace_bytes, stream, false);
+}
+
+/* Failure-path self-test: the same kernel as jg_gemm_tf32, but the producer leaves out fill number
+ * `withhold` of every CTA's ring and every wait gives up after `wait_spins` polls.  The consumer's bounded
+ * wait runs out, the CTAs free their TMEM and return, the error word is set: jg_gemm_tf32_status then
+ * reports JG_ETIMEOUT.  `out` is left partly written.  Needs the TMA producer (k % 4 == 0, aligned x and
+ * wt).  Nothing traps and the context stays usable. */
+int jg_gemm_tf32_timeout_selftest(float* out, const float* x, const float* wt, int64_t n_rows, int64_t k, int64_t m,
+                                  int32_t withhold, uint32_t wait_spins, void* workspace, size_t workspace_bytes, jg_stream_t stream) {
+    JG_CHECK_ARG(k % 4 == 0 && (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wt)) % 16 == 0, JG_EINVAL,
+                 "gemm_tf32_timeout_selftest: needs the TMA producer (k %% 4 == 0, 16-byte aligned operands)");
+    JG_CHECK_ARG(withhold >= 0 && wait_spins >= 128 && wait_spins <= kWaitSpins, JG_EINVAL, "gemm_tf32_timeout_selftest: bad hook values");
+    g_test_wait_spins = wait_spins;
+    g_test_withhold = withhold;
+    const int rc = gemm_impl(out, nullptr, x, wt, nullptr, n_rows, k, m, 0, workspace, workspace_bytes, stream);
+    g_test_wait_spins = kWaitSpins;
+    g_test_withhold = -1;
+    return rc;
 }
 
 static int tn_slices(int64_t n_rows, int64_t k) {

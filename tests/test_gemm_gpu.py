@@ -138,6 +138,33 @@ def test_status_word_is_polled_without_a_synchronisation(cuda):
     ops.linear_tf32(x, w, check_status=True)                         # and the path works again
 
 
+def test_bounded_wait_runs_out_and_the_kernel_returns(cuda):
+    """Failure path of the transform without any fault: the self-test entry runs the same kernel with one
+    ring fill left out per CTA and a short wait limit.  The consumer's wait runs out, the CTAs free their
+    TMEM and return, the status call reports JG_ETIMEOUT; the very next transform on the device (which needs
+    its TMEM) runs and is correct."""
+    import ctypes
+    from jittorgeometric_b200 import ops
+    from jittorgeometric_b200._lib import lib, ptr, stream_for
+    n, k, m = 40000, 256, 64                       # 313 row tiles: every CTA of the persistent grid has work
+    x = torch.randn((n, k), device="cuda")
+    w = torch.randn((k, m), device="cuda")
+    wt = w.t().contiguous()
+    out = torch.zeros((n, m), device="cuda")
+    ws = torch.zeros(lib().jg_gemm_tf32_workspace_bytes(), dtype=torch.uint8, device="cuda")
+    rc = lib().jg_gemm_tf32_timeout_selftest(ptr(out), ptr(x), ptr(wt), n, k, m, 1, 1 << 12, ptr(ws), ws.numel(), stream_for(x))
+    assert rc == 0
+    status = lib().jg_gemm_tf32_status(ptr(ws), stream_for(x))
+    assert status == -5                            # JG_ETIMEOUT
+    torch.cuda.synchronize()                       # the context is intact
+    rc = lib().jg_gemm_tf32(ptr(out), ptr(x), ptr(wt), None, n, k, m, 0, ptr(ws), ws.numel(), stream_for(x))
+    assert rc == 0 and lib().jg_gemm_tf32_status(ptr(ws), stream_for(x)) == 0
+    want = x.double() @ w.double()
+    scale = x.abs().double() @ w.abs().double()
+    assert ((out.double() - want).abs() / scale).max().item() <= 2e-3
+    assert torch.equal(out, ops.linear_tf32(x, w))
+
+
 @pytest.mark.parametrize("M,N,K,ta,tb", [(300, 70, 45, False, False), (64, 64, 16, False, False), (2708, 256, 1433, False, False),
                                         (1433, 256, 2708, True, False), (5000, 1433, 256, False, True), (128, 64, 300000, True, False),
                                         (7, 5, 100000, True, False), (1, 1, 1, False, False)])
