@@ -41,7 +41,7 @@ class ClockSampler:
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.proc, self.lines, self.first = index, None, [], 0
 
     def start(self):
         try:
@@ -53,6 +53,15 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def mark(self, wait_s=4.0):
+        """Call where the timed region starts (the sampler was started before the warm-up: nvidia-smi takes
+        up to a few seconds to deliver its first line on a box with several GPUs).  Waits for that first line,
+        then remembers how many lines came before the timed region."""
+        t0 = time.time()
+        while self.proc is not None and not self.lines and time.time() - t0 < wait_s:
+            time.sleep(0.02)
+        self.first = len(self.lines)
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -60,7 +69,10 @@ class ClockSampler:
         self.proc.terminate()
         self.t.join(timeout=2)
         sm, mx, reasons = [], [], set()
-        for ln in self.lines:
+        window = self.lines[self.first:]
+        if not window:                      # timed region shorter than one sampling period: the nearest samples
+            window = self.lines[-3:]
+        for ln in window:
             parts = [p.strip() for p in ln.split(",")]
             if len(parts) < 8:
                 continue
@@ -267,14 +279,15 @@ def run_single(args):
             if events is not None:
                 events[f][1].record()
 
+    sampler = ClockSampler(dev.index); sampler.start()
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
-    sampler = ClockSampler(dev.index); sampler.start()
     evs = [{f: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for f in WIDTHS}
            for _ in range(args.steps)]
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
+    sampler.mark()
     t0.record()
     for k in range(args.steps):
         step(evs[k])

@@ -123,14 +123,16 @@ def gcn_forward_record(args, dev, rank, world, sampler_cls=None):
             del z1
             return jg.segment_aggregate(h2, idx, off, w, plan=plan, bias=b2)
 
-    for _ in range(args.gcn_warmup):
-        forward()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
     sampler = sampler_cls(dev.index) if (sampler_cls is not None and rank == 0) else None
     if sampler:
         sampler.start()
+    for _ in range(args.gcn_warmup):
+        forward()
+    torch.cuda.synchronize()
+    if sampler:
+        sampler.mark()
+    if world > 1:
+        dist.barrier()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     a.record()
@@ -249,25 +251,34 @@ def run(args):
         ys.extend(g.finish(p) for p in pending)
         return ys
 
-    for _ in range(args.warmup):
-        step()
-    torch.cuda.synchronize(); dist.barrier()
     sampler = bench.ClockSampler(dev.index)
     if rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize(); dist.barrier()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    if rank == 0:
+        sampler.mark()
     torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
     t0.record()
-    for _ in range(args.steps):
+    for k in range(args.steps):
         ys = step()
+        marks[k].record()
     t1.record()
     torch.cuda.synchronize(); dist.barrier()
     clocks = sampler.stop() if rank == 0 else None
     if g.direct:
         g.transport.check()
     ms = torch.tensor([t0.elapsed_time(t1) / args.steps], device=dev)
+    mine = ms.clone()
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms_step = float(ms.item())
+    every = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(every, mine)
+    timeline = {"mean_step_ms_by_rank": [float(v.item()) for v in every],
+                "steps_ms_rank0": [([t0] + marks)[k].elapsed_time(marks[k]) for k in range(args.steps)]}
 
     # where the time of a step goes (one extra, untimed step; events around every aggregation)
     breakdown = None
@@ -394,6 +405,7 @@ def run(args):
             "exchange": "referenced remote rows only (%.0f %% of the remote rows on rank 0), " % (
                 100.0 * halo_rows / max(remote_rows, 1)) + exchange_text,
             "breakdown_rank0": breakdown,
+            "timeline": timeline,
             "parity": par, "parity_ok": bool(float(okmin[0]) == 1.0),
             "gcn_forward": gcn,
             "clocks": clocks,
