@@ -169,7 +169,12 @@ def run_gemm(args):
         b = 4 * n * (k + m)
         res[f"{k}x{m}"] = {"ms": ms, "gbs": b / ms / 1e6, "frac_of_hbm_peak": b / ms / 1e6 / peak,
                            "tflops": 2.0 * n * k * m / ms / 1e9, "library_fp32_ms": ms_lib}
-        del x
+        # the weight gradient of the same layer, x^T g (tcgen05 with MN-major operands), beside the fp32 CUDA-core form
+        g = torch.randn((n, m), device=dev)
+        ms_wg = _time(lambda: jg.ops.weight_grad_tf32(x, g), args.steps, args.warmup)
+        res[f"{k}x{m}"]["weight_grad"] = {"ms": ms_wg, "gbs": b / ms_wg / 1e6, "frac_of_hbm_peak": b / ms_wg / 1e6 / peak,
+                                          "fp32_cuda_core_ms": _time(lambda: jg.ops.matmul_f32(x, g, trans_a=True), 2, 1)}
+        del x, g
     first = res["128x128"]
     return _line(args, "dense_transform_rows_per_s", "row/s", n / (first["ms"] * 1e-3), first["ms"],
           f"dense feature transform H = X W, {n} rows, TF32 products with fp32 accumulation on tcgen05; shapes 128->128, "
@@ -177,7 +182,7 @@ def run_gemm(args):
           {"bound": "hbm", "achieved": first["gbs"], "peak": peak, "unit": "GB/s", "frac": first["frac_of_hbm_peak"],
            "traffic": None, "peak_kind": kind, "kernel": "gemm_tf32_kernel",
            "note": "skinny GEMM: read X once, write H once; tensor-pipe utilisation is reported by ncu"},
-          {"shapes": res, "dtype": "tf32", "gpu_launches": args.steps * 3})
+          {"shapes": res, "dtype": "tf32", "gpu_launches": args.steps * 3 * 3})
 
 
 def run_gcn(args):
@@ -282,7 +287,9 @@ def run_edgeops(args):
         cases = [("scatter_to_edge_src", lambda: jg.ScatterToEdge(h, csc, "src"), E * (4 + 4 * C) + 4 * n * C),
                  ("scatter_to_edge_dst", lambda: jg.ScatterToEdge(h, csc, "dst"), E * 4 * C + 4 * n * C),
                  ("scatter_to_vertex", lambda: jg.ScatterToVertex(msg, csc, "src"), E * 4 * C + 4 * n * C),
-                 ("edge_softmax", lambda: jg.EdgeSoftmax(score, csc), 2 * E * 4 * H)]
+                 ("edge_softmax", lambda: jg.EdgeSoftmax(score, csc), 2 * E * 4 * H),
+                 ("edge_softmax_backward", lambda: jg.ops._edge_softmax(score, csc.column_offset, bwd_y=prob), 3 * E * 4 * H)]
+        prob = jg.EdgeSoftmax(score, csc)
         for name, fn, nbytes in cases:
             ms = _time(fn, args.steps, args.warmup)
             res[name] = {"ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peak}
@@ -298,7 +305,7 @@ def run_edgeops(args):
           {"bound": "hbm", "achieved": top["gbs"], "peak": peak, "unit": "GB/s", "frac": top["frac_of_hbm_peak"], "traffic": None,
            "peak_kind": kind, "kernel": "edge_to_vertex_kernel", "note": "bytes = the [E, C] messages read once + the [N, C] result"},
           {"operators": res, "attention_op_by_op_ms": ms_unfused, "attention_fused_ms": ms_fused,
-           "gpu_launches": args.steps * 4, "clocks": clocks})
+           "gpu_launches": args.steps * 5, "clocks": clocks})
 
 
 def run_citation(args):

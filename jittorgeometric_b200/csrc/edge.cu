@@ -266,6 +266,140 @@ __global__ void __launch_bounds__(kEdgeBlock) edge_softmax_fwd_hub_kernel(float*
     }
 }
 
+// 128-bit form of the two kernels above for H = 4, 8, 16, 32 (16-byte aligned x and y): a lane
+// carries the four columns of one float4 (column group lane % (H/4)), so four times the bytes are in
+// flight per lane for the same number of requests.  Same two sweeps, same merge order per column.
+__device__ __forceinline__ void merge_lanes(MaxSum& st, int lane, int o) {
+    const float m2 = __shfl_xor_sync(kFull, st.m, o), s2 = __shfl_xor_sync(kFull, st.s, o);
+    if (lane & o) {
+        MaxSum other = {m2, s2};
+        other.merge(st.m, st.s);
+        st = other;
+    } else {
+        st.merge(m2, s2);
+    }
+}
+
+__device__ __forceinline__ float4 softmax_values(const float4& a, const float (&mx)[4], const float (&inv)[4]) {
+    return make_float4(expf(a.x - mx[0]) * inv[0], expf(a.y - mx[1]) * inv[1], expf(a.z - mx[2]) * inv[2], expf(a.w - mx[3]) * inv[3]);
+}
+
+template <int HP>
+__device__ __forceinline__ void softmax_fwd_vec_warps(float4* __restrict__ y, const float4* __restrict__ x,
+                                                      const int32_t* __restrict__ off, int64_t n, int block, int n_blocks) {
+    constexpr int Q = HP / 4;
+    const int lane = lane_id();
+    const int64_t warp = ((int64_t)block * blockDim.x + threadIdx.x) >> 5;
+    const int64_t n_warps = ((int64_t)n_blocks * blockDim.x) >> 5;
+    for (int64_t v = warp; v < n; v += n_warps) {
+        if (off[v + 1] - off[v] >= kSoftmaxHub) continue;
+        const int64_t s = (int64_t)off[v] * Q, e = (int64_t)off[v + 1] * Q;
+        if (s >= e) continue;
+        MaxSum st[4] = {{-INFINITY, 0.f}, {-INFINITY, 0.f}, {-INFINITY, 0.f}, {-INFINITY, 0.f}};
+        int64_t i = s + lane;
+        for (; i + 96 < e; i += 128) {
+            const float4 a0 = x[i], a1 = x[i + 32], a2 = x[i + 64], a3 = x[i + 96];
+            st[0].add4(a0.x, a1.x, a2.x, a3.x); st[1].add4(a0.y, a1.y, a2.y, a3.y);
+            st[2].add4(a0.z, a1.z, a2.z, a3.z); st[3].add4(a0.w, a1.w, a2.w, a3.w);
+        }
+        for (; i < e; i += 32) {
+            const float4 a = x[i];
+            st[0].add(a.x); st[1].add(a.y); st[2].add(a.z); st[3].add(a.w);
+        }
+#pragma unroll
+        for (int o = 16; o >= Q; o >>= 1) {
+#pragma unroll
+            for (int c = 0; c < 4; c++) merge_lanes(st[c], lane, o);
+        }
+        float mx[4], inv[4];
+#pragma unroll
+        for (int c = 0; c < 4; c++) { mx[c] = st[c].m; inv[c] = 1.f / st[c].s; }
+        i = s + lane;
+        for (; i + 96 < e; i += 128) {
+            const float4 a0 = x[i], a1 = x[i + 32], a2 = x[i + 64], a3 = x[i + 96];
+            __stcs(y + i, softmax_values(a0, mx, inv)); __stcs(y + i + 32, softmax_values(a1, mx, inv));
+            __stcs(y + i + 64, softmax_values(a2, mx, inv)); __stcs(y + i + 96, softmax_values(a3, mx, inv));
+        }
+        for (; i < e; i += 32) __stcs(y + i, softmax_values(x[i], mx, inv));
+    }
+}
+
+template <int HP>
+__device__ __forceinline__ void softmax_fwd_vec_block(float4* __restrict__ y, const float4* __restrict__ x,
+                                                      const int32_t* __restrict__ off, int64_t n, int block, int n_blocks,
+                                                      float (*s_m)[kEdgeBlock], float (*s_s)[kEdgeBlock]) {
+    constexpr int Q = HP / 4;
+    const int lane = threadIdx.x & 31;
+    for (int64_t v = block; v < n; v += n_blocks) {
+        if (off[v + 1] - off[v] < kSoftmaxHub) continue;   // block-uniform
+        const int64_t s = (int64_t)off[v] * Q, e = (int64_t)off[v + 1] * Q;
+        MaxSum st[4] = {{-INFINITY, 0.f}, {-INFINITY, 0.f}, {-INFINITY, 0.f}, {-INFINITY, 0.f}};
+        int64_t i = s + threadIdx.x;
+        for (; i + 7 * kEdgeBlock < e; i += 8 * kEdgeBlock) {   // a block alone on a long segment: eight loads in flight per thread
+            float4 a[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) a[u] = x[i + u * kEdgeBlock];
+            st[0].add4(a[0].x, a[1].x, a[2].x, a[3].x); st[1].add4(a[0].y, a[1].y, a[2].y, a[3].y);
+            st[2].add4(a[0].z, a[1].z, a[2].z, a[3].z); st[3].add4(a[0].w, a[1].w, a[2].w, a[3].w);
+            st[0].add4(a[4].x, a[5].x, a[6].x, a[7].x); st[1].add4(a[4].y, a[5].y, a[6].y, a[7].y);
+            st[2].add4(a[4].z, a[5].z, a[6].z, a[7].z); st[3].add4(a[4].w, a[5].w, a[6].w, a[7].w);
+        }
+        for (; i + 3 * kEdgeBlock < e; i += 4 * kEdgeBlock) {
+            const float4 a0 = x[i], a1 = x[i + kEdgeBlock], a2 = x[i + 2 * kEdgeBlock], a3 = x[i + 3 * kEdgeBlock];
+            st[0].add4(a0.x, a1.x, a2.x, a3.x); st[1].add4(a0.y, a1.y, a2.y, a3.y);
+            st[2].add4(a0.z, a1.z, a2.z, a3.z); st[3].add4(a0.w, a1.w, a2.w, a3.w);
+        }
+        for (; i < e; i += kEdgeBlock) {
+            const float4 a = x[i];
+            st[0].add(a.x); st[1].add(a.y); st[2].add(a.z); st[3].add(a.w);
+        }
+#pragma unroll
+        for (int o = 16; o >= Q; o >>= 1) {
+#pragma unroll
+            for (int c = 0; c < 4; c++) merge_lanes(st[c], lane, o);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int c = 0; c < 4; c++) { s_m[c][threadIdx.x] = st[c].m; s_s[c][threadIdx.x] = st[c].s; }
+        __syncthreads();
+        float mx[4], inv[4];
+#pragma unroll
+        for (int c = 0; c < 4; c++) {             // warps in order: every thread ends with the same state per column
+            MaxSum all = {s_m[c][lane], s_s[c][lane]};
+#pragma unroll
+            for (int w = 1; w < kEdgeBlock / 32; w++) all.merge(s_m[c][w * 32 + lane], s_s[c][w * 32 + lane]);
+            mx[c] = all.m; inv[c] = 1.f / all.s;
+        }
+        i = s + threadIdx.x;
+        for (; i + 7 * kEdgeBlock < e; i += 8 * kEdgeBlock) {
+            float4 a[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) a[u] = x[i + u * kEdgeBlock];
+#pragma unroll
+            for (int u = 0; u < 8; u++) __stcs(y + i + u * kEdgeBlock, softmax_values(a[u], mx, inv));
+        }
+        for (; i + 3 * kEdgeBlock < e; i += 4 * kEdgeBlock) {
+            const float4 a0 = x[i], a1 = x[i + kEdgeBlock], a2 = x[i + 2 * kEdgeBlock], a3 = x[i + 3 * kEdgeBlock];
+            __stcs(y + i, softmax_values(a0, mx, inv)); __stcs(y + i + kEdgeBlock, softmax_values(a1, mx, inv));
+            __stcs(y + i + 2 * kEdgeBlock, softmax_values(a2, mx, inv)); __stcs(y + i + 3 * kEdgeBlock, softmax_values(a3, mx, inv));
+        }
+        for (; i < e; i += kEdgeBlock) __stcs(y + i, softmax_values(x[i], mx, inv));
+    }
+}
+
+// ONE launch for both roles: the first `hub_blocks` blocks take the long segments (a block each, scheduled
+// first), the others the short ones (a warp each), so the long segments' tail runs beside the bulk of the
+// work instead of after it.
+template <int HP>
+__global__ void __launch_bounds__(kEdgeBlock) edge_softmax_fwd_vec_kernel(float4* __restrict__ y, const float4* __restrict__ x,
+                                                                          const int32_t* __restrict__ off, int64_t n, int hub_blocks) {
+    __shared__ float s_m[4][kEdgeBlock], s_s[4][kEdgeBlock];
+    if ((int)blockIdx.x < hub_blocks)
+        softmax_fwd_vec_block<HP>(y, x, off, n, (int)blockIdx.x, hub_blocks, s_m, s_s);
+    else
+        softmax_fwd_vec_warps<HP>(y, x, off, n, (int)blockIdx.x - hub_blocks, (int)gridDim.x - hub_blocks);
+}
+
 // Any H: one (segment, column) pair per warp pass, strided access.
 __global__ void __launch_bounds__(kEdgeBlock) edge_softmax_fwd_any_kernel(float* __restrict__ y, const float* __restrict__ x,
                                                                           const int32_t* __restrict__ off, int64_t n, int64_t H) {
@@ -338,6 +472,99 @@ __global__ void __launch_bounds__(kEdgeBlock) edge_softmax_bwd_hub_kernel(float*
     }
 }
 
+// 128-bit forms for H = 4, 8, 16, 32 (16-byte aligned operands): a lane carries the four columns of a float4.
+__device__ __forceinline__ float4 softmax_grad(const float4& yy, const float4& gg, const float (&dot)[4]) {
+    return make_float4(__fsub_rn(__fmul_rn(yy.x, gg.x), __fmul_rn(yy.x, dot[0])), __fsub_rn(__fmul_rn(yy.y, gg.y), __fmul_rn(yy.y, dot[1])),
+                       __fsub_rn(__fmul_rn(yy.z, gg.z), __fmul_rn(yy.z, dot[2])), __fsub_rn(__fmul_rn(yy.w, gg.w), __fmul_rn(yy.w, dot[3])));
+}
+__device__ __forceinline__ void dot_add(float (&dot)[4], const float4& yy, const float4& gg) {
+    dot[0] += yy.x * gg.x; dot[1] += yy.y * gg.y; dot[2] += yy.z * gg.z; dot[3] += yy.w * gg.w;
+}
+
+template <int HP>
+__device__ __forceinline__ void softmax_bwd_vec_warps(float4* __restrict__ dx, const float4* __restrict__ g,
+                                                      const float4* __restrict__ y, const int32_t* __restrict__ off, int64_t n,
+                                                      int block, int n_blocks) {
+    constexpr int Q = HP / 4;
+    const int lane = lane_id();
+    const int64_t warp = ((int64_t)block * blockDim.x + threadIdx.x) >> 5;
+    const int64_t n_warps = ((int64_t)n_blocks * blockDim.x) >> 5;
+    for (int64_t v = warp; v < n; v += n_warps) {
+        if (off[v + 1] - off[v] >= kSoftmaxHub) continue;
+        const int64_t s = (int64_t)off[v] * Q, e = (int64_t)off[v + 1] * Q;
+        float dot[4] = {0.f, 0.f, 0.f, 0.f};
+        int64_t i = s + lane;
+        for (; i + 32 < e; i += 64) {   // four independent 16-byte loads in flight, added in order
+            const float4 y0 = y[i], g0 = g[i], y1 = y[i + 32], g1 = g[i + 32];
+            dot_add(dot, y0, g0);
+            dot_add(dot, y1, g1);
+        }
+        for (; i < e; i += 32) dot_add(dot, y[i], g[i]);
+#pragma unroll
+        for (int c = 0; c < 4; c++) dot[c] = reduce_same_column_sum<Q>(dot[c]);
+        i = s + lane;
+        for (; i + 32 < e; i += 64) {
+            const float4 y0 = y[i], g0 = g[i], y1 = y[i + 32], g1 = g[i + 32];
+            __stcs(dx + i, softmax_grad(y0, g0, dot));
+            __stcs(dx + i + 32, softmax_grad(y1, g1, dot));
+        }
+        for (; i < e; i += 32) __stcs(dx + i, softmax_grad(y[i], g[i], dot));
+    }
+}
+
+template <int HP>
+__device__ __forceinline__ void softmax_bwd_vec_block(float4* __restrict__ dx, const float4* __restrict__ g,
+                                                      const float4* __restrict__ y, const int32_t* __restrict__ off, int64_t n,
+                                                      int block, int n_blocks, float* s_buf) {
+    constexpr int Q = HP / 4;
+    for (int64_t v = block; v < n; v += n_blocks) {
+        if (off[v + 1] - off[v] < kSoftmaxHub) continue;   // block-uniform
+        const int64_t s = (int64_t)off[v] * Q, e = (int64_t)off[v + 1] * Q;
+        float dot[4] = {0.f, 0.f, 0.f, 0.f};
+        int64_t i = s + threadIdx.x;
+        for (; i + 3 * kEdgeBlock < e; i += 4 * kEdgeBlock) {   // eight loads in flight per thread, added in order
+            float4 yy[4], gg[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) { yy[u] = y[i + u * kEdgeBlock]; gg[u] = g[i + u * kEdgeBlock]; }
+#pragma unroll
+            for (int u = 0; u < 4; u++) dot_add(dot, yy[u], gg[u]);
+        }
+        for (; i + kEdgeBlock < e; i += 2 * kEdgeBlock) {
+            const float4 y0 = y[i], g0 = g[i], y1 = y[i + kEdgeBlock], g1 = g[i + kEdgeBlock];
+            dot_add(dot, y0, g0);
+            dot_add(dot, y1, g1);
+        }
+        for (; i < e; i += kEdgeBlock) dot_add(dot, y[i], g[i]);
+#pragma unroll
+        for (int c = 0; c < 4; c++) dot[c] = block_same_column<Q, false>(dot[c], s_buf);
+        i = s + threadIdx.x;
+        for (; i + 3 * kEdgeBlock < e; i += 4 * kEdgeBlock) {
+            float4 yy[4], gg[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) { yy[u] = y[i + u * kEdgeBlock]; gg[u] = g[i + u * kEdgeBlock]; }
+#pragma unroll
+            for (int u = 0; u < 4; u++) __stcs(dx + i + u * kEdgeBlock, softmax_grad(yy[u], gg[u], dot));
+        }
+        for (; i + kEdgeBlock < e; i += 2 * kEdgeBlock) {
+            const float4 y0 = y[i], g0 = g[i], y1 = y[i + kEdgeBlock], g1 = g[i + kEdgeBlock];
+            __stcs(dx + i, softmax_grad(y0, g0, dot));
+            __stcs(dx + i + kEdgeBlock, softmax_grad(y1, g1, dot));
+        }
+        for (; i < e; i += kEdgeBlock) __stcs(dx + i, softmax_grad(y[i], g[i], dot));
+    }
+}
+
+template <int HP>
+__global__ void __launch_bounds__(kEdgeBlock) edge_softmax_bwd_vec_kernel(float4* __restrict__ dx, const float4* __restrict__ g,
+                                                                          const float4* __restrict__ y,
+                                                                          const int32_t* __restrict__ off, int64_t n, int hub_blocks) {
+    __shared__ float s_buf[kEdgeBlock];
+    if ((int)blockIdx.x < hub_blocks)
+        softmax_bwd_vec_block<HP>(dx, g, y, off, n, (int)blockIdx.x, hub_blocks, s_buf);
+    else
+        softmax_bwd_vec_warps<HP>(dx, g, y, off, n, (int)blockIdx.x - hub_blocks, (int)gridDim.x - hub_blocks);
+}
+
 __global__ void __launch_bounds__(kEdgeBlock) edge_softmax_bwd_any_kernel(float* __restrict__ dx, const float* __restrict__ g,
                                                                           const float* __restrict__ y,
                                                                           const int32_t* __restrict__ off, int64_t n, int64_t H) {
@@ -380,7 +607,7 @@ static int grid_for_warps(int64_t warps_wanted) {
 
 // blocks of the block-per-segment kernels: they scan all segments for the long ones
 static int hub_blocks(int64_t n_nodes) {
-    const int64_t cap = (int64_t)sm_count() * 4;
+    const int64_t cap = (int64_t)sm_count() * 8;
     return (int)(n_nodes < cap ? (n_nodes > 0 ? n_nodes : 1) : cap);
 }
 
@@ -441,6 +668,18 @@ int jg_edge_softmax_fwd_f32(float* y, const float* x, const int32_t* off, int64_
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int grid = grid_for_warps(n_nodes);
     const int hub_grid = hub_blocks(n_nodes);
+    if ((h == 4 || h == 8 || h == 16 || h == 32) && (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16 == 0) {
+        float4* y4 = reinterpret_cast<float4*>(y);
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+#define JG_SOFTMAX_VEC(HP) edge_softmax_fwd_vec_kernel<HP><<<hub_grid + grid, kEdgeBlock, 0, st>>>(y4, x4, off, n_nodes, hub_grid)
+        if (h == 4) { JG_SOFTMAX_VEC(4); }
+        else if (h == 8) { JG_SOFTMAX_VEC(8); }
+        else if (h == 16) { JG_SOFTMAX_VEC(16); }
+        else { JG_SOFTMAX_VEC(32); }
+#undef JG_SOFTMAX_VEC
+        JG_LAUNCH_CHECK();
+        return JG_OK;
+    }
     switch (h) {
         case 1: edge_softmax_fwd_kernel<1><<<grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes);
                 edge_softmax_fwd_hub_kernel<1><<<hub_grid, kEdgeBlock, 0, st>>>(y, x, off, n_nodes); break;
@@ -468,6 +707,20 @@ int jg_edge_softmax_bwd_f32(float* dx, const float* grad, const float* y, const 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int grid = grid_for_warps(n_nodes);
     const int hub_grid = hub_blocks(n_nodes);
+    if ((h == 4 || h == 8 || h == 16 || h == 32) &&
+        (reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(grad) | reinterpret_cast<uintptr_t>(y)) % 16 == 0) {
+        float4* d4 = reinterpret_cast<float4*>(dx);
+        const float4* g4 = reinterpret_cast<const float4*>(grad);
+        const float4* y4 = reinterpret_cast<const float4*>(y);
+#define JG_SOFTMAX_BWD_VEC(HP) edge_softmax_bwd_vec_kernel<HP><<<hub_grid + grid, kEdgeBlock, 0, st>>>(d4, g4, y4, off, n_nodes, hub_grid)
+        if (h == 4) { JG_SOFTMAX_BWD_VEC(4); }
+        else if (h == 8) { JG_SOFTMAX_BWD_VEC(8); }
+        else if (h == 16) { JG_SOFTMAX_BWD_VEC(16); }
+        else { JG_SOFTMAX_BWD_VEC(32); }
+#undef JG_SOFTMAX_BWD_VEC
+        JG_LAUNCH_CHECK();
+        return JG_OK;
+    }
     switch (h) {
         case 1: edge_softmax_bwd_kernel<1><<<grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes);
                  edge_softmax_bwd_hub_kernel<1><<<hub_grid, kEdgeBlock, 0, st>>>(dx, grad, y, off, n_nodes); break;

@@ -84,7 +84,7 @@ def test_scatter_and_gather(cuda, oracle, c):
     assert np.array_equal(host(ms.grad), oracle.scatter_to_edge(x, idx, off, 1))
 
 
-@pytest.mark.parametrize("h", [1, 2, 3, 8, 32])
+@pytest.mark.parametrize("h", [1, 2, 3, 4, 8, 16, 32])
 def test_edge_softmax(cuda, oracle, h):
     rng = np.random.default_rng(10 + h)
     n = 600
