@@ -184,6 +184,15 @@ int jg_halo_pull(void* halo, const int32_t* needed, void* const* peer_x_host, vo
                  const int64_t* seg_begin_host, const int32_t* lo_host, int world, int rank, int64_t row_bytes, int slot,
                  uint32_t epoch, void* counter, int32_t* error, int64_t wait_ns, int max_ctas, int plain, int src_half,
                  jg_stream_t stream);
+/* The same pull for a PART of every owner's segment: halo slots [part_begin_host[q], part_end_host[q]) inside
+ * [seg_begin_host[q], seg_begin_host[q+1]).  An owner that produces its rows block after block (a transform
+ * that follows an aggregation of a row range) posts one epoch word per block (its own `slot` each), and its
+ * readers fetch the rows of a block while the owner computes the next one.  No counterpart in the reference,
+ * whose broadcast moves whole blocks of every rank (ops/distspmm.py:31-39). */
+int jg_halo_pull_part(void* halo, const int32_t* needed, void* const* peer_x_host, void* const* peer_flags_host,
+                      const int64_t* seg_begin_host, const int64_t* part_begin_host, const int64_t* part_end_host,
+                      const int32_t* lo_host, int world, int rank, int64_t row_bytes, int slot, uint32_t epoch, void* counter,
+                      int32_t* error, int64_t wait_ns, int max_ctas, int plain, int src_half, jg_stream_t stream);
 /* Half-width payload of the exchange: jg_rows_to_half rounds n_values fp32 values (a multiple of 4) to
  * fp16 (values beyond +-65504 saturate), the copy of its rows an owner offers; jg_halo_pull with
  * src_half != 0 then reads rows of row_bytes = 2 * width bytes (a multiple of 16) from the peers' fp16

@@ -43,6 +43,8 @@ SIGNATURES = {
     "jg_halo_wait": (ctypes.c_int, [vp, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_uint32, vp, i64, vp]),
     "jg_halo_pull": (ctypes.c_int, [vp, vp, vp, vp, vp, vp, ctypes.c_int, ctypes.c_int, i64, ctypes.c_int, ctypes.c_uint32,
                                     vp, vp, i64, ctypes.c_int, ctypes.c_int, ctypes.c_int, vp]),
+    "jg_halo_pull_part": (ctypes.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, ctypes.c_int, ctypes.c_int, i64, ctypes.c_int,
+                                         ctypes.c_uint32, vp, vp, i64, ctypes.c_int, ctypes.c_int, ctypes.c_int, vp]),
     "jg_rows_to_half": (ctypes.c_int, [vp, vp, i64, vp]),
     "jg_partition_split_workspace_bytes": (sz, [i64]),
     "jg_partition_split": (ctypes.c_int, [vp, vp, vp, i64, i64, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]),

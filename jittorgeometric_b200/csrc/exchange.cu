@@ -75,6 +75,7 @@ struct PeerTable {
     const void* x[kMaxRanks];       // every rank's feature buffer (own rows first), as mapped here
     uint32_t* flags[kMaxRanks];     // every rank's flag block, as mapped here
     int64_t seg_begin[kMaxRanks + 1];  // halo slots [seg_begin[q], seg_begin[q+1]) hold rows owned by rank q
+    int64_t seg_end[kMaxRanks];        // this call fetches the slots [seg_begin[q], seg_end[q]) (a part of the segment, or all of it)
     int32_t lo[kMaxRanks];          // first global row id of rank q
     int32_t order[kMaxRanks];       // the peers in the order this rank visits them (rank+1, rank+2, ...)
     int32_t n_blocks[kMaxRanks];    // blocks of rows_per_block halo slots in rank q's segment
@@ -138,7 +139,7 @@ __device__ __forceinline__ bool decode_block(const PullArgs& a, int64_t v, int& 
     q = a.t.order[j];
     if (lb >= a.t.n_blocks[q]) return false;
     r0 = a.t.seg_begin[q] + lb * a.rows_per_block;
-    const int64_t left = a.t.seg_begin[q + 1] - r0;
+    const int64_t left = a.t.seg_end[q] - r0;
     cnt = left < a.rows_per_block ? (int)left : a.rows_per_block;
     return true;
 }
@@ -497,7 +498,10 @@ static int fill_table(PeerTable* t, int world, void* const* peer_x, void* const*
     for (int q = 0; q < world; q++) {
         t->x[q] = peer_x ? peer_x[q] : nullptr;
         t->flags[q] = static_cast<uint32_t*>(peer_flags[q]);
-        if (seg_begin) t->seg_begin[q] = seg_begin[q];
+        if (seg_begin) {
+            t->seg_begin[q] = seg_begin[q];
+            t->seg_end[q] = seg_begin[q + 1];
+        }
         if (lo) t->lo[q] = lo[q];
     }
     if (seg_begin) t->seg_begin[world] = seg_begin[world];
@@ -535,22 +539,32 @@ int jg_halo_wait(const void* my_flags, int world, int rank, int slot, int kind, 
     return JG_OK;
 }
 
-int jg_halo_pull(void* halo, const int32_t* needed, void* const* peer_x_host, void* const* peer_flags_host,
-                 const int64_t* seg_begin_host, const int32_t* lo_host, int world, int rank, int64_t row_bytes, int slot,
-                 uint32_t epoch, void* counter, int32_t* error, int64_t wait_ns, int max_ctas, int plain, int src_half,
-                 jg_stream_t stream) {
+static int halo_pull_impl(void* halo, const int32_t* needed, void* const* peer_x_host, void* const* peer_flags_host,
+                          const int64_t* seg_begin_host, const int64_t* part_begin_host, const int64_t* part_end_host,
+                          const int32_t* lo_host, int world, int rank, int64_t row_bytes, int slot, uint32_t epoch, void* counter,
+                          int32_t* error, int64_t wait_ns, int max_ctas, int plain, int src_half, jg_stream_t stream) {
     JG_CHECK_ARG(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world, JG_EINVAL, "halo_pull: bad rank/world");
     JG_CHECK_ARG(peer_x_host && peer_flags_host && seg_begin_host && lo_host && counter, JG_EINVAL, "halo_pull: null table");
     JG_CHECK_ARG(slot >= 0 && slot < kFlagSlots && wait_ns > 0, JG_EINVAL, "halo_pull: bad slot or limit");
     JG_CHECK_ARG(row_bytes > 0 && row_bytes % 4 == 0 && row_bytes < (int64_t(1) << 24), JG_ESHAPE, "halo_pull: row bytes must be a multiple of 4");
-    const int64_t n_halo = seg_begin_host[world];
-    JG_CHECK_ARG(n_halo >= 0 && seg_begin_host[rank + 1] == seg_begin_host[rank], JG_EINVAL,
+    JG_CHECK_ARG(seg_begin_host[world] >= 0 && seg_begin_host[rank + 1] == seg_begin_host[rank], JG_EINVAL,
                  "halo_pull: a rank's own segment must be empty");
+    JG_CHECK_ARG((part_begin_host == nullptr) == (part_end_host == nullptr), JG_EINVAL, "halo_pull: part bounds come in pairs");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     PullArgs a = {};
     a.halo = static_cast<unsigned char*>(halo);
     a.needed = needed;
     fill_table(&a.t, world, peer_x_host, peer_flags_host, seg_begin_host, lo_host);
+    int64_t n_halo = 0;          // rows this call fetches
+    for (int q = 0; q < world; q++) {
+        if (part_begin_host) {
+            JG_CHECK_ARG(part_begin_host[q] >= seg_begin_host[q] && part_begin_host[q] <= part_end_host[q] &&
+                             part_end_host[q] <= seg_begin_host[q + 1], JG_EINVAL, "halo_pull: a part must lie inside its owner's segment");
+            a.t.seg_begin[q] = part_begin_host[q];
+            a.t.seg_end[q] = part_end_host[q];
+        }
+        n_halo += a.t.seg_end[q] - a.t.seg_begin[q];
+    }
     a.world = world; a.rank = rank; a.row_bytes = (uint32_t)row_bytes;
     a.my_flags = a.t.flags[rank];
     a.slot = slot; a.epoch = epoch;
@@ -572,7 +586,7 @@ int jg_halo_pull(void* halo, const int32_t* needed, void* const* peer_x_host, vo
     a.max_blocks = 0;
     for (int j = 0; j < world - 1; j++) a.t.order[j] = (rank + 1 + j) % world;
     for (int q = 0; q < world; q++) {
-        const int64_t rows = seg_begin_host[q + 1] - seg_begin_host[q];
+        const int64_t rows = a.t.seg_end[q] - a.t.seg_begin[q];
         JG_CHECK_ARG(rows >= 0, JG_EINVAL, "halo_pull: segment bounds must not decrease");
         const int64_t nb = (rows + rpb - 1) / rpb;
         a.t.n_blocks[q] = (int32_t)nb;
@@ -640,6 +654,23 @@ int jg_halo_pull(void* halo, const int32_t* needed, void* const* peer_x_host, vo
     }
     JG_LAUNCH_CHECK();
     return JG_OK;
+}
+
+int jg_halo_pull(void* halo, const int32_t* needed, void* const* peer_x_host, void* const* peer_flags_host,
+                 const int64_t* seg_begin_host, const int32_t* lo_host, int world, int rank, int64_t row_bytes, int slot,
+                 uint32_t epoch, void* counter, int32_t* error, int64_t wait_ns, int max_ctas, int plain, int src_half,
+                 jg_stream_t stream) {
+    return halo_pull_impl(halo, needed, peer_x_host, peer_flags_host, seg_begin_host, nullptr, nullptr, lo_host, world, rank,
+                          row_bytes, slot, epoch, counter, error, wait_ns, max_ctas, plain, src_half, stream);
+}
+
+int jg_halo_pull_part(void* halo, const int32_t* needed, void* const* peer_x_host, void* const* peer_flags_host,
+                      const int64_t* seg_begin_host, const int64_t* part_begin_host, const int64_t* part_end_host,
+                      const int32_t* lo_host, int world, int rank, int64_t row_bytes, int slot, uint32_t epoch, void* counter,
+                      int32_t* error, int64_t wait_ns, int max_ctas, int plain, int src_half, jg_stream_t stream) {
+    JG_CHECK_ARG(part_begin_host && part_end_host, JG_EINVAL, "halo_pull_part: null part bounds");
+    return halo_pull_impl(halo, needed, peer_x_host, peer_flags_host, seg_begin_host, part_begin_host, part_end_host, lo_host,
+                          world, rank, row_bytes, slot, epoch, counter, error, wait_ns, max_ctas, plain, src_half, stream);
 }
 
 int jg_rows_to_half(void* out, const float* x, int64_t n_values, jg_stream_t stream) {

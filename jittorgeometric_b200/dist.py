@@ -67,6 +67,14 @@ class RowPartition:
         return min(max(bisect.bisect_right(self.bounds, int(row)) - 1, 0), self.world - 1)
 
 
+def part_rows(n_local, parts):
+    """Boundaries of ``parts`` blocks of a rank's ``n_local`` rows: equal blocks rounded up to multiples of
+    128 rows (the tile of the dense transform).  Every rank computes the same boundaries for every owner."""
+    step = -(-int(n_local) // int(parts)) if n_local else 0
+    step = -(-step // 128) * 128
+    return [min(int(n_local), c * step) for c in range(int(parts))] + [int(n_local)]
+
+
 class DeviceBackend:
     """The CUDA library: interior/halo split, halo map, row packing and aggregation kernels."""
 
@@ -196,6 +204,8 @@ class _Slot:
         self.acquired = 0        # epoch whose readers have been waited for
         self.buf16 = None        # fp16 copy of the own rows offered to the readers (half-width payload)
         self.ptrs16 = None
+        self.part_flags = {}     # number of row blocks -> flag slots of a block-wise exchange
+        self.last_flags = [index]   # flag slots the last exchange used (the words `acquire` waits on)
 
 
 class DirectTransport(CollectiveTransport):
@@ -230,6 +240,7 @@ class DirectTransport(CollectiveTransport):
         self.side = torch.cuda.Stream(device=self.device, priority=-1)
         self.profile = False
         self._slots = {}
+        self._next_flag = 0
         words = lib().jg_halo_flag_bytes() // 4
         self._flags = symm.empty((words,), dtype=torch.int32, device=self.device)
         self._flags.zero_()
@@ -255,13 +266,20 @@ class DirectTransport(CollectiveTransport):
     def _slot(self, g, f):
         slot = self._slots.get(f)
         if slot is None:
-            if len(self._slots) >= lib().jg_halo_flag_slots():
-                raise RuntimeError(f"DirectTransport holds at most {lib().jg_halo_flag_slots()} feature widths")
             buf = self._symm.empty((max(g.buffer_rows, 1), f), dtype=torch.float32, device=self.device)
             hdl = self._symm.rendezvous(buf, self.symm_group.group_name)
-            slot = _Slot(len(self._slots), buf, hdl.buffer_ptrs)
+            slot = _Slot(self._take_flags(1)[0], buf, hdl.buffer_ptrs)
             self._slots[f] = slot
         return slot
+
+    def _take_flags(self, count):
+        """``count`` unused flag slots (every rank asks in the same order, so they agree on the numbers)."""
+        if self._next_flag + count > lib().jg_halo_flag_slots():
+            raise RuntimeError(f"DirectTransport has {lib().jg_halo_flag_slots()} flag slots (one per feature width, "
+                               "one more per row block of a block-wise exchange)")
+        got = list(range(self._next_flag, self._next_flag + count))
+        self._next_flag += count
+        return got
 
     def feature_buffer(self, g, f):
         """The rank's buffer for width ``f`` (``[own rows | halo rows]``; collective on first use:
@@ -273,8 +291,9 @@ class DirectTransport(CollectiveTransport):
         of the last exchange of width ``f``: call it before overwriting the head of the buffer."""
         slot = self._slot(g, f)
         if slot.epoch > slot.acquired and self.world > 1:
-            check(lib().jg_halo_wait(ptr(self._flags), self.world, self.rank, slot.index, 1, slot.epoch, self._eptr(),
-                                     self.wait_ns, stream_for(slot.buf)), "jg_halo_wait")
+            for flag in slot.last_flags:
+                check(lib().jg_halo_wait(ptr(self._flags), self.world, self.rank, flag, 1, slot.epoch, self._eptr(),
+                                         self.wait_ns, stream_for(slot.buf)), "jg_halo_wait")
         slot.acquired = slot.epoch
 
     def _eptr(self):
@@ -297,6 +316,7 @@ class DirectTransport(CollectiveTransport):
         self.check()
         slot = self._slot(g, f)
         slot.epoch += 1
+        slot.last_flags = [slot.index]
         st = stream_for(slot.buf)
         half = bool(getattr(g, "halo_half", False))
         if half:
@@ -306,12 +326,7 @@ class DirectTransport(CollectiveTransport):
         check(lib().jg_halo_post(self._flag_ptrs, self.world, self.rank, slot.index, 0, slot.epoch, st), "jg_halo_post")
         cur = torch.cuda.current_stream(self.device)
         self.side.wait_stream(cur)
-        tables = getattr(g, "_pull_tables", None)
-        if tables is None:                       # per-graph constants of the pull, built once
-            tables = ((ctypes.c_int64 * (self.world + 1))(*([int(v) for v in g.recv_offset] + [int(g.n_halo)])),
-                      (ctypes.c_int32 * self.world)(*[int(g.part.bounds[q]) for q in range(self.world)]))
-            g._pull_tables = tables
-        seg, los = tables
+        seg, los = self._tables(g)
         halo_ptr = ctypes.c_void_p(slot.buf.data_ptr() + g.n_local * f * 4)
         begun = None
         if self.profile:                      # timing events around the pull (benchmarks: where a step's time goes)
@@ -324,6 +339,50 @@ class DirectTransport(CollectiveTransport):
         landed = torch.cuda.Event(enable_timing=self.profile)
         landed.record(self.side)
         return _DirectHandle(self, landed, begun)
+
+    def begin_part(self, g, f, c, parts, half_ready=False, ctas=None):
+        """Block ``c`` of ``parts`` (:func:`part_rows`) of the rank's rows of width ``f`` is in place: tells the
+        peers and starts pulling the halo rows that lie in block ``c`` of THEIR owners.  A rank that produces
+        its rows block after block (an aggregation of a row range followed by its transform) calls this after
+        every block, in order, so the rows of a block travel while the next one is computed; every block has its
+        own epoch words.  ``ctas``: CTA slots for the pull (default ``pull_ctas``; 0 = nothing runs beside it)."""
+        self.check()
+        slot = self._slot(g, f)
+        flags = slot.part_flags.get(parts)
+        if flags is None:
+            flags = slot.part_flags[parts] = self._take_flags(parts)
+        if c == 0:
+            slot.epoch += 1
+            slot.last_flags = flags
+        st = stream_for(slot.buf)
+        half = bool(getattr(g, "halo_half", False))
+        rows = part_rows(g.n_local, parts)
+        if half:
+            self.half_buffer(g, f)
+            if not half_ready and rows[c + 1] > rows[c]:
+                check(lib().jg_rows_to_half(ptr(slot.buf16[rows[c]:]), ptr(slot.buf[rows[c]:]), (rows[c + 1] - rows[c]) * f, st),
+                      "jg_rows_to_half")
+        check(lib().jg_halo_post(self._flag_ptrs, self.world, self.rank, flags[c], 0, slot.epoch, st), "jg_halo_post")
+        self.side.wait_stream(torch.cuda.current_stream(self.device))
+        seg, los = self._tables(g)
+        begins, ends = g.part_tables(parts)[c]
+        halo_ptr = ctypes.c_void_p(slot.buf.data_ptr() + g.n_local * f * 4)
+        check(lib().jg_halo_pull_part(halo_ptr, ptr(g.needed), slot.ptrs16 if half else slot.ptrs, self._flag_ptrs, seg, begins,
+                                      ends, los, self.world, self.rank, (2 if half else 4) * f, flags[c], slot.epoch,
+                                      ptr(self._counter), self._eptr(), self.wait_ns, self.pull_ctas if ctas is None else int(ctas),
+                                      1 if self.plain else 0, 1 if half else 0, ctypes.c_void_p(self.side.cuda_stream)),
+              "jg_halo_pull_part")
+        landed = torch.cuda.Event()
+        landed.record(self.side)
+        return _DirectHandle(self, landed)
+
+    def _tables(self, g):
+        tables = getattr(g, "_pull_tables", None)
+        if tables is None:                       # per-graph constants of the pull, built once
+            tables = ((ctypes.c_int64 * (self.world + 1))(*([int(v) for v in g.recv_offset] + [int(g.n_halo)])),
+                      (ctypes.c_int32 * self.world)(*[int(g.part.bounds[q]) for q in range(self.world)]))
+            g._pull_tables = tables
+        return tables
 
 
 class EmulatedRanks:
@@ -343,6 +402,8 @@ class EmulatedRanks:
         self.flags = [torch.zeros(words, dtype=torch.int32, device=self.device) for _ in range(self.world)]
         self.flag_ptrs = (ctypes.c_void_p * self.world)(*[t.data_ptr() for t in self.flags])
         self.buffers = {}            # f -> [tensor per rank]
+        self._flag_of = {}           # (f, parts) -> first flag slot
+        self._next_flag = 0
         self.rows = [0] * self.world
         self.views = [_EmulatedRank(self, r, wait_ms, plain, pull_ctas) for r in range(self.world)]
 
@@ -360,14 +421,19 @@ class EmulatedRanks:
     def buffer(self, f, rank):
         bufs = self.buffers.get(f)
         if bufs is None:
-            if len(self.buffers) >= lib().jg_halo_flag_slots():
-                raise RuntimeError("too many feature widths")
             bufs = [torch.zeros((max(self.rows[r], 1), f), dtype=torch.float32, device=self.device) for r in range(self.world)]
             self.buffers[f] = bufs
         return bufs[rank]
 
-    def slot_index(self, f):
-        return list(self.buffers).index(f)
+    def slot_index(self, f, parts=1):
+        """First of the ``parts`` flag slots of width ``f`` (1: the whole-segment exchange)."""
+        key = (f, parts)
+        if key not in self._flag_of:
+            if self._next_flag + parts > lib().jg_halo_flag_slots():
+                raise RuntimeError("too many flag slots")
+            self._flag_of[key] = self._next_flag
+            self._next_flag += parts
+        return self._flag_of[key]
 
 
 class _EmulatedRank(CollectiveTransport):
@@ -425,6 +491,30 @@ class _EmulatedRank(CollectiveTransport):
                                  self.pull_ctas, 1 if self.plain else 0, 1 if half else 0, st), "jg_halo_pull")
         for t in sources:
             t.record_stream(torch.cuda.current_stream())
+        return _Done()
+
+    def begin_part(self, g, f, c, parts, half_ready=False, ctas=None):
+        """Block ``c`` of a block-wise exchange (see :meth:`DirectTransport.begin_part`); the emulated owners'
+        words for the block are posted here on their behalf, fp32 payload only."""
+        self.check()
+        if getattr(g, "halo_half", False):
+            raise RuntimeError("emulated ranks exchange blocks in fp32 only")
+        buf = self.feature_buffer(g, f)
+        first = self.owner.slot_index(f, parts)
+        if c == 0:
+            self.epochs[(f, parts)] = self.epochs.get((f, parts), 0) + 1
+        epoch = self.epochs[(f, parts)]
+        st = stream_for(buf)
+        for q in (range(self.world) if self.post_for_peers else [self.rank]):
+            check(lib().jg_halo_post(self.owner.flag_ptrs, self.world, q, first + c, 0, epoch, st), "jg_halo_post")
+        ptrs = (ctypes.c_void_p * self.world)(*[self.owner.buffer(f, q).data_ptr() for q in range(self.world)])
+        seg = (ctypes.c_int64 * (self.world + 1))(*([int(v) for v in g.recv_offset] + [int(g.n_halo)]))
+        los = (ctypes.c_int32 * self.world)(*[int(g.part.bounds[q]) for q in range(self.world)])
+        begins, ends = g.part_tables(parts)[c]
+        check(lib().jg_halo_pull_part(ptr(buf[g.n_local:]), ptr(g.needed), ptrs, self.owner.flag_ptrs, seg, begins, ends, los,
+                                      self.world, self.rank, 4 * f, first + c, epoch, ptr(self._counter), self._eptr(), self.wait_ns,
+                                      self.pull_ctas if ctas is None else int(ctas), 1 if self.plain else 0, 0, st),
+              "jg_halo_pull_part")
         return _Done()
 
 
@@ -568,6 +658,67 @@ class ShardedGraph:
 
     def _aggregate(self, x, bias=None, relu=False):
         return self.finish(self.start(x), bias, relu)
+
+    # ---- block-wise exchange (direct transport): rows produced and fetched block after block
+    def part_tables(self, parts):
+        """For every block ``c`` of ``parts``: the halo slots ``[begin[q], end[q])`` whose rows lie in block
+        ``c`` of owner ``q`` (``needed`` is ascending, so a block of an owner is one run of it)."""
+        cache = self.__dict__.setdefault("_part_tables", {})
+        tables = cache.get(parts)
+        if tables is None:
+            world = self.part.world
+            marks = [[self.part.bounds[q] + r for r in part_rows(self.part.n_local(q), parts)] for q in range(world)]
+            flat = torch.tensor([m for row in marks for m in row], dtype=self.needed.dtype, device=self.needed.device)
+            pos = torch.searchsorted(self.needed.contiguous(), flat).reshape(world, parts + 1).tolist() if self.n_halo else \
+                [[0] * (parts + 1) for _ in range(world)]
+            tables = [((ctypes.c_int64 * world)(*[int(pos[q][c]) for q in range(world)]),
+                       (ctypes.c_int64 * world)(*[int(pos[q][c + 1]) for q in range(world)])) for c in range(parts)]
+            cache[parts] = tables
+        return tables
+
+    def start_part(self, f, c, parts, half_ready=False, ctas=None):
+        """Block ``c`` of ``parts`` (:func:`part_rows`) of the rank's rows has been written into
+        ``feature_buffer(f)`` (and ``half_buffer(f)`` when ``half_ready``): offers it to the peers and starts
+        fetching the halo rows of the same block of every owner.  Call for ``c = 0 .. parts - 1`` in order, then
+        :meth:`finish_parts` with the handles.  Direct transport, merged schedule, forward only."""
+        if not (self.direct and self.mode == "merged"):
+            raise RuntimeError("start_part: needs the direct transport and the merged schedule")
+        if c == 0:
+            if f in self._inflight:
+                raise RuntimeError(f"an aggregation of width {f} is already in flight on this graph")
+            self._inflight.add(f)
+        return self.transport.begin_part(self, f, c, parts, half_ready, ctas)
+
+    def finish_parts(self, f, handles, bias=None, relu=False):
+        """Waits for every block's halo rows and aggregates (the second half of :meth:`start_part`)."""
+        for h in handles:
+            h.wait()
+        buf = self.transport.feature_buffer(self, f)
+        extra = {"reserve_ctas": self.transport.pull_ctas} if len(self._inflight) > 1 and self.transport.pull_ctas > 0 else {}
+        y = self.backend.aggregate(buf, self.merged[0], self.merged[1], self.merged[2], self.n_local, self.merged_plan,
+                                   bias=bias, relu=relu, **extra)
+        self._inflight.discard(f)
+        return y
+
+    def aggregate_rows(self, pending, first, last, bias=None, relu=False, reserve_ctas=0):
+        """The rows ``[first, last)`` of an aggregation whose exchange was started with :meth:`start` (wait for it
+        with ``pending[2].wait()`` once, then call this for every row range; :meth:`done` ends it).  The rows of a
+        range can feed the next layer's transform and exchange while the next range is aggregated."""
+        if self.mode != "merged":
+            raise RuntimeError("aggregate_rows: merged schedule only")
+        buf = pending[1]
+        idx, off, w = self.merged
+        plans = self.__dict__.setdefault("_range_plans", {})
+        plan = plans.get((first, last))
+        if plan is None:
+            plan = plans[(first, last)] = self.backend.plan(off[first: last + 1], idx.numel())
+        return self.backend.aggregate(buf, idx, off[first: last + 1], w, last - first, plan, bias=bias, relu=relu,
+                                      reserve_ctas=reserve_ctas)
+
+    def done(self, pending):
+        """Ends an aggregation that was consumed through :meth:`aggregate_rows`."""
+        pending[2].release()
+        self._inflight.discard(pending[0].shape[1])
 
     def start(self, x, half_ready=False):
         """First half of an aggregation: starts the exchange of the halo rows.  Aggregations of

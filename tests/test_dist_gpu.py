@@ -128,6 +128,53 @@ def build_emulated(jd, world, n, f, E=60000, seed=None, mode="merged", **kw):
     return (idx, off, w, x), part, emu, graphs
 
 
+@pytest.mark.parametrize("world,n,f,parts", [(2, 5001, 128, 2), (4, 4096, 64, 4), (3, 2500, 256, 3), (8, 3000, 32, 2), (2, 300, 16, 4)])
+def test_block_wise_exchange_and_row_range_aggregation(cuda, oracle, world, n, f, parts):
+    """Rows offered and fetched block after block (one epoch word per block, ``jg_halo_pull_part``) land exactly
+    where the whole-segment exchange puts them and give the same aggregation bit for bit; the aggregation of
+    row ranges (what produces the blocks of the next layer) equals the whole one row for row."""
+    from jittorgeometric_b200 import dist as jd
+    (idx, off, w, x), part, emu, graphs = build_emulated(jd, world, n, f, E=20 * n)
+    want = oracle.aggregate(x, idx, off, w)
+    _, scale = oracle.aggregate_f64(x, idx, off, w)
+    for r, g in enumerate(graphs):
+        lo, hi = part.range(r)
+        whole = g.aggregate(g.feature_buffer(f)).cpu().numpy()
+        halo_whole = emu.buffer(f, r)[g.n_local: g.n_local + g.n_halo].clone()
+        emu.buffer(f, r)[g.n_local:].zero_()
+        # the blocks of every owner partition its segment of the needed rows
+        tables = g.part_tables(parts)
+        for q in range(world):
+            assert tables[0][0][q] == g.recv_offset[q] and tables[-1][1][q] == g.recv_offset[q] + g.recv_counts[q]
+            for c in range(parts - 1):
+                assert tables[c][1][q] == tables[c + 1][0][q]
+        handles = []
+        for c in range(parts):
+            handles.append(g.start_part(f, c, parts))
+            if c < parts - 1:                    # later blocks have not arrived yet
+                end = max(tables[c][1])
+                later = [(tables[c2][0][q], tables[c2][1][q]) for c2 in range(c + 1, parts) for q in range(world)]
+                torch.cuda.synchronize()
+                for a, b in later:
+                    assert not emu.buffer(f, r)[g.n_local + a: g.n_local + b].any()
+        y = g.finish_parts(f, handles).cpu().numpy()
+        emu.transport(r).check()
+        assert torch.equal(emu.buffer(f, r)[g.n_local: g.n_local + g.n_halo], halo_whole)
+        assert np.array_equal(y, whole)
+        assert (np.abs(y - want[lo:hi]) / (scale[lo:hi] + 1e-30)).max() <= 1e-5
+        # row ranges of one aggregation
+        pending = g.start(g.feature_buffer(f))
+        pending[2].wait()
+        rows = jd.part_rows(g.n_local, parts)
+        pieces = [g.aggregate_rows(pending, rows[c], rows[c + 1]) for c in range(parts) if rows[c + 1] > rows[c]]
+        g.done(pending)
+        got = torch.cat(pieces).cpu().numpy()
+        assert got.shape == whole.shape
+        assert (np.abs(got - want[lo:hi]) / (scale[lo:hi] + 1e-30)).max() <= 1e-5
+        short = np.diff(off[lo: hi + 1]) <= 256            # rows no plan splits: the same sum whatever the range
+        assert np.array_equal(got[short], whole[short])
+
+
 @pytest.mark.parametrize("mode", ["merged", "overlap"])
 @pytest.mark.parametrize("world,n,f,plain", [(2, 5001, 128, False), (4, 4096, 32, False), (8, 3000, 7, False), (3, 2500, 256, False),
                                              (4, 4096, 64, True), (2, 40000, 512, False)])
