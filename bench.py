@@ -425,7 +425,7 @@ def main():
     ap.add_argument("--gcn-scale", type=int, default=26, help="R-MAT scale of the gcn_forward sub-record (0 = skip)")
     ap.add_argument("--gcn-halo", default="fp16", choices=["fp16", "fp32"],
                     help="N > 1, gcn_forward: payload of the halo rows (fp16 stays within 5e-4, inside the 2e-3 of the TF32 transform)")
-    ap.add_argument("--gcn-steps", type=int, default=5)
+    ap.add_argument("--gcn-steps", type=int, default=10)
     ap.add_argument("--gcn-warmup", type=int, default=3)
     args = ap.parse_args()
     global WIDTHS

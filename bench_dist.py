@@ -108,9 +108,33 @@ def gcn_forward_record(args, dev, rank, world, sampler_cls=None):
             jg.linear_tf32(src, W, weight_t=Wt, out=h, out_half=g.half_buffer(f) if fused_half else None)
             return h
 
-        def forward():
+        def forward_serial():
             z1 = g.aggregate(transform(x, W1, W1t, 128), bias=b1, relu=True, half_ready=fused_half)
             return g.aggregate(transform(z1, W2, W2t, 64), bias=b2, half_ready=fused_half)
+
+        # Block-wise second layer: the first layer's aggregation runs over `parts` row ranges; as soon as a range
+        # is done its rows go through the second transform and are offered to the peers, whose pulls (and this
+        # rank's) run beside the aggregation of the next range.  Only the last block's exchange is exposed.
+        parts = max(1, int(os.environ.get("JG_GCN_PARTS", "2"))) if g.direct else 1
+        beside = int(os.environ.get("JG_GCN_BESIDE_CTAS", "16"))     # CTA slots a pull gets beside an aggregation
+        rows = jd.part_rows(n_local, parts)
+
+        def forward_blocks():
+            pending = g.start(transform(x, W1, W1t, 128), fused_half)
+            h2 = g.feature_buffer(64, x)                          # also waits for the readers of the last forward
+            half2 = g.half_buffer(64) if fused_half else None
+            pending[2].wait()
+            handles = []
+            for c in range(parts):
+                a, b = rows[c], rows[c + 1]
+                last = c == parts - 1
+                z = g.aggregate_rows(pending, a, b, bias=b1, relu=True, reserve_ctas=beside if c > 0 else 0)
+                jg.linear_tf32(z, W2, weight_t=W2t, out=h2[a:b], out_half=half2[a:b] if fused_half else None)
+                handles.append(g.start_part(64, c, parts, half_ready=fused_half, ctas=0 if last else beside))
+            g.done(pending)
+            return g.finish_parts(64, handles, bias=b2)
+
+        forward = forward_blocks if parts > 1 else forward_serial
     else:
         plan = jg.SpmmPlan(off, nnz)
         h1 = torch.empty((n, 128), device=dev)
@@ -144,9 +168,30 @@ def gcn_forward_record(args, dev, rank, world, sampler_cls=None):
     ms = torch.tensor([a.elapsed_time(b) / args.gcn_steps], device=dev)
     # one more forward with a synchronisation after every phase: where the time goes (not part of `ms`)
     phases = {}
+    schedule, serial_ms, blocks_vs_serial = None, None, None
     if world > 1:
         dist.barrier()
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        schedule = "serial: transform, exchange, aggregation per layer"
+        if parts > 1:
+            schedule = (f"layer-1 aggregation in {parts} row ranges; each range's layer-2 transform and halo exchange "
+                        f"run beside the aggregation of the next range (block-wise pulls, {beside} CTA slots)")
+            # the serial schedule beside it, and the two results against each other
+            ref = forward_serial()
+            diff = torch.tensor([float((out - ref).abs().max() / ref.abs().max().clamp_min(1e-30))], device=dev)
+            dist.all_reduce(diff, op=dist.ReduceOp.MAX)
+            blocks_vs_serial = float(diff.item())
+            del ref
+            torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+            a.record()
+            for _ in range(args.gcn_steps):
+                ref = forward_serial()
+            b.record()
+            torch.cuda.synchronize()
+            del ref
+            sm = torch.tensor([a.elapsed_time(b) / args.gcn_steps], device=dev)
+            dist.all_reduce(sm, op=dist.ReduceOp.MAX)
+            serial_ms = float(sm.item())
 
         def timed(name, fn):
             torch.cuda.synchronize(); t0 = time.perf_counter()
@@ -181,7 +226,8 @@ def gcn_forward_record(args, dev, rank, world, sampler_cls=None):
            "alg_gbs_per_gpu": alg / world / ms / 1e6, "frac_of_hbm_peak_per_gpu": alg / world / ms / 1e6 / peak, "peak_kind": kind,
            "halo_payload": None if world == 1 else ("fp16 (rows widened to fp32 on arrival; own rows fp32)" if halo_half else "fp32"),
            "halo_rows_rank0": halo_rows, "halo_bytes_per_forward_rank0": halo_rows * (128 + 64) * (2 if halo_half else 4),
-           "remote_rows_rank0": n - n_local, "phases_ms_max_over_ranks": phases or None,
+           "remote_rows_rank0": n - n_local, "schedule": schedule, "serial_schedule_ms": serial_ms,
+           "max_rel_diff_to_serial_schedule": blocks_vs_serial, "phases_ms_max_over_ranks": phases or None,
            "output_finite": finite, "peak_device_memory_gb": peak_mem, "graph_build_s": t_build, "clocks": clocks}
     return rec
 

@@ -311,6 +311,22 @@ def nccl_worker(rank, world, port, n, E, f, q, exchange):
         ya, yb = g.finish(pa), g.finish(pb, relu=True)
         torch.cuda.synchronize()
         assert torch.equal(ya, y) and torch.equal(yb, torch.relu(g.aggregate(xb)))
+        if g.direct:
+            # block-wise exchange between real ranks: rows written and offered block after block, twice
+            # (the second round reuses the blocks' epoch words), then a whole-segment exchange again
+            buf = g.feature_buffer(f)
+            rows = jd.part_rows(g.n_local, 3)
+            for _ in range(2):
+                buf = g.feature_buffer(f)                      # waits for the readers of the previous round
+                handles = []
+                for c in range(3):
+                    buf[rows[c]: rows[c + 1]].copy_(t(x[lo + rows[c]: lo + rows[c + 1]].copy()))
+                    handles.append(g.start_part(f, c, 3, ctas=0 if c == 2 else 32))
+                yp = g.finish_parts(f, handles)
+                torch.cuda.synchronize()
+                g.transport.check()
+                assert torch.equal(yp, y)
+            assert torch.equal(g.aggregate(t(x[lo:hi].copy())), y)
         # the reference-shaped API: one sub-CSR per source rank, one broadcast round each
         import oracle as O
         import jittorgeometric_b200 as jg
