@@ -159,13 +159,16 @@ def gcn_forward_record(args, dev, rank, world, sampler_cls=None):
         dist.barrier()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.gcn_steps)]
     a.record()
-    for _ in range(args.gcn_steps):
+    for k in range(args.gcn_steps):
         out = forward()
+        marks[k].record()
     b.record()
     torch.cuda.synchronize()
     clocks = sampler.stop() if sampler else None
     ms = torch.tensor([a.elapsed_time(b) / args.gcn_steps], device=dev)
+    each = sorted(([a] + marks)[k].elapsed_time(marks[k]) for k in range(args.gcn_steps))   # this rank's forwards, one by one
     # one more forward with a synchronisation after every phase: where the time goes (not part of `ms`)
     phases = {}
     schedule, serial_ms, blocks_vs_serial = None, None, None
@@ -219,7 +222,8 @@ def gcn_forward_record(args, dev, rank, world, sampler_cls=None):
     import bench
     peak, kind = bench.measured_peaks()
     rec = {"metric": "gcn_forward_edge_feat_per_s", "value": nnz * (128 + 64) / (ms * 1e-3), "unit": "edge*feat/s",
-           "ms": ms, "steps": args.gcn_steps, "warmup": args.gcn_warmup, "n_gpus": world,
+           "ms": ms, "ms_median_forward_rank0": each[len(each) // 2], "ms_slowest_forward_rank0": each[-1],
+           "steps": args.gcn_steps, "warmup": args.gcn_warmup, "n_gpus": world,
            "workload": f"2-layer GCN forward 128->128->64 (TF32 transform on tcgen05, fp32 aggregation, bias+ReLU fused): R-MAT "
                        f"scale {scale}, {n} nodes, {nnz} directed edges incl. self-loops, gcn_norm weights; {world} contiguous "
                        f"destination-row shard(s), each generated and converted by its own rank",
