@@ -218,27 +218,44 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 if (round > 0 && !mbar_wait(&ctl->empty[s], (round - 1) & 1, p.wait_spins)) { ok = false; break; }
                 const uint32_t a_dst = smem_u32(ring + s * stage_bytes);
                 const int64_t row0 = (int64_t)tile * kTileM;
+                // Everything that does not change from row to row is worked out once per k-block: a lane's rows are
+                // r = r_first + 8 j (8-byte form) or r = pw + 4 j (4-byte form), so r & 7 - the swizzle term - is fixed
+                // (or alternates between two values), the destination advances by whole 1024-byte groups and the
+                // source by a fixed number of rows.  The loop body is one copy and two additions; the first version
+                // recomputed addresses, swizzle and bounds per copy (about 50 instructions each) and the four producer
+                // warps, not memory, set the pace (602 -> 64 on 233 k rows: 0.45 ms).
+                const bool full_tile = row0 + kTileM <= p.n_rows;
                 if (p.plain_loads == 2) {
                     // even K: a lane copies two neighbouring values, a half-warp one 128-byte row segment, a
                     // warp two rows per instruction
                     const uint32_t half = (uint32_t)lane >> 4, hl = (uint32_t)lane & 15u;
                     const int kc = kb * kTileK + 2 * (int)hl;
                     const bool kin2 = kc < p.k;
-                    const uint32_t col_off = (hl & 1u) * 8u;
-                    const float* src2 = p.x + row0 * p.k + kc;
-#pragma unroll 8
-                    for (uint32_t rr = pw; rr < (uint32_t)kTileM / 2; rr += kPlainWarps) {
-                        const uint32_t r = 2 * rr + half;
-                        const bool in = kin2 && row0 + r < p.n_rows;
-                        cp_async8(a_dst + r * 128 + (((hl >> 1) ^ (r & 7)) << 4) + col_off, in ? src2 + (int64_t)r * p.k : p.x, in);
+                    const uint32_t r_first = 2 * pw + half;                       // 0..7 = r & 7 for all of this lane's rows
+                    const uint32_t lane_off = r_first * 128 + (((hl >> 1) ^ r_first) << 4) + (hl & 1u) * 8u;
+                    const int64_t step = 8 * (int64_t)p.k;
+                    {
+                        const uint32_t dst = a_dst + lane_off;
+                        const float* src = p.x + (row0 + r_first) * p.k + kc;
+                        if (full_tile && kin2) {
+#pragma unroll
+                            for (int j = 0; j < kTileM / 8; j++) cp_async8(dst + j * 1024, src + j * step, true);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < kTileM / 8; j++) {
+                                const bool in = kin2 && row0 + r_first + 8 * j < p.n_rows;
+                                cp_async8(dst + j * 1024, in ? src + j * step : p.x, in);
+                            }
+                        }
                     }
-                    const uint32_t b_dst2 = a_dst + a_bytes;
-                    const float* wsrc2 = p.wt + kc;
-#pragma unroll 8
-                    for (uint32_t rr = pw; rr < b_rows / 2; rr += kPlainWarps) {
-                        const uint32_t r = 2 * rr + half;
-                        const bool in = kin2 && (int)r < p.m;
-                        cp_async8(b_dst2 + r * 128 + (((hl >> 1) ^ (r & 7)) << 4) + col_off, in ? wsrc2 + (int64_t)r * p.k : p.wt, in);
+                    {
+                        const uint32_t dst = a_dst + a_bytes + lane_off;
+                        const float* src = p.wt + (int64_t)r_first * p.k + kc;
+                        const int groups = (int)b_rows / 8;
+                        for (int j = 0; j < groups; j++) {
+                            const bool in = kin2 && (int)(r_first + 8 * j) < p.m;
+                            cp_async8(dst + j * 1024, in ? src + j * step : p.wt, in);
+                        }
                     }
                     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&ctl->full[s])) : "memory");
                     continue;
@@ -246,19 +263,39 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 const int kcol = kb * kTileK + lane;
                 const bool kin = kcol < p.k;
                 // asynchronous 4-byte copies straight into shared memory (zero-filled outside the
-                // matrix): nothing waits here, the barrier counts the copies as they land
-                const float* src = p.x + row0 * p.k + kcol;
-#pragma unroll 8
-                for (uint32_t r = pw; r < (uint32_t)kTileM; r += kPlainWarps) {
-                    const bool in = kin && row0 + r < p.n_rows;
-                    cp_async4(a_dst + r * 128 + ((chunk_off ^ (r & 7)) << 4) + in_chunk, in ? src + (int64_t)r * p.k : p.x, in);
+                // matrix): nothing waits here, the barrier counts the copies as they land.  Rows r = pw + 4 j:
+                // r & 7 is pw for even j and pw + 4 for odd j.
+                const uint32_t off_even = pw * 128 + ((chunk_off ^ pw) << 4) + in_chunk;
+                const uint32_t off_odd = (pw + 4) * 128 + ((chunk_off ^ (pw + 4)) << 4) + in_chunk;
+                const int64_t step = 8 * (int64_t)p.k;
+                {
+                    const float* src_even = p.x + (row0 + pw) * p.k + kcol;
+                    const float* src_odd = src_even + 4 * (int64_t)p.k;
+                    if (full_tile && kin) {
+#pragma unroll
+                        for (int j = 0; j < kTileM / 8; j++) {
+                            cp_async4(a_dst + off_even + j * 1024, src_even + j * step, true);
+                            cp_async4(a_dst + off_odd + j * 1024, src_odd + j * step, true);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < kTileM / 8; j++) {
+                            const bool in_e = kin && row0 + pw + 8 * j < p.n_rows, in_o = kin && row0 + pw + 4 + 8 * j < p.n_rows;
+                            cp_async4(a_dst + off_even + j * 1024, in_e ? src_even + j * step : p.x, in_e);
+                            cp_async4(a_dst + off_odd + j * 1024, in_o ? src_odd + j * step : p.x, in_o);
+                        }
+                    }
                 }
-                const uint32_t b_dst = a_dst + a_bytes;
-                const float* wsrc = p.wt + kcol;
-#pragma unroll 8
-                for (uint32_t r = pw; r < b_rows; r += kPlainWarps) {
-                    const bool in = kin && (int)r < p.m;
-                    cp_async4(b_dst + r * 128 + ((chunk_off ^ (r & 7)) << 4) + in_chunk, in ? wsrc + (int64_t)r * p.k : p.wt, in);
+                {
+                    const uint32_t b_dst = a_dst + a_bytes;
+                    const float* src_even = p.wt + (int64_t)pw * p.k + kcol;
+                    const float* src_odd = src_even + 4 * (int64_t)p.k;
+                    const int groups = (int)b_rows / 8;
+                    for (int j = 0; j < groups; j++) {
+                        const bool in_e = kin && (int)(pw + 8 * j) < p.m, in_o = kin && (int)(pw + 4 + 8 * j) < p.m;
+                        cp_async4(b_dst + off_even + j * 1024, in_e ? src_even + j * step : p.wt, in_e);
+                        cp_async4(b_dst + off_odd + j * 1024, in_o ? src_odd + j * step : p.wt, in_o);
+                    }
                 }
                 asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&ctl->full[s])) : "memory");
             }

@@ -399,3 +399,17 @@ def test_a_rank_that_never_posts_its_halo_ends_in_a_timeout_not_a_hang(oracle):
     for rank, what, secs in got[: world - 1]:
         assert what == "timeout", got
         assert 2.0 <= secs <= 7.5, got
+
+
+def test_row_blocks_cover_the_rows_in_whole_tiles():
+    """``part_rows``: the row blocks of a block-wise exchange start on multiples of 128 rows (the transform's
+    tile), cover every row once, and every rank derives the same boundaries for every owner."""
+    from jittorgeometric_b200.dist import part_rows
+    for n_local in (0, 1, 127, 128, 129, 1000, 8388608, 8388609, 12345677):
+        for parts in (1, 2, 3, 4, 7):
+            rows = part_rows(n_local, parts)
+            assert len(rows) == parts + 1 and rows[0] == 0 and rows[-1] == n_local
+            assert all(a <= b for a, b in zip(rows[:-1], rows[1:]))
+            assert all(r % 128 == 0 or r == n_local for r in rows)
+            sizes = [b - a for a, b in zip(rows[:-1], rows[1:])]
+            assert sum(sizes) == n_local
