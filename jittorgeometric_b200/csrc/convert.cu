@@ -136,11 +136,12 @@ __global__ void __launch_bounds__(kSortThreads) sort_hist_kernel(SortSrc s, int 
     s_hist[threadIdx.x] = 0;
     __syncthreads();
     const int64_t base = (int64_t)blockIdx.x * kSortTile;
-#pragma unroll 4
-    for (int i = 0; i < kSortItems; i++) {
-        const Elem e = load_elem(s, base + (int64_t)i * kSortThreads + threadIdx.x);
-        if (e.valid) atomicAdd(&s_hist[digit_of(e, shift, from_idx)], 1);
-    }
+    Elem e[kSortItems];
+#pragma unroll
+    for (int i = 0; i < kSortItems; i++) e[i] = load_elem(s, base + (int64_t)i * kSortThreads + threadIdx.x);   // all loads in flight
+#pragma unroll
+    for (int i = 0; i < kSortItems; i++)
+        if (e[i].valid) atomicAdd(&s_hist[digit_of(e[i], shift, from_idx)], 1);
     __syncthreads();
     matrix[(int64_t)blockIdx.x * kRadix + threadIdx.x] = s_hist[threadIdx.x];   // [tile][digit]: one coalesced row
     (void)n_tiles;
@@ -180,9 +181,12 @@ __global__ void __launch_bounds__(kSortThreads, 4) sort_scatter_kernel(SortSrc s
     int rank[kSortItems];
     int* my_hist = s_whist + wid * kRadix;
     const unsigned lt_mask = (1u << lane) - 1u;
+    // every load of the tile first (independent, all in flight), the ranking rounds after them: with the load
+    // inside the round each of the eight rounds waited for its own memory latency behind the warp barriers
+#pragma unroll
+    for (int r = 0; r < kSortItems; r++) el[r] = load_elem(s, wbase + r * 32 + lane);
 #pragma unroll
     for (int r = 0; r < kSortItems; r++) {
-        el[r] = load_elem(s, wbase + r * 32 + lane);
         dig[r] = el[r].valid ? digit_of(el[r], shift, from_idx) : kRadix;  // kRadix: not an element
         const unsigned peers = __match_any_sync(kFull, dig[r]);
         int before = 0;
@@ -622,12 +626,29 @@ int jg_gcn_norm_compressed(const int32_t* edge_index, const float* w, int64_t n_
         JG_LAUNCH_CHECK();
     }
     if (csr_idx) {
-        first.by = 0;
-        rc = radix_sort(first, n_nodes, canonical, ws.kept, ws, csr_idx, csr_w, &skey, st, !unit);
+        bool weights_done = false;
+        if (canonical) {
+            // The canonical CSC list is ordered by (destination, source); ONE stable sort of it by source gives
+            // (source, destination), the canonical CSR, in half the passes of sorting the input again by both
+            // keys.  The normalised weight of an entry is the same number in both formats, so it travels with
+            // the entry (unit weights are not carried at all and are written afterwards, as for the CSC).
+            SortSrc from_csc = {};
+            from_csc.mode = 0;
+            from_csc.key = csc_idx;                 // source of every entry, the new key
+            from_csc.idx = skey;                    // its destination (the sorted keys of the CSC sort)
+            from_csc.w = unit ? nullptr : csc_w;
+            from_csc.count = first.count;
+            from_csc.dcount = ws.kept;
+            rc = radix_sort(from_csc, n_nodes, 0, ws.kept, ws, csr_idx, csr_w, &skey, st, !unit);
+            weights_done = !unit;
+        } else {
+            first.by = 0;
+            rc = radix_sort(first, n_nodes, canonical, ws.kept, ws, csr_idx, csr_w, &skey, st, !unit);
+        }
         if (rc != JG_OK) return rc;
         offsets_from_sorted_keys<<<blocks_for(cap + 1, 256), 256, 0, st>>>(skey, 0, ws.kept, n_nodes, csr_off);
         JG_LAUNCH_CHECK();
-        if (cap > 0) {
+        if (cap > 0 && !weights_done) {
             norm_weight_kernel<<<blocks_for(cap, 256), 256, 0, st>>>(skey, csr_idx, csr_w, ws.dis, ws.kept, 0, unit ? 1 : 0);
             JG_LAUNCH_CHECK();
         }
