@@ -172,6 +172,7 @@ __global__ void __launch_bounds__(kSortThreads, 4) sort_scatter_kernel(SortSrc s
     __shared__ int s_total;
 
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int tile_first = matrix[(int64_t)blockIdx.x * kRadix + threadIdx.x];   // this tile's global start of digit `threadIdx.x`: fetched first, needed last
     for (int i = threadIdx.x; i < kSortWarps * kRadix; i += kSortThreads) s_whist[i] = 0;
     __syncthreads();
 
@@ -209,7 +210,7 @@ __global__ void __launch_bounds__(kSortThreads, 4) sort_scatter_kernel(SortSrc s
         }
         const int start = block_exclusive_scan(run, &s_total, s_scan);
         s_dstart[dgt] = start;
-        s_gbase[dgt] = matrix[(int64_t)blockIdx.x * kRadix + dgt] - start;  // global position = gbase + tile slot
+        s_gbase[dgt] = tile_first - start;  // global position = gbase + tile slot
         (void)n_tiles;
     }
     __syncthreads();
