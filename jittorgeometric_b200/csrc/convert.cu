@@ -136,12 +136,27 @@ __global__ void __launch_bounds__(kSortThreads) sort_hist_kernel(SortSrc s, int 
     s_hist[threadIdx.x] = 0;
     __syncthreads();
     const int64_t base = (int64_t)blockIdx.x * kSortTile;
-    Elem e[kSortItems];
+    if (s.mode == 0) {
+        // sorted-buffer passes: only the array the digit comes from is read (half the bytes of a full element)
+        const int32_t* from = from_idx ? s.idx : s.key;
+        const int64_t count = s.dcount ? (int64_t)*s.dcount : s.count;
+        int32_t v[kSortItems];
 #pragma unroll
-    for (int i = 0; i < kSortItems; i++) e[i] = load_elem(s, base + (int64_t)i * kSortThreads + threadIdx.x);   // all loads in flight
+        for (int i = 0; i < kSortItems; i++) {
+            const int64_t p = base + (int64_t)i * kSortThreads + threadIdx.x;
+            v[i] = p < count ? from[p] : -1;
+        }
 #pragma unroll
-    for (int i = 0; i < kSortItems; i++)
-        if (e[i].valid) atomicAdd(&s_hist[digit_of(e[i], shift, from_idx)], 1);
+        for (int i = 0; i < kSortItems; i++)
+            if (v[i] >= 0) atomicAdd(&s_hist[(v[i] >> shift) & (kRadix - 1)], 1);
+    } else {
+        Elem e[kSortItems];
+#pragma unroll
+        for (int i = 0; i < kSortItems; i++) e[i] = load_elem(s, base + (int64_t)i * kSortThreads + threadIdx.x);   // all loads in flight
+#pragma unroll
+        for (int i = 0; i < kSortItems; i++)
+            if (e[i].valid) atomicAdd(&s_hist[digit_of(e[i], shift, from_idx)], 1);
+    }
     __syncthreads();
     matrix[(int64_t)blockIdx.x * kRadix + threadIdx.x] = s_hist[threadIdx.x];   // [tile][digit]: one coalesced row
     (void)n_tiles;
@@ -306,6 +321,44 @@ __global__ void norm_weight_kernel(const int32_t* __restrict__ key, const int32_
     const int32_t k = key[j], o = idx[j];
     const float ds = dis[key_is_dst ? o : k], dd = dis[key_is_dst ? k : o];
     w[j] = __fmul_rn(__fmul_rn(ds, unit ? 1.f : w[j]), dd);   // unit: the sort did not carry the (all-one) weights
+}
+
+// Four entries per thread (16-byte loads and store; all three arrays 16-byte aligned): with one entry per
+// thread the pass was bound by occupancy times a chain of three dependent latencies (count, endpoints, dis).
+__global__ void __launch_bounds__(256) norm_weight_vec_kernel(const int32_t* __restrict__ key, const int32_t* __restrict__ idx,
+                                                              float* __restrict__ w, const float* __restrict__ dis,
+                                                              const unsigned long long* __restrict__ dcount, int key_is_dst, int unit) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t count = (int64_t)*dcount;
+    const int64_t j = 4 * t;
+    if (j >= count) return;
+    if (j + 4 <= count) {
+        const int4 k = reinterpret_cast<const int4*>(key)[t], o = reinterpret_cast<const int4*>(idx)[t];
+        float4 v = unit ? make_float4(1.f, 1.f, 1.f, 1.f) : reinterpret_cast<const float4*>(w)[t];
+        const int4 a = key_is_dst ? o : k, b = key_is_dst ? k : o;     // a: sources, b: destinations
+        const float s0 = dis[a.x], s1 = dis[a.y], s2 = dis[a.z], s3 = dis[a.w];
+        const float d0 = dis[b.x], d1 = dis[b.y], d2 = dis[b.z], d3 = dis[b.w];
+        v.x = __fmul_rn(__fmul_rn(s0, v.x), d0); v.y = __fmul_rn(__fmul_rn(s1, v.y), d1);
+        v.z = __fmul_rn(__fmul_rn(s2, v.z), d2); v.w = __fmul_rn(__fmul_rn(s3, v.w), d3);
+        reinterpret_cast<float4*>(w)[t] = v;
+    } else {
+        for (int64_t i = j; i < count; i++) {
+            const int32_t kk = key[i], oo = idx[i];
+            const float ds = dis[key_is_dst ? oo : kk], dd = dis[key_is_dst ? kk : oo];
+            w[i] = __fmul_rn(__fmul_rn(ds, unit ? 1.f : w[i]), dd);
+        }
+    }
+}
+
+static int launch_norm_weights(const int32_t* key, const int32_t* idx, float* w, const float* dis, const unsigned long long* dcount,
+                               int key_is_dst, int unit, int64_t cap, cudaStream_t st) {
+    if (cap <= 0) return JG_OK;
+    if ((reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(idx) | reinterpret_cast<uintptr_t>(w)) % 16 == 0)
+        norm_weight_vec_kernel<<<(unsigned)(((cap + 3) / 4 + 255) / 256), 256, 0, st>>>(key, idx, w, dis, dcount, key_is_dst, unit);
+    else
+        norm_weight_kernel<<<(unsigned)((cap + 255) / 256), 256, 0, st>>>(key, idx, w, dis, dcount, key_is_dst, unit);
+    JG_LAUNCH_CHECK();
+    return JG_OK;
 }
 
 // keep[i] = 1 for input entries that are not (v,v)
@@ -622,10 +675,8 @@ int jg_gcn_norm_compressed(const int32_t* edge_index, const float* w, int64_t n_
         degree_kernel<<<blocks_for(n_nodes, 256), 256, 0, st>>>(csc_off, csc_w, n_nodes, unit ? 1 : 0, ws.dis);
         JG_LAUNCH_CHECK();
     }
-    if (cap > 0) {
-        norm_weight_kernel<<<blocks_for(cap, 256), 256, 0, st>>>(skey, csc_idx, csc_w, ws.dis, ws.kept, 1, unit ? 1 : 0);
-        JG_LAUNCH_CHECK();
-    }
+    rc = launch_norm_weights(skey, csc_idx, csc_w, ws.dis, ws.kept, 1, unit ? 1 : 0, cap, st);
+    if (rc != JG_OK) return rc;
     if (csr_idx) {
         bool weights_done = false;
         if (canonical) {
@@ -649,9 +700,9 @@ int jg_gcn_norm_compressed(const int32_t* edge_index, const float* w, int64_t n_
         if (rc != JG_OK) return rc;
         offsets_from_sorted_keys<<<blocks_for(cap + 1, 256), 256, 0, st>>>(skey, 0, ws.kept, n_nodes, csr_off);
         JG_LAUNCH_CHECK();
-        if (cap > 0 && !weights_done) {
-            norm_weight_kernel<<<blocks_for(cap, 256), 256, 0, st>>>(skey, csr_idx, csr_w, ws.dis, ws.kept, 0, unit ? 1 : 0);
-            JG_LAUNCH_CHECK();
+        if (!weights_done) {
+            rc = launch_norm_weights(skey, csr_idx, csr_w, ws.dis, ws.kept, 0, unit ? 1 : 0, cap, st);
+            if (rc != JG_OK) return rc;
         }
     }
     JG_CUDA(cudaMemcpyAsync(out_count, ws.kept, sizeof(unsigned long long), cudaMemcpyDeviceToDevice, st));
