@@ -180,10 +180,8 @@ __global__ void __launch_bounds__(kSortThreads, 4) sort_scatter_kernel(SortSrc s
     int* s_dstart = s_whist + kSortWarps * kRadix;                     // [kRadix] first tile slot of a digit
     int* s_gbase = s_dstart + kRadix;                                  // [kRadix] global offset of a digit for this tile
     int* s_scan = s_gbase + kRadix;                                    // [32]
-    int32_t* s_key = s_scan + 32;                                      // [kSortTile]
-    int32_t* s_idx = s_key + kSortTile;
-    float* s_w = reinterpret_cast<float*>(s_idx + kSortTile);
-    unsigned short* s_dig = reinterpret_cast<unsigned short*>(s_w + kSortTile);  // [kSortTile]
+    int2* s_pair = reinterpret_cast<int2*>(s_scan + 32);               // [kSortTile] (key, index): one 8-byte access per element
+    float* s_w = reinterpret_cast<float*>(s_pair + kSortTile);         // [kSortTile]
     __shared__ int s_total;
 
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -233,25 +231,23 @@ __global__ void __launch_bounds__(kSortThreads, 4) sort_scatter_kernel(SortSrc s
     for (int r = 0; r < kSortItems; r++) {
         if (el[r].valid) {
             const int q = s_dstart[dig[r]] + my_hist[dig[r]] + rank[r];
-            s_key[q] = el[r].key;
-            s_idx[q] = el[r].idx;
+            s_pair[q] = make_int2(el[r].key, el[r].idx);
             if (HAS_W) s_w[q] = el[r].w;
-            s_dig[q] = (unsigned short)dig[r];
         }
     }
     __syncthreads();
     const int total = s_total;
     for (int q = threadIdx.x; q < total; q += kSortThreads) {
-        const int64_t g = (int64_t)s_gbase[s_dig[q]] + q;
-        if (d.key) d.key[g] = s_key[q];
-        d.idx[g] = s_idx[q];
+        const int2 e = s_pair[q];
+        const int64_t g = (int64_t)s_gbase[((from_idx ? e.y : e.x) >> shift) & (kRadix - 1)] + q;   // the digit again, from the element
+        if (d.key) d.key[g] = e.x;
+        d.idx[g] = e.y;
         if (HAS_W) d.w[g] = s_w[q];
     }
 }
 
 constexpr size_t kScatterSmem = sizeof(int) * (kSortWarps * kRadix + kRadix + kRadix + 32) +
-                                sizeof(int32_t) * 2 * kSortTile + sizeof(float) * kSortTile +
-                                sizeof(unsigned short) * kSortTile;
+                                sizeof(int2) * kSortTile + sizeof(float) * kSortTile;
 
 // ------------------------------------------------------------------------------- small kernels
 // off[k] = first position whose key is >= k, for k in [0, n]; keys sorted, E entries.
