@@ -253,12 +253,27 @@ constexpr size_t kScatterSmem = sizeof(int) * (kSortWarps * kRadix + kRadix + kR
 // off[k] = first position whose key is >= k, for k in [0, n]; keys sorted, E entries.
 __global__ void offsets_from_sorted_keys(const int32_t* __restrict__ key, int64_t E_host,
                                          const unsigned long long* __restrict__ dcount, int64_t n, int32_t* __restrict__ off) {
+    // four positions per thread: one 16-byte load of their keys (when aligned) and the key before them
     const int64_t E = dcount ? (int64_t)*dcount : E_host;
-    const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (j > E) return;
-    const int64_t lo = j == 0 ? -1 : key[j - 1];
-    const int64_t hi = j == E ? n : key[j];
-    for (int64_t k = lo + 1; k <= hi; k++) off[k] = (int32_t)j;
+    const int64_t j0 = 4 * ((int64_t)blockIdx.x * blockDim.x + threadIdx.x);
+    if (j0 > E) return;
+    int64_t prev = j0 == 0 ? -1 : key[j0 - 1];
+    int32_t k4[4];
+    if (j0 + 4 <= E && reinterpret_cast<uintptr_t>(key) % 16 == 0) {
+        const int4 v = *reinterpret_cast<const int4*>(key + j0);
+        k4[0] = v.x; k4[1] = v.y; k4[2] = v.z; k4[3] = v.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++) k4[i] = j0 + i < E ? key[j0 + i] : 0;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int64_t j = j0 + i;
+        if (j > E) break;
+        const int64_t hi = j == E ? n : k4[i];
+        for (int64_t k = prev + 1; k <= hi; k++) off[k] = (int32_t)j;
+        prev = hi;
+    }
 }
 
 __global__ void set_count_kernel(unsigned long long* p, unsigned long long v) { *p = v; }
@@ -608,7 +623,7 @@ int jg_coo_to_compressed(const int32_t* edge_index, const float* w, int64_t n_ed
         fill_int_kernel<<<blocks_for(n_edges, 256), 256, 0, st>>>(reinterpret_cast<int*>(out_w), 0x3f800000, n_edges);
         JG_LAUNCH_CHECK();
     }
-    offsets_from_sorted_keys<<<blocks_for(n_edges + 1, 256), 256, 0, st>>>(skey, n_edges, nullptr, n_nodes, out_off);
+    offsets_from_sorted_keys<<<blocks_for((n_edges + 4) / 4, 256), 256, 0, st>>>(skey, n_edges, nullptr, n_nodes, out_off);
     JG_LAUNCH_CHECK();
     return JG_OK;
 }
@@ -665,7 +680,7 @@ int jg_gcn_norm_compressed(const int32_t* edge_index, const float* w, int64_t n_
     first.by = 1;
     int rc = radix_sort(first, n_nodes, canonical, ws.kept, ws, csc_idx, csc_w, &skey, st, !unit);
     if (rc != JG_OK) return rc;
-    offsets_from_sorted_keys<<<blocks_for(cap + 1, 256), 256, 0, st>>>(skey, 0, ws.kept, n_nodes, csc_off);
+    offsets_from_sorted_keys<<<blocks_for((cap + 4) / 4, 256), 256, 0, st>>>(skey, 0, ws.kept, n_nodes, csc_off);
     JG_LAUNCH_CHECK();
     if (n_nodes > 0) {
         degree_kernel<<<blocks_for(n_nodes, 256), 256, 0, st>>>(csc_off, csc_w, n_nodes, unit ? 1 : 0, ws.dis);
@@ -694,7 +709,7 @@ int jg_gcn_norm_compressed(const int32_t* edge_index, const float* w, int64_t n_
             rc = radix_sort(first, n_nodes, canonical, ws.kept, ws, csr_idx, csr_w, &skey, st, !unit);
         }
         if (rc != JG_OK) return rc;
-        offsets_from_sorted_keys<<<blocks_for(cap + 1, 256), 256, 0, st>>>(skey, 0, ws.kept, n_nodes, csr_off);
+        offsets_from_sorted_keys<<<blocks_for((cap + 4) / 4, 256), 256, 0, st>>>(skey, 0, ws.kept, n_nodes, csr_off);
         JG_LAUNCH_CHECK();
         if (!weights_done) {
             rc = launch_norm_weights(skey, csr_idx, csr_w, ws.dis, ws.kept, 0, unit ? 1 : 0, cap, st);
