@@ -97,30 +97,56 @@ struct Elem {
     bool valid;
 };
 
-__device__ __forceinline__ Elem load_elem(const SortSrc& s, int64_t p) {
-    Elem e;
-    e.valid = p < (s.dcount ? (int64_t)*s.dcount : s.count);
-    e.key = 0; e.idx = 0; e.w = 0.f;
-    if (!e.valid) return e;
+// An element is fetched in two steps so that a tile's loads can all be issued before anything looks at a
+// loaded value: load_raw only loads (what it returns is not inspected), finish_elem derives key, index and
+// validity.  With the two fused, the self-loop test of the first pass (a == b) made every element wait for
+// its own loads before the next element's were issued, and every element re-read the device-side count.
+struct Raw {
+    int32_t a, b;
+    float w;
+};
+
+__device__ __forceinline__ int64_t list_count(const SortSrc& s) { return s.dcount ? (int64_t)*s.dcount : s.count; }
+
+__device__ __forceinline__ Raw load_raw(const SortSrc& s, int64_t p, int64_t count) {
+    Raw r;
+    r.a = 0; r.b = 0; r.w = 1.f;
+    if (p >= count) return r;
     if (s.mode == 0) {
-        e.key = s.key[p]; e.idx = s.idx[p]; e.w = s.w ? s.w[p] : 1.f;
+        r.a = s.key[p]; r.b = s.idx[p];
+        if (s.w) r.w = s.w[p];
     } else if (s.mode == 2) {
         // mirrored list: position 2i is edge i as given, 2i + 1 the same edge reversed
         const int64_t i = p >> 1;
-        const int32_t a = s.coo_src[i], b = s.coo_dst[i];
-        e.key = (p & 1) ? b : a;
-        e.idx = (p & 1) ? a : b;
-        e.w = s.coo_w ? s.coo_w[i] : 1.f;
+        r.a = s.coo_src[i]; r.b = s.coo_dst[i];
+        if (s.coo_w) r.w = s.coo_w[i];
     } else if (p < s.e0) {
-        const int32_t a = s.coo_src[p], b = s.coo_dst[p];
-        e.key = s.by == 0 ? a : b;
-        e.idx = s.by == 0 ? b : a;
-        e.w = s.coo_w ? s.coo_w[p] : 1.f;
-        if (s.drop_loops && a == b) e.valid = false;
+        r.a = s.coo_src[p]; r.b = s.coo_dst[p];
+        if (s.coo_w) r.w = s.coo_w[p];
     } else {
         const int32_t v = (int32_t)(p - s.e0);
-        e.key = v; e.idx = v;
-        e.w = s.loop_w ? s.loop_w[v] : 1.f;
+        r.a = v; r.b = v;
+        if (s.loop_w) r.w = s.loop_w[v];
+    }
+    return r;
+}
+
+__device__ __forceinline__ Elem finish_elem(const SortSrc& s, int64_t p, int64_t count, const Raw& r) {
+    Elem e;
+    e.valid = p < count;
+    e.key = 0; e.idx = 0; e.w = r.w;
+    if (!e.valid) { e.w = 0.f; return e; }
+    if (s.mode == 0) {
+        e.key = r.a; e.idx = r.b;
+    } else if (s.mode == 2) {
+        e.key = (p & 1) ? r.b : r.a;
+        e.idx = (p & 1) ? r.a : r.b;
+    } else if (p < s.e0) {
+        e.key = s.by == 0 ? r.a : r.b;
+        e.idx = s.by == 0 ? r.b : r.a;
+        if (s.drop_loops && r.a == r.b) e.valid = false;
+    } else {
+        e.key = r.a; e.idx = r.a;
     }
     return e;
 }
@@ -150,12 +176,15 @@ __global__ void __launch_bounds__(kSortThreads) sort_hist_kernel(SortSrc s, int 
         for (int i = 0; i < kSortItems; i++)
             if (v[i] >= 0) atomicAdd(&s_hist[(v[i] >> shift) & (kRadix - 1)], 1);
     } else {
-        Elem e[kSortItems];
+        const int64_t count = list_count(s);
+        Raw raw[kSortItems];
 #pragma unroll
-        for (int i = 0; i < kSortItems; i++) e[i] = load_elem(s, base + (int64_t)i * kSortThreads + threadIdx.x);   // all loads in flight
+        for (int i = 0; i < kSortItems; i++) raw[i] = load_raw(s, base + (int64_t)i * kSortThreads + threadIdx.x, count);   // all loads in flight
 #pragma unroll
-        for (int i = 0; i < kSortItems; i++)
-            if (e[i].valid) atomicAdd(&s_hist[digit_of(e[i], shift, from_idx)], 1);
+        for (int i = 0; i < kSortItems; i++) {
+            const Elem e = finish_elem(s, base + (int64_t)i * kSortThreads + threadIdx.x, count, raw[i]);
+            if (e.valid) atomicAdd(&s_hist[digit_of(e, shift, from_idx)], 1);
+        }
     }
     __syncthreads();
     matrix[(int64_t)blockIdx.x * kRadix + threadIdx.x] = s_hist[threadIdx.x];   // [tile][digit]: one coalesced row
@@ -197,8 +226,14 @@ __global__ void __launch_bounds__(kSortThreads, 4) sort_scatter_kernel(SortSrc s
     const unsigned lt_mask = (1u << lane) - 1u;
     // every load of the tile first (independent, all in flight), the ranking rounds after them: with the load
     // inside the round each of the eight rounds waited for its own memory latency behind the warp barriers
+    {
+        const int64_t count = list_count(s);
+        Raw raw[kSortItems];
 #pragma unroll
-    for (int r = 0; r < kSortItems; r++) el[r] = load_elem(s, wbase + r * 32 + lane);
+        for (int r = 0; r < kSortItems; r++) raw[r] = load_raw(s, wbase + r * 32 + lane, count);
+#pragma unroll
+        for (int r = 0; r < kSortItems; r++) el[r] = finish_elem(s, wbase + r * 32 + lane, count, raw[r]);
+    }
 #pragma unroll
     for (int r = 0; r < kSortItems; r++) {
         dig[r] = el[r].valid ? digit_of(el[r], shift, from_idx) : kRadix;  // kRadix: not an element
