@@ -156,13 +156,16 @@ __device__ __forceinline__ int digit_of(const Elem& e, int shift, int from_idx) 
     return ((from_idx ? e.idx : e.key) >> shift) & (kRadix - 1);
 }
 
+// SORTED: the source is a sorted buffer (mode 0); a separate instantiation, so that the register needs of the
+// first pass's element loader do not lower the occupancy of the other passes.
+template <bool SORTED>
 __global__ void __launch_bounds__(kSortThreads) sort_hist_kernel(SortSrc s, int shift, int from_idx, int* __restrict__ matrix,
                                                                  int64_t n_tiles) {
     __shared__ int s_hist[kRadix];
     s_hist[threadIdx.x] = 0;
     __syncthreads();
     const int64_t base = (int64_t)blockIdx.x * kSortTile;
-    if (s.mode == 0) {
+    if (SORTED) {
         // sorted-buffer passes: only the array the digit comes from is read (half the bytes of a full element)
         const int32_t* from = from_idx ? s.idx : s.key;
         const int64_t count = s.dcount ? (int64_t)*s.dcount : s.count;
@@ -584,7 +587,10 @@ static int radix_sort(SortSrc first, int64_t n, int canonical, const unsigned lo
     for (int p = 0; p < total_passes; p++) {
         const int from_idx = canonical && p < key_passes;
         const int shift = 8 * (canonical && !from_idx ? p - key_passes : p);
-        sort_hist_kernel<<<(unsigned)tiles, kSortThreads, 0, st>>>(src, shift, from_idx, ws.matrix, tiles);
+        if (src.mode == 0)
+            sort_hist_kernel<true><<<(unsigned)tiles, kSortThreads, 0, st>>>(src, shift, from_idx, ws.matrix, tiles);
+        else
+            sort_hist_kernel<false><<<(unsigned)tiles, kSortThreads, 0, st>>>(src, shift, from_idx, ws.matrix, tiles);
         JG_LAUNCH_CHECK();
         {
             const int64_t chunks = (tiles + kChunkTiles - 1) / kChunkTiles;
