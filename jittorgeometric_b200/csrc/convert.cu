@@ -209,8 +209,7 @@ __global__ void __launch_bounds__(kSortThreads, 4) sort_scatter_kernel(SortSrc s
                                                                     const int* __restrict__ matrix, int64_t n_tiles) {
     extern __shared__ __align__(16) unsigned char smem[];
     int* s_whist = reinterpret_cast<int*>(smem);                       // [kSortWarps][kRadix]
-    int* s_dstart = s_whist + kSortWarps * kRadix;                     // [kRadix] first tile slot of a digit
-    int* s_gbase = s_dstart + kRadix;                                  // [kRadix] global offset of a digit for this tile
+    int* s_gbase = s_whist + kSortWarps * kRadix;                      // [kRadix] global offset of a digit for this tile
     int* s_scan = s_gbase + kRadix;                                    // [32]
     int2* s_pair = reinterpret_cast<int2*>(s_scan + 32);               // [kSortTile] (key, index): one 8-byte access per element
     float* s_w = reinterpret_cast<float*>(s_pair + kSortTile);         // [kSortTile]
@@ -251,16 +250,23 @@ __global__ void __launch_bounds__(kSortThreads, 4) sort_scatter_kernel(SortSrc s
     __syncthreads();
     // one thread per digit: exclusive prefix over warps, tile total
     {
+        // per warp and digit: first tile slot of that warp's elements of the digit (digit start + the earlier
+        // warps' counts), so that staging needs one look-up per element
         const int dgt = threadIdx.x;
+        int cnt_w[kSortWarps];
         int run = 0;
 #pragma unroll
         for (int w = 0; w < kSortWarps; w++) {
-            const int c = s_whist[w * kRadix + dgt];
-            s_whist[w * kRadix + dgt] = run;
-            run += c;
+            cnt_w[w] = s_whist[w * kRadix + dgt];
+            run += cnt_w[w];
         }
         const int start = block_exclusive_scan(run, &s_total, s_scan);
-        s_dstart[dgt] = start;
+        int at = start;
+#pragma unroll
+        for (int w = 0; w < kSortWarps; w++) {
+            s_whist[w * kRadix + dgt] = at;
+            at += cnt_w[w];
+        }
         s_gbase[dgt] = tile_first - start;  // global position = gbase + tile slot
         (void)n_tiles;
     }
@@ -268,7 +274,7 @@ __global__ void __launch_bounds__(kSortThreads, 4) sort_scatter_kernel(SortSrc s
 #pragma unroll
     for (int r = 0; r < kSortItems; r++) {
         if (el[r].valid) {
-            const int q = s_dstart[dig[r]] + my_hist[dig[r]] + rank[r];
+            const int q = my_hist[dig[r]] + rank[r];
             s_pair[q] = make_int2(el[r].key, el[r].idx);
             if (HAS_W) s_w[q] = el[r].w;
         }
@@ -284,7 +290,7 @@ __global__ void __launch_bounds__(kSortThreads, 4) sort_scatter_kernel(SortSrc s
     }
 }
 
-constexpr size_t kScatterSmem = sizeof(int) * (kSortWarps * kRadix + kRadix + kRadix + 32) +
+constexpr size_t kScatterSmem = sizeof(int) * (kSortWarps * kRadix + kRadix + 32) +
                                 sizeof(int2) * kSortTile + sizeof(float) * kSortTile;
 
 // ------------------------------------------------------------------------------- small kernels
