@@ -66,6 +66,9 @@ class ClockSampler:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
+        t0 = time.time()
+        while not self.lines and time.time() - t0 < 3.0:      # a slow start of nvidia-smi: wait for its first line
+            time.sleep(0.05)
         self.proc.terminate()
         self.t.join(timeout=2)
         sm, mx, reasons = [], [], set()
