@@ -69,6 +69,36 @@ def test_canonical_order(cuda, oracle):
     assert np.array_equal(host(got.edge_weight), cw)       # equal (row, col) pairs keep list order
 
 
+@pytest.mark.parametrize("n,E,weighted", [(300, 4000, False), (300, 4000, True), (40000, 500000, False), (40000, 500000, True),
+                                          (70000, 300000, True)])
+def test_gcn_norm_sorted_columns(cuda, oracle, n, E, weighted):
+    """``sorted=True``: both formats with the columns of every row in ascending order.  The CSR is built from
+    the finished CSC list by one stable sort (equal pairs keep list order, weights travel with their
+    entries); it must equal the reference's conversion of the normalised list, sorted inside its rows."""
+    rng = np.random.default_rng(3 * n + E + weighted)
+    ei = rng.integers(0, n, size=(2, E)).astype(np.int32)
+    ei[:, : E // 50] = ei[:, E // 50: 2 * (E // 50)]            # repeated (source, destination) pairs
+    w = rng.standard_normal(E).astype(np.float32) ** 2 + 0.1 if weighted else None
+    csc, csr = cuda.gcn_norm_csc_csr(dev(ei), None if w is None else dev(w), n, sorted=True)
+    nei, nw = oracle.gcn_norm(ei, w, n)
+    for got, conv in ((csc, oracle.coo_to_csc), (csr, oracle.coo_to_csr)):
+        idx, off, ow = conv(nei, nw, n)
+        cidx, cw, _ = oracle.sort_within_rows(idx, off, ow)
+        g_idx = got.row_indices if hasattr(got, "row_indices") else got.column_indices
+        g_off = got.column_offset if hasattr(got, "column_offset") else got.row_offset
+        assert np.array_equal(host(g_off), off)
+        assert np.array_equal(host(g_idx), cidx)
+        # the degree of a node is a sequential fp32 sum over its column in LIST order, and the sorted list is
+        # in another order than the input list the reference sums over: a few ulp on weighted graphs
+        gw = host(got.edge_weight)
+        assert np.abs(gw - cw).max() <= 2e-6 * np.abs(cw).max() and (ulp_diff(gw, cw) <= 4 or weighted)
+    # the CSR's weights were carried with their entries, not recomputed: the two formats hold the same numbers
+    a = np.stack([np.repeat(np.arange(n), np.diff(host(csc.column_offset))), host(csc.row_indices), host(csc.edge_weight).view(np.int32)])
+    b = np.stack([host(csr.column_indices), np.repeat(np.arange(n), np.diff(host(csr.row_offset))), host(csr.edge_weight).view(np.int32)])
+    key_a = np.lexsort((a[2], a[1], a[0])); key_b = np.lexsort((b[2], b[1], b[0]))
+    assert np.array_equal(a[:, key_a], b[:, key_b])
+
+
 def check_gcn(cuda, oracle, ei, w, n, improved=False):
     csc, csr = cuda.gcn_norm_csc_csr(dev(ei), None if w is None else dev(w), n, improved=improved)
     if improved:
