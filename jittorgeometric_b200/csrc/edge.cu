@@ -137,6 +137,11 @@ __device__ __forceinline__ float reduce_same_column_sum(float v) {
 // Segments of kSoftmaxHub edges or more are left to the block-per-segment kernels below: one warp
 // walking tens of thousands of entries alone would be the tail of the whole launch.
 constexpr int kSoftmaxHub = 2048;
+// The backward pass has no exponentials and a cheap block-wide sum, and a block that owns a segment finds it in
+// L2 on its second sweep (far fewer segments are in flight than with a warp each): measured on the attention
+// workload 0.77 ms with the forward's threshold, 0.57 ms with this one.  The forward's block role pays a
+// four-column (maximum, sum) merge with exponentials per segment and was slower below 2048 edges (1.0 vs 0.58 ms).
+constexpr int kSoftmaxBwdHub = 384;
 
 // Running (maximum, sum of exp(x - maximum)) of the elements a lane has met; merging two such states
 // rescales the one with the smaller maximum.  An empty state is (-inf, 0).
@@ -429,7 +434,7 @@ __global__ void __launch_bounds__(kEdgeBlock) edge_softmax_bwd_kernel(float* __r
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     for (int64_t v = warp; v < n; v += n_warps) {
-        if (off[v + 1] - off[v] >= kSoftmaxHub) continue;
+        if (off[v + 1] - off[v] >= kSoftmaxBwdHub) continue;
         const int64_t s = (int64_t)off[v] * HP, e = (int64_t)off[v + 1] * HP;
         float dot = 0.f;
         int64_t i = s + lane;
@@ -449,7 +454,7 @@ __global__ void __launch_bounds__(kEdgeBlock) edge_softmax_bwd_hub_kernel(float*
                                                                           const int32_t* __restrict__ off, int64_t n) {
     __shared__ float s_buf[kEdgeBlock];
     for (int64_t v = blockIdx.x; v < n; v += gridDim.x) {
-        if (off[v + 1] - off[v] < kSoftmaxHub) continue;   // block-uniform
+        if (off[v + 1] - off[v] < kSoftmaxBwdHub) continue;   // block-uniform
         const int64_t s = (int64_t)off[v] * HP, e = (int64_t)off[v + 1] * HP;
         float dot = 0.f;
         int64_t i = s + threadIdx.x;
@@ -490,7 +495,7 @@ __device__ __forceinline__ void softmax_bwd_vec_warps(float4* __restrict__ dx, c
     const int64_t warp = ((int64_t)block * blockDim.x + threadIdx.x) >> 5;
     const int64_t n_warps = ((int64_t)n_blocks * blockDim.x) >> 5;
     for (int64_t v = warp; v < n; v += n_warps) {
-        if (off[v + 1] - off[v] >= kSoftmaxHub) continue;
+        if (off[v + 1] - off[v] >= kSoftmaxBwdHub) continue;
         const int64_t s = (int64_t)off[v] * Q, e = (int64_t)off[v + 1] * Q;
         float dot[4] = {0.f, 0.f, 0.f, 0.f};
         int64_t i = s + lane;
@@ -518,7 +523,7 @@ __device__ __forceinline__ void softmax_bwd_vec_block(float4* __restrict__ dx, c
                                                       int block, int n_blocks, float* s_buf) {
     constexpr int Q = HP / 4;
     for (int64_t v = block; v < n; v += n_blocks) {
-        if (off[v + 1] - off[v] < kSoftmaxHub) continue;   // block-uniform
+        if (off[v + 1] - off[v] < kSoftmaxBwdHub) continue;   // block-uniform
         const int64_t s = (int64_t)off[v] * Q, e = (int64_t)off[v + 1] * Q;
         float dot[4] = {0.f, 0.f, 0.f, 0.f};
         int64_t i = s + threadIdx.x;
