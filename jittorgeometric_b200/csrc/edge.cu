@@ -142,6 +142,9 @@ constexpr int kSoftmaxHub = 2048;
 // workload 0.77 ms with the forward's threshold, 0.57 ms with this one.  The forward's block role pays a
 // four-column (maximum, sum) merge with exponentials per segment and was slower below 2048 edges (1.0 vs 0.58 ms).
 constexpr int kSoftmaxBwdHub = 384;
+// 128-bit forward kernel: its block role makes three sweeps (maxima, sums, values) with plain block
+// reductions, the second and third out of L2, and takes the same segments as the backward's.
+constexpr int kSoftmaxFwdVecHub = 384;
 
 // Running (maximum, sum of exp(x - maximum)) of the elements a lane has met; merging two such states
 // rescales the one with the smaller maximum.  An empty state is (-inf, 0).
@@ -297,7 +300,7 @@ __device__ __forceinline__ void softmax_fwd_vec_warps(float4* __restrict__ y, co
     const int64_t warp = ((int64_t)block * blockDim.x + threadIdx.x) >> 5;
     const int64_t n_warps = ((int64_t)n_blocks * blockDim.x) >> 5;
     for (int64_t v = warp; v < n; v += n_warps) {
-        if (off[v + 1] - off[v] >= kSoftmaxHub) continue;
+        if (off[v + 1] - off[v] >= kSoftmaxFwdVecHub) continue;
         const int64_t s = (int64_t)off[v] * Q, e = (int64_t)off[v + 1] * Q;
         if (s >= e) continue;
         MaxSum st[4] = {{-INFINITY, 0.f}, {-INFINITY, 0.f}, {-INFINITY, 0.f}, {-INFINITY, 0.f}};
@@ -329,60 +332,74 @@ __device__ __forceinline__ void softmax_fwd_vec_warps(float4* __restrict__ y, co
     }
 }
 
+// Four per-thread values reduced over the threads of the block that meet the same columns (thread t carries the
+// columns of float4 number t % Q): shuffles inside the warp, one pass through shared memory across the warps
+// (in warp order), two barriers for all four values.
+template <int Q, bool IS_MAX>
+__device__ __forceinline__ void block_same_columns4(float (&v)[4], float (*s_buf)[kEdgeBlock]) {
+#pragma unroll
+    for (int c = 0; c < 4; c++) v[c] = IS_MAX ? reduce_same_column_max<Q>(v[c]) : reduce_same_column_sum<Q>(v[c]);
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < 4; c++) s_buf[c][threadIdx.x] = v[c];
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        float r = s_buf[c][lane];
+#pragma unroll
+        for (int w = 1; w < kEdgeBlock / 32; w++) {
+            const float o = s_buf[c][w * 32 + lane];
+            r = IS_MAX ? fmaxf(r, o) : r + o;
+        }
+        v[c] = r;
+    }
+}
+
+// Block role of the 128-bit forward kernel: a block owns a segment and sweeps it three times - column maxima,
+// sums of exp(x - maximum), normalised values.  Only the first sweep comes from DRAM: with a block per segment
+// few segments are in flight and the other two find theirs in L2.  The reductions are plain maxima and sums
+// (no rescaling exponentials), two barriers each.
 template <int HP>
 __device__ __forceinline__ void softmax_fwd_vec_block(float4* __restrict__ y, const float4* __restrict__ x,
                                                       const int32_t* __restrict__ off, int64_t n, int block, int n_blocks,
-                                                      float (*s_m)[kEdgeBlock], float (*s_s)[kEdgeBlock]) {
+                                                      float (*s_buf)[kEdgeBlock]) {
     constexpr int Q = HP / 4;
-    const int lane = threadIdx.x & 31;
     for (int64_t v = block; v < n; v += n_blocks) {
-        if (off[v + 1] - off[v] < kSoftmaxHub) continue;   // block-uniform
+        if (off[v + 1] - off[v] < kSoftmaxFwdVecHub) continue;   // block-uniform
         const int64_t s = (int64_t)off[v] * Q, e = (int64_t)off[v + 1] * Q;
-        MaxSum st[4] = {{-INFINITY, 0.f}, {-INFINITY, 0.f}, {-INFINITY, 0.f}, {-INFINITY, 0.f}};
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
         int64_t i = s + threadIdx.x;
-        for (; i + 7 * kEdgeBlock < e; i += 8 * kEdgeBlock) {   // a block alone on a long segment: eight loads in flight per thread
-            float4 a[8];
-#pragma unroll
-            for (int u = 0; u < 8; u++) a[u] = x[i + u * kEdgeBlock];
-            st[0].add4(a[0].x, a[1].x, a[2].x, a[3].x); st[1].add4(a[0].y, a[1].y, a[2].y, a[3].y);
-            st[2].add4(a[0].z, a[1].z, a[2].z, a[3].z); st[3].add4(a[0].w, a[1].w, a[2].w, a[3].w);
-            st[0].add4(a[4].x, a[5].x, a[6].x, a[7].x); st[1].add4(a[4].y, a[5].y, a[6].y, a[7].y);
-            st[2].add4(a[4].z, a[5].z, a[6].z, a[7].z); st[3].add4(a[4].w, a[5].w, a[6].w, a[7].w);
-        }
         for (; i + 3 * kEdgeBlock < e; i += 4 * kEdgeBlock) {
             const float4 a0 = x[i], a1 = x[i + kEdgeBlock], a2 = x[i + 2 * kEdgeBlock], a3 = x[i + 3 * kEdgeBlock];
-            st[0].add4(a0.x, a1.x, a2.x, a3.x); st[1].add4(a0.y, a1.y, a2.y, a3.y);
-            st[2].add4(a0.z, a1.z, a2.z, a3.z); st[3].add4(a0.w, a1.w, a2.w, a3.w);
+            mx[0] = fmaxf(mx[0], fmaxf(fmaxf(a0.x, a1.x), fmaxf(a2.x, a3.x)));
+            mx[1] = fmaxf(mx[1], fmaxf(fmaxf(a0.y, a1.y), fmaxf(a2.y, a3.y)));
+            mx[2] = fmaxf(mx[2], fmaxf(fmaxf(a0.z, a1.z), fmaxf(a2.z, a3.z)));
+            mx[3] = fmaxf(mx[3], fmaxf(fmaxf(a0.w, a1.w), fmaxf(a2.w, a3.w)));
         }
         for (; i < e; i += kEdgeBlock) {
             const float4 a = x[i];
-            st[0].add(a.x); st[1].add(a.y); st[2].add(a.z); st[3].add(a.w);
+            mx[0] = fmaxf(mx[0], a.x); mx[1] = fmaxf(mx[1], a.y); mx[2] = fmaxf(mx[2], a.z); mx[3] = fmaxf(mx[3], a.w);
         }
-#pragma unroll
-        for (int o = 16; o >= Q; o >>= 1) {
-#pragma unroll
-            for (int c = 0; c < 4; c++) merge_lanes(st[c], lane, o);
-        }
-        __syncthreads();
-#pragma unroll
-        for (int c = 0; c < 4; c++) { s_m[c][threadIdx.x] = st[c].m; s_s[c][threadIdx.x] = st[c].s; }
-        __syncthreads();
-        float mx[4], inv[4];
-#pragma unroll
-        for (int c = 0; c < 4; c++) {             // warps in order: every thread ends with the same state per column
-            MaxSum all = {s_m[c][lane], s_s[c][lane]};
-#pragma unroll
-            for (int w = 1; w < kEdgeBlock / 32; w++) all.merge(s_m[c][w * 32 + lane], s_s[c][w * 32 + lane]);
-            mx[c] = all.m; inv[c] = 1.f / all.s;
-        }
+        block_same_columns4<Q, true>(mx, s_buf);
+        float sm[4] = {0.f, 0.f, 0.f, 0.f};
         i = s + threadIdx.x;
-        for (; i + 7 * kEdgeBlock < e; i += 8 * kEdgeBlock) {
-            float4 a[8];
-#pragma unroll
-            for (int u = 0; u < 8; u++) a[u] = x[i + u * kEdgeBlock];
-#pragma unroll
-            for (int u = 0; u < 8; u++) __stcs(y + i + u * kEdgeBlock, softmax_values(a[u], mx, inv));
+        for (; i + 3 * kEdgeBlock < e; i += 4 * kEdgeBlock) {
+            const float4 a0 = x[i], a1 = x[i + kEdgeBlock], a2 = x[i + 2 * kEdgeBlock], a3 = x[i + 3 * kEdgeBlock];
+            sm[0] += (expf(a0.x - mx[0]) + expf(a1.x - mx[0])) + (expf(a2.x - mx[0]) + expf(a3.x - mx[0]));
+            sm[1] += (expf(a0.y - mx[1]) + expf(a1.y - mx[1])) + (expf(a2.y - mx[1]) + expf(a3.y - mx[1]));
+            sm[2] += (expf(a0.z - mx[2]) + expf(a1.z - mx[2])) + (expf(a2.z - mx[2]) + expf(a3.z - mx[2]));
+            sm[3] += (expf(a0.w - mx[3]) + expf(a1.w - mx[3])) + (expf(a2.w - mx[3]) + expf(a3.w - mx[3]));
         }
+        for (; i < e; i += kEdgeBlock) {
+            const float4 a = x[i];
+            sm[0] += expf(a.x - mx[0]); sm[1] += expf(a.y - mx[1]); sm[2] += expf(a.z - mx[2]); sm[3] += expf(a.w - mx[3]);
+        }
+        block_same_columns4<Q, false>(sm, s_buf);
+        float inv[4];
+#pragma unroll
+        for (int c = 0; c < 4; c++) inv[c] = 1.f / sm[c];
+        i = s + threadIdx.x;
         for (; i + 3 * kEdgeBlock < e; i += 4 * kEdgeBlock) {
             const float4 a0 = x[i], a1 = x[i + kEdgeBlock], a2 = x[i + 2 * kEdgeBlock], a3 = x[i + 3 * kEdgeBlock];
             __stcs(y + i, softmax_values(a0, mx, inv)); __stcs(y + i + kEdgeBlock, softmax_values(a1, mx, inv));
@@ -398,9 +415,9 @@ __device__ __forceinline__ void softmax_fwd_vec_block(float4* __restrict__ y, co
 template <int HP>
 __global__ void __launch_bounds__(kEdgeBlock) edge_softmax_fwd_vec_kernel(float4* __restrict__ y, const float4* __restrict__ x,
                                                                           const int32_t* __restrict__ off, int64_t n, int hub_blocks) {
-    __shared__ float s_m[4][kEdgeBlock], s_s[4][kEdgeBlock];
+    __shared__ float s_buf[4][kEdgeBlock];
     if ((int)blockIdx.x < hub_blocks)
-        softmax_fwd_vec_block<HP>(y, x, off, n, (int)blockIdx.x, hub_blocks, s_m, s_s);
+        softmax_fwd_vec_block<HP>(y, x, off, n, (int)blockIdx.x, hub_blocks, s_buf);
     else
         softmax_fwd_vec_warps<HP>(y, x, off, n, (int)blockIdx.x - hub_blocks, (int)gridDim.x - hub_blocks);
 }
